@@ -1,0 +1,128 @@
+/* swin3d_b200 -- C ABI of the B200 (sm_100a) library for Swin3D's sparse-voxel window attention
+ * with contextual relative signal encoding (cRSE), its window builder, and the KNN used by
+ * knn_down / Upsample.
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer unless its name ends in _host.  The caller owns every
+ *    buffer; the library allocates nothing, frees nothing and keeps no state between calls.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).  Calls only
+ *    enqueue work; they never synchronise.
+ *  - Return value: S3D_OK or an S3D_ERR_* code; s3d_status_string() names it.  Nothing here
+ *    aborts the process (the reference's shape checks are host assert()s that abort).
+ *  - dtype codes: S3D_F32 = 0, S3D_F16 = 1.  Accumulation is always fp32.
+ *  - File:line citations name the interface of microsoft/Swin3D each entry point replaces.
+ */
+#ifndef SWIN3D_B200_H
+#define SWIN3D_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define S3D_OK 0
+#define S3D_ERR_BAD_ARG 1        /* null pointer, negative size, unknown dtype           */
+#define S3D_ERR_UNSUPPORTED 2    /* head_dim, signal-dim count, K or window size not built */
+#define S3D_ERR_LAUNCH 3         /* the CUDA runtime reported an error at launch           */
+#define S3D_ERR_WORKSPACE 4      /* caller-provided workspace too small                    */
+
+#define S3D_F32 0
+#define S3D_F16 1
+
+#define S3D_MAX_SIGNAL_DIMS 9
+#define S3D_KNN_MAX_K 64
+
+const char *s3d_status_string(int status);
+
+/* Library/ABI version (major*1000 + minor). */
+int s3d_version(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Fused cRSE window attention, forward.
+ * Replaces the pair  attn_cuda.cal_max_coffs + attn_cuda.self_attn_forward  and the host-side
+ * normalisation (Swin3D/src/attn/self_attn_aio_fwd.h:11-26, Swin3D/src/attn/attn_api.cpp:20-23,
+ * Swin3D/sparse_dl/attn/attn_coff.py:180-184) for IndexMode.INDIRECT + PosEmb.SEPARATE.
+ *
+ *  q,k,v        [N,H,hd] contiguous, ORIGINAL voxel order, dtype `dtype`; q already scaled.
+ *  tq,tk,tv     flat tables, dtype `dtype`: concat over signal dims n of [L_n,H,hd].
+ *  table_sizes_host  int32[D] on the HOST: elements per signal dim (L_n*H*hd).
+ *  w_sizes,w2n  int32[W]: voxels per window, first sorted position of each window.
+ *  n2n          int32[N]: sorted position -> voxel row.
+ *  n_coords     float[N,D]: quantised signals in WINDOW-SORTED order.
+ *  out          [N,H,hd] dtype `dtype`, original order: softmax-weighted values.
+ *  lse          float[N,H], original order: log-sum-exp of each (voxel, head) score row.
+ * Supported: hd in {8,16,32}; D in {3,6,9}; any H; any window size >= 1.
+ */
+int s3d_attn_fwd(const void *q, const void *k, const void *v,
+                 const void *tq, const void *tk, const void *tv,
+                 const int32_t *table_sizes_host, int D,
+                 const int32_t *w_sizes, const int32_t *w2n, const int32_t *n2n,
+                 const float *n_coords, int64_t N, int64_t W, int H, int hd, int dtype,
+                 void *out, float *lse, void *stream);
+
+/* Fused cRSE window attention, backward.
+ * Replaces  attn_cuda.cal_exp_sum_grads + attn_cuda.self_attn_indir_backward  and the host-side
+ * raw = norm*sum (Swin3D/src/attn/self_attn_aio_bwd.h:9-32, Swin3D/src/attn/attn_api.cpp:21,24,
+ * Swin3D/sparse_dl/attn/attn_coff.py:219-224).
+ *
+ *  out, lse     the forward's outputs;  dout [N,H,hd] dtype `dtype`: upstream gradient.
+ *  dq,dk,dv     [N,H,hd] dtype `dtype`, overwritten.
+ *  dtq,dtk,dtv  float[sum table_sizes], overwritten (zeroed on `stream`, then accumulated).
+ */
+int s3d_attn_bwd(const void *q, const void *k, const void *v,
+                 const void *tq, const void *tk, const void *tv,
+                 const int32_t *table_sizes_host, int D,
+                 const int32_t *w_sizes, const int32_t *w2n, const int32_t *n2n,
+                 const float *n_coords, int64_t N, int64_t W, int H, int hd, int dtype,
+                 const void *out, const float *lse, const void *dout,
+                 void *dq, void *dk, void *dv, float *dtq, float *dtk, float *dtv,
+                 void *stream);
+
+/* Dump of the cRSE row indices idx[q,k,n] of one window (for bit-exact index tests).
+ * Replaces nothing callable in the reference; it exposes PositionEmbedding::set_qk_offset
+ * (Swin3D/src/attn/attn_utils.cuh:437-453).  idx_out: int32[n*n*D], n = w_sizes[window].    */
+int s3d_debug_crse_indices(const float *n_coords, const int32_t *table_sizes_host, int D,
+                           int H, int hd, int32_t first_pos, int32_t n, int32_t *idx_out,
+                           void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Window builder.  Replaces BasicLayer.get_map_pair / get_window_mapping / get_index01 and
+ * sparse_self_attention (Swin3D/modules/swin3d_layers.py:713-822 and :76-150), i.e. the
+ * MinkowskiEngine pooling + insert_and_map + kernel_map + torch.sort + cumsum chain.
+ *
+ *  coords       int32[N,4] (batch, x, y, z), multiples of `stride` (the tensor stride).
+ *  shift        window shift in voxels (0 or ws/2); window = floor((c + shift*stride)/(ws*stride)).
+ *  feats        float[N,F] per-voxel signals: columns 0..2 = position inside the voxel in [0,1),
+ *               columns 3.. = colour / normal signals (F = 3, 6 or 9).
+ *  Outputs: n2n int32[N]; n_coords float[N,F] (cell + local xyz, then the other signals, sorted
+ *  order); w_sizes, w2n int32[>=N] (first W valid);
+ *  counts_out int64[4] = {W, M = sum w^2, max w, error word (1 = a coordinate or batch index is
+ *  outside the key range: batch < 1024, |window index| < 16384)}.
+ *  Windows come out in lexicographic (batch, wx, wy, wz) order, voxels inside a window in
+ *  ascending cell id cx*ws^2 + cy*ws + cz.
+ *  workspace: s3d_window_build_workspace_bytes(N) bytes.
+ */
+int64_t s3d_window_build_workspace_bytes(int64_t N);
+int s3d_window_build(const int32_t *coords, const float *feats, int64_t N, int F,
+                     int stride, int ws, int shift,
+                     int32_t *n2n, float *n_coords, int32_t *w_sizes, int32_t *w2n,
+                     int64_t *counts_out,
+                     void *workspace, int64_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Brute-force KNN.  Replaces knn_cuda.knn_cuda (Swin3D/src/knn/knn_cuda_kernel.h:5-12,
+ * Swin3D/src/knn/knn_api.cpp:4-6).
+ *  src [Ns,3], query [Nq,3] float; src_offset, query_offset int32[B] cumulative scene ends.
+ *  ret_idx int32[Nq,K] (row numbers into src), ret_dist float[Nq,K] SQUARED distances,
+ *  ascending; selection and tie behaviour identical to the reference's max-heap scan.
+ *  Slots without a candidate keep distance 2^31 and index 0.  1 <= K <= 64.
+ */
+int s3d_knn(int K, const float *src, const float *query, const int32_t *src_offset,
+            const int32_t *query_offset, int B, int64_t Ns, int64_t Nq,
+            int32_t *ret_idx, float *ret_dist, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SWIN3D_B200_H */

@@ -1,0 +1,136 @@
+/* CPU oracle for the Swin3D hot path -- TEST INFRASTRUCTURE ONLY.
+ *
+ * A plain-C restatement of the algorithms of microsoft/Swin3D's CUDA kernels, used to check
+ * the CUDA library of this repository and, timed on the host cores, as the reported CPU
+ * baseline.  The shipped library never links or calls this file.
+ *
+ * Parity pin: the reference ships no tests, fixtures or golden vectors for this path.  The
+ * oracle is pinned instead (a) against outputs of the reference's own compiled CUDA kernels
+ * recorded on a B200 and committed under tests/golden/, and (b) for the offset builder against
+ * the reference's Python function run in-process when the fixtures were generated.
+ *
+ * Build: make -C oracle   (gcc -O2 -fopenmp -shared)
+ */
+#include <float.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define REAL float
+#define SUF f32
+#include "attn_oracle_impl.inc"
+#undef REAL
+#undef SUF
+
+#define REAL double
+#define SUF f64
+#include "attn_oracle_impl.inc"
+#undef REAL
+#undef SUF
+
+int orc_max_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* cRSE row indices idx[q,k,n] (not offsets) of every pair of one window, for the bit-exact
+ * index test.  Follows Swin3D/src/attn/attn_utils.cuh:437-453; out is [n*n*D] int32.        */
+int orc_crse_indices(const float *n_coords, int D, const int32_t *table_sizes, int HC,
+                     int32_t base, int32_t n, int32_t *out)
+{
+    for (int32_t i = 0; i < n; ++i)
+        for (int32_t j = 0; j < n; ++j)
+            for (int d = 0; d < D; ++d) {
+                float rel = n_coords[(int64_t)(base + i) * D + d] -
+                            n_coords[(int64_t)(base + j) * D + d];
+                int32_t L = table_sizes[d] / HC;
+                rel += (float)(L / 2);
+                rel = fminf(fmaxf(0.0f, rel), (float)((double)L - 1e-10));
+                int32_t idx = (int32_t)rel;
+                if (d == D - 1 && idx >= L) idx = L - 1;
+                out[((int64_t)i * n + j) * D + d] = idx;
+            }
+    return 0;
+}
+
+/* ---- KNN: literal restatement of Swin3D/src/knn/knn_cuda_kernel.cu:29-62,139-204 ---------- */
+
+static void knn_max_heapify(float *heap, int32_t *idx, int start, int end)
+{
+    int curr = start;
+    int child = curr * 2 + 1;
+    while (child < end) {
+        if (child + 1 < end && heap[child] < heap[child + 1]) child++;
+        if (heap[curr] > heap[child]) return;
+        float tf = heap[curr]; heap[curr] = heap[child]; heap[child] = tf;
+        int32_t ti = idx[curr]; idx[curr] = idx[child]; idx[child] = ti;
+        curr = child;
+        child = curr * 2 + 1;
+    }
+}
+
+/* fma_mode selects how the fp32 expression dx*dx + dy*dy + dz*dz is contracted:
+ *   0: no contraction (three multiplies, two adds)
+ *   1: fma(dz,dz, fma(dy,dy, dx*dx))
+ *   2: fma(dz,dz, fma(dx,dx, dy*dy))
+ * nvcc contracts the reference's expression with its default -fmad=true; mode 1 is what the
+ * compiled reference kernel produces on sm_100 (checked bit-for-bit by the GPU parity tests).
+ * Slots that never receive a candidate keep distance 2^31 ((float)0x7fffffff, :5,165) and get
+ * index 0 here (the reference leaves them uninitialised).  Output: squared distances.        */
+int orc_knn(int K, const float *src, const float *query, const int32_t *src_offset,
+            const int32_t *query_offset, int B, int64_t Nq, int fma_mode,
+            int32_t *ret_idx, float *ret_dist, int nthreads)
+{
+    if (K < 1 || K > 64) return 1;
+#ifdef _OPENMP
+    if (nthreads > 0) omp_set_num_threads(nthreads);
+#endif
+#pragma omp parallel for schedule(dynamic, 64)
+    for (int64_t g = 0; g < Nq; ++g) {
+        float heap[64];
+        int32_t hidx[64];
+        for (int i = 0; i < K; ++i) { heap[i] = (float)0x7fffffff; hidx[i] = 0; }
+        const float qx = query[g * 3], qy = query[g * 3 + 1], qz = query[g * 3 + 2];
+        int b = 0;
+        for (; b < B; ++b)
+            if (g < query_offset[b]) break;
+        if (b >= B) b = B - 1; /* the reference would read past the offsets here */
+        const int32_t s0 = b > 0 ? src_offset[b - 1] : 0, s1 = src_offset[b];
+        for (int32_t i = s0; i < s1; ++i) {
+            const float dx = src[(int64_t)i * 3] - qx;
+            const float dy = src[(int64_t)i * 3 + 1] - qy;
+            const float dz = src[(int64_t)i * 3 + 2] - qz;
+            float d;
+            if (fma_mode == 1) d = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+            else if (fma_mode == 2) d = fmaf(dz, dz, fmaf(dx, dx, dy * dy));
+            else {
+                volatile float a = dx * dx, bb = dy * dy, c = dz * dz;
+                volatile float ab = a + bb;
+                d = ab + c;
+            }
+            if (d < heap[0]) {
+                heap[0] = d;
+                hidx[0] = i;
+                knn_max_heapify(heap, hidx, 0, K);
+            }
+        }
+        for (int i = K - 1; i > 0; --i) {
+            float tf = heap[0]; heap[0] = heap[i]; heap[i] = tf;
+            int32_t ti = hidx[0]; hidx[0] = hidx[i]; hidx[i] = ti;
+            knn_max_heapify(heap, hidx, 0, i);
+        }
+        for (int i = 0; i < K; ++i) {
+            ret_dist[g * K + i] = heap[i];
+            ret_idx[g * K + i] = hidx[i];
+        }
+    }
+    return 0;
+}

@@ -1,0 +1,30 @@
+// Host-side argument block and entry points of the attention kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace s3d {
+
+struct AttnArgs {
+    const void *q, *k, *v, *tq, *tk, *tv;
+    CrseMeta meta;
+    const int32_t *w_sizes, *w2n, *n2n;
+    const float *n_coords;
+    int64_t N, W;
+    int H, hd, dtype;
+    void *out;        // forward: written; backward: read
+    float *lse;       // forward: written; backward: read
+    const void *dout; // backward only
+    void *dq, *dk, *dv;
+    float *dtq, *dtk, *dtv;
+};
+
+// Generic path (attn_scalar.cu).
+int attn_scalar_forward(const AttnArgs &a, cudaStream_t st);
+int attn_scalar_backward(const AttnArgs &a, cudaStream_t st);
+int crse_indices_dump(const float *n_coords, const CrseMeta &meta, int first_pos, int n,
+                      int32_t *out, cudaStream_t st);
+
+}  // namespace s3d

@@ -1,0 +1,135 @@
+// extern "C" entry points of libswin3d_b200.so: argument validation and dispatch only.
+// The declarations, with the reference interfaces they replace, are in include/swin3d_b200.h.
+#include "attn_kernels.cuh"
+#include "knn_kernels.cuh"
+#include "window_kernels.cuh"
+
+using namespace s3d;
+
+namespace {
+
+int make_meta(const int32_t *table_sizes_host, int D, int H, int hd, CrseMeta &m)
+{
+    if (!table_sizes_host || H < 1) return S3D_ERR_BAD_ARG;
+    if (D != 3 && D != 6 && D != 9) return S3D_ERR_UNSUPPORTED;
+    if (hd != 8 && hd != 16 && hd != 32) return S3D_ERR_UNSUPPORTED;
+    const int HC = H * hd;
+    m.D = D;
+    int rows = 0;
+    for (int n = 0; n < S3D_MAX_SIGNAL_DIMS; ++n) { m.L[n] = 0; m.rowbase[n] = 0; }
+    for (int n = 0; n < D; ++n) {
+        if (table_sizes_host[n] <= 0 || table_sizes_host[n] % HC != 0) return S3D_ERR_BAD_ARG;
+        m.L[n] = table_sizes_host[n] / HC;
+        m.rowbase[n] = rows;
+        rows += m.L[n];
+    }
+    m.R = rows;
+    return S3D_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *s3d_status_string(int status)
+{
+    switch (status) {
+        case S3D_OK: return "ok";
+        case S3D_ERR_BAD_ARG: return "bad argument (null pointer, negative size, unknown dtype, or table size not a multiple of H*hd)";
+        case S3D_ERR_UNSUPPORTED: return "unsupported shape (head_dim must be 8, 16 or 32; signal dims 3, 6 or 9; K <= 64; window size <= 8)";
+        case S3D_ERR_LAUNCH: return "CUDA launch error";
+        case S3D_ERR_WORKSPACE: return "workspace too small";
+        default: return "unknown status";
+    }
+}
+
+int s3d_version(void) { return 1000; }
+
+int s3d_attn_fwd(const void *q, const void *k, const void *v, const void *tq, const void *tk,
+                 const void *tv, const int32_t *table_sizes_host, int D, const int32_t *w_sizes,
+                 const int32_t *w2n, const int32_t *n2n, const float *n_coords, int64_t N, int64_t W,
+                 int H, int hd, int dtype, void *out, float *lse, void *stream)
+{
+    if (N < 0 || W < 0 || (dtype != S3D_F32 && dtype != S3D_F16)) return S3D_ERR_BAD_ARG;
+    AttnArgs a{};
+    const int rc = make_meta(table_sizes_host, D, H, hd, a.meta);
+    if (rc != S3D_OK) return rc;
+    if (N == 0 || W == 0) return S3D_OK;
+    if (!q || !k || !v || !tq || !tk || !tv || !w_sizes || !w2n || !n2n || !n_coords || !out || !lse)
+        return S3D_ERR_BAD_ARG;
+    a.q = q; a.k = k; a.v = v; a.tq = tq; a.tk = tk; a.tv = tv;
+    a.w_sizes = w_sizes; a.w2n = w2n; a.n2n = n2n; a.n_coords = n_coords;
+    a.N = N; a.W = W; a.H = H; a.hd = hd; a.dtype = dtype;
+    a.out = out; a.lse = lse;
+    return attn_scalar_forward(a, static_cast<cudaStream_t>(stream));
+}
+
+int s3d_attn_bwd(const void *q, const void *k, const void *v, const void *tq, const void *tk,
+                 const void *tv, const int32_t *table_sizes_host, int D, const int32_t *w_sizes,
+                 const int32_t *w2n, const int32_t *n2n, const float *n_coords, int64_t N, int64_t W,
+                 int H, int hd, int dtype, const void *out, const float *lse, const void *dout,
+                 void *dq, void *dk, void *dv, float *dtq, float *dtk, float *dtv, void *stream)
+{
+    if (N < 0 || W < 0 || (dtype != S3D_F32 && dtype != S3D_F16)) return S3D_ERR_BAD_ARG;
+    AttnArgs a{};
+    const int rc = make_meta(table_sizes_host, D, H, hd, a.meta);
+    if (rc != S3D_OK) return rc;
+    if (!dtq || !dtk || !dtv) return S3D_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t tbytes = (size_t)a.meta.R * H * hd * sizeof(float);
+    if (cudaMemsetAsync(dtq, 0, tbytes, st) != cudaSuccess || cudaMemsetAsync(dtk, 0, tbytes, st) != cudaSuccess ||
+        cudaMemsetAsync(dtv, 0, tbytes, st) != cudaSuccess)
+        return S3D_ERR_LAUNCH;
+    if (N == 0 || W == 0) return S3D_OK;
+    if (!q || !k || !v || !tq || !tk || !tv || !w_sizes || !w2n || !n2n || !n_coords || !out || !lse ||
+        !dout || !dq || !dk || !dv)
+        return S3D_ERR_BAD_ARG;
+    a.q = q; a.k = k; a.v = v; a.tq = tq; a.tk = tk; a.tv = tv;
+    a.w_sizes = w_sizes; a.w2n = w2n; a.n2n = n2n; a.n_coords = n_coords;
+    a.N = N; a.W = W; a.H = H; a.hd = hd; a.dtype = dtype;
+    a.out = const_cast<void *>(out); a.lse = const_cast<float *>(lse); a.dout = dout;
+    a.dq = dq; a.dk = dk; a.dv = dv; a.dtq = dtq; a.dtk = dtk; a.dtv = dtv;
+    return attn_scalar_backward(a, st);
+}
+
+int s3d_debug_crse_indices(const float *n_coords, const int32_t *table_sizes_host, int D, int H,
+                           int hd, int32_t first_pos, int32_t n, int32_t *idx_out, void *stream)
+{
+    CrseMeta m;
+    const int rc = make_meta(table_sizes_host, D, H, hd, m);
+    if (rc != S3D_OK) return rc;
+    if (n < 0 || first_pos < 0) return S3D_ERR_BAD_ARG;
+    if (n == 0) return S3D_OK;
+    if (!n_coords || !idx_out) return S3D_ERR_BAD_ARG;
+    return crse_indices_dump(n_coords, m, first_pos, n, idx_out, static_cast<cudaStream_t>(stream));
+}
+
+int64_t s3d_window_build_workspace_bytes(int64_t N) { return window_build_workspace_bytes(N); }
+
+int s3d_window_build(const int32_t *coords, const float *feats, int64_t N, int F, int stride, int ws,
+                     int shift, int32_t *n2n, float *n_coords, int32_t *w_sizes, int32_t *w2n,
+                     int64_t *counts_out, void *workspace, int64_t workspace_bytes, void *stream)
+{
+    if (N < 0 || stride < 1 || shift < 0 || F < 3 || F > 3 + 2 * 3) return S3D_ERR_BAD_ARG;
+    if (ws < 1 || ws > 8) return S3D_ERR_UNSUPPORTED;
+    if (N >= (int64_t)1 << 31) return S3D_ERR_UNSUPPORTED;
+    if (!counts_out || !workspace) return S3D_ERR_BAD_ARG;
+    if (N > 0 && (!coords || !feats || !n2n || !n_coords || !w_sizes || !w2n)) return S3D_ERR_BAD_ARG;
+    return window_build_launch(coords, feats, N, F, stride, ws, shift, n2n, n_coords, w_sizes, w2n,
+                               counts_out, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int s3d_knn(int K, const float *src, const float *query, const int32_t *src_offset,
+            const int32_t *query_offset, int B, int64_t Ns, int64_t Nq, int32_t *ret_idx,
+            float *ret_dist, void *stream)
+{
+    if (K < 1 || K > S3D_KNN_MAX_K) return S3D_ERR_UNSUPPORTED;
+    if (B < 1 || Ns < 0 || Nq < 0) return S3D_ERR_BAD_ARG;
+    if (Nq == 0) return S3D_OK;
+    if (!query || !src_offset || !query_offset || !ret_idx || !ret_dist || (Ns > 0 && !src))
+        return S3D_ERR_BAD_ARG;
+    return knn_launch(K, src, query, src_offset, query_offset, B, Nq, ret_idx, ret_dist,
+                      static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,190 @@
+"""All-in-one cRSE window attention as an autograd Function.
+
+Call-compatible with the reference's ``Swin3D.sparse_dl.attn.attn_coff.SelfAttnAIOFunction``
+(microsoft/Swin3D, Swin3D/sparse_dl/attn/attn_coff.py:155-232): same positional arguments, same
+enums and enum values (:20-40), same dtype policy (:172-178, :207-217), same returned gradient
+tuple (six gradients, six None).  What runs underneath is one fused forward kernel and one fused
+backward kernel of libswin3d_b200.so instead of the reference's four kernels plus host-side
+normalisation; the forward saves (out, lse) instead of (sum, max, norm).
+"""
+import enum
+import weakref
+from typing import Any, List
+
+import torch
+from torch import Tensor
+from torch.autograd.function import Function
+
+from ... import _lib
+
+
+class PosEmb(enum.Enum):
+    NONE = enum.auto()
+    LINEAR = enum.auto()
+    SEPARATE = enum.auto()
+
+
+class TableDims(enum.Enum):
+    WHCD = enum.auto()
+    DWHC = enum.auto()
+    D0 = enum.auto()
+
+
+class IndexMode(enum.Enum):
+    DIRECT = enum.auto()
+    INDIRECT = enum.auto()
+
+
+class PrecisionMode(enum.Enum):
+    HALF_ALL = enum.auto()
+    HALF_FORWARD = enum.auto()
+    HALF_NONE = enum.auto()
+
+
+_DTYPE_CODE = {torch.float32: _lib.S3D_F32, torch.float16: _lib.S3D_F16}
+
+# int64 index tensors arrive unchanged for every block of a stage; convert each once.
+# Keyed by id() because tensors compare element-wise; the weak reference guards against id reuse.
+_int32_cache = {}
+
+
+def _as_int32(t: Tensor) -> Tensor:
+    if t.dtype == torch.int32 and t.is_contiguous():
+        return t
+    key = id(t)
+    hit = _int32_cache.get(key)
+    if hit is not None and hit[0]() is t and hit[1] == t._version:
+        return hit[2]
+    conv = t.to(torch.int32).contiguous()
+    _int32_cache[key] = (weakref.ref(t, lambda _r, key=key: _int32_cache.pop(key, None)),
+                         t._version, conv)
+    return conv
+
+
+def _table_sizes_host(table_offsets) -> List[int]:
+    """Elements per signal dimension as Python ints (a device tensor costs one D2H copy)."""
+    if isinstance(table_offsets, Tensor):
+        return [int(x) for x in table_offsets.detach().cpu().tolist()]
+    return [int(x) for x in table_offsets]
+
+
+def _check_inputs(q: Tensor, k: Tensor, v: Tensor, tables, indices):
+    for name, t in (("query", q), ("key", k), ("value", v)):
+        if not t.is_cuda:
+            raise RuntimeError(f"{name}_feats must be a CUDA tensor")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name}_feats must be contiguous")
+        if t.dim() != 3 or t.shape != q.shape:
+            raise ValueError(f"{name}_feats must have shape [N, heads, head_dim] like the query")
+    for t in tables:
+        if not t.is_cuda or not t.is_contiguous():
+            raise RuntimeError("tables must be contiguous CUDA tensors")
+    if len(indices) != 6:
+        raise ValueError("IndexMode.INDIRECT takes six index tensors "
+                         "[m2w, w_sizes, w2m, w2n, n2n, n_coords]")
+
+
+def attn_forward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n_coords):
+    """One fused forward launch.  Tensors must already have the compute dtype.  -> (out, lse)."""
+    import ctypes
+    N, H, hd = q.shape
+    W = w_sizes.shape[0]
+    D = len(sizes)
+    if n_coords.shape != (N, D):
+        raise ValueError(f"n_coords must have shape [{N}, {D}]")
+    out = torch.empty_like(q)
+    lse = torch.empty((N, H), dtype=torch.float32, device=q.device)
+    arr = (ctypes.c_int32 * D)(*sizes)
+    with torch.cuda.device(q.device):
+        st = torch.cuda.current_stream().cuda_stream
+        rc = _lib.lib.s3d_attn_fwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(),
+            ctypes.cast(arr, ctypes.c_void_p), D, w_sizes.data_ptr(), w2n.data_ptr(),
+            n2n.data_ptr(), n_coords.data_ptr(), N, W, H, hd, _DTYPE_CODE[q.dtype],
+            out.data_ptr(), lse.data_ptr(), st)
+    _lib.check(rc, "s3d_attn_fwd")
+    return out, lse
+
+
+def attn_backward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n_coords,
+                      out, lse, dout):
+    """One fused backward launch -> (dq, dk, dv, dtq, dtk, dtv); table grads are fp32."""
+    import ctypes
+    N, H, hd = q.shape
+    W = w_sizes.shape[0]
+    D = len(sizes)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    tn = sum(sizes)
+    dt = torch.empty((3, tn), dtype=torch.float32, device=q.device)
+    arr = (ctypes.c_int32 * D)(*sizes)
+    with torch.cuda.device(q.device):
+        st = torch.cuda.current_stream().cuda_stream
+        rc = _lib.lib.s3d_attn_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(),
+            ctypes.cast(arr, ctypes.c_void_p), D, w_sizes.data_ptr(), w2n.data_ptr(),
+            n2n.data_ptr(), n_coords.data_ptr(), N, W, H, hd, _DTYPE_CODE[q.dtype],
+            out.data_ptr(), lse.data_ptr(), dout.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+            dv.data_ptr(), dt[0].data_ptr(), dt[1].data_ptr(), dt[2].data_ptr(), st)
+    _lib.check(rc, "s3d_attn_bwd")
+    return dq, dk, dv, dt[0], dt[1], dt[2]
+
+
+class SelfAttnAIOFunction(Function):
+    """Function of all-in-one self-attention (fused forward / fused backward)."""
+
+    @staticmethod
+    def forward(ctx, raw_query_feats, raw_key_feats, raw_value_feats, query_table, key_table,
+                value_table, table_offsets, indices: List[Tensor], pe: PosEmb,
+                table_dim: TableDims, mode: IndexMode, precision: PrecisionMode):
+        assert table_dim == TableDims.D0
+        if mode != IndexMode.INDIRECT or pe != PosEmb.SEPARATE:
+            raise NotImplementedError(
+                "only IndexMode.INDIRECT with PosEmb.SEPARATE is implemented "
+                "(the combination WindowAttention passes)")
+        _check_inputs(raw_query_feats, raw_key_feats, raw_value_feats,
+                      (query_table, key_table, value_table), indices)
+        ctx.precision = precision
+
+        # dtype policy of the reference (attn_coff.py:172-178)
+        if torch.is_autocast_enabled() and precision != PrecisionMode.HALF_NONE:
+            c_dtype = torch.get_autocast_gpu_dtype()
+        else:
+            c_dtype = torch.float32
+        if c_dtype not in _DTYPE_CODE:
+            raise ValueError(f"compute dtype {c_dtype} is not supported (float32 or float16)")
+
+        qkv = [t.to(c_dtype) for t in (raw_query_feats, raw_key_feats, raw_value_feats)]
+        tabs = [t.to(c_dtype).contiguous() for t in (query_table, key_table, value_table)]
+        sizes = _table_sizes_host(table_offsets)
+        _, w_sizes, _, w2n, n2n, n_coords = indices
+        w_sizes, w2n, n2n = _as_int32(w_sizes), _as_int32(w2n), _as_int32(n2n)
+        n_coords = n_coords.to(torch.float32).contiguous()
+
+        out, lse = attn_forward_raw(*qkv, *tabs, sizes, w_sizes, w2n, n2n, n_coords)
+
+        ctx.sizes = sizes
+        ctx.save_for_backward(out, lse, raw_query_feats, raw_key_feats, raw_value_feats,
+                              query_table, key_table, value_table, w_sizes, w2n, n2n, n_coords)
+        return out
+
+    @staticmethod
+    def backward(ctx: Any, *grad_outputs: Any) -> Any:
+        (grad,) = grad_outputs
+        (out, lse, q, k, v, tq, tk, tv, w_sizes, w2n, n2n, n_coords) = ctx.saved_tensors
+        precision: PrecisionMode = ctx.precision
+        # dtype policy of the reference (attn_coff.py:207-217)
+        if precision == PrecisionMode.HALF_ALL:
+            c_dtype = grad.dtype
+        else:
+            c_dtype = torch.float32
+        if c_dtype not in _DTYPE_CODE:
+            raise ValueError(f"compute dtype {c_dtype} is not supported (float32 or float16)")
+        qkv = [t.to(c_dtype) for t in (q, k, v)]
+        tabs = [t.to(c_dtype).contiguous() for t in (tq, tk, tv)]
+        dq, dk, dv, dtq, dtk, dtv = attn_backward_raw(
+            *qkv, *tabs, ctx.sizes, w_sizes, w2n, n2n, n_coords,
+            out.to(c_dtype), lse, grad.to(c_dtype).contiguous())
+        grads = (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype),
+                 dtq.to(tq.dtype).view_as(tq), dtk.to(tk.dtype).view_as(tk),
+                 dtv.to(tv.dtype).view_as(tv))
+        return (*grads, None, None, None, None, None, None)

@@ -1,0 +1,171 @@
+"""GPU parity: the CUDA attention kernels (through the C-ABI) against the CPU oracle.
+
+Tolerances (relative = max|a-b| / max|b|, as the benchmark's north star states them):
+fp32 outputs and gradients 1e-4; fp16 storage 2e-2; cRSE indices bit-exact.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from swin3d_b200 import synthetic as S
+from tests.helpers import make_problem, oracle_fwd_bwd, rel_err
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-4
+FP16_TOL = 2e-2
+
+CASES = [
+    # crse, H, hd, ws, shift
+    ("XYZ", 2, 8, 5, 0),
+    ("XYZ_RGB", 6, 8, 5, 0),       # the single-layer CPU-sized config: 6 heads of 8, window 5
+    ("XYZ_RGB", 6, 8, 5, 2),
+    ("XYZ_RGB_NORM", 10, 8, 5, 2), # Swin3D-L stage-1 head layout
+    ("XYZ_RGB_NORM", 3, 16, 7, 3),
+    ("XYZ_RGB", 1, 32, 5, 0),
+]
+
+
+@pytest.mark.parametrize("crse,H,hd,ws,shift", CASES)
+def test_fp32_forward_backward_match_oracle(crse, H, hd, ws, shift):
+    from tests.gpu_helpers import cuda_fwd_bwd
+    p = make_problem(seed=11, n_voxels=1200, grid=28, ws=ws, shift=shift, H=H, hd=hd, crse=crse)
+    o_ref, lse_ref, g_ref = oracle_fwd_bwd(p, np.float64)
+    out, lse, grads = cuda_fwd_bwd(p, torch.float32)
+    assert rel_err(out, o_ref) < FP32_TOL
+    assert np.abs(lse - lse_ref).max() < 1e-4
+    for name, a, b in zip("dq dk dv dtq dtk dtv".split(), grads, g_ref):
+        assert rel_err(a, b) < FP32_TOL, name
+
+
+@pytest.mark.parametrize("crse,H,hd,ws,shift", CASES[1:5])
+def test_fp16_forward_backward_match_oracle(crse, H, hd, ws, shift):
+    from tests.gpu_helpers import cuda_fwd_bwd
+    p = make_problem(seed=12, n_voxels=1200, grid=28, ws=ws, shift=shift, H=H, hd=hd, crse=crse,
+                     round_fp16=True)
+    o_ref, lse_ref, g_ref = oracle_fwd_bwd(p, np.float64)
+    out, lse, grads = cuda_fwd_bwd(p, torch.float16)
+    assert rel_err(out, o_ref) < FP16_TOL
+    for name, a, b in zip("dq dk dv dtq dtk dtv".split(), grads, g_ref):
+        assert rel_err(a, b) < FP16_TOL, name
+
+
+def test_config1_full_size_fp32():
+    """4,096 voxels from 3 planes + 2 boxes in a 64^3 grid, C=48, 6 heads, window 5, XYZ_RGB."""
+    from tests.gpu_helpers import cuda_fwd_bwd
+    for shift in (0, 2):
+        p = make_problem(seed=0, n_voxels=4096, grid=64, ws=5, shift=shift, H=6, hd=8, crse="XYZ_RGB")
+        o_ref, _, g_ref = oracle_fwd_bwd(p, np.float64)
+        out, _, grads = cuda_fwd_bwd(p, torch.float32)
+        assert rel_err(out, o_ref) < FP32_TOL
+        for a, b in zip(grads, g_ref):
+            assert rel_err(a, b) < FP32_TOL
+
+
+def test_dense_windows_up_to_full_occupancy():
+    """Fully occupied 5^3 and 7^3 windows (125 and 343 voxels) plus single-voxel windows."""
+    from tests.gpu_helpers import cuda_fwd_bwd
+    g = np.stack(np.meshgrid(*[np.arange(7)] * 3, indexing="ij"), -1).reshape(-1, 3)
+    lonely = np.array([[40, 40, 40], [60, 3, 9], [90, 90, 90]])
+    pts = np.concatenate([g, lonely])
+    n = len(pts)
+    rng = np.random.default_rng(5)
+    sc = S.Scene(np.concatenate([np.zeros((n, 1)), pts], 1).astype(np.int32),
+                 rng.random((n, 3), dtype=np.float32) * 0.999, rng.random((n, 3), dtype=np.float32),
+                 np.tile(np.array([[0, 0, 1]], dtype=np.float32), (n, 1)))
+    for ws in (5, 7):
+        p = make_problem(seed=2, ws=ws, H=2, hd=8, crse="XYZ_RGB_NORM", scene=sc)
+        assert p.w_sizes.max() == ws ** 3 and p.w_sizes.min() == 1
+        o_ref, _, g_ref = oracle_fwd_bwd(p, np.float64)
+        out, _, grads = cuda_fwd_bwd(p, torch.float32)
+        assert rel_err(out, o_ref) < FP32_TOL
+        for a, b in zip(grads, g_ref):
+            assert rel_err(a, b) < FP32_TOL
+
+
+def test_crse_indices_bit_exact_including_clamp_quirk():
+    import ctypes
+    from swin3d_b200 import _lib
+    from tests.gpu_helpers import dev
+    p = make_problem(seed=21, n_voxels=900, grid=24, H=2, hd=8, crse="XYZ_RGB_NORM")
+    nc = p.n_crse.copy()
+    w = int(np.argmax(p.w_sizes))
+    base, n = int(p.w2n[w]), int(p.w_sizes[w])
+    # force differences of exactly +-2*quant*2 = +-16 in a colour and in the last normal dimension
+    nc[base, 4], nc[base + 1, 4] = 8.0, -8.0
+    nc[base, 8], nc[base + 1, 8] = 8.0, -8.0
+    ref = O.crse_indices(nc, p.sizes, p.H, p.hd, base, n)
+    assert ref[0, 1, 4] == 32 and ref[0, 1, 8] == 31
+    out = torch.empty((n, n, p.D), dtype=torch.int32, device="cuda")
+    arr = (ctypes.c_int32 * p.D)(*p.sizes)
+    rc = _lib.lib.s3d_debug_crse_indices(dev(nc).data_ptr(), ctypes.cast(arr, ctypes.c_void_p), p.D,
+                                         p.H, p.hd, base, n, out.data_ptr(), None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), ref)
+
+
+def test_index_equal_to_L_uses_next_dimension_row_zero():
+    """With idx == L in a non-last dimension the flat table addressing of the reference selects
+    row 0 of the next dimension; the kernels and the oracle must agree on that."""
+    from tests.gpu_helpers import cuda_fwd_bwd
+    p = make_problem(seed=22, n_voxels=500, grid=20, H=2, hd=8, crse="XYZ_RGB")
+    p.n_crse[::7, 3] = 8.0
+    p.n_crse[3::7, 3] = -8.0
+    o_ref, _, g_ref = oracle_fwd_bwd(p, np.float64)
+    out, _, grads = cuda_fwd_bwd(p, torch.float32)
+    assert rel_err(out, o_ref) < FP32_TOL
+    for a, b in zip(grads, g_ref):
+        assert rel_err(a, b) < FP32_TOL
+
+
+def test_autograd_function_all_precision_modes():
+    """The drop-in Function: gradients through torch.autograd, dtype policy of the reference."""
+    from swin3d_b200.sparse_dl.attn.attn_coff import (SelfAttnAIOFunction, PosEmb, TableDims,
+                                                      IndexMode, PrecisionMode)
+    from tests.gpu_helpers import dev
+    p = make_problem(seed=31, n_voxels=800, grid=24, H=6, hd=8, crse="XYZ_RGB", round_fp16=True)
+    o_ref, _, g_ref = oracle_fwd_bwd(p, np.float64)
+    x_off, y_off, m2w, ws64, w2n64, w2m = O.window_offsets(p.w_sizes)
+    indices = [dev(m2w), dev(ws64), dev(w2m), dev(w2n64), dev(p.n2n.astype(np.int64)), dev(p.n_crse)]
+    offsets = torch.IntTensor(p.sizes).cuda()
+    for precision, autocast, tol in ((PrecisionMode.HALF_NONE, False, FP32_TOL),
+                                     (PrecisionMode.HALF_NONE, True, FP32_TOL),
+                                     (PrecisionMode.HALF_FORWARD, True, FP16_TOL),
+                                     (PrecisionMode.HALF_ALL, True, FP16_TOL),
+                                     (PrecisionMode.HALF_ALL, False, FP32_TOL)):
+        q, k, v = (dev(a).requires_grad_() for a in (p.q, p.k, p.v))
+        tq, tk, tv = (dev(a).requires_grad_() for a in (p.tq, p.tk, p.tv))
+        with torch.autocast("cuda", dtype=torch.float16, enabled=autocast):
+            out = SelfAttnAIOFunction.apply(q, k, v, tq, tk, tv, offsets, indices, PosEmb.SEPARATE,
+                                            TableDims.D0, IndexMode.INDIRECT, precision)
+        expect = torch.float16 if (autocast and precision != PrecisionMode.HALF_NONE) else torch.float32
+        assert out.dtype == expect
+        out.backward(dev(p.g).to(out.dtype))
+        assert rel_err(out.detach().double().cpu().numpy(), o_ref) < tol
+        for t, b in zip((q, k, v, tq, tk, tv), g_ref):
+            assert t.grad is not None and t.grad.dtype == torch.float32
+            assert rel_err(t.grad.double().cpu().numpy(), b) < tol
+
+
+def test_empty_and_degenerate_inputs():
+    from swin3d_b200.sparse_dl.attn import attn_coff as C
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device="cuda")
+    sizes = [40 * 16] * 3
+    out, lse = C.attn_forward_raw(z(0, 2, 8), z(0, 2, 8), z(0, 2, 8), z(1920), z(1920), z(1920), sizes,
+                                  z(0, dt=torch.int32), z(0, dt=torch.int32), z(0, dt=torch.int32), z(0, 3))
+    assert out.shape == (0, 2, 8) and lse.shape == (0, 2)
+    with pytest.raises(ValueError):
+        C.attn_forward_raw(z(4, 2, 12), z(4, 2, 12), z(4, 2, 12), z(2880), z(2880), z(2880), [960] * 3,
+                           z(1, dt=torch.int32), z(1, dt=torch.int32), z(4, dt=torch.int32), z(4, 3))
+
+
+def test_run_to_run_determinism_of_forward():
+    from tests.gpu_helpers import cuda_fwd_bwd
+    p = make_problem(seed=41, n_voxels=700, grid=22, H=2, hd=8, crse="XYZ_RGB")
+    a = cuda_fwd_bwd(p)
+    b = cuda_fwd_bwd(p)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    for i in range(3):   # dq, dk, dv are owned by one thread each: bit-identical
+        assert np.array_equal(a[2][i], b[2][i])
