@@ -1,0 +1,404 @@
+#!/usr/bin/env python
+"""Benchmark of the cRSE window-attention hot path (forward + backward).
+
+Workload (single GPU): the Swin3D-L stage-1 attention micro-benchmark -- 8 synthetic rooms,
+about 1 M occupied voxels, 80 channels as 10 heads of 8, window 5, quant_size 4, cRSE
+XYZ_RGB_NORM (9 signal dims), fp16 storage, fp32 accumulation; one step = one fused forward and
+one fused backward launch over the whole batch (steps alternate between the unshifted and the
+shifted window set, as consecutive Swin blocks do).  Metric: voxels per second, forward+backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload attn|knn]
+
+N > 1: launched under torchrun, one rank per GPU; every rank owns its own batch of rooms (weak
+scaling, as in data-parallel training) and the only exchange is the NCCL all-reduce of the three
+table-gradient arrays.  `--impl reference` times the CPU restatement of the reference kernels
+(the reference has no CPU code of its own) on the host cores, on a bounded sample.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG = dict(H=10, hd=8, ws=5, quant=4, crse="XYZ_RGB_NORM", rooms=8, voxels_per_room=125_000)
+
+
+def bytes_fwd(C, b, D, H):
+    """Algorithmic HBM bytes per voxel, forward: q,k,v read + out written, n_coords, n2n, lse."""
+    return 4 * C * b + 4 * D + 4 + 4 * H
+
+
+def bytes_bwd(C, b, D, H):
+    """Backward: q,k,v,out,dout read + dq,dk,dv written, n_coords, n2n, lse."""
+    return 8 * C * b + 4 * D + 4 + 4 * H
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_batch(rank: int, rooms: int, voxels_per_room: int):
+    from swin3d_b200 import synthetic as S
+    scenes = [S.make_room(1000 * rank + s, target_voxels=voxels_per_room, batch_index=s)
+              for s in range(rooms)]
+    return S.concat_scenes(scenes)
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-i", str(self.gpu), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def cpu_baseline_attention(sample_rooms=1, voxels=None, threads=0, steps=1, warmup=0):
+    """Times the CPU oracle (fp32, all host threads) on a bounded sample of the workload."""
+    from oracle import oracle as O
+    from swin3d_b200 import synthetic as S
+    c = CFG
+    sc = make_batch(0, sample_rooms, voxels or c["voxels_per_room"])
+    feats = S.signal_feats(sc, c["crse"])
+    n2n, n_coords, w_sizes, w2n = O.window_grouping(sc.coords, feats, c["ws"], 0)
+    ncr = S.quantise_signals(n_coords, c["quant"])
+    sizes = S.table_sizes(c["ws"], c["quant"], c["H"], c["hd"], c["crse"])
+    t = S.make_tables(1, sizes)
+    N = sc.coords.shape[0]
+    rng = np.random.default_rng(0)
+    q, k, v, g = (rng.standard_normal((N, c["H"], c["hd"])).astype(np.float32) for _ in range(4))
+    q *= c["hd"] ** -0.5
+    nthreads = threads or O.max_threads()
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        out, s, mx = O.attn_forward(q, k, v, t[0], t[1], t[2], sizes, w_sizes, w2n, n2n, ncr,
+                                    dtype=np.float32, nthreads=nthreads)
+        O.attn_backward(q, k, v, t[0], t[1], t[2], sizes, w_sizes, w2n, n2n, ncr, out, s, mx, g,
+                        dtype=np.float32, nthreads=nthreads)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    return {"value": N / sec, "unit": "voxels/s", "cores": nthreads, "kind": "port",
+            "sample": f"{sample_rooms} room(s), {N} voxels, fp32 fwd+bwd, {sec:.2f} s per pass"}, sec, N
+
+
+def workload_config():
+    c = CFG
+    return {"workload": "Swin3D-L stage-1 cRSE window attention fwd+bwd, 8 synthetic rooms ~1M voxels",
+            "channels": c["H"] * c["hd"], "heads": c["H"], "window": c["ws"], "quant_size": c["quant"],
+            "cRSE": c["crse"], "rooms_per_gpu": c["rooms"], "voxels_per_room": c["voxels_per_room"],
+            "l2": "inputs larger than L2 (q,k,v,dout,out = 5 x ~160 MB per step)"}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    base, sec, N = cpu_baseline_attention(sample_rooms=4, steps=max(args.steps, 1),
+                                          warmup=min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": "attn fwd+bwd voxels/sec @Swin3D-L stage1",
+        "value": base["value"], "unit": "voxels/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(),
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "voxels/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "note": "the reference has no CPU implementation of this path; this is the C restatement of "
+                "its kernels (oracle/) on the host cores, a four-room sample (half the batch) per step",
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_attention(args):
+    import torch
+    import torch.distributed as dist
+    from swin3d_b200 import synthetic as S
+    from swin3d_b200.sparse_dl.attn import attn_coff as C
+    from swin3d_b200.window import build_windows
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    c = CFG
+    H, hd, ws, quant, crse = c["H"], c["hd"], c["ws"], c["quant"], c["crse"]
+    Cc = H * hd
+    sc = make_batch(rank, args.rooms or c["rooms"], c["voxels_per_room"])
+    N = sc.coords.shape[0]
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    coords_d, feats_d = dev(sc.coords), dev(S.signal_feats(sc, crse))
+    sizes = S.table_sizes(ws, quant, H, hd, crse)
+    D = len(sizes)
+
+    # window sets for the unshifted and the shifted blocks (built by the library's own kernels)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    win, wb_ms = [], []
+    for shift in (0, ws // 2):
+        ms = 0.0
+        for _ in range(2):
+            torch.cuda.synchronize()
+            e0.record()
+            wi = build_windows(coords_d, feats_d, ws, shift)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+        wb_ms.append(ms)
+        ncr = wi.n_coords.clone()
+        ncr[:, :3] *= quant
+        ncr[:, 3:] *= 2 * quant
+        win.append((wi, ncr.contiguous()))
+    M = [w.num_pairs for w, _ in win]
+
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    rnd = lambda: torch.randn((N, H, hd), device="cuda", generator=gen, dtype=torch.float32)
+    q = (rnd() * hd ** -0.5).half()
+    k, v, g = rnd().half(), rnd().half(), rnd().half()
+    tabs = [dev(t).half() for t in S.make_tables(1, sizes)]
+    table_grads = torch.zeros((3, sum(sizes)), dtype=torch.float32, device="cuda")
+
+    def step(i, ev=None):
+        wi, ncr = win[i % 2]
+        if ev:
+            ev[0].record()
+        out, lse = C.attn_forward_raw(q, k, v, *tabs, sizes, wi.w_sizes, wi.w2n, wi.n2n, ncr)
+        if ev:
+            ev[1].record()
+        grads = C.attn_backward_raw(q, k, v, *tabs, sizes, wi.w_sizes, wi.w2n, wi.n2n, ncr, out, lse, g)
+        if ev:
+            ev[2].record()
+        if world > 1:
+            table_grads.copy_(torch.stack(grads[3:6]))
+            dist.all_reduce(table_grads)
+        return out, grads
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0.record()
+    for i in range(args.steps):
+        step(i, evs[i])
+    t1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t0.elapsed_time(t1)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+
+    # ---- end to end through the public autograd Function, host buffers in and out ------------
+    x_pin = [t.cpu().pin_memory() for t in (q, k, v, g)]
+    out_pin = [torch.empty((N, H, hd), dtype=torch.float16).pin_memory() for _ in range(4)]
+    tg_pin = torch.empty((3, sum(sizes)), dtype=torch.float32).pin_memory()
+    offsets_cpu = torch.IntTensor(sizes)
+    tab_params = [t.float().requires_grad_() for t in tabs]
+    idx_lists = [wi.reference_indices(ncr) for wi, ncr in win]
+
+    def e2e_step(i):
+        dq_, dk_, dv_, dg_ = (x.cuda(non_blocking=True) for x in x_pin)
+        dq_.requires_grad_()
+        dk_.requires_grad_()
+        dv_.requires_grad_()
+        for p in tab_params:
+            p.grad = None
+        with torch.autocast("cuda", dtype=torch.float16):
+            o = C.SelfAttnAIOFunction.apply(dq_, dk_, dv_, *tab_params, offsets_cpu, idx_lists[i % 2],
+                                            C.PosEmb.SEPARATE, C.TableDims.D0, C.IndexMode.INDIRECT,
+                                            C.PrecisionMode.HALF_ALL)
+        o.backward(dg_)
+        out_pin[0].copy_(o.detach(), non_blocking=True)
+        out_pin[1].copy_(dq_.grad, non_blocking=True)
+        out_pin[2].copy_(dk_.grad, non_blocking=True)
+        out_pin[3].copy_(dv_.grad, non_blocking=True)
+        tgs = torch.stack([p.grad for p in tab_params])
+        if world > 1:
+            dist.all_reduce(tgs)
+        tg_pin.copy_(tgs, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    for i in range(2):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    t1.record()
+    torch.cuda.synchronize()
+    e2e_ms = t0.elapsed_time(t1) / e2e_steps
+
+    stats = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e_ms, float(N)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms, fwd_ms, bwd_ms, e2e_ms = (float(x) for x in mx[:4])
+        n_total = float(sm[4])
+    else:
+        n_total = float(N)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    ms_per_step = total_ms / args.steps
+    value = n_total / (ms_per_step * 1e-3)
+    peak, peak_src = load_peaks()
+    b = 2
+    pv_fwd, pv_bwd = bytes_fwd(Cc, b, D, H), bytes_bwd(Cc, b, D, H)
+    bwd_gbs = N * pv_bwd / (bwd_ms * 1e-3) / 1e9
+    fwd_gbs = N * pv_fwd / (fwd_ms * 1e-3) / 1e9
+    both_gbs = N * (pv_fwd + pv_bwd) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as fh:
+            per_voxel = json.load(fh).get("attn_bwd_dram_bytes_per_voxel")
+            traffic = per_voxel * N if per_voxel else None
+    cpu_base = None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu_base, _, _ = cpu_baseline_attention(sample_rooms=2)
+    line = {
+        "metric": "attn fwd+bwd voxels/sec @Swin3D-L stage1", "value": value, "unit": "voxels/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 storage, f32 accumulate", "data": "synthetic", "config": workload_config(),
+        "voxels_per_gpu": N, "pairs_per_gpu": M, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+        "window_build_ms": wb_ms,
+        "roofline": {"bound": "hbm", "kernel": "attention backward", "achieved": bwd_gbs, "peak": peak,
+                     "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": traffic, "peak_source": peak_src,
+                     "algorithmic_bytes_per_voxel": {"fwd": pv_fwd, "bwd": pv_bwd},
+                     "fwd": {"achieved": fwd_gbs, "frac": fwd_gbs / peak},
+                     "fwd_plus_bwd": {"achieved": both_gbs, "frac": both_gbs / peak}},
+        "cpu_baseline": cpu_base,
+        "e2e": {"value": n_total / (e2e_ms * 1e-3), "unit": "voxels/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": 4 * N * Cc * 2,
+                "d2h_bytes_per_step": 4 * N * Cc * 2 + 3 * sum(sizes) * 4},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_knn(args):
+    """Secondary workload: KNN stress (200k queries x 50k sources per scene, 8 scenes, K=16 and 3)."""
+    import torch
+    from swin3d_b200 import synthetic as S
+    from swin3d_b200.sparse_dl.knn.knn import knn_raw
+    rank = int(os.environ.get("RANK", "0"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    scenes = [S.make_knn_scene(100 * rank + s, 200_000, 50_000) for s in range(8)]
+    src = torch.from_numpy(np.concatenate([s for s, _ in scenes])).cuda()
+    qry = torch.from_numpy(np.concatenate([q for _, q in scenes])).cuda()
+    so = torch.arange(1, 9, dtype=torch.int32, device="cuda") * 50_000
+    qo = torch.arange(1, 9, dtype=torch.int32, device="cuda") * 200_000
+    res = {}
+    for K in (16, 3):
+        for _ in range(max(args.warmup, 1)):
+            knn_raw(K, src, qry, so, qo)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            knn_raw(K, src, qry, so, qo)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        res[f"K{K}"] = {"ms": ms, "queries_per_s": qry.shape[0] / (ms * 1e-3),
+                        "pair_evals_per_s": 8 * 200_000 * 50_000 / (ms * 1e-3)}
+    if rank == 0:
+        print(json.dumps({"metric": "knn queries/sec (8 scenes x 200k queries x 50k sources)",
+                          "unit": "queries/s", "value": res["K16"]["queries_per_s"], "detail": res,
+                          "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "data": "synthetic",
+                          "dtype": "f32", "higher_is_better": True}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="attn", choices=["attn", "knn"])
+    ap.add_argument("--rooms", type=int, default=0, help="rooms per GPU (default 8)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    if args.workload == "knn":
+        return run_knn(args)
+    return run_attention(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

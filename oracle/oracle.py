@@ -108,7 +108,7 @@ def crse_indices(n_coords, table_sizes, H, hd, first_pos, n):
     return out
 
 
-def knn(K, src, query, src_offset, query_offset, fma_mode: int = 1, nthreads: int = 0):
+def knn(K, src, query, src_offset, query_offset, fma_mode: int = 2, nthreads: int = 0):
     """Literal max-heap KNN -> (idx int32 [Nq,K], SQUARED dist float32 [Nq,K])."""
     src = np.ascontiguousarray(src, dtype=np.float32)
     query = np.ascontiguousarray(query, dtype=np.float32)

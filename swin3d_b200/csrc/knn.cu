@@ -34,17 +34,13 @@ __device__ __forceinline__ void knn_sift_down(float *heap, int *idx, int start, 
 }
 
 // fp32 squared distance.  The reference writes dx*dx + dy*dy + dz*dz and lets nvcc contract it;
-// the contraction below is the one its compiled kernel produces (pinned bit-for-bit by the GPU
-// parity test against the compiled reference).
+// its compiled kernel (nvcc 12.9, default -fmad=true, sm_100) evaluates
+// fma(dz,dz, fma(dx,dx, dy*dy)), established by comparing bit patterns of its output with the
+// three possible contractions.  The expression is spelled with intrinsics so that it cannot
+// drift with compiler versions; the GPU parity test re-checks it against the compiled reference.
 __device__ __forceinline__ float knn_dist2(float dx, float dy, float dz)
 {
-#if S3D_KNN_FMA_MODE == 2
     return __fmaf_rn(dz, dz, __fmaf_rn(dx, dx, __fmul_rn(dy, dy)));
-#elif S3D_KNN_FMA_MODE == 0
-    return __fadd_rn(__fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy)), __fmul_rn(dz, dz));
-#else
-    return __fmaf_rn(dz, dz, __fmaf_rn(dy, dy, __fmul_rn(dx, dx)));
-#endif
 }
 
 template <int KMAX>

@@ -30,9 +30,11 @@ ATTN_CASES = {
     "f32_hd16_xyz": dict(kw=dict(seed=101, n_voxels=350, grid=18, H=2, hd=16, crse="XYZ"), dtype="float32"),
     "f32_hd16_rgb_shift": dict(kw=dict(seed=102, n_voxels=350, grid=18, H=2, hd=16, crse="XYZ_RGB", shift=2), dtype="float32"),
     "f32_hd32_norm": dict(kw=dict(seed=103, n_voxels=300, grid=18, H=2, hd=32, crse="XYZ_RGB_NORM"), dtype="float32"),
-    "f64_hd16_norm": dict(kw=dict(seed=104, n_voxels=300, grid=18, H=4, hd=16, crse="XYZ_RGB_NORM"), dtype="float64"),
+    "f64_hd16_rgb": dict(kw=dict(seed=104, n_voxels=200, grid=16, H=2, hd=16, crse="XYZ_RGB"), dtype="float64"),
     "f16_hd32_rgb": dict(kw=dict(seed=105, n_voxels=300, grid=18, H=2, hd=32, crse="XYZ_RGB", round_fp16=True), dtype="float16"),
 }
+# the cases whose reference outputs are committed as a fixture (the others only run on the GPU)
+GOLDEN = ("f32_hd16_rgb_shift", "f64_hd16_rgb", "f16_hd32_rgb", "knn_k3", "knn_k16")
 KNN_CASES = {"knn_k3": dict(seed=201, K=3), "knn_k16": dict(seed=202, K=16), "knn_k64": dict(seed=203, K=64)}
 
 
@@ -93,11 +95,15 @@ def main():
         return 0
     out = {}
     for name, c in ATTN_CASES.items():
+        if name not in GOLDEN:
+            continue
         p = make_problem(**c["kw"])
         res = run_ref_attention(ref, p, c["dtype"])
         for k, v in res.items():
             out[f"{name}.{k}"] = v
     for name, c in KNN_CASES.items():
+        if name not in GOLDEN:
+            continue
         src, qry, so, qo = knn_inputs(c["seed"])
         idx, d2 = run_ref_knn(ref, c["K"], src, qry, so, qo)
         out[f"{name}.idx"], out[f"{name}.d2"] = idx, d2

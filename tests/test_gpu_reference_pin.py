@@ -51,7 +51,7 @@ def test_reference_knn_bit_exact(ref, name):
     c = G.KNN_CASES[name]
     src, qry, so, qo = G.knn_inputs(c["seed"])
     ridx, rd2 = G.run_ref_knn(ref, c["K"], src, qry, so, qo)
-    oidx, od2 = O.knn(c["K"], src, qry, so, qo, fma_mode=1)
+    oidx, od2 = O.knn(c["K"], src, qry, so, qo, fma_mode=2)
     assert np.array_equal(rd2.view(np.uint32), od2.view(np.uint32)), "fp32 distance bits differ"
     assert np.array_equal(ridx, oidx)
     d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()

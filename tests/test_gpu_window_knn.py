@@ -75,7 +75,7 @@ def test_knn_bit_exact_vs_heap_oracle(K):
     so = np.cumsum([len(s) for s in srcs])
     qo = np.cumsum([len(q) for q in qrys])
     idx, d2 = _knn_gpu(K, src, qry, so, qo)
-    ridx, rd2 = O.knn(K, src, qry, so, qo, fma_mode=1)
+    ridx, rd2 = O.knn(K, src, qry, so, qo, fma_mode=2)
     assert np.array_equal(d2.view(np.uint32), rd2.view(np.uint32))
     assert np.array_equal(idx, ridx)
 
@@ -88,7 +88,7 @@ def test_knn_ties_follow_the_reference_heap():
     qry = g[::3] + 0.5
     for K in (3, 16):
         idx, d2 = _knn_gpu(K, src, qry, [len(src)], [len(qry)])
-        ridx, rd2 = O.knn(K, src, qry, [len(src)], [len(qry)], fma_mode=1)
+        ridx, rd2 = O.knn(K, src, qry, [len(src)], [len(qry)], fma_mode=2)
         assert np.array_equal(idx, ridx) and np.array_equal(d2, rd2)
 
 
