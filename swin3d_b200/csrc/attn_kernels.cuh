@@ -27,4 +27,8 @@ int attn_scalar_backward(const AttnArgs &a, cudaStream_t st);
 int crse_indices_dump(const float *n_coords, const CrseMeta &meta, int first_pos, int n,
                       int32_t *out, cudaStream_t st);
 
+// Tensor-core path (attn_tc_fwd.cu): fp16 storage, head_dim 8, even head count.
+bool attn_tc_supported(const AttnArgs &a);
+int attn_tc_forward(const AttnArgs &a, cudaStream_t st);
+
 }  // namespace s3d

@@ -1,0 +1,93 @@
+// Building blocks of the factorised, tensor-core cRSE window-attention kernels (fp16 storage,
+// head_dim 8, two heads per thread block packed as half2).
+//
+// Factorisation.  With P_q[r] = q . Tq[r] and P_k[r] = k . Tk[r] for every table row r (two small
+// GEMMs per window and head), the score of a pair is
+//     s_qk = q.k + sum_n P_q[row_n(q,k)] + sum_n P_k[row_n(q,k)]
+// i.e. 2*D scalar look-ups instead of 2*D*hd multiply-adds, and the value term becomes
+//     sum_k p_qk * sum_n Tv[row_n(q,k)] = hist_q . Tv,   hist_q[r] = sum_k p_qk [row_n(q,k) == r]
+// a per-query histogram followed by one more small GEMM.  The GEMMs run on the tensor cores
+// (mma.sync m16n8k8 / m16n8k16, fp16 in, fp32 accumulate); the look-ups and histogram updates
+// are shared-memory traffic arranged to be bank-conflict free:
+//   * per-query arrays (P_q, hist) are laid out [row][32 queries] with the query of lane l stored
+//     in column pos(l) = (l%8)*4 + l/8, one 4-byte half2 (head 0, head 1) per entry.  A warp
+//     whose lanes are queries therefore always hits 32 different banks whatever rows the lanes
+//     select, and a 16-byte load at column 4g returns queries {g, g+8, g+16, g+24}: exactly the
+//     rows of the two m16 tiles an mma lane (g, t) needs.
+//   * the per-key array P_k is laid out [key][row] with a row stride == 4 (mod 32) words; lanes
+//     (queries) read the same key at nearby rows.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace s3d {
+namespace tc {
+
+constexpr int QT = 32;        // queries per tile (= lanes)
+constexpr int KT = 16;        // keys per tile
+constexpr int NWARP = 8;
+constexpr int NTHREADS = NWARP * 32;
+constexpr int IDX_BITS = 6;   // cRSE indices are packed 5 per 32-bit word, 6 bits each
+
+__device__ __forceinline__ int qpos(int q) { return ((q & 7) << 2) | (q >> 3); }
+
+__device__ __forceinline__ void mma_k8(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0)
+{
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
+}
+
+__device__ __forceinline__ void mma_k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                        uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_lo(uint32_t x, uint32_t y) { return __byte_perm(x, y, 0x5410); }
+__device__ __forceinline__ uint32_t pack_hi(uint32_t x, uint32_t y) { return __byte_perm(x, y, 0x7632); }
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+
+// Orderable atomic max on a float held in shared memory (initialised to -inf).
+__device__ __forceinline__ void atomic_max_float(float *addr, float v)
+{
+    if (v >= 0.f)
+        atomicMax(reinterpret_cast<int *>(addr), __float_as_int(v));
+    else
+        atomicMin(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
+}
+
+// Shared-memory carve-up (byte offsets) for a table of R rows.
+struct SmemLayout {
+    int R16;      // rows rounded up to a multiple of 16
+    int Rp;       // row stride (words) of the per-key array, == 4 (mod 32)
+    int off_pq, off_hist, off_pk, off_s, off_idx, off_kv, off_kc, off_misc, total;
+};
+
+__host__ __device__ inline SmemLayout make_layout(int R, int n_rowq_arrays)
+{
+    SmemLayout L;
+    L.R16 = (R + 15) / 16 * 16;
+    L.Rp = (L.R16 + 31) / 32 * 32 + 4;
+    int off = 0;
+    L.off_pq = off;   off += n_rowq_arrays * L.R16 * QT * 4;   // P_q (and dB in the backward)
+    L.off_hist = off; off += n_rowq_arrays * L.R16 * QT * 4;   // histograms
+    // the per-key array doubles as the cross-warp reduction buffer of the epilogue (18 KB)
+    L.off_pk = off;   off += (KT * L.Rp * 4 > 18432) ? KT * L.Rp * 4 : 18432;
+    L.off_s = off;    off += KT * QT * 8;                      // float2 scores / half2 probabilities
+    L.off_idx = off;  off += KT * 2 * QT * 4;                  // packed cRSE indices
+    L.off_kv = off;   off += 2 * KT * 16 * 2;                  // key and value rows of the tile
+    L.off_kc = off;   off += KT * 12 * 4;                      // key coordinates, padded to 12
+    L.off_misc = off; off += 1024;
+    L.total = off;
+    return L;
+}
+
+}  // namespace tc
+}  // namespace s3d

@@ -1,0 +1,477 @@
+// Fused forward of the cRSE window attention, tensor-core path (fp16 storage, head_dim 8).
+//
+// grid = (x, H/2): a block serves one pair of heads for the windows x, x+gridDim.x, ... and keeps
+// that head pair's table slices as mma fragments in registers for its whole life.  Work item =
+// (window, tile of 32 queries); keys are streamed in tiles of 16 with an online softmax whose
+// rescale happens once per key tile.  Per key tile:
+//   GEMM    P_k = K.Tk^T (this tile's keys), S0 = K.Q^T                          [tensor cores]
+//   phase 1 lane = query, each warp two keys: cRSE indices, 2*D look-ups, score, running max
+//   phase 1.5 probabilities p = exp(s - m), row sums
+//   phase 2 one signal dimension per warp: hist[row][q] += p      (no atomics: rows of different
+//           dimensions are disjoint and a warp owns its dimension)      | warp 7: O += P.V [tc]
+// and per item:  P_q = Q.Tq^T before, O += hist.Tv after                        [tensor cores]
+// See attn_tc.cuh for the factorisation and the shared-memory layouts.
+#include "attn_kernels.cuh"
+#include "attn_tc.cuh"
+
+namespace s3d {
+namespace tc {
+
+template <int D, int MTW>
+__global__ void __launch_bounds__(NTHREADS, 2)
+attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
+                   const __half *__restrict__ v, const __half *__restrict__ tq,
+                   const __half *__restrict__ tk, const __half *__restrict__ tv,
+                   const CrseMeta meta, const int32_t *__restrict__ w_sizes,
+                   const int32_t *__restrict__ w2n, const int32_t *__restrict__ n2n,
+                   const float *__restrict__ n_coords, int64_t W, int H,
+                   __half *__restrict__ out, float *__restrict__ lse)
+{
+    extern __shared__ __align__(16) unsigned char smem[];
+    const SmemLayout L = make_layout(meta.R, 1);
+    uint32_t *s_pq = reinterpret_cast<uint32_t *>(smem + L.off_pq);      // [R16][32] half2
+    uint32_t *s_hist = reinterpret_cast<uint32_t *>(smem + L.off_hist);  // [R16][32] half2
+    uint32_t *s_pk = reinterpret_cast<uint32_t *>(smem + L.off_pk);      // [KT][Rp] half2
+    float2 *s_s = reinterpret_cast<float2 *>(smem + L.off_s);            // [KT][32] (h0,h1)
+    uint32_t *s_idx = reinterpret_cast<uint32_t *>(smem + L.off_idx);    // [KT][2][32]
+    __half *s_k = reinterpret_cast<__half *>(smem + L.off_kv);           // [KT][16]
+    __half *s_v = s_k + KT * 16;                                         // [KT][16]
+    float *s_kc = reinterpret_cast<float *>(smem + L.off_kc);            // [KT][12]
+    float *s_mtile = reinterpret_cast<float *>(smem + L.off_misc);       // [32][2]
+    float *s_alpha = s_mtile + 64;                                       // [32][2]
+    int *s_qrow = reinterpret_cast<int *>(s_alpha + 64);                 // [32]
+    __half *s_q = reinterpret_cast<__half *>(smem + L.off_s);            // [32][16], aliases s_s
+    float *s_red = reinterpret_cast<float *>(smem + L.off_pk);           // [8][32][16], aliases s_pk
+    float *s_lsum = s_red + NWARP * QT * 16;                             // [8][32][2]
+
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int hp = blockIdx.y;
+    const int HC = H * 8, co = hp * 16;
+    const int R = meta.R, n_mt = L.R16 / 16, Rp = L.Rp;
+    const int mypos = qpos(lane);
+    constexpr float LOG2E = 1.4426950408889634f;
+
+    // ---- this head pair's tables as mma fragments, resident in registers -----------------------
+    uint32_t tqA[MTW][2][2], tkA[MTW][2][2], tvB[MTW][2][2];
+#pragma unroll
+    for (int i = 0; i < MTW; ++i) {
+        const int mt = wid + NWARP * i;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int hh = 2 * hp + h;
+            const int r0 = mt * 16 + g, r1 = r0 + 8;
+            tqA[i][h][0] = r0 < R ? *reinterpret_cast<const uint32_t *>(tq + ((int64_t)r0 * H + hh) * 8 + 2 * t) : 0u;
+            tqA[i][h][1] = r1 < R ? *reinterpret_cast<const uint32_t *>(tq + ((int64_t)r1 * H + hh) * 8 + 2 * t) : 0u;
+            tkA[i][h][0] = r0 < R ? *reinterpret_cast<const uint32_t *>(tk + ((int64_t)r0 * H + hh) * 8 + 2 * t) : 0u;
+            tkA[i][h][1] = r1 < R ? *reinterpret_cast<const uint32_t *>(tk + ((int64_t)r1 * H + hh) * 8 + 2 * t) : 0u;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int ra = mt * 16 + 2 * t + 8 * half, rb = ra + 1;
+                const __half lo = ra < R ? tv[((int64_t)ra * H + hh) * 8 + g] : __float2half(0.f);
+                const __half hi = rb < R ? tv[((int64_t)rb * H + hh) * 8 + g] : __float2half(0.f);
+                tvB[i][h][half] = h2_as_u32(__halves2half2(lo, hi));
+            }
+        }
+    }
+
+    for (int64_t w = blockIdx.x; w < W; w += gridDim.x) {
+        const int n = __ldg(w_sizes + w);
+        const int base = __ldg(w2n + w);
+        for (int q0 = 0; q0 < n; q0 += QT) {
+            const int nq = min(QT, n - q0);
+            // ---- item set-up -------------------------------------------------------------------
+            __syncthreads();  // previous item's epilogue has finished with s_red / s_qrow
+            float cq[D];
+#pragma unroll
+            for (int d = 0; d < D; ++d)
+                cq[d] = lane < nq ? __ldg(n_coords + (int64_t)(base + q0 + lane) * D + d) : 0.f;
+            if (tid < 64) {
+                const int qi = tid >> 1, hf = tid & 1;
+                uint4 val = make_uint4(0, 0, 0, 0);
+                if (qi < nq) {
+                    const int row = __ldg(n2n + base + q0 + qi);
+                    if (hf == 0) s_qrow[qi] = row;
+                    val = __ldg(reinterpret_cast<const uint4 *>(q + (int64_t)row * HC + co + hf * 8));
+                }
+                *reinterpret_cast<uint4 *>(s_q + qi * 16 + hf * 8) = val;
+            }
+            for (int i = tid; i < L.R16 * QT / 4; i += NTHREADS)
+                reinterpret_cast<uint4 *>(s_hist)[i] = make_uint4(0, 0, 0, 0);
+            __syncthreads();
+            uint32_t qB[4][2];  // B fragments of Q^T: n-tile j <-> queries 8j..8j+7
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    qB[j][h] = *reinterpret_cast<const uint32_t *>(s_q + (8 * j + g) * 16 + h * 8 + 2 * t);
+            // P_q^T[row][q] = Tq . Q^T
+#pragma unroll
+            for (int i = 0; i < MTW; ++i) {
+                const int mt = wid + NWARP * i;
+                if (mt < n_mt) {
+                    float c[2][4][4];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            c[h][j][0] = c[h][j][1] = c[h][j][2] = c[h][j][3] = 0.f;
+                            mma_k8(c[h][j], tqA[i][h][0], tqA[i][h][1], qB[j][h]);
+                        }
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr)      // row g / row g+8
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {   // query 8j+2t / 8j+2t+1
+                            uint4 o;
+                            o.x = h2_as_u32(__floats2half2_rn(c[0][0][2 * rr + e], c[1][0][2 * rr + e]));
+                            o.y = h2_as_u32(__floats2half2_rn(c[0][1][2 * rr + e], c[1][1][2 * rr + e]));
+                            o.z = h2_as_u32(__floats2half2_rn(c[0][2][2 * rr + e], c[1][2][2 * rr + e]));
+                            o.w = h2_as_u32(__floats2half2_rn(c[0][3][2 * rr + e], c[1][3][2 * rr + e]));
+                            *reinterpret_cast<uint4 *>(s_pq + (mt * 16 + g + 8 * rr) * QT + 8 * t + 4 * e) = o;
+                        }
+                }
+            }
+            float m_run[2] = {-INFINITY, -INFINITY};
+            float l_part[2] = {0.f, 0.f};
+            float oacc[2][2][4];  // [head][m-tile][c-frag]; meaningful in warp 7 only
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) oacc[h][i][0] = oacc[h][i][1] = oacc[h][i][2] = oacc[h][i][3] = 0.f;
+
+            for (int k0 = 0; k0 < n; k0 += KT) {
+                const int nk = min(KT, n - k0);
+                __syncthreads();  // P_q stored / previous key tile fully consumed
+                // ---- stage the key tile -----------------------------------------------------------
+                if (tid < 64) {
+                    const int ki = tid >> 2, which = (tid >> 1) & 1, hf = tid & 1;
+                    uint4 val = make_uint4(0, 0, 0, 0);
+                    if (ki < nk) {
+                        const int row = __ldg(n2n + base + k0 + ki);
+                        const __half *src = which ? v : k;
+                        val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)row * HC + co + hf * 8));
+                    }
+                    *reinterpret_cast<uint4 *>((which ? s_v : s_k) + ki * 16 + hf * 8) = val;
+                } else if (tid < 64 + KT * D) {
+                    const int e = tid - 64, ki = e / D, d = e - ki * D;
+                    s_kc[ki * 12 + d] = ki < nk ? __ldg(n_coords + (int64_t)(base + k0 + ki) * D + d) : 0.f;
+                } else if (tid >= 224) {
+                    s_mtile[(tid - 224) * 2] = -INFINITY;
+                    s_mtile[(tid - 224) * 2 + 1] = -INFINITY;
+                }
+                __syncthreads();
+                // ---- P_k^T[row][key] = Tk . K^T  ->  s_pk[key][row] ;  S0^T[key][q] = K . Q^T --------
+                {
+                    uint32_t kB[2][2];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+                            kB[j][h] = *reinterpret_cast<const uint32_t *>(s_k + (8 * j + g) * 16 + h * 8 + 2 * t);
+#pragma unroll
+                    for (int i = 0; i < MTW; ++i) {
+                        const int mt = wid + NWARP * i;
+                        if (mt < n_mt) {
+                            float c[2][2][4];
+#pragma unroll
+                            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                                for (int j = 0; j < 2; ++j) {
+                                    c[h][j][0] = c[h][j][1] = c[h][j][2] = c[h][j][3] = 0.f;
+                                    mma_k8(c[h][j], tkA[i][h][0], tkA[i][h][1], kB[j][h]);
+                                }
+#pragma unroll
+                            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                                for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+                                    for (int e = 0; e < 2; ++e)
+                                        s_pk[(8 * j + 2 * t + e) * Rp + mt * 16 + g + 8 * rr] =
+                                            h2_as_u32(__floats2half2_rn(c[0][j][2 * rr + e], c[1][j][2 * rr + e]));
+                        }
+                    }
+                    if (wid == NWARP - 1) {
+                        uint32_t ka[2][2];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            ka[h][0] = *reinterpret_cast<const uint32_t *>(s_k + g * 16 + h * 8 + 2 * t);
+                            ka[h][1] = *reinterpret_cast<const uint32_t *>(s_k + (g + 8) * 16 + h * 8 + 2 * t);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+                            mma_k8(c0, ka[0][0], ka[0][1], qB[j][0]);
+                            mma_k8(c1, ka[1][0], ka[1][1], qB[j][1]);
+                            *reinterpret_cast<float4 *>(s_s + g * QT + 8 * j + 2 * t) = make_float4(c0[0], c1[0], c0[1], c1[1]);
+                            *reinterpret_cast<float4 *>(s_s + (g + 8) * QT + 8 * j + 2 * t) = make_float4(c0[2], c1[2], c0[3], c1[3]);
+                        }
+                    }
+                }
+                __syncthreads();
+                // ---- phase 1: scores of this warp's two keys --------------------------------------
+                float mloc[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int kk2 = 0; kk2 < 2; ++kk2) {
+                    const int kk = 2 * wid + kk2;
+                    if (kk < nk) {
+                        __half2 bq = __float2half2_rn(0.f), bk = __float2half2_rn(0.f);
+                        uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+                        for (int d = 0; d < D; ++d) {
+                            const int idx = crse_index(cq[d], s_kc[kk * 12 + d], meta.L[d], d == D - 1);
+                            const int row = meta.rowbase[d] + idx;
+                            bq = __hadd2(bq, u32_as_h2(s_pq[row * QT + mypos]));
+                            bk = __hadd2(bk, u32_as_h2(s_pk[kk * Rp + row]));
+                            if (d < 5) w0 |= (uint32_t)idx << (IDX_BITS * d);
+                            else w1 |= (uint32_t)idx << (IDX_BITS * (d - 5));
+                        }
+                        s_idx[(kk * 2 + 0) * QT + lane] = w0;
+                        if (D > 5) s_idx[(kk * 2 + 1) * QT + lane] = w1;
+                        const float2 b = __half22float2(__hadd2(bq, bk));
+                        float2 s = s_s[kk * QT + lane];
+                        s.x += b.x;
+                        s.y += b.y;
+                        s_s[kk * QT + lane] = s;
+                        mloc[0] = fmaxf(mloc[0], s.x);
+                        mloc[1] = fmaxf(mloc[1], s.y);
+                    }
+                }
+                if (2 * wid < nk) {
+                    atomic_max_float(s_mtile + lane * 2, mloc[0]);
+                    atomic_max_float(s_mtile + lane * 2 + 1, mloc[1]);
+                }
+                __syncthreads();
+                // ---- phase 1.5: probabilities with the updated running maximum -----------------------
+                float alpha[2];
+                bool unchanged = true;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float mnew = fmaxf(m_run[h], s_mtile[lane * 2 + h]);
+                    alpha[h] = exp2f((m_run[h] - mnew) * LOG2E);   // 0 on the first tile (m_run = -inf)
+                    unchanged = unchanged && (mnew == m_run[h]);
+                    m_run[h] = mnew;
+                    l_part[h] *= alpha[h];
+                }
+                if (wid == 0) {
+                    s_alpha[lane * 2] = alpha[0];
+                    s_alpha[lane * 2 + 1] = alpha[1];
+                }
+#pragma unroll
+                for (int kk2 = 0; kk2 < 2; ++kk2) {
+                    const int kk = 2 * wid + kk2;
+                    uint32_t ph = 0;
+                    if (kk < nk) {
+                        const float2 s = s_s[kk * QT + lane];
+                        const float p0 = exp2f((s.x - m_run[0]) * LOG2E);
+                        const float p1 = exp2f((s.y - m_run[1]) * LOG2E);
+                        l_part[0] += p0;
+                        l_part[1] += p1;
+                        ph = h2_as_u32(__floats2half2_rn(p0, p1));
+                    }
+                    reinterpret_cast<uint32_t *>(s_s + kk * QT + lane)[0] = ph;  // p replaces s
+                }
+                const int any_changed = __syncthreads_or((k0 > 0 && !unchanged) ? 1 : 0);
+                // ---- rescale what was accumulated under the old maximum ------------------------------
+                if (any_changed) {
+                    const int c4 = tid & 7;  // 16-byte column: queries {c4, c4+8, c4+16, c4+24}
+                    __half2 a[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        a[j] = __floats2half2_rn(s_alpha[(c4 + 8 * j) * 2], s_alpha[(c4 + 8 * j) * 2 + 1]);
+                    for (int r = tid >> 3; r < L.R16; r += NTHREADS / 8) {
+                        uint4 x = *reinterpret_cast<uint4 *>(s_hist + r * QT + 4 * c4);
+                        x.x = h2_as_u32(__hmul2(u32_as_h2(x.x), a[0]));
+                        x.y = h2_as_u32(__hmul2(u32_as_h2(x.y), a[1]));
+                        x.z = h2_as_u32(__hmul2(u32_as_h2(x.z), a[2]));
+                        x.w = h2_as_u32(__hmul2(u32_as_h2(x.w), a[3]));
+                        *reinterpret_cast<uint4 *>(s_hist + r * QT + 4 * c4) = x;
+                    }
+                    if (wid == NWARP - 1) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                const float a0 = s_alpha[(16 * i + g) * 2 + h], a1 = s_alpha[(16 * i + g + 8) * 2 + h];
+                                oacc[h][i][0] *= a0; oacc[h][i][1] *= a0;
+                                oacc[h][i][2] *= a1; oacc[h][i][3] *= a1;
+                            }
+                    }
+                    __syncthreads();
+                }
+                // ---- phase 2: histogram update, one signal dimension per warp -------------------------
+#pragma unroll
+                for (int rep = 0; rep < 2; ++rep) {
+                    const int d = wid + NWARP * rep;
+                    if (d < D) {
+                        const int wsel = d / 5, sh = IDX_BITS * (d % 5);
+                        const int rb = meta.rowbase[d];
+                        for (int kk = 0; kk < nk; ++kk) {
+                            const uint32_t ph = reinterpret_cast<const uint32_t *>(s_s + kk * QT + lane)[0];
+                            const int idx = (s_idx[(kk * 2 + wsel) * QT + lane] >> sh) & ((1 << IDX_BITS) - 1);
+                            uint32_t *cell = s_hist + (rb + idx) * QT + mypos;
+                            *cell = h2_as_u32(__hadd2(u32_as_h2(*cell), u32_as_h2(ph)));
+                        }
+                    }
+                }
+                // ---- O += P.V on the tensor cores (warp 7) --------------------------------------------
+                if (wid == NWARP - 1) {
+                    uint32_t pa[2][2][4];  // [head][m-tile][a0..a3]
+#pragma unroll
+                    for (int i = 0; i < 2; ++i)
+#pragma unroll
+                        for (int kh = 0; kh < 2; ++kh)      // keys 2t.. / keys 2t+8..
+#pragma unroll
+                            for (int rr = 0; rr < 2; ++rr) { // query 16i+g / 16i+g+8
+                                const int qq = 16 * i + g + 8 * rr, ka = 2 * t + 8 * kh;
+                                const uint32_t x = reinterpret_cast<const uint32_t *>(s_s + ka * QT + qq)[0];
+                                const uint32_t y = reinterpret_cast<const uint32_t *>(s_s + (ka + 1) * QT + qq)[0];
+                                pa[0][i][2 * kh + rr] = pack_lo(x, y);
+                                pa[1][i][2 * kh + rr] = pack_hi(x, y);
+                            }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t vb[2];
+#pragma unroll
+                        for (int kh = 0; kh < 2; ++kh) {
+                            const int ka = 2 * t + 8 * kh;
+                            vb[kh] = h2_as_u32(__halves2half2(s_v[ka * 16 + h * 8 + g], s_v[(ka + 1) * 16 + h * 8 + g]));
+                        }
+#pragma unroll
+                        for (int i = 0; i < 2; ++i)
+                            mma_k16(oacc[h][i], pa[h][i][0], pa[h][i][1], pa[h][i][2], pa[h][i][3], vb[0], vb[1]);
+                    }
+                }
+            }  // key tiles
+            __syncthreads();
+            // ---- O += hist . Tv, K split over the warps, then reduce, normalise and store --------------
+            float part[2][2][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) part[h][i][e] = (wid == NWARP - 1) ? oacc[h][i][e] : 0.f;
+#pragma unroll
+            for (int i = 0; i < MTW; ++i) {
+                const int ks = wid + NWARP * i;
+                if (ks < n_mt) {
+                    // rows 2t, 2t+1, 2t+8, 2t+9 of this k-step; columns = queries {g, g+8, g+16, g+24}
+                    uint32_t x0[4], x1[4], x2[4], x3[4];
+                    {
+                        const uint4 y0 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t) * QT + 4 * g);
+                        const uint4 y1 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t + 1) * QT + 4 * g);
+                        const uint4 y2 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t + 8) * QT + 4 * g);
+                        const uint4 y3 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t + 9) * QT + 4 * g);
+                        x0[0] = y0.x; x0[1] = y0.y; x0[2] = y0.z; x0[3] = y0.w;
+                        x1[0] = y1.x; x1[1] = y1.y; x1[2] = y1.z; x1[3] = y1.w;
+                        x2[0] = y2.x; x2[1] = y2.y; x2[2] = y2.z; x2[3] = y2.w;
+                        x3[0] = y3.x; x3[1] = y3.y; x3[2] = y3.z; x3[3] = y3.w;
+                    }
+#pragma unroll
+                    for (int mtile = 0; mtile < 2; ++mtile) {
+                        const int ja = 2 * mtile, jb = 2 * mtile + 1;   // queries g+16m and g+16m+8
+                        mma_k16(part[0][mtile], pack_lo(x0[ja], x1[ja]), pack_lo(x0[jb], x1[jb]),
+                                pack_lo(x2[ja], x3[ja]), pack_lo(x2[jb], x3[jb]), tvB[i][0][0], tvB[i][0][1]);
+                        mma_k16(part[1][mtile], pack_hi(x0[ja], x1[ja]), pack_hi(x0[jb], x1[jb]),
+                                pack_hi(x2[ja], x3[ja]), pack_hi(x2[jb], x3[jb]), tvB[i][1][0], tvB[i][1][1]);
+                    }
+                }
+            }
+            // s_red aliases s_pk, which nobody reads after the last phase 1 (a barrier ago)
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const int qq = 16 * i + g + 8 * rr;
+                        *reinterpret_cast<float2 *>(s_red + (wid * QT + qq) * 16 + h * 8 + 2 * t) =
+                            make_float2(part[h][i][2 * rr], part[h][i][2 * rr + 1]);
+                    }
+            s_lsum[(wid * QT + lane) * 2] = l_part[0];
+            s_lsum[(wid * QT + lane) * 2 + 1] = l_part[1];
+            if (wid == 0) {   // final maxima for the log-sum-exp
+                s_mtile[lane * 2] = m_run[0];
+                s_mtile[lane * 2 + 1] = m_run[1];
+            }
+            __syncthreads();
+            {
+                const int qq = tid >> 3, ch = (tid & 7) * 2, h = ch >> 3;
+                if (qq < nq) {
+                    float a = 0.f, b = 0.f, ls = 0.f;
+#pragma unroll
+                    for (int ww = 0; ww < NWARP; ++ww) {
+                        const float2 pr = *reinterpret_cast<const float2 *>(s_red + (ww * QT + qq) * 16 + ch);
+                        a += pr.x;
+                        b += pr.y;
+                        ls += s_lsum[(ww * QT + qq) * 2 + h];
+                    }
+                    const float inv = 1.f / ls;
+                    const int64_t row = s_qrow[qq];
+                    *reinterpret_cast<__half2 *>(out + row * HC + co + ch) = __floats2half2_rn(a * inv, b * inv);
+                    if ((ch & 7) == 0) lse[row * H + 2 * hp + h] = s_mtile[qq * 2 + h] + __logf(ls);
+                }
+            }
+        }  // query tiles
+    }      // windows
+}
+
+template <int D, int MTW>
+static int launch(const AttnArgs &a, cudaStream_t st)
+{
+    const SmemLayout L = make_layout(a.meta.R, 1);
+    auto kern = attn_fwd_tc_kernel<D, MTW>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total) != cudaSuccess)
+        return S3D_ERR_LAUNCH;
+    const int hp = a.H / 2;
+    int dev = 0, sms = 148, per_sm = 1;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NTHREADS, L.total) != cudaSuccess || per_sm < 1)
+        return S3D_ERR_LAUNCH;
+    // exactly one wave of resident blocks, shared evenly between the head pairs
+    int gx = sms * per_sm / hp;
+    if (gx > a.W) gx = (int)a.W;
+    if (gx < 1) gx = 1;
+    dim3 grid((unsigned)gx, (unsigned)hp);
+    kern<<<grid, NTHREADS, L.total, st>>>(
+        (const __half *)a.q, (const __half *)a.k, (const __half *)a.v, (const __half *)a.tq,
+        (const __half *)a.tk, (const __half *)a.tv, a.meta, a.w_sizes, a.w2n, a.n2n, a.n_coords, a.W,
+        a.H, (__half *)a.out, a.lse);
+    return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
+}
+
+}  // namespace tc
+
+bool attn_tc_supported(const AttnArgs &a)
+{
+    if (a.dtype != S3D_F16 || a.hd != 8 || (a.H & 1)) return false;
+    if (a.meta.R > 16 * tc::NWARP * 3) return false;
+    for (int d = 0; d < a.meta.D; ++d)
+        if (a.meta.L[d] >= (1 << tc::IDX_BITS)) return false;   // idx may reach L
+    if (tc::make_layout(a.meta.R, 1).total > 227 * 1024) return false;
+    return true;
+}
+
+int attn_tc_forward(const AttnArgs &a, cudaStream_t st)
+{
+    if (a.W == 0) return S3D_OK;
+    const int n_mt = (a.meta.R + 15) / 16;
+    const int mtw = (n_mt + tc::NWARP - 1) / tc::NWARP;
+#define S3D_TC_FWD(DD)                                            \
+    switch (mtw) {                                                \
+        case 1: return tc::launch<DD, 1>(a, st);                  \
+        case 2: return tc::launch<DD, 2>(a, st);                  \
+        case 3: return tc::launch<DD, 3>(a, st);                  \
+        default: return S3D_ERR_UNSUPPORTED;                      \
+    }
+    switch (a.meta.D) {
+        case 3: S3D_TC_FWD(3)
+        case 6: S3D_TC_FWD(6)
+        case 9: S3D_TC_FWD(9)
+        default: return S3D_ERR_UNSUPPORTED;
+    }
+#undef S3D_TC_FWD
+}
+
+}  // namespace s3d

@@ -4,9 +4,19 @@
 #include "knn_kernels.cuh"
 #include "window_kernels.cuh"
 
+#include <cstdlib>
+
 using namespace s3d;
 
 namespace {
+
+// S3D_FORCE_SCALAR=1 in the environment routes every attention call to the generic kernels
+// (used by the tests to cross-check the two paths on the GPU).
+bool force_scalar()
+{
+    const char *e = std::getenv("S3D_FORCE_SCALAR");
+    return e && e[0] == '1';
+}
 
 int make_meta(const int32_t *table_sizes_host, int D, int H, int hd, CrseMeta &m)
 {
@@ -61,6 +71,7 @@ int s3d_attn_fwd(const void *q, const void *k, const void *v, const void *tq, co
     a.w_sizes = w_sizes; a.w2n = w2n; a.n2n = n2n; a.n_coords = n_coords;
     a.N = N; a.W = W; a.H = H; a.hd = hd; a.dtype = dtype;
     a.out = out; a.lse = lse;
+    if (!force_scalar() && attn_tc_supported(a)) return attn_tc_forward(a, static_cast<cudaStream_t>(stream));
     return attn_scalar_forward(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -30,7 +30,7 @@ ATTN_CASES = {
     "f32_hd16_xyz": dict(kw=dict(seed=101, n_voxels=350, grid=18, H=2, hd=16, crse="XYZ"), dtype="float32"),
     "f32_hd16_rgb_shift": dict(kw=dict(seed=102, n_voxels=350, grid=18, H=2, hd=16, crse="XYZ_RGB", shift=2), dtype="float32"),
     "f32_hd32_norm": dict(kw=dict(seed=103, n_voxels=300, grid=18, H=2, hd=32, crse="XYZ_RGB_NORM"), dtype="float32"),
-    "f64_hd16_rgb": dict(kw=dict(seed=104, n_voxels=200, grid=16, H=2, hd=16, crse="XYZ_RGB"), dtype="float64"),
+    "f64_hd16_rgb": dict(kw=dict(seed=104, n_voxels=200, grid=18, H=2, hd=16, crse="XYZ_RGB"), dtype="float64"),
     "f16_hd32_rgb": dict(kw=dict(seed=105, n_voxels=300, grid=18, H=2, hd=32, crse="XYZ_RGB", round_fp16=True), dtype="float16"),
 }
 # the cases whose reference outputs are committed as a fixture (the others only run on the GPU)

@@ -169,3 +169,60 @@ def test_run_to_run_determinism_of_forward():
     assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
     for i in range(3):   # dq, dk, dv are owned by one thread each: bit-identical
         assert np.array_equal(a[2][i], b[2][i])
+
+
+def _dense_scene():
+    g = np.stack(np.meshgrid(*[np.arange(7)] * 3, indexing="ij"), -1).reshape(-1, 3)
+    lonely = np.array([[40, 40, 40], [60, 3, 9], [90, 90, 90]])
+    pts = np.concatenate([g, lonely])
+    n = len(pts)
+    rng = np.random.default_rng(5)
+    return S.Scene(np.concatenate([np.zeros((n, 1)), pts], 1).astype(np.int32),
+                   rng.random((n, 3), dtype=np.float32) * 0.999, rng.random((n, 3), dtype=np.float32),
+                   np.tile(np.array([[0, 0, 1]], dtype=np.float32), (n, 1)))
+
+
+@pytest.mark.parametrize("ws,crse,H", [(5, "XYZ_RGB_NORM", 10), (7, "XYZ_RGB_NORM", 2), (7, "XYZ", 4),
+                                       (5, "XYZ_RGB", 6)])
+def test_fp16_tensor_core_path_dense_and_tiny_windows(ws, crse, H):
+    """fp16, head_dim 8: windows of 1, 125 and 343 voxels go through several query and key tiles
+    of the tensor-core kernels."""
+    from tests.gpu_helpers import cuda_fwd_bwd
+    p = make_problem(seed=2, ws=ws, H=H, hd=8, crse=crse, scene=_dense_scene(), round_fp16=True)
+    o_ref, lse_ref, g_ref = oracle_fwd_bwd(p, np.float64)
+    out, lse, grads = cuda_fwd_bwd(p, torch.float16)
+    assert rel_err(out, o_ref) < FP16_TOL
+    assert np.abs(lse - lse_ref).max() < 2e-2
+    for name, a, b in zip("dq dk dv dtq dtk dtv".split(), grads, g_ref):
+        assert rel_err(a, b) < FP16_TOL, name
+
+
+def test_fp16_tensor_core_path_large_scores_stay_finite():
+    """Scores of magnitude ~30 exercise the running-maximum rescale across key tiles."""
+    from tests.gpu_helpers import cuda_fwd_bwd
+    p = make_problem(seed=51, n_voxels=1500, grid=24, H=2, hd=8, crse="XYZ_RGB", round_fp16=True,
+                     feat_scale=4.0)
+    o_ref, lse_ref, g_ref = oracle_fwd_bwd(p, np.float64)
+    out, lse, grads = cuda_fwd_bwd(p, torch.float16)
+    assert np.isfinite(out).all() and np.isfinite(lse).all()
+    assert rel_err(out, o_ref) < FP16_TOL
+    assert np.abs(lse - lse_ref).max() < 5e-2
+
+
+def test_room_scale_tensor_core_path_equals_generic_path():
+    """A 60k-voxel room, Swin3D-L stage-1 head layout: the tensor-core kernels against the
+    generic kernels of the same library (forced with S3D_FORCE_SCALAR=1), same inputs."""
+    import os
+    from tests.gpu_helpers import cuda_fwd_bwd
+    sc = S.make_room(7, target_voxels=60_000)
+    p = make_problem(seed=61, ws=5, shift=2, H=10, hd=8, crse="XYZ_RGB_NORM", scene=sc, round_fp16=True)
+    fast = cuda_fwd_bwd(p, torch.float16)
+    os.environ["S3D_FORCE_SCALAR"] = "1"
+    try:
+        slow = cuda_fwd_bwd(p, torch.float16)
+    finally:
+        os.environ.pop("S3D_FORCE_SCALAR")
+    assert rel_err(fast[0], slow[0]) < 5e-3
+    assert np.abs(fast[1] - slow[1]).max() < 1e-2
+    for a, b in zip(fast[2], slow[2]):
+        assert rel_err(a, b) < 5e-3
