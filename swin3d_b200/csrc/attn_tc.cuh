@@ -14,7 +14,7 @@
 //     whose lanes are queries therefore always hits 32 different banks whatever rows the lanes
 //     select, and a 16-byte load at column 4g returns queries {g, g+8, g+16, g+24}: exactly the
 //     rows of the two m16 tiles an mma lane (g, t) needs.
-//   * the per-key array P_k is laid out [key][row] with a row stride == 4 (mod 32) words; lanes
+//   * the per-key array P_k is laid out [key][row] with a row stride == 8 (mod 32) words; lanes
 //     (queries) read the same key at nearby rows.
 #pragma once
 #include <cuda_fp16.h>
@@ -48,6 +48,37 @@ __device__ __forceinline__ void mma_k16(float (&d)[4], uint32_t a0, uint32_t a1,
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Both heads in one instruction: K index = (head, channel) = the 16 contiguous halves of a table or
+// feature row, N index = (voxel, head) with a block-diagonal B operand.  fp16 accumulators come out
+// as half2 (head 0, head 1) per (row, voxel): exactly the shared-memory entry format, no repacking.
+__device__ __forceinline__ void mma_k16_h(uint32_t &d0, uint32_t &d1, uint32_t a0, uint32_t a1,
+                                          uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    const uint32_t z = 0u;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f16.f16.f16.f16 {%0,%1}, {%2,%3,%4,%5}, {%6,%7}, {%8,%8};\n"
+                 : "=r"(d0), "=r"(d1)
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
+}
+
+// Same shape, fp32 accumulators, C = 0.
+__device__ __forceinline__ void mma_k16_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    const float z = 0.f;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(z));
+}
+
+// cRSE index with one unsigned clamp: cvt.rzi.u32 maps negatives (and NaN) to 0, so
+// min(uint(rel), L) equals (int)fminf(fmaxf(0, rel), L) for every input.
+__device__ __forceinline__ int crse_index_fast(float cq, float ck, int L, bool last_dim)
+{
+    const float rel = __fadd_rn(__fsub_rn(cq, ck), (float)(L / 2));
+    const unsigned u = __float2uint_rz(rel);
+    return (int)min(u, (unsigned)(last_dim ? L - 1 : L));
+}
+
 __device__ __forceinline__ uint32_t pack_lo(uint32_t x, uint32_t y) { return __byte_perm(x, y, 0x5410); }
 __device__ __forceinline__ uint32_t pack_hi(uint32_t x, uint32_t y) { return __byte_perm(x, y, 0x7632); }
 
@@ -66,7 +97,7 @@ __device__ __forceinline__ void atomic_max_float(float *addr, float v)
 // Shared-memory carve-up (byte offsets) for a table of R rows.
 struct SmemLayout {
     int R16;      // rows rounded up to a multiple of 16
-    int Rp;       // row stride (words) of the per-key array, == 4 (mod 32)
+    int Rp;       // row stride (words) of the per-key array, == 8 (mod 32)
     int off_pq, off_hist, off_pk, off_s, off_idx, off_kv, off_kc, off_misc, total;
 };
 
@@ -74,7 +105,7 @@ __host__ __device__ inline SmemLayout make_layout(int R, int n_rowq_arrays)
 {
     SmemLayout L;
     L.R16 = (R + 15) / 16 * 16;
-    L.Rp = (L.R16 + 31) / 32 * 32 + 4;
+    L.Rp = (L.R16 + 31) / 32 * 32 + 8;
     int off = 0;
     L.off_pq = off;   off += n_rowq_arrays * L.R16 * QT * 4;   // P_q (and dB in the backward)
     L.off_hist = off; off += n_rowq_arrays * L.R16 * QT * 4;   // histograms

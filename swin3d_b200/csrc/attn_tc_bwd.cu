@@ -1,0 +1,593 @@
+// Fused backward of the cRSE window attention, tensor-core path (fp16 storage, head_dim 8).
+//
+// One templated kernel, launched twice per call:
+//   SIDE 0  lanes = queries (x = q, y = k):  dQ, dTq, dTv
+//   SIDE 1  lanes = keys    (x = k, y = q):  dK, dV, dTk
+// Both sweeps recompute, per pair, s = q.k + sum_n P_q[row_n] + sum_n P_k[row_n], p = exp(s - lse),
+// dP = dO.v + sum_n dB_q[row_n] (dB_q = dO_q . Tv^T) and ds = p (dP - delta_q), with the three
+// projections P_q, P_k, dB produced by tensor-core GEMMs per window.  The x side owns per-voxel
+// histograms  H0[x][row] += ds  (and, SIDE 0, H1[x][row] += p); they turn the table terms into GEMMs:
+//   dX     += H0 . T0                 (T0 = Tq on SIDE 0, Tk on SIDE 1)
+//   dT0    += H0^T . X0               (dTq += histQ^T.Q ; dTk += histK^T.K)
+//   dTv    += H1^T . dO               (SIDE 0)
+// Table gradients are accumulated in registers over every window a block processes and reach
+// global memory once per block (atomicAdd of fp32), instead of once per pair, head and channel.
+// grid = (x, H/2); one block per SM (16 warps); shared-memory layouts as in attn_tc.cuh.
+#include "attn_kernels.cuh"
+#include "attn_tc.cuh"
+
+namespace s3d {
+namespace tc {
+
+constexpr int BW_NWARP = 16;
+constexpr int BW_THREADS = BW_NWARP * 32;
+
+struct BwdSmem {
+    int R16, Rp;
+    int off_px, px_stride, off_hx, off_py, py_stride, off_s, off_dp, off_idx, off_yt, off_yc, off_misc, total;
+};
+
+__host__ __device__ inline BwdSmem make_bwd_layout(int R, int npx, int nh, int npy)
+{
+    BwdSmem L;
+    L.R16 = (R + 15) / 16 * 16;
+    L.Rp = (L.R16 + 31) / 32 * 32 + 8;
+    L.px_stride = L.R16 * QT * 4;
+    L.py_stride = KT * L.Rp * 4;
+    int off = 0;
+    const int px_bytes = npx * L.px_stride;
+    L.off_px = off; off += px_bytes > 36864 ? px_bytes : 36864;   // doubles as the 34 KB reduction buffer
+    L.off_hx = off; off += nh * L.px_stride;
+    L.off_py = off; off += npy * L.py_stride;
+    L.off_s = off;  off += KT * QT * 8;      // float2 scores, then (p, ds) half2 pairs
+    L.off_dp = off; off += KT * QT * 8;      // float2 dO.v
+    L.off_idx = off; off += KT * 2 * QT * 4;
+    L.off_yt = off; off += 2 * KT * 16 * 2;
+    L.off_yc = off; off += KT * 12 * 4;
+    L.off_misc = off; off += 1024;
+    L.total = off;
+    return L;
+}
+
+struct BwdParams {
+    const __half *x0, *x1, *y0, *y1;   // feature rows [N][H][8]: SIDE 0: q, dout, k, v ; SIDE 1: k, v, q, dout
+    const __half *o;                   // forward output (for delta)
+    const float *lse;
+    const __half *t_px0, *t_px1, *t_py0, *t_py1;   // tables of the x / y projections
+    __half *dx0, *dx1;                 // SIDE 0: dq, - ; SIDE 1: dk, dv
+    float *dt0, *dt1;                  // SIDE 0: dtq, dtv ; SIDE 1: dtk, -
+    const int32_t *w_sizes, *w2n, *n2n;
+    const float *n_coords;
+    int64_t W;
+    int H;
+};
+
+// A-operand fragments (m16 x k16, both heads on K) of a table slice for the row tiles this warp owns.
+template <int MTW>
+__device__ __forceinline__ void load_table_a(const __half *tab, int R, int H, int hp, int wid, int g, int t,
+                                             uint32_t (&a)[MTW][2][2])
+{
+#pragma unroll
+    for (int i = 0; i < MTW; ++i) {
+        const int mt = wid + BW_NWARP * i;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int hh = 2 * hp + h;
+            const int r0 = mt * 16 + g, r1 = r0 + 8;
+            a[i][h][0] = r0 < R ? *reinterpret_cast<const uint32_t *>(tab + ((int64_t)r0 * H + hh) * 8 + 2 * t) : 0u;
+            a[i][h][1] = r1 < R ? *reinterpret_cast<const uint32_t *>(tab + ((int64_t)r1 * H + hh) * 8 + 2 * t) : 0u;
+        }
+    }
+}
+
+// Projection GEMM  P^T[row][(voxel, head)] = T . F^T  for NT n-tiles of 4 voxels, written either in the
+// lane-major layout [row][32] (column = qpos(voxel)) or in the tile layout [voxel][Rp].
+template <int MTW, bool LANE_MAJOR>
+__device__ __forceinline__ void project(const uint32_t (&ta)[MTW][2][2], const __half *feat /*[nv][16]*/,
+                                        uint32_t *dst, int n_mt, int Rp, int wid, int g, int t)
+{
+    constexpr int NT = LANE_MAJOR ? 8 : 4;
+    uint32_t b[NT][2];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const uint32_t wv = *reinterpret_cast<const uint32_t *>(feat + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+        b[j][0] = (g & 1) ? 0u : wv;
+        b[j][1] = (g & 1) ? wv : 0u;
+    }
+#pragma unroll
+    for (int i = 0; i < MTW; ++i) {
+        const int mt = wid + BW_NWARP * i;
+        if (mt < n_mt) {
+            uint32_t d0[NT], d1[NT];
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+                mma_k16_h(d0[j], d1[j], ta[i][0][0], ta[i][0][1], ta[i][1][0], ta[i][1][1], b[j][0], b[j][1]);
+            if (LANE_MAJOR) {
+                uint32_t *r0 = dst + (mt * 16 + g) * QT + 4 * t;
+                *reinterpret_cast<uint4 *>(r0) = make_uint4(d0[0], d0[2], d0[4], d0[6]);
+                *reinterpret_cast<uint4 *>(r0 + 16) = make_uint4(d0[1], d0[3], d0[5], d0[7]);
+                *reinterpret_cast<uint4 *>(r0 + 8 * QT) = make_uint4(d1[0], d1[2], d1[4], d1[6]);
+                *reinterpret_cast<uint4 *>(r0 + 8 * QT + 16) = make_uint4(d1[1], d1[3], d1[5], d1[7]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    uint32_t *p = dst + (4 * j + t) * Rp + mt * 16 + g;
+                    p[0] = d0[j];
+                    p[8] = d1[j];
+                }
+            }
+        }
+    }
+}
+
+// acc[head][m-tile] += E^T-tile . Y : rows = the 32 x of the item, k = the 16 y of the tile, E the
+// p (WHICH = 1) or ds (WHICH = 0) half of the (p, ds) entries s_pd[y][x]; Y the staged y rows [16][16].
+template <int WHICH>
+__device__ __forceinline__ void dx_gemm(float (&acc)[2][2][4], const uint2 *s_pd, const __half *ysrc, int g, int t)
+{
+    uint32_t fa[2][2][4];   // [head][m-tile][a0..a3]
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh)
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int xx = 16 * i + g + 8 * rr, ya = 2 * t + 8 * kh;
+                const uint2 e0 = s_pd[ya * QT + xx], e1 = s_pd[(ya + 1) * QT + xx];
+                const uint32_t u = WHICH == 0 ? e0.y : e0.x, v2 = WHICH == 0 ? e1.y : e1.x;
+                fa[0][i][2 * kh + rr] = pack_lo(u, v2);
+                fa[1][i][2 * kh + rr] = pack_hi(u, v2);
+            }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t yb[2];
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh) {
+            const int ya = 2 * t + 8 * kh;
+            yb[kh] = h2_as_u32(__halves2half2(ysrc[ya * 16 + h * 8 + g], ysrc[(ya + 1) * 16 + h * 8 + g]));
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            mma_k16(acc[h][i], fa[h][i][0], fa[h][i][1], fa[h][i][2], fa[h][i][3], yb[0], yb[1]);
+    }
+}
+
+template <int D, int MTW, int SIDE>
+__global__ void __launch_bounds__(BW_THREADS, 1)
+attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
+{
+    constexpr int NPX = SIDE == 0 ? 2 : 1;   // x-side projections: (P_q, dB) | (P_k)
+    constexpr int NH = SIDE == 0 ? 2 : 1;    // x-side histograms:  (ds, p)   | (ds)
+    constexpr int NPY = SIDE == 0 ? 1 : 2;   // y-side projections: (P_k)     | (P_q, dB)
+    extern __shared__ __align__(16) unsigned char smem[];
+    const BwdSmem L = make_bwd_layout(meta.R, NPX, NH, NPY);
+    uint32_t *s_px = reinterpret_cast<uint32_t *>(smem + L.off_px);   // [NPX][R16][32]
+    uint32_t *s_hx = reinterpret_cast<uint32_t *>(smem + L.off_hx);   // [NH][R16][32]
+    uint32_t *s_py = reinterpret_cast<uint32_t *>(smem + L.off_py);   // [NPY][KT][Rp]
+    float2 *s_s = reinterpret_cast<float2 *>(smem + L.off_s);         // [KT][32]
+    uint2 *s_pd = reinterpret_cast<uint2 *>(smem + L.off_s);          // same storage: (p, ds) half2 pairs
+    float2 *s_dp = reinterpret_cast<float2 *>(smem + L.off_dp);       // [KT][32]
+    uint32_t *s_idx = reinterpret_cast<uint32_t *>(smem + L.off_idx); // [KT][2][32]
+    __half *s_y0 = reinterpret_cast<__half *>(smem + L.off_yt);       // [KT][16]
+    __half *s_y1 = s_y0 + KT * 16;
+    float *s_yc = reinterpret_cast<float *>(smem + L.off_yc);         // [KT][12]
+    float *s_ylse = reinterpret_cast<float *>(smem + L.off_misc);     // [KT][2]   (SIDE 1)
+    float *s_ydel = s_ylse + 2 * KT;                                  // [KT][2]   (SIDE 1)
+    float *s_xlse = s_ydel + 2 * KT;                                  // [32][2]   (SIDE 0)
+    float *s_xdel = s_xlse + 64;                                      // [32][2]   (SIDE 0)
+    int *s_xrow = reinterpret_cast<int *>(s_xdel + 64);               // [32]
+    __half *s_x0 = reinterpret_cast<__half *>(smem + L.off_s);        // [32][16] aliases s_s (set-up only)
+    __half *s_x1 = reinterpret_cast<__half *>(smem + L.off_dp);       // [32][16] aliases s_dp (set-up only)
+    float *s_red = reinterpret_cast<float *>(smem + L.off_px);        // [16][32][16] aliases s_px (epilogue)
+    float *s_red2 = s_red + BW_NWARP * QT * 16;                       // [32][16]
+
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int hp = blockIdx.y, H = P.H;
+    const int HC = H * 8, co = hp * 16;
+    const int R = meta.R, n_mt = L.R16 / 16, Rp = L.Rp;
+    const int pxw = L.px_stride / 4, pyw = L.py_stride / 4;
+    const int mypos = qpos(lane);
+    constexpr float LOG2E = 1.4426950408889634f;
+
+    // ---- resident table fragments --------------------------------------------------------------------
+    uint32_t ta_px0[MTW][2][2], ta_px1[MTW][2][2], ta_py0[MTW][2][2], ta_py1[MTW][2][2];
+    load_table_a<MTW>(P.t_px0, R, H, hp, wid, g, t, ta_px0);
+    load_table_a<MTW>(P.t_py0, R, H, hp, wid, g, t, ta_py0);
+    if (SIDE == 0) load_table_a<MTW>(P.t_px1, R, H, hp, wid, g, t, ta_px1);
+    else load_table_a<MTW>(P.t_py1, R, H, hp, wid, g, t, ta_py1);
+    // B fragments (k = row, n = channel) of T0 for dX += H0 . T0
+    uint32_t t0B[MTW][2][2];
+#pragma unroll
+    for (int i = 0; i < MTW; ++i) {
+        const int ks = wid + BW_NWARP * i;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int ra = ks * 16 + 2 * t + 8 * half, rb = ra + 1;
+                const int hh = 2 * hp + h;
+                const __half lo = ra < R ? P.t_px0[((int64_t)ra * H + hh) * 8 + g] : __float2half(0.f);
+                const __half hi = rb < R ? P.t_px0[((int64_t)rb * H + hh) * 8 + g] : __float2half(0.f);
+                t0B[i][h][half] = h2_as_u32(__halves2half2(lo, hi));
+            }
+    }
+    // table-gradient accumulators: [hist][row tile of this warp][head][c-frag]
+    float dt_acc[NH][MTW][2][4];
+#pragma unroll
+    for (int a = 0; a < NH; ++a)
+#pragma unroll
+        for (int i = 0; i < MTW; ++i)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) dt_acc[a][i][h][0] = dt_acc[a][i][h][1] = dt_acc[a][i][h][2] = dt_acc[a][i][h][3] = 0.f;
+
+    for (int64_t w = blockIdx.x; w < P.W; w += gridDim.x) {
+        const int n = __ldg(P.w_sizes + w);
+        const int base = __ldg(P.w2n + w);
+        for (int x0 = 0; x0 < n; x0 += QT) {
+            const int nx = min(QT, n - x0);
+            // ---- item set-up: x rows, x coordinates, projections of the x side, empty histograms --------
+            __syncthreads();
+            float cx[D];
+#pragma unroll
+            for (int d = 0; d < D; ++d)
+                cx[d] = lane < nx ? __ldg(P.n_coords + (int64_t)(base + x0 + lane) * D + d) : 0.f;
+            if (tid < 128) {
+                const int xi = tid >> 2, which = (tid >> 1) & 1, hf = tid & 1;
+                uint4 val = make_uint4(0, 0, 0, 0);
+                if (xi < nx) {
+                    const int row = __ldg(P.n2n + base + x0 + xi);
+                    if (which == 0 && hf == 0) s_xrow[xi] = row;
+                    const __half *src = which ? P.x1 : P.x0;
+                    val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)row * HC + co + hf * 8));
+                    if (SIDE == 0 && which == 1) {
+                        // delta[x][head hf] = sum_c dO . O ; lse
+                        const uint4 ov = __ldg(reinterpret_cast<const uint4 *>(P.o + (int64_t)row * HC + co + hf * 8));
+                        const __half2 *a2 = reinterpret_cast<const __half2 *>(&val);
+                        const __half2 *b2 = reinterpret_cast<const __half2 *>(&ov);
+                        float acc = 0.f;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
+                            acc += fa.x * fb.x + fa.y * fb.y;
+                        }
+                        s_xdel[xi * 2 + hf] = acc;
+                        s_xlse[xi * 2 + hf] = __ldg(P.lse + (int64_t)row * H + 2 * hp + hf);
+                    }
+                } else if (SIDE == 0 && which == 1) {
+                    s_xdel[xi * 2 + hf] = 0.f;
+                    s_xlse[xi * 2 + hf] = 0.f;
+                }
+                *reinterpret_cast<uint4 *>((which ? s_x1 : s_x0) + xi * 16 + hf * 8) = val;
+            }
+            for (int i = tid; i < NH * L.R16 * QT / 4; i += BW_THREADS)
+                reinterpret_cast<uint4 *>(s_hx)[i] = make_uint4(0, 0, 0, 0);
+            __syncthreads();
+            float xlse[2] = {0.f, 0.f}, xdel[2] = {0.f, 0.f};
+            if (SIDE == 0) {
+                xlse[0] = s_xlse[lane * 2]; xlse[1] = s_xlse[lane * 2 + 1];
+                xdel[0] = s_xdel[lane * 2]; xdel[1] = s_xdel[lane * 2 + 1];
+            }
+            // block-diagonal B fragments of X0^T / X1^T for the n-tile this warp multiplies in S0 / dPV0
+            uint32_t xS[2];
+            {
+                const __half *src = (wid < 8) ? s_x0 : s_x1;
+                const int j = wid & 7;
+                const uint32_t wv = *reinterpret_cast<const uint32_t *>(src + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+                xS[0] = (g & 1) ? 0u : wv;
+                xS[1] = (g & 1) ? wv : 0u;
+            }
+            // B fragments (k = position, n = channel) of X0 / X1 for the table-gradient GEMMs
+            uint32_t xTB[NH][2][2][2];   // [hist][k-step][head][b0,b1]
+#pragma unroll
+            for (int a = 0; a < NH; ++a) {
+                // SIDE 0: hist 0 (ds) pairs with X0 = Q, hist 1 (p) with X1 = dO ; SIDE 1: hist 0 with X0 = K
+                const __half *src = a == 0 ? s_x0 : s_x1;
+#pragma unroll
+                for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            const int p0 = 16 * ks + 4 * t + 2 * half, p1 = p0 + 1;
+                            const int xa = (p0 >> 2) + 8 * (p0 & 3), xb = (p1 >> 2) + 8 * (p1 & 3);
+                            xTB[a][ks][h][half] = h2_as_u32(__halves2half2(src[xa * 16 + h * 8 + g], src[xb * 16 + h * 8 + g]));
+                        }
+            }
+            project<MTW, true>(ta_px0, s_x0, s_px, n_mt, Rp, wid, g, t);
+            if (SIDE == 0) project<MTW, true>(ta_px1, s_x1, s_px + pxw, n_mt, Rp, wid, g, t);
+
+            float dxacc[2][2][2][4];   // [which: ds.Y0 | p.Y1][head][m-tile][c-frag], warps 15 / 14
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) dxacc[a][h][i][0] = dxacc[a][h][i][1] = dxacc[a][h][i][2] = dxacc[a][h][i][3] = 0.f;
+
+            for (int y0 = 0; y0 < n; y0 += KT) {
+                const int ny = min(KT, n - y0);
+                __syncthreads();
+                // ---- stage the y tile ---------------------------------------------------------------
+                if (tid < 64) {
+                    const int yi = tid >> 2, which = (tid >> 1) & 1, hf = tid & 1;
+                    uint4 val = make_uint4(0, 0, 0, 0);
+                    float del = 0.f, ls = 0.f;
+                    if (yi < ny) {
+                        const int row = __ldg(P.n2n + base + y0 + yi);
+                        const __half *src = which ? P.y1 : P.y0;
+                        val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)row * HC + co + hf * 8));
+                        if (SIDE == 1 && which == 1) {
+                            const uint4 ov = __ldg(reinterpret_cast<const uint4 *>(P.o + (int64_t)row * HC + co + hf * 8));
+                            const __half2 *a2 = reinterpret_cast<const __half2 *>(&val);
+                            const __half2 *b2 = reinterpret_cast<const __half2 *>(&ov);
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
+                                del += fa.x * fb.x + fa.y * fb.y;
+                            }
+                            ls = __ldg(P.lse + (int64_t)row * H + 2 * hp + hf);
+                        }
+                    }
+                    if (SIDE == 1 && which == 1) {
+                        s_ydel[yi * 2 + hf] = del;
+                        s_ylse[yi * 2 + hf] = ls;
+                    }
+                    *reinterpret_cast<uint4 *>((which ? s_y1 : s_y0) + yi * 16 + hf * 8) = val;
+                } else if (tid < 64 + KT * D) {
+                    const int e = tid - 64, yi = e / D, d = e - yi * D;
+                    s_yc[yi * 12 + d] = yi < ny ? __ldg(P.n_coords + (int64_t)(base + y0 + yi) * D + d) : 0.f;
+                }
+                __syncthreads();
+                // ---- y-side projections, S0 = Y0 . X0^T (warps 0-7), dPV0 = Y1 . X1^T (warps 8-15) -------
+                project<MTW, false>(ta_py0, s_y0, s_py, n_mt, Rp, wid, g, t);
+                if (SIDE == 1) project<MTW, false>(ta_py1, s_y1, s_py + pyw, n_mt, Rp, wid, g, t);
+                {
+                    const __half *ysrc = (wid < 8) ? s_y0 : s_y1;
+                    const uint32_t a0 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 2 * t);
+                    const uint32_t a1 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 2 * t);
+                    const uint32_t a2 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 8 + 2 * t);
+                    const uint32_t a3 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 8 + 2 * t);
+                    float c[4];
+                    mma_k16_z(c, a0, a1, a2, a3, xS[0], xS[1]);
+                    float2 *dst = (wid < 8) ? s_s : s_dp;
+                    const int j = wid & 7;
+                    dst[g * QT + 4 * j + t] = make_float2(c[0], c[1]);
+                    dst[(g + 8) * QT + 4 * j + t] = make_float2(c[2], c[3]);
+                }
+                __syncthreads();
+                // ---- phase 1: one y per warp, lane = x: indices, 3*D look-ups, p and ds -----------------
+                {
+                    const int yy = wid;
+                    uint2 pd = make_uint2(0u, 0u);
+                    if (yy < ny) {
+                        __half2 b0 = __float2half2_rn(0.f), b1 = b0, b2 = b0;
+                        uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+                        for (int d = 0; d < D; ++d) {
+                            const float cy = s_yc[yy * 12 + d];
+                            const int idx = SIDE == 0 ? crse_index_fast(cx[d], cy, meta.L[d], d == D - 1)
+                                                      : crse_index_fast(cy, cx[d], meta.L[d], d == D - 1);
+                            const int row = meta.rowbase[d] + idx;
+                            b0 = __hadd2(b0, u32_as_h2(s_px[row * QT + mypos]));
+                            b1 = __hadd2(b1, u32_as_h2(s_py[yy * Rp + row]));
+                            if (SIDE == 0) b2 = __hadd2(b2, u32_as_h2(s_px[pxw + row * QT + mypos]));
+                            else b2 = __hadd2(b2, u32_as_h2(s_py[pyw + yy * Rp + row]));
+                            if (d < 5) w0 |= (uint32_t)idx << (IDX_BITS * d);
+                            else w1 |= (uint32_t)idx << (IDX_BITS * (d - 5));
+                        }
+                        s_idx[(yy * 2 + 0) * QT + lane] = w0;
+                        if (D > 5) s_idx[(yy * 2 + 1) * QT + lane] = w1;
+                        const float2 bs = __half22float2(__hadd2(b0, b1));
+                        const float2 bd = __half22float2(b2);
+                        const float2 s0 = s_s[yy * QT + lane];
+                        const float2 dp0 = s_dp[yy * QT + lane];
+                        float ls0, ls1, de0, de1;
+                        if (SIDE == 0) { ls0 = xlse[0]; ls1 = xlse[1]; de0 = xdel[0]; de1 = xdel[1]; }
+                        else { ls0 = s_ylse[yy * 2]; ls1 = s_ylse[yy * 2 + 1]; de0 = s_ydel[yy * 2]; de1 = s_ydel[yy * 2 + 1]; }
+                        float p0 = exp2f((s0.x + bs.x - ls0) * LOG2E);
+                        float p1 = exp2f((s0.y + bs.y - ls1) * LOG2E);
+                        if (lane >= nx) { p0 = 0.f; p1 = 0.f; }
+                        const float ds0 = p0 * (dp0.x + bd.x - de0);
+                        const float ds1 = p1 * (dp0.y + bd.y - de1);
+                        pd.x = h2_as_u32(__floats2half2_rn(p0, p1));
+                        pd.y = h2_as_u32(__floats2half2_rn(ds0, ds1));
+                    }
+                    s_pd[yy * QT + lane] = pd;   // replaces the score; zero for padded y
+                }
+                __syncthreads();
+                // ---- phase 2: histogram updates, one signal dimension per warp ---------------------------
+                if (wid < D) {
+                    const int d = wid;
+                    const int wsel = d / 5, sh = IDX_BITS * (d % 5);
+                    const int rb = meta.rowbase[d];
+                    for (int yy = 0; yy < ny; ++yy) {
+                        const uint2 pd = s_pd[yy * QT + lane];
+                        const int idx = (s_idx[(yy * 2 + wsel) * QT + lane] >> sh) & ((1 << IDX_BITS) - 1);
+                        uint32_t *cell = s_hx + (rb + idx) * QT + mypos;
+                        *cell = h2_as_u32(__hadd2(u32_as_h2(*cell), u32_as_h2(pd.y)));
+                        if (SIDE == 0) {
+                            uint32_t *cell1 = cell + pxw;
+                            *cell1 = h2_as_u32(__hadd2(u32_as_h2(*cell1), u32_as_h2(pd.x)));
+                        }
+                    }
+                }
+                // ---- dX += dS^T-tile . Y0 (warp 15) ; SIDE 1: dX1 += P^T-tile . Y1 (warp 14), tensor cores ----
+                if (wid == BW_NWARP - 1) dx_gemm<0>(dxacc[0], s_pd, s_y0, g, t);
+                if (SIDE == 1 && wid == BW_NWARP - 2) dx_gemm<1>(dxacc[1], s_pd, s_y1, g, t);
+            }  // y tiles
+            __syncthreads();
+            // ---- table gradients: dT[a][row][c] += sum_x H_a[row][x] X_a[x][c] --------------------------------
+#pragma unroll
+            for (int i = 0; i < MTW; ++i) {
+                const int mt = wid + BW_NWARP * i;
+                if (mt < n_mt) {
+#pragma unroll
+                    for (int a = 0; a < NH; ++a)
+#pragma unroll
+                        for (int ks = 0; ks < 2; ++ks) {
+                            // lane (g,t): rows g and g+8 of the tile, positions 16ks+4t .. +3  <->  k = 2t, 2t+1, 2t+8, 2t+9
+                            const uint4 u = *reinterpret_cast<const uint4 *>(s_hx + a * pxw + (mt * 16 + g) * QT + 16 * ks + 4 * t);
+                            const uint4 v2 = *reinterpret_cast<const uint4 *>(s_hx + a * pxw + (mt * 16 + g + 8) * QT + 16 * ks + 4 * t);
+                            mma_k16(dt_acc[a][i][0], pack_lo(u.x, u.y), pack_lo(v2.x, v2.y), pack_lo(u.z, u.w), pack_lo(v2.z, v2.w),
+                                    xTB[a][ks][0][0], xTB[a][ks][0][1]);
+                            mma_k16(dt_acc[a][i][1], pack_hi(u.x, u.y), pack_hi(v2.x, v2.y), pack_hi(u.z, u.w), pack_hi(v2.z, v2.w),
+                                    xTB[a][ks][1][0], xTB[a][ks][1][1]);
+                        }
+                }
+            }
+            // ---- dX += H0 . T0 (row range split over the warps), reduce, store ---------------------------------
+            float part[2][2][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) part[h][i][e] = (wid == BW_NWARP - 1) ? dxacc[0][h][i][e] : 0.f;
+#pragma unroll
+            for (int i = 0; i < MTW; ++i) {
+                const int ks = wid + BW_NWARP * i;
+                if (ks < n_mt) {
+                    const uint4 y0v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t) * QT + 4 * g);
+                    const uint4 y1v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t + 1) * QT + 4 * g);
+                    const uint4 y2v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t + 8) * QT + 4 * g);
+                    const uint4 y3v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t + 9) * QT + 4 * g);
+                    // m-tile 0: queries g, g+8 (columns .x, .y) ; m-tile 1: queries g+16, g+24 (.z, .w)
+                    mma_k16(part[0][0], pack_lo(y0v.x, y1v.x), pack_lo(y0v.y, y1v.y), pack_lo(y2v.x, y3v.x), pack_lo(y2v.y, y3v.y), t0B[i][0][0], t0B[i][0][1]);
+                    mma_k16(part[1][0], pack_hi(y0v.x, y1v.x), pack_hi(y0v.y, y1v.y), pack_hi(y2v.x, y3v.x), pack_hi(y2v.y, y3v.y), t0B[i][1][0], t0B[i][1][1]);
+                    mma_k16(part[0][1], pack_lo(y0v.z, y1v.z), pack_lo(y0v.w, y1v.w), pack_lo(y2v.z, y3v.z), pack_lo(y2v.w, y3v.w), t0B[i][0][0], t0B[i][0][1]);
+                    mma_k16(part[1][1], pack_hi(y0v.z, y1v.z), pack_hi(y0v.w, y1v.w), pack_hi(y2v.z, y3v.z), pack_hi(y2v.w, y3v.w), t0B[i][1][0], t0B[i][1][1]);
+                }
+            }
+            __syncthreads();   // every warp is done with s_px (phase 1 look-ups) before it becomes s_red
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const int xx = 16 * i + g + 8 * rr;
+                        *reinterpret_cast<float2 *>(s_red + (wid * QT + xx) * 16 + h * 8 + 2 * t) =
+                            make_float2(part[h][i][2 * rr], part[h][i][2 * rr + 1]);
+                        if (SIDE == 1 && wid == BW_NWARP - 2)
+                            *reinterpret_cast<float2 *>(s_red2 + xx * 16 + h * 8 + 2 * t) =
+                                make_float2(dxacc[1][h][i][2 * rr], dxacc[1][h][i][2 * rr + 1]);
+                    }
+            __syncthreads();
+            {
+                const int xx = tid >> 4, ch = tid & 15;
+                if (xx < nx) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int ww = 0; ww < BW_NWARP; ++ww) a += s_red[(ww * QT + xx) * 16 + ch];
+                    const int64_t row = s_xrow[xx];
+                    P.dx0[row * HC + co + ch] = __float2half_rn(a);
+                    if (SIDE == 1) P.dx1[row * HC + co + ch] = __float2half_rn(s_red2[xx * 16 + ch]);
+                }
+            }
+        }  // x tiles
+    }      // windows
+
+    // ---- flush the table gradients of this block ---------------------------------------------------------------
+#pragma unroll
+    for (int a = 0; a < NH; ++a) {
+        float *dst = a == 0 ? P.dt0 : P.dt1;
+#pragma unroll
+        for (int i = 0; i < MTW; ++i) {
+            const int mt = wid + BW_NWARP * i;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int row = mt * 16 + g + 8 * rr;
+                    if (mt < n_mt && row < R) {
+                        float *p = dst + ((int64_t)row * H + 2 * hp + h) * 8 + 2 * t;
+                        atomicAdd(p, dt_acc[a][i][h][2 * rr]);
+                        atomicAdd(p + 1, dt_acc[a][i][h][2 * rr + 1]);
+                    }
+                }
+        }
+    }
+}
+
+template <int D, int MTW, int SIDE>
+static int launch_side(const BwdParams &p, const CrseMeta &meta, cudaStream_t st)
+{
+    const BwdSmem L = make_bwd_layout(meta.R, SIDE == 0 ? 2 : 1, SIDE == 0 ? 2 : 1, SIDE == 0 ? 1 : 2);
+    auto kern = attn_bwd_tc_kernel<D, MTW, SIDE>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total) != cudaSuccess)
+        return S3D_ERR_LAUNCH;
+    int dev = 0, sms = 148, per_sm = 1;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, BW_THREADS, L.total) != cudaSuccess || per_sm < 1)
+        return S3D_ERR_LAUNCH;
+    const int hp = p.H / 2;
+    int gx = sms * per_sm / hp;
+    if (gx > p.W) gx = (int)p.W;
+    if (gx < 1) gx = 1;
+    dim3 grid((unsigned)gx, (unsigned)hp);
+    kern<<<grid, BW_THREADS, L.total, st>>>(p, meta);
+    return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
+}
+
+template <int D, int MTW>
+static int launch_both(const AttnArgs &a, cudaStream_t st)
+{
+    BwdParams pq{};
+    pq.x0 = (const __half *)a.q;   pq.x1 = (const __half *)a.dout;
+    pq.y0 = (const __half *)a.k;   pq.y1 = (const __half *)a.v;
+    pq.o = (const __half *)a.out;  pq.lse = a.lse;
+    pq.t_px0 = (const __half *)a.tq; pq.t_px1 = (const __half *)a.tv;
+    pq.t_py0 = (const __half *)a.tk; pq.t_py1 = nullptr;
+    pq.dx0 = (__half *)a.dq; pq.dx1 = nullptr;
+    pq.dt0 = a.dtq; pq.dt1 = a.dtv;
+    pq.w_sizes = a.w_sizes; pq.w2n = a.w2n; pq.n2n = a.n2n; pq.n_coords = a.n_coords;
+    pq.W = a.W; pq.H = a.H;
+    int rc = launch_side<D, MTW, 0>(pq, a.meta, st);
+    if (rc != S3D_OK) return rc;
+    BwdParams pk = pq;
+    pk.x0 = (const __half *)a.k;   pk.x1 = (const __half *)a.v;
+    pk.y0 = (const __half *)a.q;   pk.y1 = (const __half *)a.dout;
+    pk.t_px0 = (const __half *)a.tk; pk.t_px1 = nullptr;
+    pk.t_py0 = (const __half *)a.tq; pk.t_py1 = (const __half *)a.tv;
+    pk.dx0 = (__half *)a.dk; pk.dx1 = (__half *)a.dv;
+    pk.dt0 = a.dtk; pk.dt1 = nullptr;
+    return launch_side<D, MTW, 1>(pk, a.meta, st);
+}
+
+}  // namespace tc
+
+bool attn_tc_bwd_supported(const AttnArgs &a)
+{
+    if (a.dtype != S3D_F16 || a.hd != 8 || (a.H & 1)) return false;
+    if (a.meta.R > 16 * tc::BW_NWARP * 2) return false;
+    for (int d = 0; d < a.meta.D; ++d)
+        if (a.meta.L[d] >= (1 << tc::IDX_BITS)) return false;
+    if (tc::make_bwd_layout(a.meta.R, 2, 2, 1).total > 227 * 1024) return false;
+    if (tc::make_bwd_layout(a.meta.R, 1, 1, 2).total > 227 * 1024) return false;
+    return true;
+}
+
+// dtq, dtk, dtv must be zero on entry (the kernels accumulate into them).
+int attn_tc_backward(const AttnArgs &a, cudaStream_t st)
+{
+    if (a.W == 0) return S3D_OK;
+    const int n_mt = (a.meta.R + 15) / 16;
+    const int mtw = (n_mt + tc::BW_NWARP - 1) / tc::BW_NWARP;
+#define S3D_TC_BWD(DD)                                            \
+    switch (mtw) {                                                \
+        case 1: return tc::launch_both<DD, 1>(a, st);             \
+        case 2: return tc::launch_both<DD, 2>(a, st);             \
+        default: return S3D_ERR_UNSUPPORTED;                      \
+    }
+    switch (a.meta.D) {
+        case 3: S3D_TC_BWD(3)
+        case 6: S3D_TC_BWD(6)
+        case 9: S3D_TC_BWD(9)
+        default: return S3D_ERR_UNSUPPORTED;
+    }
+#undef S3D_TC_BWD
+}
+
+}  // namespace s3d

@@ -99,36 +99,35 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
             for (int i = tid; i < L.R16 * QT / 4; i += NTHREADS)
                 reinterpret_cast<uint4 *>(s_hist)[i] = make_uint4(0, 0, 0, 0);
             __syncthreads();
-            uint32_t qB[4][2];  // B fragments of Q^T: n-tile j <-> queries 8j..8j+7
+            // block-diagonal B fragments of Q^T: n-tile j <-> (queries 4j..4j+3) x (head 0, head 1)
+            uint32_t qB[8][2];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-                    qB[j][h] = *reinterpret_cast<const uint32_t *>(s_q + (8 * j + g) * 16 + h * 8 + 2 * t);
-            // P_q^T[row][q] = Tq . Q^T
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t wq = *reinterpret_cast<const uint32_t *>(s_q + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+                qB[j][0] = (g & 1) ? 0u : wq;
+                qB[j][1] = (g & 1) ? wq : 0u;
+            }
+            uint32_t qS[2];   // the n-tile of Q^T this warp multiplies with K for the plain q.k scores
+            {
+                const uint32_t wq = *reinterpret_cast<const uint32_t *>(s_q + (4 * wid + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+                qS[0] = (g & 1) ? 0u : wq;
+                qS[1] = (g & 1) ? wq : 0u;
+            }
+            // P_q^T[row][(q, head)] = Tq . Q^T, fp16 accumulate, stored as it comes out
 #pragma unroll
             for (int i = 0; i < MTW; ++i) {
                 const int mt = wid + NWARP * i;
                 if (mt < n_mt) {
-                    float c[2][4][4];
+                    uint32_t d0[8], d1[8];
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            c[h][j][0] = c[h][j][1] = c[h][j][2] = c[h][j][3] = 0.f;
-                            mma_k8(c[h][j], tqA[i][h][0], tqA[i][h][1], qB[j][h]);
-                        }
-#pragma unroll
-                    for (int rr = 0; rr < 2; ++rr)      // row g / row g+8
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {   // query 8j+2t / 8j+2t+1
-                            uint4 o;
-                            o.x = h2_as_u32(__floats2half2_rn(c[0][0][2 * rr + e], c[1][0][2 * rr + e]));
-                            o.y = h2_as_u32(__floats2half2_rn(c[0][1][2 * rr + e], c[1][1][2 * rr + e]));
-                            o.z = h2_as_u32(__floats2half2_rn(c[0][2][2 * rr + e], c[1][2][2 * rr + e]));
-                            o.w = h2_as_u32(__floats2half2_rn(c[0][3][2 * rr + e], c[1][3][2 * rr + e]));
-                            *reinterpret_cast<uint4 *>(s_pq + (mt * 16 + g + 8 * rr) * QT + 8 * t + 4 * e) = o;
-                        }
+                    for (int j = 0; j < 8; ++j)
+                        mma_k16_h(d0[j], d1[j], tqA[i][0][0], tqA[i][0][1], tqA[i][1][0], tqA[i][1][1], qB[j][0], qB[j][1]);
+                    // query 4j+t sits in column 4t + j/2 (j even) or 16 + 4t + j/2 (j odd)
+                    uint32_t *r0 = s_pq + (mt * 16 + g) * QT + 4 * t;
+                    *reinterpret_cast<uint4 *>(r0) = make_uint4(d0[0], d0[2], d0[4], d0[6]);
+                    *reinterpret_cast<uint4 *>(r0 + 16) = make_uint4(d0[1], d0[3], d0[5], d0[7]);
+                    *reinterpret_cast<uint4 *>(r0 + 8 * QT) = make_uint4(d1[0], d1[2], d1[4], d1[6]);
+                    *reinterpret_cast<uint4 *>(r0 + 8 * QT + 16) = make_uint4(d1[1], d1[3], d1[5], d1[7]);
                 }
             }
             float m_run[2] = {-INFINITY, -INFINITY};
@@ -160,51 +159,33 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                     s_mtile[(tid - 224) * 2 + 1] = -INFINITY;
                 }
                 __syncthreads();
-                // ---- P_k^T[row][key] = Tk . K^T  ->  s_pk[key][row] ;  S0^T[key][q] = K . Q^T --------
+                // ---- P_k^T[row][(key, head)] = Tk . K^T -> s_pk[key][row];  S0^T[key][(q, head)] = K . Q^T ----
                 {
-                    uint32_t kB[2][2];
 #pragma unroll
-                    for (int j = 0; j < 2; ++j)
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t wk = *reinterpret_cast<const uint32_t *>(s_k + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+                        const uint32_t b0 = (g & 1) ? 0u : wk, b1 = (g & 1) ? wk : 0u;
 #pragma unroll
-                        for (int h = 0; h < 2; ++h)
-                            kB[j][h] = *reinterpret_cast<const uint32_t *>(s_k + (8 * j + g) * 16 + h * 8 + 2 * t);
-#pragma unroll
-                    for (int i = 0; i < MTW; ++i) {
-                        const int mt = wid + NWARP * i;
-                        if (mt < n_mt) {
-                            float c[2][2][4];
-#pragma unroll
-                            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                                for (int j = 0; j < 2; ++j) {
-                                    c[h][j][0] = c[h][j][1] = c[h][j][2] = c[h][j][3] = 0.f;
-                                    mma_k8(c[h][j], tkA[i][h][0], tkA[i][h][1], kB[j][h]);
-                                }
-#pragma unroll
-                            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                                for (int rr = 0; rr < 2; ++rr)
-#pragma unroll
-                                    for (int e = 0; e < 2; ++e)
-                                        s_pk[(8 * j + 2 * t + e) * Rp + mt * 16 + g + 8 * rr] =
-                                            h2_as_u32(__floats2half2_rn(c[0][j][2 * rr + e], c[1][j][2 * rr + e]));
+                        for (int i = 0; i < MTW; ++i) {
+                            const int mt = wid + NWARP * i;
+                            if (mt < n_mt) {
+                                uint32_t d0, d1;
+                                mma_k16_h(d0, d1, tkA[i][0][0], tkA[i][0][1], tkA[i][1][0], tkA[i][1][1], b0, b1);
+                                uint32_t *dst = s_pk + (4 * j + t) * Rp + mt * 16 + g;
+                                dst[0] = d0;
+                                dst[8] = d1;
+                            }
                         }
                     }
-                    if (wid == NWARP - 1) {
-                        uint32_t ka[2][2];
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            ka[h][0] = *reinterpret_cast<const uint32_t *>(s_k + g * 16 + h * 8 + 2 * t);
-                            ka[h][1] = *reinterpret_cast<const uint32_t *>(s_k + (g + 8) * 16 + h * 8 + 2 * t);
-                        }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-                            mma_k8(c0, ka[0][0], ka[0][1], qB[j][0]);
-                            mma_k8(c1, ka[1][0], ka[1][1], qB[j][1]);
-                            *reinterpret_cast<float4 *>(s_s + g * QT + 8 * j + 2 * t) = make_float4(c0[0], c1[0], c0[1], c1[1]);
-                            *reinterpret_cast<float4 *>(s_s + (g + 8) * QT + 8 * j + 2 * t) = make_float4(c0[2], c1[2], c0[3], c1[3]);
-                        }
+                    {   // one n-tile (4 queries x 2 heads) of S0 per warp
+                        const uint32_t a0 = *reinterpret_cast<const uint32_t *>(s_k + g * 16 + 2 * t);
+                        const uint32_t a1 = *reinterpret_cast<const uint32_t *>(s_k + (g + 8) * 16 + 2 * t);
+                        const uint32_t a2 = *reinterpret_cast<const uint32_t *>(s_k + g * 16 + 8 + 2 * t);
+                        const uint32_t a3 = *reinterpret_cast<const uint32_t *>(s_k + (g + 8) * 16 + 8 + 2 * t);
+                        float c[4];
+                        mma_k16_z(c, a0, a1, a2, a3, qS[0], qS[1]);
+                        s_s[g * QT + 4 * wid + t] = make_float2(c[0], c[1]);
+                        s_s[(g + 8) * QT + 4 * wid + t] = make_float2(c[2], c[3]);
                     }
                 }
                 __syncthreads();
@@ -218,7 +199,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                         uint32_t w0 = 0, w1 = 0;
 #pragma unroll
                         for (int d = 0; d < D; ++d) {
-                            const int idx = crse_index(cq[d], s_kc[kk * 12 + d], meta.L[d], d == D - 1);
+                            const int idx = crse_index_fast(cq[d], s_kc[kk * 12 + d], meta.L[d], d == D - 1);
                             const int row = meta.rowbase[d] + idx;
                             bq = __hadd2(bq, u32_as_h2(s_pq[row * QT + mypos]));
                             bk = __hadd2(bk, u32_as_h2(s_pk[kk * Rp + row]));

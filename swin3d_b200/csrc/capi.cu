@@ -100,6 +100,7 @@ int s3d_attn_bwd(const void *q, const void *k, const void *v, const void *tq, co
     a.N = N; a.W = W; a.H = H; a.hd = hd; a.dtype = dtype;
     a.out = const_cast<void *>(out); a.lse = const_cast<float *>(lse); a.dout = dout;
     a.dq = dq; a.dk = dk; a.dv = dv; a.dtq = dtq; a.dtk = dtk; a.dtv = dtv;
+    if (!force_scalar() && attn_tc_bwd_supported(a)) return attn_tc_backward(a, st);
     return attn_scalar_backward(a, st);
 }
 
