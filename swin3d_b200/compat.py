@@ -1,0 +1,36 @@
+"""Makes the reference's import paths resolve to this package.
+
+``Swin3D/modules/swin3d_layers.py:16-24`` imports ``Swin3D.sparse_dl.attn.attn_coff`` and
+``Swin3D.sparse_dl.knn``.  ``install_as_swin3d()`` registers this package's modules under those
+names so that the reference's ``WindowAttention``, ``GridKNNDownsample`` and ``Upsample`` call the
+kernels of libswin3d_b200.so without a change to their source.
+"""
+import importlib
+import sys
+import types
+
+
+def install_as_swin3d(force: bool = False) -> None:
+    """Call before ``import Swin3D.modules`` / ``Swin3D.models``."""
+    mapping = {
+        "Swin3D.sparse_dl": "swin3d_b200.sparse_dl",
+        "Swin3D.sparse_dl.attn": "swin3d_b200.sparse_dl.attn",
+        "Swin3D.sparse_dl.attn.attn_coff": "swin3d_b200.sparse_dl.attn.attn_coff",
+        "Swin3D.sparse_dl.knn": "swin3d_b200.sparse_dl.knn",
+        "Swin3D.sparse_dl.knn.knn": "swin3d_b200.sparse_dl.knn.knn",
+    }
+    if "Swin3D" not in sys.modules:
+        try:
+            importlib.import_module("Swin3D")
+        except ImportError:
+            pkg = types.ModuleType("Swin3D")
+            pkg.__path__ = []
+            sys.modules["Swin3D"] = pkg
+    for alias, target in mapping.items():
+        if alias in sys.modules and not force:
+            continue
+        mod = importlib.import_module(target)
+        sys.modules[alias] = mod
+        parent, _, leaf = alias.rpartition(".")
+        if parent in sys.modules:
+            setattr(sys.modules[parent], leaf, mod)

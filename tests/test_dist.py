@@ -1,0 +1,97 @@
+"""CPU: window sharding and the table-gradient all-reduce on two gloo ranks."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import oracle as O
+from swin3d_b200.dist import allreduce_table_grads, shard_voxel_range, shard_windows
+from tests.helpers import make_problem
+
+
+def test_shard_windows_covers_and_balances():
+    rng = np.random.default_rng(0)
+    w = rng.integers(1, 126, size=5000)
+    for world in (1, 2, 3, 8):
+        parts = shard_windows(w, world)
+        assert parts[0][0] == 0 and parts[-1][1] == len(w)
+        assert all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
+        cost = np.array([(w[a:b].astype(np.int64) ** 2).sum() for a, b in parts])
+        assert cost.sum() == (w.astype(np.int64) ** 2).sum()
+        assert cost.max() <= cost.sum() / world + 125 ** 2
+    assert shard_windows([], 4) == [(0, 0)] * 4
+    assert shard_windows([3], 2) in ([(0, 1), (1, 1)], [(0, 0), (0, 1)])
+    w2n = np.cumsum(w) - w
+    a, b = shard_windows(w, 2)[1]
+    lo, hi = shard_voxel_range(w, w2n, a, b)
+    assert lo == w[:a].sum() and hi == w.sum()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    p = make_problem(seed=71, n_voxels=500, grid=20, H=2, hd=8, crse="XYZ_RGB")
+    out, s, mx = O.attn_forward(p.q, p.k, p.v, p.tq, p.tk, p.tv, p.sizes, p.w_sizes, p.w2n, p.n2n, p.n_crse)
+    a, b = shard_windows(p.w_sizes, world)[rank]
+    # this rank's windows only: same arrays, window list cut to [a, b)
+    g = O.attn_backward(p.q, p.k, p.v, p.tq, p.tk, p.tv, p.sizes, p.w_sizes[a:b], p.w2n[a:b], p.n2n,
+                        p.n_crse, out, s, mx, p.g)
+    dq, dk, dv = (torch.from_numpy(x) for x in g[:3])
+    tg = allreduce_table_grads(tuple(torch.from_numpy(x) for x in g[3:]))
+    for t in (dq, dk, dv):          # disjoint rows per rank: a sum reassembles the full gradient
+        dist.all_reduce(t)
+    if rank == 0:
+        q.put([x.numpy() for x in (dq, dk, dv, *tg)])
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_two_rank_window_sharding_reproduces_single_rank_gradients():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    got = q.get(timeout=240)
+    for pr in procs:
+        pr.join(60)
+        assert pr.exitcode == 0
+    p = make_problem(seed=71, n_voxels=500, grid=20, H=2, hd=8, crse="XYZ_RGB")
+    out, s, mx = O.attn_forward(p.q, p.k, p.v, p.tq, p.tk, p.tv, p.sizes, p.w_sizes, p.w2n, p.n2n, p.n_crse)
+    ref = O.attn_backward(p.q, p.k, p.v, p.tq, p.tk, p.tv, p.sizes, p.w_sizes, p.w2n, p.n2n, p.n_crse,
+                          out, s, mx, p.g)
+    for a, b in zip(got, ref):
+        assert np.allclose(a, b, rtol=1e-12, atol=1e-14)
+
+
+def test_compat_aliases_resolve_reference_import_paths():
+    import importlib
+    import sys
+    import swin3d_b200.compat as compat
+    saved = {k: v for k, v in sys.modules.items() if k == "Swin3D" or k.startswith("Swin3D.")}
+    for k in saved:
+        del sys.modules[k]
+    try:
+        compat.install_as_swin3d()
+        coff = importlib.import_module("Swin3D.sparse_dl.attn.attn_coff")
+        knn = importlib.import_module("Swin3D.sparse_dl.knn")
+        from swin3d_b200.sparse_dl.attn.attn_coff import SelfAttnAIOFunction
+        from swin3d_b200.sparse_dl.knn import KNN
+        assert coff.SelfAttnAIOFunction is SelfAttnAIOFunction and knn.KNN is KNN
+        assert coff.PrecisionMode.HALF_NONE.value == 3 and coff.IndexMode.INDIRECT.value == 2
+    finally:
+        for k in [k for k in sys.modules if k == "Swin3D" or k.startswith("Swin3D.")]:
+            del sys.modules[k]
+        sys.modules.update(saved)
