@@ -26,6 +26,7 @@ extern "C" {
 #define S3D_ERR_UNSUPPORTED 2    /* head_dim, signal-dim count, K or window size not built */
 #define S3D_ERR_LAUNCH 3         /* the CUDA runtime reported an error at launch           */
 #define S3D_ERR_WORKSPACE 4      /* caller-provided workspace too small                    */
+#define S3D_ERR_TOO_LARGE 5      /* input exceeds the fixed capacity of a *_static entry   */
 
 #define S3D_F32 0
 #define S3D_F16 1
@@ -109,6 +110,27 @@ int s3d_window_build(const int32_t *coords, const float *feats, int64_t N, int F
                      int32_t *n2n, float *n_coords, int32_t *w_sizes, int32_t *w2n,
                      int64_t *counts_out,
                      void *workspace, int64_t workspace_bytes, void *stream);
+
+/* Window builder for callers that cannot allocate device memory (no counterpart in the
+ * reference, whose builder allocates freely through PyTorch).  Same inputs, outputs and results as
+ * s3d_window_build, but the scratch memory is a fixed 4.25 MiB array that is part of the library
+ * image on every GPU that loads it, so neither the caller nor the library allocates anything: no
+ * cudaMalloc, no cudaFree, no allocating library routine.  Meant for hosts whose memory is
+ * frozen after start-up (an inference server that gave its arena every spare byte) or that
+ * must not enter an allocator from the context they call from.
+ *  - At most S3D_WINDOW_BUILD_STATIC_MAX_VOXELS voxels per call; more returns S3D_ERR_TOO_LARGE
+ *    and launches nothing.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress
+ *    with that device current) and caches it; make that first call before any stream capture.
+ *  - All calls on one device share the one array: calls that overlap on the GPU (different
+ *    streams, or threads) race and corrupt each other's results.  Serialise them.  The array
+ *    keeps whatever the last call left; no call depends on it.
+ */
+#define S3D_WINDOW_BUILD_STATIC_MAX_VOXELS 131072
+int s3d_window_build_static(const int32_t *coords, const float *feats, int64_t N, int F,
+                            int stride, int ws, int shift,
+                            int32_t *n2n, float *n_coords, int32_t *w_sizes, int32_t *w2n,
+                            int64_t *counts_out, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Brute-force KNN.  Replaces knn_cuda.knn_cuda (Swin3D/src/knn/knn_cuda_kernel.h:5-12,

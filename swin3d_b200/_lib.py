@@ -30,6 +30,8 @@ SIGNATURES = {
     "s3d_window_build_workspace_bytes": (_i64, [_i64]),
     "s3d_window_build": (_i32, [_c_void_p, _c_void_p, _i64, _i32, _i32, _i32, _i32] +
                          [_c_void_p] * 5 + [_c_void_p, _i64, _c_void_p]),
+    "s3d_window_build_static": (_i32, [_c_void_p, _c_void_p, _i64, _i32, _i32, _i32, _i32] +
+                                [_c_void_p] * 5 + [_c_void_p]),
     "s3d_knn": (_i32, [_i32, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _i32, _i64, _i64,
                        _c_void_p, _c_void_p, _c_void_p]),
 }

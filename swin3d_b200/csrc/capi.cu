@@ -49,6 +49,7 @@ const char *s3d_status_string(int status)
         case S3D_ERR_UNSUPPORTED: return "unsupported shape (head_dim must be 8, 16 or 32; signal dims 3, 6 or 9; K <= 64; window size <= 8)";
         case S3D_ERR_LAUNCH: return "CUDA launch error";
         case S3D_ERR_WORKSPACE: return "workspace too small";
+        case S3D_ERR_TOO_LARGE: return "input larger than the fixed capacity of this *_static entry point (see its limit in swin3d_b200.h)";
         default: return "unknown status";
     }
 }

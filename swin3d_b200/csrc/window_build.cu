@@ -11,6 +11,8 @@
 // All kernels are plain integer/byte work bound by HBM bandwidth: keys are read and written
 // with coalesced accesses, digit ranking uses warp match + shared counters, and radix passes
 // whose digit is identical for every key are skipped on the device (no host round trip).
+#include <mutex>
+
 #include "common.cuh"
 #include "window_kernels.cuh"
 
@@ -367,3 +369,60 @@ int window_build_launch(const int32_t *coords, const float *feats, int64_t N, in
 }
 
 }  // namespace s3d
+
+// ---- window builder without any allocation by anybody -------------------------------------------------
+// Some callers of this library cannot provide device scratch memory at the moment they need the
+// window sets: code running while a memory pool is frozen (for instance a serving process that
+// has handed every spare byte to its own arena and forbids driver allocations after start-up),
+// or a host integration that may not call into an allocator from the thread or callback it runs
+// on.  For them the scratch of the builder is a fixed array inside the library image.
+//
+// The array below is device memory that every GPU which loads this library keeps until the
+// process exits.  Its name is only a host-side handle: passing `g_wb_static_scratch` itself to a
+// kernel from host code would hand over a host address.  The device address is obtained with
+// cudaGetSymbolAddress, once per device, with that device current, and cached.
+namespace {
+
+constexpr long long WB_STATIC_BYTES = 4456448;   // 4.25 MiB: the layout of S3D_WINDOW_BUILD_STATIC_MAX_VOXELS voxels
+static __device__ __align__(256) unsigned char g_wb_static_scratch[WB_STATIC_BYTES];
+
+constexpr int WB_MAX_DEVICES = 64;
+void *g_wb_static_addr[WB_MAX_DEVICES] = {nullptr};
+std::mutex g_wb_static_mutex;
+
+// Device address of the scratch array on the current device (looked up on the first call per device).
+int wb_static_scratch(void **out)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= WB_MAX_DEVICES) return S3D_ERR_LAUNCH;
+    std::lock_guard<std::mutex> lock(g_wb_static_mutex);
+    if (g_wb_static_addr[dev] == nullptr) {
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_wb_static_scratch) != cudaSuccess || ptr == nullptr) return S3D_ERR_LAUNCH;
+        g_wb_static_addr[dev] = ptr;
+    }
+    *out = g_wb_static_addr[dev];
+    return S3D_OK;
+}
+
+}  // namespace
+
+extern "C" int s3d_window_build_static(const int32_t *coords, const float *feats, int64_t N, int F, int stride,
+                                       int ws, int shift, int32_t *n2n, float *n_coords, int32_t *w_sizes,
+                                       int32_t *w2n, int64_t *counts_out, void *stream)
+{
+    if (N < 0 || stride < 1 || shift < 0 || F < 3 || F > 9) return S3D_ERR_BAD_ARG;
+    if (ws < 1 || ws > 8) return S3D_ERR_UNSUPPORTED;
+    if (N > S3D_WINDOW_BUILD_STATIC_MAX_VOXELS) return S3D_ERR_TOO_LARGE;
+    if (s3d::window_build_workspace_bytes(N) > WB_STATIC_BYTES) return S3D_ERR_TOO_LARGE;
+    if (!counts_out) return S3D_ERR_BAD_ARG;
+    if (N > 0 && (!coords || !feats || !n2n || !n_coords || !w_sizes || !w2n)) return S3D_ERR_BAD_ARG;
+    void *scratch = nullptr;
+    const int rc = wb_static_scratch(&scratch);
+    if (rc != S3D_OK) return rc;
+    // Nothing in the scratch has to start at zero: every field the kernels read is written earlier
+    // in the same call (keys, values, digit histograms, scans, flags, pass bookkeeping), so the
+    // contents left behind by the previous call are simply overwritten.
+    return s3d::window_build_launch(coords, feats, N, F, stride, ws, shift, n2n, n_coords, w_sizes, w2n,
+                                    counts_out, scratch, WB_STATIC_BYTES, static_cast<cudaStream_t>(stream));
+}
