@@ -94,6 +94,45 @@ __device__ __forceinline__ void atomic_max_float(float *addr, float v)
         atomicMin(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
 }
 
+// Histogram update  hist[a][row_j] += v[a][j]  for four voxels j of a tile at once, for NDIM signal
+// dimensions (disjoint row ranges) and NARR histograms sharing the row index.  All loads are issued
+// before any store, so the shared-memory latency is paid once per group instead of once per voxel;
+// equal rows inside a group are chained in registers (later voxel wins the store, carrying the sum).
+// `cell` points at this lane's column of histogram 0; `off[d][j]` = row * QT (words).
+template <int NDIM, int NARR>
+__device__ __forceinline__ void hist_add4(uint32_t *cell, int arr_stride, const int (&off)[NDIM][4],
+                                          const uint32_t (&v)[NARR][4])
+{
+    uint32_t c[NDIM][NARR][4];
+#pragma unroll
+    for (int d = 0; d < NDIM; ++d)
+#pragma unroll
+        for (int a = 0; a < NARR; ++a)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) c[d][a][j] = cell[a * arr_stride + off[d][j]];
+#pragma unroll
+    for (int d = 0; d < NDIM; ++d) {
+        const bool e10 = off[d][1] == off[d][0];
+        const bool e20 = off[d][2] == off[d][0], e21 = off[d][2] == off[d][1];
+        const bool e30 = off[d][3] == off[d][0], e31 = off[d][3] == off[d][1], e32 = off[d][3] == off[d][2];
+#pragma unroll
+        for (int a = 0; a < NARR; ++a) {
+            const __half2 s0 = __hadd2(u32_as_h2(c[d][a][0]), u32_as_h2(v[a][0]));
+            const __half2 s1 = __hadd2(e10 ? s0 : u32_as_h2(c[d][a][1]), u32_as_h2(v[a][1]));
+            const __half2 s2 = __hadd2(e21 ? s1 : (e20 ? s0 : u32_as_h2(c[d][a][2])), u32_as_h2(v[a][2]));
+            const __half2 s3 = __hadd2(e32 ? s2 : (e31 ? s1 : (e30 ? s0 : u32_as_h2(c[d][a][3]))), u32_as_h2(v[a][3]));
+            c[d][a][0] = h2_as_u32(s0); c[d][a][1] = h2_as_u32(s1);
+            c[d][a][2] = h2_as_u32(s2); c[d][a][3] = h2_as_u32(s3);
+        }
+    }
+#pragma unroll
+    for (int d = 0; d < NDIM; ++d)
+#pragma unroll
+        for (int a = 0; a < NARR; ++a)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) cell[a * arr_stride + off[d][j]] = c[d][a][j];
+}
+
 // Shared-memory carve-up (byte offsets) for a table of R rows.
 struct SmemLayout {
     int R16;      // rows rounded up to a multiple of 16

@@ -21,30 +21,32 @@ namespace tc {
 
 constexpr int BW_NWARP = 16;
 constexpr int BW_THREADS = BW_NWARP * 32;
+// y voxels per tile: 32 (two per warp) where shared memory allows it, else 16
+__host__ __device__ constexpr int bkt_of(int side) { return side == 0 ? 16 : 32; }
 
 struct BwdSmem {
     int R16, Rp;
     int off_px, px_stride, off_hx, off_py, py_stride, off_s, off_dp, off_idx, off_yt, off_yc, off_misc, total;
 };
 
-__host__ __device__ inline BwdSmem make_bwd_layout(int R, int npx, int nh, int npy)
+__host__ __device__ inline BwdSmem make_bwd_layout(int R, int npx, int nh, int npy, int BKT)
 {
     BwdSmem L;
     L.R16 = (R + 15) / 16 * 16;
     L.Rp = (L.R16 + 31) / 32 * 32 + 8;
     L.px_stride = L.R16 * QT * 4;
-    L.py_stride = KT * L.Rp * 4;
+    L.py_stride = BKT * L.Rp * 4;
     int off = 0;
     const int px_bytes = npx * L.px_stride;
     L.off_px = off; off += px_bytes > 36864 ? px_bytes : 36864;   // doubles as the 34 KB reduction buffer
     L.off_hx = off; off += nh * L.px_stride;
     L.off_py = off; off += npy * L.py_stride;
-    L.off_s = off;  off += KT * QT * 8;      // float2 scores, then (p, ds) half2 pairs
-    L.off_dp = off; off += KT * QT * 8;      // float2 dO.v
-    L.off_idx = off; off += KT * 2 * QT * 4;
-    L.off_yt = off; off += 2 * KT * 16 * 2;
-    L.off_yc = off; off += KT * 12 * 4;
-    L.off_misc = off; off += 1024;
+    L.off_s = off;  off += BKT * QT * 8;     // float2 scores, then (p, ds) half2 pairs
+    L.off_dp = off; off += BKT * QT * 8;     // float2 dO.v
+    L.off_idx = off; off += BKT * 2 * QT * 4;
+    L.off_yt = off; off += 2 * BKT * 16 * 2;
+    L.off_yc = off; off += BKT * 12 * 4;
+    L.off_misc = off; off += 1536;
     L.total = off;
     return L;
 }
@@ -83,14 +85,14 @@ __device__ __forceinline__ void load_table_a(const __half *tab, int R, int H, in
 // Projection GEMM  P^T[row][(voxel, head)] = T . F^T  for NT n-tiles of 4 voxels, written either in the
 // lane-major layout [row][32] (column = qpos(voxel)) or in the tile layout [voxel][Rp].
 template <int MTW, bool LANE_MAJOR>
-__device__ __forceinline__ void project(const uint32_t (&ta)[MTW][2][2], const __half *feat /*[nv][16]*/,
-                                        uint32_t *dst, int n_mt, int Rp, int wid, int g, int t)
+__device__ __forceinline__ void project(const uint32_t (&ta)[MTW][2][2], const __half *feat /*[32][16]*/,
+                                        uint32_t *dst, int n_mt, int Rp, int nvalid, int wid, int g, int t)
 {
-    constexpr int NT = LANE_MAJOR ? 8 : 4;
+    constexpr int NT = 8;
     uint32_t b[NT][2];
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
-        const uint32_t wv = *reinterpret_cast<const uint32_t *>(feat + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+        const uint32_t wv = 4 * j < nvalid ? *reinterpret_cast<const uint32_t *>(feat + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t) : 0u;
         b[j][0] = (g & 1) ? 0u : wv;
         b[j][1] = (g & 1) ? wv : 0u;
     }
@@ -100,8 +102,14 @@ __device__ __forceinline__ void project(const uint32_t (&ta)[MTW][2][2], const _
         if (mt < n_mt) {
             uint32_t d0[NT], d1[NT];
 #pragma unroll
-            for (int j = 0; j < NT; ++j)
-                mma_k16_h(d0[j], d1[j], ta[i][0][0], ta[i][0][1], ta[i][1][0], ta[i][1][1], b[j][0], b[j][1]);
+            for (int j = 0; j < NT; ++j) {
+                if (4 * j < nvalid) {   // n-tiles made of padding voxels only are not computed
+                    mma_k16_h(d0[j], d1[j], ta[i][0][0], ta[i][0][1], ta[i][1][0], ta[i][1][1], b[j][0], b[j][1]);
+                } else {
+                    d0[j] = 0u;
+                    d1[j] = 0u;
+                }
+            }
             if (LANE_MAJOR) {
                 uint32_t *r0 = dst + (mt * 16 + g) * QT + 4 * t;
                 *reinterpret_cast<uint4 *>(r0) = make_uint4(d0[0], d0[2], d0[4], d0[6]);
@@ -111,9 +119,11 @@ __device__ __forceinline__ void project(const uint32_t (&ta)[MTW][2][2], const _
             } else {
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
-                    uint32_t *p = dst + (4 * j + t) * Rp + mt * 16 + g;
-                    p[0] = d0[j];
-                    p[8] = d1[j];
+                    if (4 * j < nvalid) {
+                        uint32_t *p = dst + (4 * j + t) * Rp + mt * 16 + g;
+                        p[0] = d0[j];
+                        p[8] = d1[j];
+                    }
                 }
             }
         }
@@ -121,9 +131,10 @@ __device__ __forceinline__ void project(const uint32_t (&ta)[MTW][2][2], const _
 }
 
 // acc[head][m-tile] += E^T-tile . Y : rows = the 32 x of the item, k = the 16 y of the tile, E the
-// p (WHICH = 1) or ds (WHICH = 0) half of the (p, ds) entries s_pd[y][x]; Y the staged y rows [16][16].
+// p (WHICH = 1) or ds (WHICH = 0) half of the (p, ds) entries s_pd[y][x]; Y the staged y rows [32][16];
+// one call covers the 16 y starting at `ybase`.
 template <int WHICH>
-__device__ __forceinline__ void dx_gemm(float (&acc)[2][2][4], const uint2 *s_pd, const __half *ysrc, int g, int t)
+__device__ __forceinline__ void dx_gemm(float (&acc)[2][2][4], const uint2 *s_pd, const __half *ysrc, int ybase, int g, int t)
 {
     uint32_t fa[2][2][4];   // [head][m-tile][a0..a3]
 #pragma unroll
@@ -132,7 +143,7 @@ __device__ __forceinline__ void dx_gemm(float (&acc)[2][2][4], const uint2 *s_pd
         for (int kh = 0; kh < 2; ++kh)
 #pragma unroll
             for (int rr = 0; rr < 2; ++rr) {
-                const int xx = 16 * i + g + 8 * rr, ya = 2 * t + 8 * kh;
+                const int xx = 16 * i + g + 8 * rr, ya = ybase + 2 * t + 8 * kh;
                 const uint2 e0 = s_pd[ya * QT + xx], e1 = s_pd[(ya + 1) * QT + xx];
                 const uint32_t u = WHICH == 0 ? e0.y : e0.x, v2 = WHICH == 0 ? e1.y : e1.x;
                 fa[0][i][2 * kh + rr] = pack_lo(u, v2);
@@ -143,7 +154,7 @@ __device__ __forceinline__ void dx_gemm(float (&acc)[2][2][4], const uint2 *s_pd
         uint32_t yb[2];
 #pragma unroll
         for (int kh = 0; kh < 2; ++kh) {
-            const int ya = 2 * t + 8 * kh;
+            const int ya = ybase + 2 * t + 8 * kh;
             yb[kh] = h2_as_u32(__halves2half2(ysrc[ya * 16 + h * 8 + g], ysrc[(ya + 1) * 16 + h * 8 + g]));
         }
 #pragma unroll
@@ -156,24 +167,25 @@ template <int D, int MTW, int SIDE>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
 {
+    constexpr int BKT = bkt_of(SIDE);
     constexpr int NPX = SIDE == 0 ? 2 : 1;   // x-side projections: (P_q, dB) | (P_k)
     constexpr int NH = SIDE == 0 ? 2 : 1;    // x-side histograms:  (ds, p)   | (ds)
     constexpr int NPY = SIDE == 0 ? 1 : 2;   // y-side projections: (P_k)     | (P_q, dB)
     extern __shared__ __align__(16) unsigned char smem[];
-    const BwdSmem L = make_bwd_layout(meta.R, NPX, NH, NPY);
+    const BwdSmem L = make_bwd_layout(meta.R, NPX, NH, NPY, BKT);
     uint32_t *s_px = reinterpret_cast<uint32_t *>(smem + L.off_px);   // [NPX][R16][32]
     uint32_t *s_hx = reinterpret_cast<uint32_t *>(smem + L.off_hx);   // [NH][R16][32]
     uint32_t *s_py = reinterpret_cast<uint32_t *>(smem + L.off_py);   // [NPY][KT][Rp]
-    float2 *s_s = reinterpret_cast<float2 *>(smem + L.off_s);         // [KT][32]
+    float2 *s_s = reinterpret_cast<float2 *>(smem + L.off_s);         // [BKT][32]
     uint2 *s_pd = reinterpret_cast<uint2 *>(smem + L.off_s);          // same storage: (p, ds) half2 pairs
-    float2 *s_dp = reinterpret_cast<float2 *>(smem + L.off_dp);       // [KT][32]
-    uint32_t *s_idx = reinterpret_cast<uint32_t *>(smem + L.off_idx); // [KT][2][32]
-    __half *s_y0 = reinterpret_cast<__half *>(smem + L.off_yt);       // [KT][16]
-    __half *s_y1 = s_y0 + KT * 16;
-    float *s_yc = reinterpret_cast<float *>(smem + L.off_yc);         // [KT][12]
-    float *s_ylse = reinterpret_cast<float *>(smem + L.off_misc);     // [KT][2]   (SIDE 1)
-    float *s_ydel = s_ylse + 2 * KT;                                  // [KT][2]   (SIDE 1)
-    float *s_xlse = s_ydel + 2 * KT;                                  // [32][2]   (SIDE 0)
+    float2 *s_dp = reinterpret_cast<float2 *>(smem + L.off_dp);       // [BKT][32]
+    uint32_t *s_idx = reinterpret_cast<uint32_t *>(smem + L.off_idx); // [BKT][2][32]
+    __half *s_y0 = reinterpret_cast<__half *>(smem + L.off_yt);       // [BKT][16]
+    __half *s_y1 = s_y0 + BKT * 16;
+    float *s_yc = reinterpret_cast<float *>(smem + L.off_yc);         // [BKT][12]
+    float *s_ylse = reinterpret_cast<float *>(smem + L.off_misc);     // [BKT][2]  (SIDE 1)
+    float *s_ydel = s_ylse + 2 * BKT;                                 // [BKT][2]  (SIDE 1)
+    float *s_xlse = s_ydel + 2 * BKT;                                  // [32][2]   (SIDE 0)
     float *s_xdel = s_xlse + 64;                                      // [32][2]   (SIDE 0)
     int *s_xrow = reinterpret_cast<int *>(s_xdel + 64);               // [32]
     __half *s_x0 = reinterpret_cast<__half *>(smem + L.off_s);        // [32][16] aliases s_s (set-up only)
@@ -269,13 +281,14 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                 xdel[0] = s_xdel[lane * 2]; xdel[1] = s_xdel[lane * 2 + 1];
             }
             // block-diagonal B fragments of X0^T / X1^T for the n-tile this warp multiplies in S0 / dPV0
-            uint32_t xS[2];
-            {
-                const __half *src = (wid < 8) ? s_x0 : s_x1;
+            uint32_t xS[2][2];   // [X0 | X1][b0, b1] for n-tile wid % 8
+#pragma unroll
+            for (int a = 0; a < 2; ++a) {
+                const __half *src = a == 0 ? s_x0 : s_x1;
                 const int j = wid & 7;
                 const uint32_t wv = *reinterpret_cast<const uint32_t *>(src + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
-                xS[0] = (g & 1) ? 0u : wv;
-                xS[1] = (g & 1) ? wv : 0u;
+                xS[a][0] = (g & 1) ? 0u : wv;
+                xS[a][1] = (g & 1) ? wv : 0u;
             }
             // B fragments (k = position, n = channel) of X0 / X1 for the table-gradient GEMMs
             uint32_t xTB[NH][2][2][2];   // [hist][k-step][head][b0,b1]
@@ -294,8 +307,8 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                             xTB[a][ks][h][half] = h2_as_u32(__halves2half2(src[xa * 16 + h * 8 + g], src[xb * 16 + h * 8 + g]));
                         }
             }
-            project<MTW, true>(ta_px0, s_x0, s_px, n_mt, Rp, wid, g, t);
-            if (SIDE == 0) project<MTW, true>(ta_px1, s_x1, s_px + pxw, n_mt, Rp, wid, g, t);
+            project<MTW, true>(ta_px0, s_x0, s_px, n_mt, Rp, nx, wid, g, t);
+            if (SIDE == 0) project<MTW, true>(ta_px1, s_x1, s_px + pxw, n_mt, Rp, nx, wid, g, t);
 
             float dxacc[2][2][2][4];   // [which: ds.Y0 | p.Y1][head][m-tile][c-frag], warps 15 / 14
 #pragma unroll
@@ -305,11 +318,11 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
 #pragma unroll
                     for (int i = 0; i < 2; ++i) dxacc[a][h][i][0] = dxacc[a][h][i][1] = dxacc[a][h][i][2] = dxacc[a][h][i][3] = 0.f;
 
-            for (int y0 = 0; y0 < n; y0 += KT) {
-                const int ny = min(KT, n - y0);
+            for (int y0 = 0; y0 < n; y0 += BKT) {
+                const int ny = min(BKT, n - y0);
                 __syncthreads();
                 // ---- stage the y tile ---------------------------------------------------------------
-                if (tid < 64) {
+                if (tid < 4 * BKT) {
                     const int yi = tid >> 2, which = (tid >> 1) & 1, hf = tid & 1;
                     uint4 val = make_uint4(0, 0, 0, 0);
                     float del = 0.f, ls = 0.f;
@@ -334,31 +347,40 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                         s_ylse[yi * 2 + hf] = ls;
                     }
                     *reinterpret_cast<uint4 *>((which ? s_y1 : s_y0) + yi * 16 + hf * 8) = val;
-                } else if (tid < 64 + KT * D) {
-                    const int e = tid - 64, yi = e / D, d = e - yi * D;
+                } else if (tid < 4 * BKT + BKT * D) {
+                    const int e = tid - 4 * BKT, yi = e / D, d = e - yi * D;
                     s_yc[yi * 12 + d] = yi < ny ? __ldg(P.n_coords + (int64_t)(base + y0 + yi) * D + d) : 0.f;
                 }
                 __syncthreads();
-                // ---- y-side projections, S0 = Y0 . X0^T (warps 0-7), dPV0 = Y1 . X1^T (warps 8-15) -------
-                project<MTW, false>(ta_py0, s_y0, s_py, n_mt, Rp, wid, g, t);
-                if (SIDE == 1) project<MTW, false>(ta_py1, s_y1, s_py + pyw, n_mt, Rp, wid, g, t);
+                // ---- y-side projections; S0 = Y0 . X0^T and dPV0 = Y1 . X1^T, one (m-tile, n-tile) per warp ----
+                project<MTW, false>(ta_py0, s_y0, s_py, n_mt, Rp, ny, wid, g, t);
+                if (SIDE == 1) project<MTW, false>(ta_py1, s_y1, s_py + pyw, n_mt, Rp, ny, wid, g, t);
                 {
-                    const __half *ysrc = (wid < 8) ? s_y0 : s_y1;
-                    const uint32_t a0 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 2 * t);
-                    const uint32_t a1 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 2 * t);
-                    const uint32_t a2 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 8 + 2 * t);
-                    const uint32_t a3 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 8 + 2 * t);
-                    float c[4];
-                    mma_k16_z(c, a0, a1, a2, a3, xS[0], xS[1]);
-                    float2 *dst = (wid < 8) ? s_s : s_dp;
-                    const int j = wid & 7;
-                    dst[g * QT + 4 * j + t] = make_float2(c[0], c[1]);
-                    dst[(g + 8) * QT + 4 * j + t] = make_float2(c[2], c[3]);
+                    constexpr int PER = (BKT / 16) * 8;     // (m-tile, n-tile) units per product
+#pragma unroll
+                    for (int u0 = 0; u0 < 2 * PER; u0 += BW_NWARP) {
+                        const int u = u0 + wid;
+                        const int a = u / PER, r = u % PER, mt = r >> 3, j = r & 7;   // y rows 16mt.., x columns 4j..
+                        if (16 * mt < ny && 4 * j < nx) {
+                            const __half *ysrc = (a == 0 ? s_y0 : s_y1) + mt * 16 * 16;
+                            const uint32_t a0 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 2 * t);
+                            const uint32_t a1 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 2 * t);
+                            const uint32_t a2 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 8 + 2 * t);
+                            const uint32_t a3 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 8 + 2 * t);
+                            float c[4];
+                            if (a == 0) mma_k16_z(c, a0, a1, a2, a3, xS[0][0], xS[0][1]);
+                            else mma_k16_z(c, a0, a1, a2, a3, xS[1][0], xS[1][1]);
+                            float2 *dst = (a == 0 ? s_s : s_dp) + mt * 16 * QT;
+                            dst[g * QT + 4 * j + t] = make_float2(c[0], c[1]);
+                            dst[(g + 8) * QT + 4 * j + t] = make_float2(c[2], c[3]);
+                        }
+                    }
                 }
                 __syncthreads();
-                // ---- phase 1: one y per warp, lane = x: indices, 3*D look-ups, p and ds -----------------
-                {
-                    const int yy = wid;
+                // ---- phase 1: BKT/16 y per warp, lane = x: indices, 3*D look-ups, p and ds -------------
+#pragma unroll
+                for (int y2 = 0; y2 < BKT / BW_NWARP; ++y2) {
+                    const int yy = (BKT / BW_NWARP) * wid + y2;
                     uint2 pd = make_uint2(0u, 0u);
                     if (yy < ny) {
                         __half2 b0 = __float2half2_rn(0.f), b1 = b0, b2 = b0;
@@ -387,34 +409,45 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                         else { ls0 = s_ylse[yy * 2]; ls1 = s_ylse[yy * 2 + 1]; de0 = s_ydel[yy * 2]; de1 = s_ydel[yy * 2 + 1]; }
                         float p0 = exp2f((s0.x + bs.x - ls0) * LOG2E);
                         float p1 = exp2f((s0.y + bs.y - ls1) * LOG2E);
-                        if (lane >= nx) { p0 = 0.f; p1 = 0.f; }
-                        const float ds0 = p0 * (dp0.x + bd.x - de0);
-                        const float ds1 = p1 * (dp0.y + bd.y - de1);
+                        float ds0 = p0 * (dp0.x + bd.x - de0);
+                        float ds1 = p1 * (dp0.y + bd.y - de1);
+                        if (lane >= nx) { p0 = 0.f; p1 = 0.f; ds0 = 0.f; ds1 = 0.f; }   // padding lanes hold no voxel
                         pd.x = h2_as_u32(__floats2half2_rn(p0, p1));
                         pd.y = h2_as_u32(__floats2half2_rn(ds0, ds1));
                     }
                     s_pd[yy * QT + lane] = pd;   // replaces the score; zero for padded y
                 }
                 __syncthreads();
-                // ---- phase 2: histogram updates, one signal dimension per warp ---------------------------
+                // ---- phase 2: histogram updates, one signal dimension per warp, four y per step ----------
                 if (wid < D) {
                     const int d = wid;
                     const int wsel = d / 5, sh = IDX_BITS * (d % 5);
                     const int rb = meta.rowbase[d];
-                    for (int yy = 0; yy < ny; ++yy) {
-                        const uint2 pd = s_pd[yy * QT + lane];
-                        const int idx = (s_idx[(yy * 2 + wsel) * QT + lane] >> sh) & ((1 << IDX_BITS) - 1);
-                        uint32_t *cell = s_hx + (rb + idx) * QT + mypos;
-                        *cell = h2_as_u32(__hadd2(u32_as_h2(*cell), u32_as_h2(pd.y)));
-                        if (SIDE == 0) {
-                            uint32_t *cell1 = cell + pxw;
-                            *cell1 = h2_as_u32(__hadd2(u32_as_h2(*cell1), u32_as_h2(pd.x)));
+                    uint32_t *cell = s_hx + mypos;
+                    for (int y4 = 0; y4 < ny; y4 += 4) {
+                        uint32_t vals[NH][4];
+                        int off[1][4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int yy = y4 + j;
+                            const uint2 pd = s_pd[yy * QT + lane];            // zero for padded y
+                            vals[0][j] = pd.y;                                 // ds -> H0
+                            if (NH == 2) vals[NH - 1][j] = pd.x;               // p  -> H1
+                            const int idx = yy < ny ? (s_idx[(yy * 2 + wsel) * QT + lane] >> sh) & ((1 << IDX_BITS) - 1) : 0;
+                            off[0][j] = (rb + idx) * QT;
                         }
+                        hist_add4<1, NH>(cell, pxw, off, vals);
                     }
                 }
                 // ---- dX += dS^T-tile . Y0 (warp 15) ; SIDE 1: dX1 += P^T-tile . Y1 (warp 14), tensor cores ----
-                if (wid == BW_NWARP - 1) dx_gemm<0>(dxacc[0], s_pd, s_y0, g, t);
-                if (SIDE == 1 && wid == BW_NWARP - 2) dx_gemm<1>(dxacc[1], s_pd, s_y1, g, t);
+                if (wid == BW_NWARP - 1) {
+                    dx_gemm<0>(dxacc[0], s_pd, s_y0, 0, g, t);
+                    if (BKT > 16 && ny > 16) dx_gemm<0>(dxacc[0], s_pd, s_y0, 16, g, t);
+                }
+                if (SIDE == 1 && wid == BW_NWARP - 2) {
+                    dx_gemm<1>(dxacc[1], s_pd, s_y1, 0, g, t);
+                    if (BKT > 16 && ny > 16) dx_gemm<1>(dxacc[1], s_pd, s_y1, 16, g, t);
+                }
             }  // y tiles
             __syncthreads();
             // ---- table gradients: dT[a][row][c] += sum_x H_a[row][x] X_a[x][c] --------------------------------
@@ -513,7 +546,7 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
 template <int D, int MTW, int SIDE>
 static int launch_side(const BwdParams &p, const CrseMeta &meta, cudaStream_t st)
 {
-    const BwdSmem L = make_bwd_layout(meta.R, SIDE == 0 ? 2 : 1, SIDE == 0 ? 2 : 1, SIDE == 0 ? 1 : 2);
+    const BwdSmem L = make_bwd_layout(meta.R, SIDE == 0 ? 2 : 1, SIDE == 0 ? 2 : 1, SIDE == 0 ? 1 : 2, bkt_of(SIDE));
     auto kern = attn_bwd_tc_kernel<D, MTW, SIDE>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total) != cudaSuccess)
         return S3D_ERR_LAUNCH;
@@ -564,8 +597,8 @@ bool attn_tc_bwd_supported(const AttnArgs &a)
     if (a.meta.R > 16 * tc::BW_NWARP * 2) return false;
     for (int d = 0; d < a.meta.D; ++d)
         if (a.meta.L[d] >= (1 << tc::IDX_BITS)) return false;
-    if (tc::make_bwd_layout(a.meta.R, 2, 2, 1).total > 227 * 1024) return false;
-    if (tc::make_bwd_layout(a.meta.R, 1, 1, 2).total > 227 * 1024) return false;
+    if (tc::make_bwd_layout(a.meta.R, 2, 2, 1, tc::bkt_of(0)).total > 227 * 1024) return false;
+    if (tc::make_bwd_layout(a.meta.R, 1, 1, 2, tc::bkt_of(1)).total > 227 * 1024) return false;
     return true;
 }
 

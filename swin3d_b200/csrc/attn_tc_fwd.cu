@@ -7,8 +7,8 @@
 //   GEMM    P_k = K.Tk^T (this tile's keys), S0 = K.Q^T                          [tensor cores]
 //   phase 1 lane = query, each warp two keys: cRSE indices, 2*D look-ups, score, running max
 //   phase 1.5 probabilities p = exp(s - m), row sums
-//   phase 2 one signal dimension per warp: hist[row][q] += p      (no atomics: rows of different
-//           dimensions are disjoint and a warp owns its dimension)      | warp 7: O += P.V [tc]
+//   phase 2 one or two signal dimensions per warp: hist[row][q] += p, four keys per step (no atomics:
+//           rows of different dimensions are disjoint, a warp owns its dimensions) | warp 7: O += P.V [tc]
 // and per item:  P_q = Q.Tq^T before, O += hist.Tv after                        [tensor cores]
 // See attn_tc.cuh for the factorisation and the shared-memory layouts.
 #include "attn_kernels.cuh"
@@ -279,18 +279,40 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                     }
                     __syncthreads();
                 }
-                // ---- phase 2: histogram update, one signal dimension per warp -------------------------
+                // ---- phase 2: histogram update; a warp owns one or two signal dimensions ----------------
+                {
+                    int dA = -1, dB = -1;
+                    if (D <= NWARP - 1) {
+                        if (wid < D) dA = wid;
+                    } else if (wid < D - 5) {
+                        dA = wid; dB = wid + 5;     // one index field from each packed word
+                    } else if (wid < 5) {
+                        dA = wid;
+                    }
+                    if (dA >= 0) {
+                        const int shA = IDX_BITS * (dA % 5), wA = dA / 5, rbA = meta.rowbase[dA];
+                        const int shB = dB >= 0 ? IDX_BITS * (dB % 5) : 0, wB = dB >= 0 ? dB / 5 : 0;
+                        const int rbB = dB >= 0 ? meta.rowbase[dB] : 0;
+                        uint32_t *cell = s_hist + mypos;
+                        for (int kk0 = 0; kk0 < nk; kk0 += 4) {
+                            uint32_t pv[1][4];
+                            int off2[2][4];
 #pragma unroll
-                for (int rep = 0; rep < 2; ++rep) {
-                    const int d = wid + NWARP * rep;
-                    if (d < D) {
-                        const int wsel = d / 5, sh = IDX_BITS * (d % 5);
-                        const int rb = meta.rowbase[d];
-                        for (int kk = 0; kk < nk; ++kk) {
-                            const uint32_t ph = reinterpret_cast<const uint32_t *>(s_s + kk * QT + lane)[0];
-                            const int idx = (s_idx[(kk * 2 + wsel) * QT + lane] >> sh) & ((1 << IDX_BITS) - 1);
-                            uint32_t *cell = s_hist + (rb + idx) * QT + mypos;
-                            *cell = h2_as_u32(__hadd2(u32_as_h2(*cell), u32_as_h2(ph)));
+                            for (int j = 0; j < 4; ++j) {
+                                const int kk = kk0 + j;
+                                pv[0][j] = reinterpret_cast<const uint32_t *>(s_s + kk * QT + lane)[0];   // 0 for padded keys
+                                const bool ok = kk < nk;
+                                const int ia = ok ? (s_idx[(kk * 2 + wA) * QT + lane] >> shA) & ((1 << IDX_BITS) - 1) : 0;
+                                off2[0][j] = (rbA + ia) * QT;
+                                const int ib = (ok && dB >= 0) ? (s_idx[(kk * 2 + wB) * QT + lane] >> shB) & ((1 << IDX_BITS) - 1) : 0;
+                                off2[1][j] = (rbB + ib) * QT;
+                            }
+                            if (dB >= 0) {
+                                hist_add4<2, 1>(cell, 0, off2, pv);
+                            } else {
+                                int off1[1][4] = {{off2[0][0], off2[0][1], off2[0][2], off2[0][3]}};
+                                hist_add4<1, 1>(cell, 0, off1, pv);
+                            }
                         }
                     }
                 }
