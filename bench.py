@@ -331,7 +331,7 @@ def run_attention(args):
         "dtype": "f16 storage, f32 accumulate", "data": "synthetic", "config": workload_config(),
         "voxels_per_gpu": N, "pairs_per_gpu": M, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
         "window_build_ms": wb_ms,
-        "roofline": {"bound": "hbm", "kernel": "attention backward", "achieved": bwd_gbs, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "attention backward (query sweep + key sweep launches)", "achieved": bwd_gbs, "peak": peak,
                      "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": traffic, "peak_source": peak_src,
                      "algorithmic_bytes_per_voxel": {"fwd": pv_fwd, "bwd": pv_bwd},
                      "fwd": {"achieved": fwd_gbs, "frac": fwd_gbs / peak},
@@ -340,7 +340,7 @@ def run_attention(args):
         "e2e": {"value": n_total / (e2e_ms * 1e-3), "unit": "voxels/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 4 * N * Cc * 2,
                 "d2h_bytes_per_step": 4 * N * Cc * 2 + 3 * sum(sizes) * 4},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": 3 * args.steps,   # forward + backward query sweep + backward key sweep
         "clocks": clocks,
     }
     print(json.dumps(line))
