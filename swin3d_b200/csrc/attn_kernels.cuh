@@ -32,5 +32,7 @@ bool attn_tc_supported(const AttnArgs &a);
 int attn_tc_forward(const AttnArgs &a, cudaStream_t st);
 bool attn_tc_bwd_supported(const AttnArgs &a);
 int attn_tc_backward(const AttnArgs &a, cudaStream_t st);   // dtq/dtk/dtv zeroed by the caller
+bool attn_tc_bwd_small_supported(const AttnArgs &a);          // attn_tc_bwd_small.cu: windows <= 32 voxels
+int attn_tc_backward_small(const AttnArgs &a, cudaStream_t st);
 
 }  // namespace s3d

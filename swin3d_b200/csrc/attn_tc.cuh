@@ -94,14 +94,38 @@ __device__ __forceinline__ void atomic_max_float(float *addr, float v)
         atomicMin(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
 }
 
+// Internal row numbering.  The reference's flat table addressing lets index L of signal dimension n
+// fall on row 0 of dimension n+1.  Inside the kernels every dimension but the last therefore owns
+// L+1 rows (its own L plus a private alias of the next dimension's row 0), so that the rows of
+// different dimensions are disjoint and can be updated by different warps without a race.
+// internal_meta() shifts rowbase[n] by n and grows R by D-1; table_row() maps an internal row back
+// to the table row it stands for (two internal rows may name the same table row), -1 past the end.
+__host__ inline CrseMeta internal_meta(const CrseMeta &m)
+{
+    CrseMeta r = m;
+    for (int d = 0; d < m.D; ++d) r.rowbase[d] = m.rowbase[d] + d;
+    r.R = m.R + m.D - 1;
+    return r;
+}
+
+__device__ __forceinline__ int table_row(const CrseMeta &im, int r)
+{
+    int n = 0;
+#pragma unroll
+    for (int d = 1; d < S3D_MAX_SIGNAL_DIMS; ++d) n += (d < im.D && r >= im.rowbase[d]) ? 1 : 0;
+    return r < im.R ? r - n : -1;
+}
+
 // Histogram update  hist[a][row_j] += v[a][j]  for four voxels j of a tile at once, for NDIM signal
 // dimensions (disjoint row ranges) and NARR histograms sharing the row index.  All loads are issued
 // before any store, so the shared-memory latency is paid once per group instead of once per voxel;
 // equal rows inside a group are chained in registers (later voxel wins the store, carrying the sum).
 // `cell` points at this lane's column of histogram 0; `off[d][j]` = row * QT (words).
+// Only the first `cnt` voxels of the group exist; the others are neither loaded into the chain nor
+// stored (a dummy store could overwrite a concurrent update of an aliased row by another warp).
 template <int NDIM, int NARR>
 __device__ __forceinline__ void hist_add4(uint32_t *cell, int arr_stride, const int (&off)[NDIM][4],
-                                          const uint32_t (&v)[NARR][4])
+                                          const uint32_t (&v)[NARR][4], int cnt)
 {
     uint32_t c[NDIM][NARR][4];
 #pragma unroll
@@ -130,7 +154,8 @@ __device__ __forceinline__ void hist_add4(uint32_t *cell, int arr_stride, const 
 #pragma unroll
         for (int a = 0; a < NARR; ++a)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) cell[a * arr_stride + off[d][j]] = c[d][a][j];
+            for (int j = 0; j < 4; ++j)
+                if (j < cnt) cell[a * arr_stride + off[d][j]] = c[d][a][j];
 }
 
 // Shared-memory carve-up (byte offsets) for a table of R rows.

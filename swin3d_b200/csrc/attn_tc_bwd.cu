@@ -62,11 +62,12 @@ struct BwdParams {
     const float *n_coords;
     int64_t W;
     int H;
+    int skip_upto;   // windows with at most this many voxels are left to the single-sweep kernel
 };
 
 // A-operand fragments (m16 x k16, both heads on K) of a table slice for the row tiles this warp owns.
 template <int MTW>
-__device__ __forceinline__ void load_table_a(const __half *tab, int R, int H, int hp, int wid, int g, int t,
+__device__ __forceinline__ void load_table_a(const __half *tab, const CrseMeta &im, int H, int hp, int wid, int g, int t,
                                              uint32_t (&a)[MTW][2][2])
 {
 #pragma unroll
@@ -75,9 +76,9 @@ __device__ __forceinline__ void load_table_a(const __half *tab, int R, int H, in
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int hh = 2 * hp + h;
-            const int r0 = mt * 16 + g, r1 = r0 + 8;
-            a[i][h][0] = r0 < R ? *reinterpret_cast<const uint32_t *>(tab + ((int64_t)r0 * H + hh) * 8 + 2 * t) : 0u;
-            a[i][h][1] = r1 < R ? *reinterpret_cast<const uint32_t *>(tab + ((int64_t)r1 * H + hh) * 8 + 2 * t) : 0u;
+            const int r0 = table_row(im, mt * 16 + g), r1 = table_row(im, mt * 16 + g + 8);
+            a[i][h][0] = r0 >= 0 ? *reinterpret_cast<const uint32_t *>(tab + ((int64_t)r0 * H + hh) * 8 + 2 * t) : 0u;
+            a[i][h][1] = r1 >= 0 ? *reinterpret_cast<const uint32_t *>(tab + ((int64_t)r1 * H + hh) * 8 + 2 * t) : 0u;
         }
     }
 }
@@ -197,17 +198,17 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
     const int g = lane >> 2, t = lane & 3;
     const int hp = blockIdx.y, H = P.H;
     const int HC = H * 8, co = hp * 16;
-    const int R = meta.R, n_mt = L.R16 / 16, Rp = L.Rp;
+    const int n_mt = L.R16 / 16, Rp = L.Rp;
     const int pxw = L.px_stride / 4, pyw = L.py_stride / 4;
     const int mypos = qpos(lane);
     constexpr float LOG2E = 1.4426950408889634f;
 
     // ---- resident table fragments --------------------------------------------------------------------
     uint32_t ta_px0[MTW][2][2], ta_px1[MTW][2][2], ta_py0[MTW][2][2], ta_py1[MTW][2][2];
-    load_table_a<MTW>(P.t_px0, R, H, hp, wid, g, t, ta_px0);
-    load_table_a<MTW>(P.t_py0, R, H, hp, wid, g, t, ta_py0);
-    if (SIDE == 0) load_table_a<MTW>(P.t_px1, R, H, hp, wid, g, t, ta_px1);
-    else load_table_a<MTW>(P.t_py1, R, H, hp, wid, g, t, ta_py1);
+    load_table_a<MTW>(P.t_px0, meta, H, hp, wid, g, t, ta_px0);
+    load_table_a<MTW>(P.t_py0, meta, H, hp, wid, g, t, ta_py0);
+    if (SIDE == 0) load_table_a<MTW>(P.t_px1, meta, H, hp, wid, g, t, ta_px1);
+    else load_table_a<MTW>(P.t_py1, meta, H, hp, wid, g, t, ta_py1);
     // B fragments (k = row, n = channel) of T0 for dX += H0 . T0
     uint32_t t0B[MTW][2][2];
 #pragma unroll
@@ -217,10 +218,10 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
         for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const int ra = ks * 16 + 2 * t + 8 * half, rb = ra + 1;
+                const int ra = table_row(meta, ks * 16 + 2 * t + 8 * half), rb = table_row(meta, ks * 16 + 2 * t + 8 * half + 1);
                 const int hh = 2 * hp + h;
-                const __half lo = ra < R ? P.t_px0[((int64_t)ra * H + hh) * 8 + g] : __float2half(0.f);
-                const __half hi = rb < R ? P.t_px0[((int64_t)rb * H + hh) * 8 + g] : __float2half(0.f);
+                const __half lo = ra >= 0 ? P.t_px0[((int64_t)ra * H + hh) * 8 + g] : __float2half(0.f);
+                const __half hi = rb >= 0 ? P.t_px0[((int64_t)rb * H + hh) * 8 + g] : __float2half(0.f);
                 t0B[i][h][half] = h2_as_u32(__halves2half2(lo, hi));
             }
     }
@@ -235,6 +236,7 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
 
     for (int64_t w = blockIdx.x; w < P.W; w += gridDim.x) {
         const int n = __ldg(P.w_sizes + w);
+        if (n <= P.skip_upto) continue;
         const int base = __ldg(P.w2n + w);
         for (int x0 = 0; x0 < n; x0 += QT) {
             const int nx = min(QT, n - x0);
@@ -436,7 +438,7 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                             const int idx = yy < ny ? (s_idx[(yy * 2 + wsel) * QT + lane] >> sh) & ((1 << IDX_BITS) - 1) : 0;
                             off[0][j] = (rb + idx) * QT;
                         }
-                        hist_add4<1, NH>(cell, pxw, off, vals);
+                        hist_add4<1, NH>(cell, pxw, off, vals, ny - y4);
                     }
                 }
                 // ---- dX += dS^T-tile . Y0 (warp 15) ; SIDE 1: dX1 += P^T-tile . Y1 (warp 14), tensor cores ----
@@ -532,8 +534,8 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
             for (int h = 0; h < 2; ++h)
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr) {
-                    const int row = mt * 16 + g + 8 * rr;
-                    if (mt < n_mt && row < R) {
+                    const int row = table_row(meta, mt * 16 + g + 8 * rr);   // aliases flush into the row they stand for
+                    if (mt < n_mt && row >= 0) {
                         float *p = dst + ((int64_t)row * H + 2 * hp + h) * 8 + 2 * t;
                         atomicAdd(p, dt_acc[a][i][h][2 * rr]);
                         atomicAdd(p + 1, dt_acc[a][i][h][2 * rr + 1]);
@@ -565,9 +567,10 @@ static int launch_side(const BwdParams &p, const CrseMeta &meta, cudaStream_t st
 }
 
 template <int D, int MTW>
-static int launch_both(const AttnArgs &a, cudaStream_t st)
+static int launch_both(const AttnArgs &a, int skip_upto, cudaStream_t st)
 {
     BwdParams pq{};
+    pq.skip_upto = skip_upto;
     pq.x0 = (const __half *)a.q;   pq.x1 = (const __half *)a.dout;
     pq.y0 = (const __half *)a.k;   pq.y1 = (const __half *)a.v;
     pq.o = (const __half *)a.out;  pq.lse = a.lse;
@@ -594,24 +597,33 @@ static int launch_both(const AttnArgs &a, cudaStream_t st)
 bool attn_tc_bwd_supported(const AttnArgs &a)
 {
     if (a.dtype != S3D_F16 || a.hd != 8 || (a.H & 1)) return false;
-    if (a.meta.R > 16 * tc::BW_NWARP * 2) return false;
+    const int Rint = a.meta.R + a.meta.D - 1;
+    if (Rint > 16 * tc::BW_NWARP * 2) return false;
     for (int d = 0; d < a.meta.D; ++d)
         if (a.meta.L[d] >= (1 << tc::IDX_BITS)) return false;
-    if (tc::make_bwd_layout(a.meta.R, 2, 2, 1, tc::bkt_of(0)).total > 227 * 1024) return false;
-    if (tc::make_bwd_layout(a.meta.R, 1, 1, 2, tc::bkt_of(1)).total > 227 * 1024) return false;
+    if (tc::make_bwd_layout(Rint, 2, 2, 1, tc::bkt_of(0)).total > 227 * 1024) return false;
+    if (tc::make_bwd_layout(Rint, 1, 1, 2, tc::bkt_of(1)).total > 227 * 1024) return false;
     return true;
 }
 
 // dtq, dtk, dtv must be zero on entry (the kernels accumulate into them).
-int attn_tc_backward(const AttnArgs &a, cudaStream_t st)
+int attn_tc_backward(const AttnArgs &a0, cudaStream_t st)
 {
-    if (a.W == 0) return S3D_OK;
+    if (a0.W == 0) return S3D_OK;
+    AttnArgs a = a0;
+    a.meta = tc::internal_meta(a0.meta);   // kernels work in the internal row numbering
+    int skip_upto = 0;
+    if (attn_tc_bwd_small_supported(a0)) {
+        const int rc = attn_tc_backward_small(a0, st);
+        if (rc != S3D_OK) return rc;
+        skip_upto = tc::QT;
+    }
     const int n_mt = (a.meta.R + 15) / 16;
     const int mtw = (n_mt + tc::BW_NWARP - 1) / tc::BW_NWARP;
 #define S3D_TC_BWD(DD)                                            \
     switch (mtw) {                                                \
-        case 1: return tc::launch_both<DD, 1>(a, st);             \
-        case 2: return tc::launch_both<DD, 2>(a, st);             \
+        case 1: return tc::launch_both<DD, 1>(a, skip_upto, st);  \
+        case 2: return tc::launch_both<DD, 2>(a, skip_upto, st);  \
         default: return S3D_ERR_UNSUPPORTED;                      \
     }
     switch (a.meta.D) {

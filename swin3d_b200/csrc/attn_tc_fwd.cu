@@ -48,7 +48,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
     const int g = lane >> 2, t = lane & 3;
     const int hp = blockIdx.y;
     const int HC = H * 8, co = hp * 16;
-    const int R = meta.R, n_mt = L.R16 / 16, Rp = L.Rp;
+    const int n_mt = L.R16 / 16, Rp = L.Rp;
     const int mypos = qpos(lane);
     constexpr float LOG2E = 1.4426950408889634f;
 
@@ -60,16 +60,16 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int hh = 2 * hp + h;
-            const int r0 = mt * 16 + g, r1 = r0 + 8;
-            tqA[i][h][0] = r0 < R ? *reinterpret_cast<const uint32_t *>(tq + ((int64_t)r0 * H + hh) * 8 + 2 * t) : 0u;
-            tqA[i][h][1] = r1 < R ? *reinterpret_cast<const uint32_t *>(tq + ((int64_t)r1 * H + hh) * 8 + 2 * t) : 0u;
-            tkA[i][h][0] = r0 < R ? *reinterpret_cast<const uint32_t *>(tk + ((int64_t)r0 * H + hh) * 8 + 2 * t) : 0u;
-            tkA[i][h][1] = r1 < R ? *reinterpret_cast<const uint32_t *>(tk + ((int64_t)r1 * H + hh) * 8 + 2 * t) : 0u;
+            const int t0 = table_row(meta, mt * 16 + g), t1 = table_row(meta, mt * 16 + g + 8);
+            tqA[i][h][0] = t0 >= 0 ? *reinterpret_cast<const uint32_t *>(tq + ((int64_t)t0 * H + hh) * 8 + 2 * t) : 0u;
+            tqA[i][h][1] = t1 >= 0 ? *reinterpret_cast<const uint32_t *>(tq + ((int64_t)t1 * H + hh) * 8 + 2 * t) : 0u;
+            tkA[i][h][0] = t0 >= 0 ? *reinterpret_cast<const uint32_t *>(tk + ((int64_t)t0 * H + hh) * 8 + 2 * t) : 0u;
+            tkA[i][h][1] = t1 >= 0 ? *reinterpret_cast<const uint32_t *>(tk + ((int64_t)t1 * H + hh) * 8 + 2 * t) : 0u;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const int ra = mt * 16 + 2 * t + 8 * half, rb = ra + 1;
-                const __half lo = ra < R ? tv[((int64_t)ra * H + hh) * 8 + g] : __float2half(0.f);
-                const __half hi = rb < R ? tv[((int64_t)rb * H + hh) * 8 + g] : __float2half(0.f);
+                const int ra = table_row(meta, mt * 16 + 2 * t + 8 * half), rb = table_row(meta, mt * 16 + 2 * t + 8 * half + 1);
+                const __half lo = ra >= 0 ? tv[((int64_t)ra * H + hh) * 8 + g] : __float2half(0.f);
+                const __half hi = rb >= 0 ? tv[((int64_t)rb * H + hh) * 8 + g] : __float2half(0.f);
                 tvB[i][h][half] = h2_as_u32(__halves2half2(lo, hi));
             }
         }
@@ -308,10 +308,10 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                                 off2[1][j] = (rbB + ib) * QT;
                             }
                             if (dB >= 0) {
-                                hist_add4<2, 1>(cell, 0, off2, pv);
+                                hist_add4<2, 1>(cell, 0, off2, pv, nk - kk0);
                             } else {
                                 int off1[1][4] = {{off2[0][0], off2[0][1], off2[0][2], off2[0][3]}};
-                                hist_add4<1, 1>(cell, 0, off1, pv);
+                                hist_add4<1, 1>(cell, 0, off1, pv, nk - kk0);
                             }
                         }
                     }
@@ -449,16 +449,19 @@ static int launch(const AttnArgs &a, cudaStream_t st)
 bool attn_tc_supported(const AttnArgs &a)
 {
     if (a.dtype != S3D_F16 || a.hd != 8 || (a.H & 1)) return false;
-    if (a.meta.R > 16 * tc::NWARP * 3) return false;
+    const int Rint = a.meta.R + a.meta.D - 1;
+    if (Rint > 16 * tc::NWARP * 3) return false;
     for (int d = 0; d < a.meta.D; ++d)
         if (a.meta.L[d] >= (1 << tc::IDX_BITS)) return false;   // idx may reach L
-    if (tc::make_layout(a.meta.R, 1).total > 227 * 1024) return false;
+    if (tc::make_layout(Rint, 1).total > 227 * 1024) return false;
     return true;
 }
 
-int attn_tc_forward(const AttnArgs &a, cudaStream_t st)
+int attn_tc_forward(const AttnArgs &a0, cudaStream_t st)
 {
-    if (a.W == 0) return S3D_OK;
+    if (a0.W == 0) return S3D_OK;
+    AttnArgs a = a0;
+    a.meta = tc::internal_meta(a0.meta);   // kernels work in the internal row numbering
     const int n_mt = (a.meta.R + 15) / 16;
     const int mtw = (n_mt + tc::NWARP - 1) / tc::NWARP;
 #define S3D_TC_FWD(DD)                                            \
