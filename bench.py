@@ -406,8 +406,11 @@ def run_knn(args):
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / args.steps
-        res[f"K{K}"] = {"ms": ms, "queries_per_s": qry.shape[0] / (ms * 1e-3),
-                        "pair_evals_per_s": 8 * 200_000 * 50_000 / (ms * 1e-3)}
+        evals = 8 * 200_000 * 50_000 / (ms * 1e-3)
+        # 8 fp32 operations per candidate (3 sub, 1 mul, 2 fma); nominal CUDA-core peak of a B200:
+        # 148 SMs x 128 lanes x 2 x 1.965 GHz = 74.4 TFLOP/s (no measured figure is recorded)
+        res[f"K{K}"] = {"ms": ms, "queries_per_s": qry.shape[0] / (ms * 1e-3), "pair_evals_per_s": evals,
+                        "fp32_tflops": evals * 8 / 1e12, "frac_of_nominal_fp32_peak": evals * 8 / 74.4e12}
     if rank == 0:
         print(json.dumps({"metric": "knn queries/sec (8 scenes x 200k queries x 50k sources)",
                           "unit": "queries/s", "value": res["K16"]["queries_per_s"], "detail": res,

@@ -96,7 +96,30 @@ knn_kernel(int K, const float *__restrict__ src, const float *__restrict__ query
         __syncthreads();
         // clip the tile to this thread's own scene
         const int jb = max(s0 - t0, 0), je = min(s1 - t0, cnt);
-        for (int j = jb; j < je; ++j) {
+        int j = jb;
+        // eight candidates per step: one test for "none is closer than the heap root" (the common
+        // case); otherwise the eight are offered to the heap one by one, in index order
+        for (; j + 8 <= je; j += 8) {
+            float dd[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float4 p = s_pts[j + u];
+                dd[u] = knn_dist2(p.x - qx, p.y - qy, p.z - qz);
+            }
+            const float m = fminf(fminf(fminf(dd[0], dd[1]), fminf(dd[2], dd[3])),
+                                  fminf(fminf(dd[4], dd[5]), fminf(dd[6], dd[7])));
+            if (m < top) {
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (dd[u] < top) {
+                        heap[0] = dd[u];
+                        hidx[0] = t0 + j + u;
+                        knn_sift_down(heap, hidx, 0, K);
+                        top = heap[0];
+                    }
+            }
+        }
+        for (; j < je; ++j) {
             const float4 p = s_pts[j];
             const float d = knn_dist2(p.x - qx, p.y - qy, p.z - qz);
             if (d < top) {
