@@ -67,7 +67,7 @@ struct BwdParams {
 
 // A-operand fragments (m16 x k16, both heads on K) of a table slice for the row tiles this warp owns.
 template <int MTW>
-__device__ __forceinline__ void load_table_a(const __half *tab, const CrseMeta &im, int H, int hp, int wid, int g, int t,
+__device__ __forceinline__ void load_table_a(const __half *tab, const CrseMeta &im, int HC, int co, int wid, int g, int t,
                                              uint32_t (&a)[MTW][2][2])
 {
 #pragma unroll
@@ -75,10 +75,9 @@ __device__ __forceinline__ void load_table_a(const __half *tab, const CrseMeta &
         const int mt = wid + BW_NWARP * i;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int hh = 2 * hp + h;
             const int r0 = table_row(im, mt * 16 + g), r1 = table_row(im, mt * 16 + g + 8);
-            a[i][h][0] = r0 >= 0 ? *reinterpret_cast<const uint32_t *>(tab + ((int64_t)r0 * H + hh) * 8 + 2 * t) : 0u;
-            a[i][h][1] = r1 >= 0 ? *reinterpret_cast<const uint32_t *>(tab + ((int64_t)r1 * H + hh) * 8 + 2 * t) : 0u;
+            a[i][h][0] = r0 >= 0 ? *reinterpret_cast<const uint32_t *>(tab + (int64_t)r0 * HC + co + h * 8 + 2 * t) : 0u;
+            a[i][h][1] = r1 >= 0 ? *reinterpret_cast<const uint32_t *>(tab + (int64_t)r1 * HC + co + h * 8 + 2 * t) : 0u;
         }
     }
 }
@@ -164,7 +163,7 @@ __device__ __forceinline__ void dx_gemm(float (&acc)[2][2][4], const uint2 *s_pd
     }
 }
 
-template <int D, int MTW, int SIDE>
+template <int D, int MTW, int SIDE, bool HD16>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
 {
@@ -197,7 +196,8 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int hp = blockIdx.y, H = P.H;
-    const int HC = H * 8, co = hp * 16;
+    // head_dim 16: the block serves head hp; its two 8-channel halves stand in for the two heads
+    const int HC = H * (HD16 ? 16 : 8), co = hp * 16;
     const int n_mt = L.R16 / 16, Rp = L.Rp;
     const int pxw = L.px_stride / 4, pyw = L.py_stride / 4;
     const int mypos = qpos(lane);
@@ -205,10 +205,10 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
 
     // ---- resident table fragments --------------------------------------------------------------------
     uint32_t ta_px0[MTW][2][2], ta_px1[MTW][2][2], ta_py0[MTW][2][2], ta_py1[MTW][2][2];
-    load_table_a<MTW>(P.t_px0, meta, H, hp, wid, g, t, ta_px0);
-    load_table_a<MTW>(P.t_py0, meta, H, hp, wid, g, t, ta_py0);
-    if (SIDE == 0) load_table_a<MTW>(P.t_px1, meta, H, hp, wid, g, t, ta_px1);
-    else load_table_a<MTW>(P.t_py1, meta, H, hp, wid, g, t, ta_py1);
+    load_table_a<MTW>(P.t_px0, meta, HC, co, wid, g, t, ta_px0);
+    load_table_a<MTW>(P.t_py0, meta, HC, co, wid, g, t, ta_py0);
+    if (SIDE == 0) load_table_a<MTW>(P.t_px1, meta, HC, co, wid, g, t, ta_px1);
+    else load_table_a<MTW>(P.t_py1, meta, HC, co, wid, g, t, ta_py1);
     // B fragments (k = row, n = channel) of T0 for dX += H0 . T0
     uint32_t t0B[MTW][2][2];
 #pragma unroll
@@ -219,9 +219,8 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int ra = table_row(meta, ks * 16 + 2 * t + 8 * half), rb = table_row(meta, ks * 16 + 2 * t + 8 * half + 1);
-                const int hh = 2 * hp + h;
-                const __half lo = ra >= 0 ? P.t_px0[((int64_t)ra * H + hh) * 8 + g] : __float2half(0.f);
-                const __half hi = rb >= 0 ? P.t_px0[((int64_t)rb * H + hh) * 8 + g] : __float2half(0.f);
+                const __half lo = ra >= 0 ? P.t_px0[(int64_t)ra * HC + co + h * 8 + g] : __float2half(0.f);
+                const __half hi = rb >= 0 ? P.t_px0[(int64_t)rb * HC + co + h * 8 + g] : __float2half(0.f);
                 t0B[i][h][half] = h2_as_u32(__halves2half2(lo, hi));
             }
     }
@@ -266,7 +265,7 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                             acc += fa.x * fb.x + fa.y * fb.y;
                         }
                         s_xdel[xi * 2 + hf] = acc;
-                        s_xlse[xi * 2 + hf] = __ldg(P.lse + (int64_t)row * H + 2 * hp + hf);
+                        s_xlse[xi * 2 + hf] = __ldg(P.lse + (int64_t)row * H + (HD16 ? hp : 2 * hp + hf));
                     }
                 } else if (SIDE == 0 && which == 1) {
                     s_xdel[xi * 2 + hf] = 0.f;
@@ -281,6 +280,7 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
             if (SIDE == 0) {
                 xlse[0] = s_xlse[lane * 2]; xlse[1] = s_xlse[lane * 2 + 1];
                 xdel[0] = s_xdel[lane * 2]; xdel[1] = s_xdel[lane * 2 + 1];
+                if (HD16) xdel[0] = xdel[1] = xdel[0] + xdel[1];   // delta of the whole head
             }
             // block-diagonal B fragments of X0^T / X1^T for the n-tile this warp multiplies in S0 / dPV0
             uint32_t xS[2][2];   // [X0 | X1][b0, b1] for n-tile wid % 8
@@ -341,7 +341,7 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                                 const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
                                 del += fa.x * fb.x + fa.y * fb.y;
                             }
-                            ls = __ldg(P.lse + (int64_t)row * H + 2 * hp + hf);
+                            ls = __ldg(P.lse + (int64_t)row * H + (HD16 ? hp : 2 * hp + hf));
                         }
                     }
                     if (SIDE == 1 && which == 1) {
@@ -409,10 +409,13 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                         float ls0, ls1, de0, de1;
                         if (SIDE == 0) { ls0 = xlse[0]; ls1 = xlse[1]; de0 = xdel[0]; de1 = xdel[1]; }
                         else { ls0 = s_ylse[yy * 2]; ls1 = s_ylse[yy * 2 + 1]; de0 = s_ydel[yy * 2]; de1 = s_ydel[yy * 2 + 1]; }
-                        float p0 = exp2f((s0.x + bs.x - ls0) * LOG2E);
-                        float p1 = exp2f((s0.y + bs.y - ls1) * LOG2E);
-                        float ds0 = p0 * (dp0.x + bd.x - de0);
-                        float ds1 = p1 * (dp0.y + bd.y - de1);
+                        if (HD16 && SIDE == 1) de0 = de1 = de0 + de1;
+                        float sc0 = s0.x + bs.x, sc1 = s0.y + bs.y, dq0 = dp0.x + bd.x, dq1 = dp0.y + bd.y;
+                        if (HD16) { sc0 = sc1 = sc0 + sc1; dq0 = dq1 = dq0 + dq1; }   // halves of one head add up
+                        float p0 = exp2f((sc0 - ls0) * LOG2E);
+                        float p1 = exp2f((sc1 - ls1) * LOG2E);
+                        float ds0 = p0 * (dq0 - de0);
+                        float ds1 = p1 * (dq1 - de1);
                         if (lane >= nx) { p0 = 0.f; p1 = 0.f; ds0 = 0.f; ds1 = 0.f; }   // padding lanes hold no voxel
                         pd.x = h2_as_u32(__floats2half2_rn(p0, p1));
                         pd.y = h2_as_u32(__floats2half2_rn(ds0, ds1));
@@ -536,7 +539,7 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                 for (int rr = 0; rr < 2; ++rr) {
                     const int row = table_row(meta, mt * 16 + g + 8 * rr);   // aliases flush into the row they stand for
                     if (mt < n_mt && row >= 0) {
-                        float *p = dst + ((int64_t)row * H + 2 * hp + h) * 8 + 2 * t;
+                        float *p = dst + (int64_t)row * HC + co + h * 8 + 2 * t;
                         atomicAdd(p, dt_acc[a][i][h][2 * rr]);
                         atomicAdd(p + 1, dt_acc[a][i][h][2 * rr + 1]);
                     }
@@ -545,11 +548,11 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
     }
 }
 
-template <int D, int MTW, int SIDE>
+template <int D, int MTW, int SIDE, bool HD16>
 static int launch_side(const BwdParams &p, const CrseMeta &meta, cudaStream_t st)
 {
     const BwdSmem L = make_bwd_layout(meta.R, SIDE == 0 ? 2 : 1, SIDE == 0 ? 2 : 1, SIDE == 0 ? 1 : 2, bkt_of(SIDE));
-    auto kern = attn_bwd_tc_kernel<D, MTW, SIDE>;
+    auto kern = attn_bwd_tc_kernel<D, MTW, SIDE, HD16>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total) != cudaSuccess)
         return S3D_ERR_LAUNCH;
     int dev = 0, sms = 148, per_sm = 1;
@@ -557,7 +560,7 @@ static int launch_side(const BwdParams &p, const CrseMeta &meta, cudaStream_t st
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, BW_THREADS, L.total) != cudaSuccess || per_sm < 1)
         return S3D_ERR_LAUNCH;
-    const int hp = p.H / 2;
+    const int hp = HD16 ? p.H : p.H / 2;
     int gx = sms * per_sm / hp;
     if (gx > p.W) gx = (int)p.W;
     if (gx < 1) gx = 1;
@@ -566,7 +569,7 @@ static int launch_side(const BwdParams &p, const CrseMeta &meta, cudaStream_t st
     return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
 }
 
-template <int D, int MTW>
+template <int D, int MTW, bool HD16>
 static int launch_both(const AttnArgs &a, int skip_upto, cudaStream_t st)
 {
     BwdParams pq{};
@@ -580,7 +583,7 @@ static int launch_both(const AttnArgs &a, int skip_upto, cudaStream_t st)
     pq.dt0 = a.dtq; pq.dt1 = a.dtv;
     pq.w_sizes = a.w_sizes; pq.w2n = a.w2n; pq.n2n = a.n2n; pq.n_coords = a.n_coords;
     pq.W = a.W; pq.H = a.H;
-    int rc = launch_side<D, MTW, 0>(pq, a.meta, st);
+    int rc = launch_side<D, MTW, 0, HD16>(pq, a.meta, st);
     if (rc != S3D_OK) return rc;
     BwdParams pk = pq;
     pk.x0 = (const __half *)a.k;   pk.x1 = (const __half *)a.v;
@@ -589,14 +592,15 @@ static int launch_both(const AttnArgs &a, int skip_upto, cudaStream_t st)
     pk.t_py0 = (const __half *)a.tq; pk.t_py1 = (const __half *)a.tv;
     pk.dx0 = (__half *)a.dk; pk.dx1 = (__half *)a.dv;
     pk.dt0 = a.dtk; pk.dt1 = nullptr;
-    return launch_side<D, MTW, 1>(pk, a.meta, st);
+    return launch_side<D, MTW, 1, HD16>(pk, a.meta, st);
 }
 
 }  // namespace tc
 
 bool attn_tc_bwd_supported(const AttnArgs &a)
 {
-    if (a.dtype != S3D_F16 || a.hd != 8 || (a.H & 1)) return false;
+    if (a.dtype != S3D_F16) return false;
+    if (!(a.hd == 16 || (a.hd == 8 && !(a.H & 1)))) return false;
     const int Rint = a.meta.R + a.meta.D - 1;
     if (Rint > 16 * tc::BW_NWARP * 2) return false;
     for (int d = 0; d < a.meta.D; ++d)
@@ -622,8 +626,8 @@ int attn_tc_backward(const AttnArgs &a0, cudaStream_t st)
     const int mtw = (n_mt + tc::BW_NWARP - 1) / tc::BW_NWARP;
 #define S3D_TC_BWD(DD)                                            \
     switch (mtw) {                                                \
-        case 1: return tc::launch_both<DD, 1>(a, skip_upto, st);  \
-        case 2: return tc::launch_both<DD, 2>(a, skip_upto, st);  \
+        case 1: return a.hd == 16 ? tc::launch_both<DD, 1, true>(a, skip_upto, st) : tc::launch_both<DD, 1, false>(a, skip_upto, st); \
+        case 2: return a.hd == 16 ? tc::launch_both<DD, 2, true>(a, skip_upto, st) : tc::launch_both<DD, 2, false>(a, skip_upto, st); \
         default: return S3D_ERR_UNSUPPORTED;                      \
     }
     switch (a.meta.D) {

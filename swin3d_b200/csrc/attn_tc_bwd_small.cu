@@ -178,7 +178,7 @@ __device__ __forceinline__ void store_part(float *red, const float (&part)[2][2]
                     make_float2(part[h][i][2 * rr], part[h][i][2 * rr + 1]);
 }
 
-template <int D, int NPU /*projection + dT units per warp*/, int NHU /*hist.T units per warp*/>
+template <int D, int NPU /*projection + dT units per warp*/, int NHU /*hist.T units per warp*/, bool HD16>
 __global__ void __launch_bounds__(SM_THREADS, 1)
 attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
 {
@@ -205,7 +205,8 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int hp = blockIdx.y, H = P.H;
-    const int HC = H * 8, co = hp * 16;
+    // head_dim 16: the block serves head hp; its two 8-channel halves stand in for the two heads
+    const int HC = H * (HD16 ? 16 : 8), co = hp * 16;
     const int n_mt = L.R16 / 16, Rp = L.Rp;
     const int mypos = qpos(lane);
     constexpr float LOG2E = 1.4426950408889634f;
@@ -221,11 +222,10 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
         const __half *T = tab == 0 ? P.tq : (tab == 1 ? P.tv : P.tk);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int hh = 2 * hp + h;
             const int r0 = table_row(meta, mt * 16 + g), r1 = table_row(meta, mt * 16 + g + 8);
             const bool ok = tab < 3;
-            ta[i][h][0] = (ok && r0 >= 0) ? *reinterpret_cast<const uint32_t *>(T + ((int64_t)r0 * H + hh) * 8 + 2 * t) : 0u;
-            ta[i][h][1] = (ok && r1 >= 0) ? *reinterpret_cast<const uint32_t *>(T + ((int64_t)r1 * H + hh) * 8 + 2 * t) : 0u;
+            ta[i][h][0] = (ok && r0 >= 0) ? *reinterpret_cast<const uint32_t *>(T + (int64_t)r0 * HC + co + h * 8 + 2 * t) : 0u;
+            ta[i][h][1] = (ok && r1 >= 0) ? *reinterpret_cast<const uint32_t *>(T + (int64_t)r1 * HC + co + h * 8 + 2 * t) : 0u;
             dt_acc[i][h][0] = dt_acc[i][h][1] = dt_acc[i][h][2] = dt_acc[i][h][3] = 0.f;
         }
     }
@@ -241,10 +241,9 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int ra = table_row(meta, ks * 16 + 2 * t + 8 * half), rb = table_row(meta, ks * 16 + 2 * t + 8 * half + 1);
-                const int hh = 2 * hp + h;
                 const bool ok = side < 2;
-                const __half lo = (ok && ra >= 0) ? T[((int64_t)ra * H + hh) * 8 + g] : __float2half(0.f);
-                const __half hi = (ok && rb >= 0) ? T[((int64_t)rb * H + hh) * 8 + g] : __float2half(0.f);
+                const __half lo = (ok && ra >= 0) ? T[(int64_t)ra * HC + co + h * 8 + g] : __float2half(0.f);
+                const __half hi = (ok && rb >= 0) ? T[(int64_t)rb * HC + co + h * 8 + g] : __float2half(0.f);
                 tb[i][h][half] = h2_as_u32(__halves2half2(lo, hi));
             }
     }
@@ -280,7 +279,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
                         acc += fa.x * fb.x + fa.y * fb.y;
                     }
                     s_del[i * 2 + hf] = acc;
-                    s_lse[i * 2 + hf] = __ldg(P.lse + (int64_t)row * H + 2 * hp + hf);
+                    s_lse[i * 2 + hf] = __ldg(P.lse + (int64_t)row * H + (HD16 ? hp : 2 * hp + hf));
                 }
             } else if (arr == 3) {
                 s_del[i * 2 + hf] = 0.f;
@@ -292,7 +291,8 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
             reinterpret_cast<uint4 *>(s_hq)[i] = make_uint4(0, 0, 0, 0);     // histQ and histV are adjacent
         __syncthreads();
         const float xlse0 = s_lse[lane * 2], xlse1 = s_lse[lane * 2 + 1];
-        const float xdel0 = s_del[lane * 2], xdel1 = s_del[lane * 2 + 1];
+        float xdel0 = s_del[lane * 2], xdel1 = s_del[lane * 2 + 1];
+        if (HD16) xdel0 = xdel1 = xdel0 + xdel1;   // delta of the whole head
         // ---- projections P_q, dB (lane-major), P_k (tile-major); S0 = K.Q^T and dPV0 = V.dO^T ---------------
 #pragma unroll
         for (int i = 0; i < NPU; ++i) {
@@ -345,10 +345,12 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
                 const float4 in = *reinterpret_cast<const float4 *>(s_e + kk * ES + lane);   // S0 (h0,h1), dPV0 (h0,h1)
                 const float2 bs = __half22float2(__hadd2(b0, b1));
                 const float2 bd = __half22float2(b2);
-                float p0 = exp2f((in.x + bs.x - xlse0) * LOG2E);
-                float p1 = exp2f((in.y + bs.y - xlse1) * LOG2E);
-                float ds0 = p0 * (in.z + bd.x - xdel0);
-                float ds1 = p1 * (in.w + bd.y - xdel1);
+                float sc0 = in.x + bs.x, sc1 = in.y + bs.y, dq0 = in.z + bd.x, dq1 = in.w + bd.y;
+                if (HD16) { sc0 = sc1 = sc0 + sc1; dq0 = dq1 = dq0 + dq1; }   // halves of one head add up
+                float p0 = exp2f((sc0 - xlse0) * LOG2E);
+                float p1 = exp2f((sc1 - xlse1) * LOG2E);
+                float ds0 = p0 * (dq0 - xdel0);
+                float ds1 = p1 * (dq1 - xdel1);
                 if (lane >= n) { p0 = 0.f; p1 = 0.f; ds0 = 0.f; ds1 = 0.f; }
                 ent.x = h2_as_u32(__floats2half2_rn(p0, p1));
                 ent.y = h2_as_u32(__floats2half2_rn(ds0, ds1));
@@ -486,7 +488,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
                 for (int rr = 0; rr < 2; ++rr) {
                     const int row = table_row(meta, mt * 16 + g + 8 * rr);   // aliases flush into the row they stand for
                     if (row >= 0) {
-                        float *p = dst + ((int64_t)row * H + 2 * hp + h) * 8 + 2 * t;
+                        float *p = dst + (int64_t)row * HC + co + h * 8 + 2 * t;
                         atomicAdd(p, dt_acc[i][h][2 * rr]);
                         atomicAdd(p + 1, dt_acc[i][h][2 * rr + 1]);
                     }
@@ -495,17 +497,17 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
     }
 }
 
-template <int D, int NPU, int NHU>
+template <int D, int NPU, int NHU, bool HD16>
 static int launch_small(const SmallParams &p, const CrseMeta &meta, cudaStream_t st)
 {
     const SmallSmem L = make_small_layout(meta.R);
-    auto kern = attn_bwd_small_kernel<D, NPU, NHU>;
+    auto kern = attn_bwd_small_kernel<D, NPU, NHU, HD16>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total) != cudaSuccess)
         return S3D_ERR_LAUNCH;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int hp = p.H / 2;
+    const int hp = HD16 ? p.H : p.H / 2;
     int gx = sms / hp;
     if (gx > p.W) gx = (int)p.W;
     if (gx < 1) gx = 1;
@@ -518,7 +520,8 @@ static int launch_small(const SmallParams &p, const CrseMeta &meta, cudaStream_t
 
 bool attn_tc_bwd_small_supported(const AttnArgs &a)
 {
-    if (a.dtype != S3D_F16 || a.hd != 8 || (a.H & 1)) return false;
+    if (a.dtype != S3D_F16) return false;
+    if (!(a.hd == 16 || (a.hd == 8 && !(a.H & 1)))) return false;
     const int Rint = a.meta.R + a.meta.D - 1;
     const int n_mt = (Rint + 15) / 16;
     if (3 * n_mt > 5 * tc::SM_NWARP) return false;
@@ -545,10 +548,16 @@ int attn_tc_backward_small(const AttnArgs &a0, cudaStream_t st)
     const int npu = (3 * n_mt + tc::SM_NWARP - 1) / tc::SM_NWARP;   // <= 5
     const int nhu = (2 * n_mt + tc::SM_NWARP - 1) / tc::SM_NWARP;   // <= 3
 #define S3D_SMALL(DD)                                                                   \
-    if (npu <= 2 && nhu <= 1) return tc::launch_small<DD, 2, 1>(p, a.meta, st);         \
-    if (npu <= 3 && nhu <= 2) return tc::launch_small<DD, 3, 2>(p, a.meta, st);         \
-    if (npu <= 4 && nhu <= 3) return tc::launch_small<DD, 4, 3>(p, a.meta, st);         \
-    return tc::launch_small<DD, 5, 3>(p, a.meta, st);
+    if (a.hd == 16) {                                                                   \
+        if (npu <= 2 && nhu <= 1) return tc::launch_small<DD, 2, 1, true>(p, a.meta, st);  \
+        if (npu <= 3 && nhu <= 2) return tc::launch_small<DD, 3, 2, true>(p, a.meta, st);  \
+        if (npu <= 4 && nhu <= 3) return tc::launch_small<DD, 4, 3, true>(p, a.meta, st);  \
+        return tc::launch_small<DD, 5, 3, true>(p, a.meta, st);                          \
+    }                                                                                   \
+    if (npu <= 2 && nhu <= 1) return tc::launch_small<DD, 2, 1, false>(p, a.meta, st);  \
+    if (npu <= 3 && nhu <= 2) return tc::launch_small<DD, 3, 2, false>(p, a.meta, st);  \
+    if (npu <= 4 && nhu <= 3) return tc::launch_small<DD, 4, 3, false>(p, a.meta, st);  \
+    return tc::launch_small<DD, 5, 3, false>(p, a.meta, st);
     switch (a.meta.D) {
         case 3: S3D_SMALL(3)
         case 6: S3D_SMALL(6)

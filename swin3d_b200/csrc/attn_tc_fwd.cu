@@ -17,7 +17,7 @@
 namespace s3d {
 namespace tc {
 
-template <int D, int MTW>
+template <int D, int MTW, bool HD16>
 __global__ void __launch_bounds__(NTHREADS, 2)
 attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                    const __half *__restrict__ v, const __half *__restrict__ tq,
@@ -47,7 +47,9 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int hp = blockIdx.y;
-    const int HC = H * 8, co = hp * 16;
+    // head_dim 8: the block serves heads 2hp, 2hp+1.  head_dim 16: it serves head hp, whose two
+    // 8-channel halves take the place of the two heads (their partial scores are summed).
+    const int HC = H * (HD16 ? 16 : 8), co = hp * 16;
     const int n_mt = L.R16 / 16, Rp = L.Rp;
     const int mypos = qpos(lane);
     constexpr float LOG2E = 1.4426950408889634f;
@@ -59,17 +61,16 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
         const int mt = wid + NWARP * i;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int hh = 2 * hp + h;
             const int t0 = table_row(meta, mt * 16 + g), t1 = table_row(meta, mt * 16 + g + 8);
-            tqA[i][h][0] = t0 >= 0 ? *reinterpret_cast<const uint32_t *>(tq + ((int64_t)t0 * H + hh) * 8 + 2 * t) : 0u;
-            tqA[i][h][1] = t1 >= 0 ? *reinterpret_cast<const uint32_t *>(tq + ((int64_t)t1 * H + hh) * 8 + 2 * t) : 0u;
-            tkA[i][h][0] = t0 >= 0 ? *reinterpret_cast<const uint32_t *>(tk + ((int64_t)t0 * H + hh) * 8 + 2 * t) : 0u;
-            tkA[i][h][1] = t1 >= 0 ? *reinterpret_cast<const uint32_t *>(tk + ((int64_t)t1 * H + hh) * 8 + 2 * t) : 0u;
+            tqA[i][h][0] = t0 >= 0 ? *reinterpret_cast<const uint32_t *>(tq + (int64_t)t0 * HC + co + h * 8 + 2 * t) : 0u;
+            tqA[i][h][1] = t1 >= 0 ? *reinterpret_cast<const uint32_t *>(tq + (int64_t)t1 * HC + co + h * 8 + 2 * t) : 0u;
+            tkA[i][h][0] = t0 >= 0 ? *reinterpret_cast<const uint32_t *>(tk + (int64_t)t0 * HC + co + h * 8 + 2 * t) : 0u;
+            tkA[i][h][1] = t1 >= 0 ? *reinterpret_cast<const uint32_t *>(tk + (int64_t)t1 * HC + co + h * 8 + 2 * t) : 0u;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int ra = table_row(meta, mt * 16 + 2 * t + 8 * half), rb = table_row(meta, mt * 16 + 2 * t + 8 * half + 1);
-                const __half lo = ra >= 0 ? tv[((int64_t)ra * H + hh) * 8 + g] : __float2half(0.f);
-                const __half hi = rb >= 0 ? tv[((int64_t)rb * H + hh) * 8 + g] : __float2half(0.f);
+                const __half lo = ra >= 0 ? tv[(int64_t)ra * HC + co + h * 8 + g] : __float2half(0.f);
+                const __half hi = rb >= 0 ? tv[(int64_t)rb * HC + co + h * 8 + g] : __float2half(0.f);
                 tvB[i][h][half] = h2_as_u32(__halves2half2(lo, hi));
             }
         }
@@ -212,6 +213,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                         float2 s = s_s[kk * QT + lane];
                         s.x += b.x;
                         s.y += b.y;
+                        if (HD16) s.x = s.y = s.x + s.y;   // one head: both halves carry the full score
                         s_s[kk * QT + lane] = s;
                         mloc[0] = fmaxf(mloc[0], s.x);
                         mloc[1] = fmaxf(mloc[1], s.y);
@@ -412,21 +414,25 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                     const float inv = 1.f / ls;
                     const int64_t row = s_qrow[qq];
                     *reinterpret_cast<__half2 *>(out + row * HC + co + ch) = __floats2half2_rn(a * inv, b * inv);
-                    if ((ch & 7) == 0) lse[row * H + 2 * hp + h] = s_mtile[qq * 2 + h] + __logf(ls);
+                    if (HD16) {
+                        if (ch == 0) lse[row * H + hp] = s_mtile[qq * 2] + __logf(ls);
+                    } else if ((ch & 7) == 0) {
+                        lse[row * H + 2 * hp + h] = s_mtile[qq * 2 + h] + __logf(ls);
+                    }
                 }
             }
         }  // query tiles
     }      // windows
 }
 
-template <int D, int MTW>
+template <int D, int MTW, bool HD16>
 static int launch(const AttnArgs &a, cudaStream_t st)
 {
     const SmemLayout L = make_layout(a.meta.R, 1);
-    auto kern = attn_fwd_tc_kernel<D, MTW>;
+    auto kern = attn_fwd_tc_kernel<D, MTW, HD16>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total) != cudaSuccess)
         return S3D_ERR_LAUNCH;
-    const int hp = a.H / 2;
+    const int hp = HD16 ? a.H : a.H / 2;
     int dev = 0, sms = 148, per_sm = 1;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -448,7 +454,8 @@ static int launch(const AttnArgs &a, cudaStream_t st)
 
 bool attn_tc_supported(const AttnArgs &a)
 {
-    if (a.dtype != S3D_F16 || a.hd != 8 || (a.H & 1)) return false;
+    if (a.dtype != S3D_F16) return false;
+    if (!(a.hd == 16 || (a.hd == 8 && !(a.H & 1)))) return false;
     const int Rint = a.meta.R + a.meta.D - 1;
     if (Rint > 16 * tc::NWARP * 3) return false;
     for (int d = 0; d < a.meta.D; ++d)
@@ -466,9 +473,9 @@ int attn_tc_forward(const AttnArgs &a0, cudaStream_t st)
     const int mtw = (n_mt + tc::NWARP - 1) / tc::NWARP;
 #define S3D_TC_FWD(DD)                                            \
     switch (mtw) {                                                \
-        case 1: return tc::launch<DD, 1>(a, st);                  \
-        case 2: return tc::launch<DD, 2>(a, st);                  \
-        case 3: return tc::launch<DD, 3>(a, st);                  \
+        case 1: return a.hd == 16 ? tc::launch<DD, 1, true>(a, st) : tc::launch<DD, 1, false>(a, st); \
+        case 2: return a.hd == 16 ? tc::launch<DD, 2, true>(a, st) : tc::launch<DD, 2, false>(a, st); \
+        case 3: return a.hd == 16 ? tc::launch<DD, 3, true>(a, st) : tc::launch<DD, 3, false>(a, st); \
         default: return S3D_ERR_UNSUPPORTED;                      \
     }
     switch (a.meta.D) {

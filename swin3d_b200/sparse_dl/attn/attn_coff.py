@@ -147,7 +147,8 @@ class SelfAttnAIOFunction(Function):
 
         # dtype policy of the reference (attn_coff.py:172-178)
         if torch.is_autocast_enabled() and precision != PrecisionMode.HALF_NONE:
-            c_dtype = torch.get_autocast_gpu_dtype()
+            c_dtype = (torch.get_autocast_dtype("cuda") if hasattr(torch, "get_autocast_dtype")
+                       else torch.get_autocast_gpu_dtype())
         else:
             c_dtype = torch.float32
         if c_dtype not in _DTYPE_CODE:

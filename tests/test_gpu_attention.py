@@ -254,3 +254,24 @@ def test_fp16_index_equal_to_L_alias_rows_and_determinism():
         assert np.array_equal(a[2][i], b[2][i])
     for i in range(3, 6):   # table gradients: fp32 atomics across blocks, order may differ
         assert rel_err(a[2][i], b[2][i]) < 1e-4
+
+
+@pytest.mark.parametrize("crse,H,ws,shift", [("XYZ_RGB_NORM", 5, 5, 2), ("XYZ_RGB", 3, 5, 0), ("XYZ", 2, 7, 3)])
+def test_fp16_head_dim_16_tensor_core_path(crse, H, ws, shift):
+    """head_dim 16 (every stage but the first of the reference models): a block serves one head
+    as two 8-channel halves.  Any head count, small and large windows."""
+    from tests.gpu_helpers import cuda_fwd_bwd
+    p = make_problem(seed=81, n_voxels=1500, grid=26, ws=ws, shift=shift, H=H, hd=16, crse=crse,
+                     round_fp16=True)
+    o_ref, lse_ref, g_ref = oracle_fwd_bwd(p, np.float64)
+    out, lse, grads = cuda_fwd_bwd(p, torch.float16)
+    assert rel_err(out, o_ref) < FP16_TOL
+    assert np.abs(lse - lse_ref).max() < 2e-2
+    for name, a, b in zip("dq dk dv dtq dtk dtv".split(), grads, g_ref):
+        assert rel_err(a, b) < FP16_TOL, name
+    q = make_problem(seed=2, ws=ws, H=H, hd=16, crse=crse, scene=_dense_scene(), round_fp16=True)
+    o_ref, _, g_ref = oracle_fwd_bwd(q, np.float64)
+    out, _, grads = cuda_fwd_bwd(q, torch.float16)
+    assert rel_err(out, o_ref) < FP16_TOL
+    for name, a, b in zip("dq dk dv dtq dtk dtv".split(), grads, g_ref):
+        assert rel_err(a, b) < FP16_TOL, name
