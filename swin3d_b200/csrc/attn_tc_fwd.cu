@@ -24,7 +24,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                    const __half *__restrict__ tk, const __half *__restrict__ tv,
                    const CrseMeta meta, const int32_t *__restrict__ w_sizes,
                    const int32_t *__restrict__ w2n, const int32_t *__restrict__ n2n,
-                   const float *__restrict__ n_coords, int64_t W, int H,
+                   const float *__restrict__ n_coords, int64_t W, int H, int skip_upto,
                    __half *__restrict__ out, float *__restrict__ lse)
 {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -78,6 +78,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
 
     for (int64_t w = blockIdx.x; w < W; w += gridDim.x) {
         const int n = __ldg(w_sizes + w);
+        if (n <= skip_upto) continue;       // left to the single-tile kernel
         const int base = __ldg(w2n + w);
         for (int q0 = 0; q0 < n; q0 += QT) {
             const int nq = min(QT, n - q0);
@@ -426,7 +427,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
 }
 
 template <int D, int MTW, bool HD16>
-static int launch(const AttnArgs &a, cudaStream_t st)
+static int launch(const AttnArgs &a, int skip_upto, cudaStream_t st)
 {
     const SmemLayout L = make_layout(a.meta.R, 1);
     auto kern = attn_fwd_tc_kernel<D, MTW, HD16>;
@@ -446,7 +447,7 @@ static int launch(const AttnArgs &a, cudaStream_t st)
     kern<<<grid, NTHREADS, L.total, st>>>(
         (const __half *)a.q, (const __half *)a.k, (const __half *)a.v, (const __half *)a.tq,
         (const __half *)a.tk, (const __half *)a.tv, a.meta, a.w_sizes, a.w2n, a.n2n, a.n_coords, a.W,
-        a.H, (__half *)a.out, a.lse);
+        a.H, skip_upto, (__half *)a.out, a.lse);
     return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
 }
 
@@ -469,13 +470,19 @@ int attn_tc_forward(const AttnArgs &a0, cudaStream_t st)
     if (a0.W == 0) return S3D_OK;
     AttnArgs a = a0;
     a.meta = tc::internal_meta(a0.meta);   // kernels work in the internal row numbering
+    int skip_upto = 0;
+    if (attn_tc_fwd_small_supported(a0)) {
+        const int rc = attn_tc_forward_small(a0, st);
+        if (rc != S3D_OK) return rc;
+        skip_upto = tc::QT;
+    }
     const int n_mt = (a.meta.R + 15) / 16;
     const int mtw = (n_mt + tc::NWARP - 1) / tc::NWARP;
 #define S3D_TC_FWD(DD)                                            \
     switch (mtw) {                                                \
-        case 1: return a.hd == 16 ? tc::launch<DD, 1, true>(a, st) : tc::launch<DD, 1, false>(a, st); \
-        case 2: return a.hd == 16 ? tc::launch<DD, 2, true>(a, st) : tc::launch<DD, 2, false>(a, st); \
-        case 3: return a.hd == 16 ? tc::launch<DD, 3, true>(a, st) : tc::launch<DD, 3, false>(a, st); \
+        case 1: return a.hd == 16 ? tc::launch<DD, 1, true>(a, skip_upto, st) : tc::launch<DD, 1, false>(a, skip_upto, st); \
+        case 2: return a.hd == 16 ? tc::launch<DD, 2, true>(a, skip_upto, st) : tc::launch<DD, 2, false>(a, skip_upto, st); \
+        case 3: return a.hd == 16 ? tc::launch<DD, 3, true>(a, skip_upto, st) : tc::launch<DD, 3, false>(a, skip_upto, st); \
         default: return S3D_ERR_UNSUPPORTED;                      \
     }
     switch (a.meta.D) {

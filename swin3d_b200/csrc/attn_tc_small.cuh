@@ -1,0 +1,132 @@
+// Warp-level GEMM building blocks shared by the single-tile (window of at most 32 voxels) kernels:
+// one projection unit, the pair-array GEMMs, one table-gradient unit, one hist.T unit.
+#pragma once
+#include "attn_tc.cuh"
+
+namespace s3d {
+namespace tc {
+
+constexpr int ES = 33;   // entry-row stride of the [32][ES] pair array (16-byte entries)
+
+// One (table, 16-row tile) projection unit:  P^T[rows][(voxel, head)] = T . F^T  for the 32 voxels of
+// the window, written lane-major ([row][qpos(voxel)]) or tile-major ([voxel][Rp]).
+template <bool LANE_MAJOR>
+__device__ __forceinline__ void project_unit(const uint32_t (&ta)[2][2], const __half *feat, uint32_t *dst,
+                                             int mt, int Rp, int nvalid, int g, int t)
+{
+    uint32_t d0[8], d1[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (4 * j < nvalid) {
+            const uint32_t wv = *reinterpret_cast<const uint32_t *>(feat + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+            mma_k16_h(d0[j], d1[j], ta[0][0], ta[0][1], ta[1][0], ta[1][1], (g & 1) ? 0u : wv, (g & 1) ? wv : 0u);
+        } else {
+            d0[j] = 0u;
+            d1[j] = 0u;
+        }
+    }
+    if (LANE_MAJOR) {
+        uint32_t *r0 = dst + (mt * 16 + g) * QT + 4 * t;
+        *reinterpret_cast<uint4 *>(r0) = make_uint4(d0[0], d0[2], d0[4], d0[6]);
+        *reinterpret_cast<uint4 *>(r0 + 16) = make_uint4(d0[1], d0[3], d0[5], d0[7]);
+        *reinterpret_cast<uint4 *>(r0 + 8 * QT) = make_uint4(d1[0], d1[2], d1[4], d1[6]);
+        *reinterpret_cast<uint4 *>(r0 + 8 * QT + 16) = make_uint4(d1[1], d1[3], d1[5], d1[7]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (4 * j < nvalid) {
+                uint32_t *p = dst + (4 * j + t) * Rp + mt * 16 + g;
+                p[0] = d0[j];
+                p[8] = d1[j];
+            }
+    }
+}
+
+// acc[head][m-tile] += A . B with A[m][kk] = field FIELD (0 = p, 1 = ds) of the pair entries and
+// B[kk][c] = rows[kk][head*8 + c].  TRANSPOSED = false: m = query, kk = key (entry [kk][m]);
+// TRANSPOSED = true: m = key, kk = query (entry [m][kk]).
+template <int FIELD, bool TRANSPOSED>
+__device__ __forceinline__ void pair_gemm(float (&acc)[2][2][4], const uint4 *s_e, const __half *rows, int nk, int g, int t)
+{
+    const uint32_t *e32 = reinterpret_cast<const uint32_t *>(s_e);
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+        if (16 * ks < nk) {
+            uint32_t fa[2][2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int kh = 0; kh < 2; ++kh)
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const int m = 16 * i + g + 8 * rr, ka = 16 * ks + 2 * t + 8 * kh;
+                        const uint32_t u = TRANSPOSED ? e32[(m * ES + ka) * 4 + FIELD] : e32[(ka * ES + m) * 4 + FIELD];
+                        const uint32_t w = TRANSPOSED ? e32[(m * ES + ka + 1) * 4 + FIELD] : e32[((ka + 1) * ES + m) * 4 + FIELD];
+                        fa[0][i][2 * kh + rr] = pack_lo(u, w);
+                        fa[1][i][2 * kh + rr] = pack_hi(u, w);
+                    }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t yb[2];
+#pragma unroll
+                for (int kh = 0; kh < 2; ++kh) {
+                    const int ka = 16 * ks + 2 * t + 8 * kh;
+                    yb[kh] = h2_as_u32(__halves2half2(rows[ka * 16 + h * 8 + g], rows[(ka + 1) * 16 + h * 8 + g]));
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+                    mma_k16(acc[h][i], fa[h][i][0], fa[h][i][1], fa[h][i][2], fa[h][i][3], yb[0], yb[1]);
+            }
+        }
+    }
+}
+
+// dT[rows of tile mt][c] += sum over the 32 voxels of hist[row][voxel] * X[voxel][c]  (both heads).
+__device__ __forceinline__ void dt_unit(float (&acc)[2][4], const uint32_t *hist, const __half *xrows, int mt, int g, int t)
+{
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+        // lane (g,t): rows g, g+8 of the tile; columns 16ks+4t .. +3  <->  k = 2t, 2t+1, 2t+8, 2t+9
+        const uint4 u = *reinterpret_cast<const uint4 *>(hist + (mt * 16 + g) * QT + 16 * ks + 4 * t);
+        const uint4 w = *reinterpret_cast<const uint4 *>(hist + (mt * 16 + g + 8) * QT + 16 * ks + 4 * t);
+        uint32_t b[2][2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int p0 = 16 * ks + 4 * t + 2 * half, p1 = p0 + 1;   // column -> voxel: (p >> 2) + 8 (p & 3)
+                const int xa = (p0 >> 2) + 8 * (p0 & 3), xb = (p1 >> 2) + 8 * (p1 & 3);
+                b[h][half] = h2_as_u32(__halves2half2(xrows[xa * 16 + h * 8 + g], xrows[xb * 16 + h * 8 + g]));
+            }
+        mma_k16(acc[0], pack_lo(u.x, u.y), pack_lo(w.x, w.y), pack_lo(u.z, u.w), pack_lo(w.z, w.w), b[0][0], b[0][1]);
+        mma_k16(acc[1], pack_hi(u.x, u.y), pack_hi(w.x, w.y), pack_hi(u.z, u.w), pack_hi(w.z, w.w), b[1][0], b[1][1]);
+    }
+}
+
+// part[head][m-tile] += hist(16 rows of k-step ks) . T(16 rows)  for the 32 voxels (m) of the window.
+__device__ __forceinline__ void ht_unit(float (&part)[2][2][4], const uint32_t *hist, const uint32_t (&tb)[2][2], int ks, int g, int t)
+{
+    const uint4 y0v = *reinterpret_cast<const uint4 *>(hist + (ks * 16 + 2 * t) * QT + 4 * g);
+    const uint4 y1v = *reinterpret_cast<const uint4 *>(hist + (ks * 16 + 2 * t + 1) * QT + 4 * g);
+    const uint4 y2v = *reinterpret_cast<const uint4 *>(hist + (ks * 16 + 2 * t + 8) * QT + 4 * g);
+    const uint4 y3v = *reinterpret_cast<const uint4 *>(hist + (ks * 16 + 2 * t + 9) * QT + 4 * g);
+    mma_k16(part[0][0], pack_lo(y0v.x, y1v.x), pack_lo(y0v.y, y1v.y), pack_lo(y2v.x, y3v.x), pack_lo(y2v.y, y3v.y), tb[0][0], tb[0][1]);
+    mma_k16(part[1][0], pack_hi(y0v.x, y1v.x), pack_hi(y0v.y, y1v.y), pack_hi(y2v.x, y3v.x), pack_hi(y2v.y, y3v.y), tb[1][0], tb[1][1]);
+    mma_k16(part[0][1], pack_lo(y0v.z, y1v.z), pack_lo(y0v.w, y1v.w), pack_lo(y2v.z, y3v.z), pack_lo(y2v.w, y3v.w), tb[0][0], tb[0][1]);
+    mma_k16(part[1][1], pack_hi(y0v.z, y1v.z), pack_hi(y0v.w, y1v.w), pack_hi(y2v.z, y3v.z), pack_hi(y2v.w, y3v.w), tb[1][0], tb[1][1]);
+}
+
+__device__ __forceinline__ void store_part(float *red, const float (&part)[2][2][4], int g, int t)
+{
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr)
+                *reinterpret_cast<float2 *>(red + (16 * i + g + 8 * rr) * 16 + h * 8 + 2 * t) =
+                    make_float2(part[h][i][2 * rr], part[h][i][2 * rr + 1]);
+}
+
+}  // namespace tc
+}  // namespace s3d
