@@ -120,7 +120,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
         for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const int ra = table_row(meta, ks * 16 + 2 * t + 8 * half), rb = table_row(meta, ks * 16 + 2 * t + 8 * half + 1);
+                const int ra = table_row(meta, ks * 16 + ht_krow(t, half, 0)), rb = table_row(meta, ks * 16 + ht_krow(t, half, 1));
                 const bool ok = side < 2;
                 const __half lo = (ok && ra >= 0) ? T[(int64_t)ra * HC + co + h * 8 + g] : __float2half(0.f);
                 const __half hi = (ok && rb >= 0) ? T[(int64_t)rb * HC + co + h * 8 + g] : __float2half(0.f);

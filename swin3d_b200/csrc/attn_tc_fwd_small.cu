@@ -101,7 +101,7 @@ attn_fwd_small_kernel(const FwdSmallParams P, const CrseMeta meta)
         for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const int ra = table_row(meta, ks * 16 + 2 * t + 8 * half), rb = table_row(meta, ks * 16 + 2 * t + 8 * half + 1);
+                const int ra = table_row(meta, ks * 16 + ht_krow(t, half, 0)), rb = table_row(meta, ks * 16 + ht_krow(t, half, 1));
                 const __half lo = ra >= 0 ? P.tv[(int64_t)ra * HC + co + h * 8 + g] : __float2half(0.f);
                 const __half hi = rb >= 0 ? P.tv[(int64_t)rb * HC + co + h * 8 + g] : __float2half(0.f);
                 tb[i][h][half] = h2_as_u32(__halves2half2(lo, hi));

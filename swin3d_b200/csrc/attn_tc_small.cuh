@@ -26,11 +26,17 @@ __device__ __forceinline__ void project_unit(const uint32_t (&ta)[2][2], const _
         }
     }
     if (LANE_MAJOR) {
+        // 16-byte stores go out a quarter warp (rows g, g+1 ; t = 0..3) at a time: odd rows write their
+        // upper half first so that the eight lanes of a quarter cover all 32 banks.
         uint32_t *r0 = dst + (mt * 16 + g) * QT + 4 * t;
-        *reinterpret_cast<uint4 *>(r0) = make_uint4(d0[0], d0[2], d0[4], d0[6]);
-        *reinterpret_cast<uint4 *>(r0 + 16) = make_uint4(d0[1], d0[3], d0[5], d0[7]);
-        *reinterpret_cast<uint4 *>(r0 + 8 * QT) = make_uint4(d1[0], d1[2], d1[4], d1[6]);
-        *reinterpret_cast<uint4 *>(r0 + 8 * QT + 16) = make_uint4(d1[1], d1[3], d1[5], d1[7]);
+        const bool od = g & 1;
+        const int o0 = od ? 16 : 0, o1 = 16 - o0;
+        const uint4 a0 = make_uint4(d0[0], d0[2], d0[4], d0[6]), a1 = make_uint4(d0[1], d0[3], d0[5], d0[7]);
+        const uint4 b0 = make_uint4(d1[0], d1[2], d1[4], d1[6]), b1 = make_uint4(d1[1], d1[3], d1[5], d1[7]);
+        *reinterpret_cast<uint4 *>(r0 + o0) = od ? a1 : a0;
+        *reinterpret_cast<uint4 *>(r0 + o1) = od ? a0 : a1;
+        *reinterpret_cast<uint4 *>(r0 + 8 * QT + o0) = od ? b1 : b0;
+        *reinterpret_cast<uint4 *>(r0 + 8 * QT + o1) = od ? b0 : b1;
     } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -84,11 +90,17 @@ __device__ __forceinline__ void pair_gemm(float (&acc)[2][2][4], const uint4 *s_
 // dT[rows of tile mt][c] += sum over the 32 voxels of hist[row][voxel] * X[voxel][c]  (both heads).
 __device__ __forceinline__ void dt_unit(float (&acc)[2][4], const uint32_t *hist, const __half *xrows, int mt, int g, int t)
 {
+    // lane (g,t): rows g, g+8 of the tile; columns 16ks+4t .. +3  <->  k = 2t, 2t+1, 2t+8, 2t+9.
+    // Odd rows fetch the two k-steps in the opposite order: a quarter warp (rows g, g+1) then covers
+    // all 32 banks with each 16-byte load.
+    const bool od = g & 1;
+    const uint32_t *hu = hist + (mt * 16 + g) * QT + 4 * t, *hw = hu + 8 * QT;
+    const uint4 ua = *reinterpret_cast<const uint4 *>(hu + (od ? 16 : 0)), ub = *reinterpret_cast<const uint4 *>(hu + (od ? 0 : 16));
+    const uint4 wa = *reinterpret_cast<const uint4 *>(hw + (od ? 16 : 0)), wb = *reinterpret_cast<const uint4 *>(hw + (od ? 0 : 16));
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
-        // lane (g,t): rows g, g+8 of the tile; columns 16ks+4t .. +3  <->  k = 2t, 2t+1, 2t+8, 2t+9
-        const uint4 u = *reinterpret_cast<const uint4 *>(hist + (mt * 16 + g) * QT + 16 * ks + 4 * t);
-        const uint4 w = *reinterpret_cast<const uint4 *>(hist + (mt * 16 + g + 8) * QT + 16 * ks + 4 * t);
+        const bool first = (ks == 0) != od;
+        const uint4 u = first ? ua : ub, w = first ? wa : wb;
         uint32_t b[2][2];
 #pragma unroll
         for (int h = 0; h < 2; ++h)
@@ -103,17 +115,35 @@ __device__ __forceinline__ void dt_unit(float (&acc)[2][4], const uint32_t *hist
     }
 }
 
+// Table row (within a 16-row k-step) that k-slot (2t + 8*half + second) of an mma lane stands for in
+// ht_unit: slots {2t, 2t+1, 2t+8, 2t+9} <-> rows {t, t+4, t+8, t+12}.  The B fragments (table rows)
+// must be loaded with the same permutation.
+__device__ __forceinline__ int ht_krow(int t, int half, int second) { return t + 8 * half + 4 * second; }
+
 // part[head][m-tile] += hist(16 rows of k-step ks) . T(16 rows)  for the 32 voxels (m) of the window.
+// The fragment an mma lane (g,t) needs (four rows, one 16-byte column chunk g) would make the four
+// t-lanes of a quarter warp hit the same banks; each lane therefore loads the conflict-free pattern
+// (lane L: rows L/8 + 4i, chunk L%8, i.e. four rows x 128 bytes per instruction) and the registers
+// are moved to their mma lane with shuffles.
 __device__ __forceinline__ void ht_unit(float (&part)[2][2][4], const uint32_t *hist, const uint32_t (&tb)[2][2], int ks, int g, int t)
 {
-    const uint4 y0v = *reinterpret_cast<const uint4 *>(hist + (ks * 16 + 2 * t) * QT + 4 * g);
-    const uint4 y1v = *reinterpret_cast<const uint4 *>(hist + (ks * 16 + 2 * t + 1) * QT + 4 * g);
-    const uint4 y2v = *reinterpret_cast<const uint4 *>(hist + (ks * 16 + 2 * t + 8) * QT + 4 * g);
-    const uint4 y3v = *reinterpret_cast<const uint4 *>(hist + (ks * 16 + 2 * t + 9) * QT + 4 * g);
-    mma_k16(part[0][0], pack_lo(y0v.x, y1v.x), pack_lo(y0v.y, y1v.y), pack_lo(y2v.x, y3v.x), pack_lo(y2v.y, y3v.y), tb[0][0], tb[0][1]);
-    mma_k16(part[1][0], pack_hi(y0v.x, y1v.x), pack_hi(y0v.y, y1v.y), pack_hi(y2v.x, y3v.x), pack_hi(y2v.y, y3v.y), tb[1][0], tb[1][1]);
-    mma_k16(part[0][1], pack_lo(y0v.z, y1v.z), pack_lo(y0v.w, y1v.w), pack_lo(y2v.z, y3v.z), pack_lo(y2v.w, y3v.w), tb[0][0], tb[0][1]);
-    mma_k16(part[1][1], pack_hi(y0v.z, y1v.z), pack_hi(y0v.w, y1v.w), pack_hi(y2v.z, y3v.z), pack_hi(y2v.w, y3v.w), tb[1][0], tb[1][1]);
+    const int lane = 4 * g + t, src = 8 * t + g;
+    const uint32_t *hp = hist + (ks * 16 + (lane >> 3)) * QT + 4 * (lane & 7);
+    uint4 y[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) y[i] = *reinterpret_cast<const uint4 *>(hp + 4 * i * QT);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        y[i].x = __shfl_sync(0xffffffffu, y[i].x, src);
+        y[i].y = __shfl_sync(0xffffffffu, y[i].y, src);
+        y[i].z = __shfl_sync(0xffffffffu, y[i].z, src);
+        y[i].w = __shfl_sync(0xffffffffu, y[i].w, src);
+    }
+    // y[i] = row t + 4i, queries {g, g+8, g+16, g+24}
+    mma_k16(part[0][0], pack_lo(y[0].x, y[1].x), pack_lo(y[0].y, y[1].y), pack_lo(y[2].x, y[3].x), pack_lo(y[2].y, y[3].y), tb[0][0], tb[0][1]);
+    mma_k16(part[1][0], pack_hi(y[0].x, y[1].x), pack_hi(y[0].y, y[1].y), pack_hi(y[2].x, y[3].x), pack_hi(y[2].y, y[3].y), tb[1][0], tb[1][1]);
+    mma_k16(part[0][1], pack_lo(y[0].z, y[1].z), pack_lo(y[0].w, y[1].w), pack_lo(y[2].z, y[3].z), pack_lo(y[2].w, y[3].w), tb[0][0], tb[0][1]);
+    mma_k16(part[1][1], pack_hi(y[0].z, y[1].z), pack_hi(y[0].w, y[1].w), pack_hi(y[2].z, y[3].z), pack_hi(y[2].w, y[3].w), tb[1][0], tb[1][1]);
 }
 
 __device__ __forceinline__ void store_part(float *red, const float (&part)[2][2][4], int g, int t)
