@@ -364,7 +364,7 @@ def run_attention(args):
         "dtype": "f16 storage, f32 accumulate", "data": "synthetic", "config": workload_config(),
         "voxels_per_gpu": N, "pairs_per_gpu": M, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
         "window_build_ms": wb_ms,
-        "roofline": {"bound": "hbm", "kernel": "attention backward (query sweep + key sweep launches)", "achieved": bwd_gbs, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "attention backward (single-tile launch for windows <= 32 voxels + query-sweep and key-sweep launches for larger ones)", "achieved": bwd_gbs, "peak": peak,
                      "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": traffic, "peak_source": peak_src,
                      "algorithmic_bytes_per_voxel": {"fwd": pv_fwd, "bwd": pv_bwd},
                      "fwd": {"achieved": fwd_gbs, "frac": fwd_gbs / peak},
@@ -373,7 +373,7 @@ def run_attention(args):
         "e2e": {"value": n_total / (e2e_ms * 1e-3), "unit": "voxels/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 4 * N * Cc * 2,
                 "d2h_bytes_per_step": 4 * N * Cc * 2 + 3 * sum(sizes) * 4},
-        "gpu_launches": 3 * args.steps,   # forward + backward query sweep + backward key sweep
+        "gpu_launches": 5 * args.steps,   # forward single-tile + tiled, backward single-tile + query sweep + key sweep
         "clocks": clocks,
     }
     print(json.dumps(line))
@@ -411,6 +411,43 @@ def run_knn(args):
         # 148 SMs x 128 lanes x 2 x 1.965 GHz = 74.4 TFLOP/s (no measured figure is recorded)
         res[f"K{K}"] = {"ms": ms, "queries_per_s": qry.shape[0] / (ms * 1e-3), "pair_evals_per_s": evals,
                         "fp32_tflops": evals * 8 / 1e12, "frac_of_nominal_fp32_peak": evals * 8 / 74.4e12}
+    # consumers of the K=3 result: inverse-distance interpolation fwd+bwd, C = 160 (HBM-bound gathers);
+    # algorithmic bytes per query: K gathered rows + the output row + K (index, distance) pairs,
+    # backward: the dOut row + K read-modify-writes of source rows
+    from swin3d_b200.sparse_dl.knn import KNNInterpolate, KNNMaxPool
+    peak, peak_src = load_peaks()
+    idx3, d3 = knn_raw(3, src, qry, so, qo)
+    dist3 = torch.sqrt(d3)
+    idx16, _ = knn_raw(16, src, qry, so, qo)
+    C = 160
+    for name, dt, b in (("f32", torch.float32, 4), ("f16", torch.float16, 2)):
+        feat = torch.randn(src.shape[0], C, device="cuda").to(dt).requires_grad_(True)
+        dout = torch.randn(qry.shape[0], C, device="cuda").to(dt)
+
+        def step():
+            feat.grad = None
+            KNNInterpolate.apply(feat, idx3, dist3).backward(dout)
+
+        def step_pool():
+            feat.grad = None
+            KNNMaxPool.apply(feat, idx16)[0].backward(dout)
+
+        for tag, fn, K, byt in (("interp_K3", step, 3, (3 * C * b + C * b + 3 * 8) + (C * b + 3 * 8 + 2 * 3 * C * 4)),
+                                ("maxpool_K16", step_pool, 16, (16 * C * b + C * b + 16 * 4 + C * 4) + (C * b + C * 4 + 2 * C * 4))):
+            for _ in range(max(args.warmup, 1)):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            gbs = qry.shape[0] * byt / (ms * 1e-3) / 1e9
+            res[f"{tag}_{name}"] = {"ms_fwd_bwd": ms, "queries_per_s": qry.shape[0] / (ms * 1e-3), "channels": C,
+                                    "algorithmic_bytes_per_query": byt, "achieved_gbs": gbs,
+                                    "frac_of_hbm_peak": gbs / peak, "peak_source": peak_src}
     if rank == 0:
         print(json.dumps({"metric": "knn queries/sec (8 scenes x 200k queries x 50k sources)",
                           "unit": "queries/s", "value": res["K16"]["queries_per_s"], "detail": res,

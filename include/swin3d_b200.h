@@ -144,6 +144,37 @@ int s3d_knn(int K, const float *src, const float *query, const int32_t *src_offs
             const int32_t *query_offset, int B, int64_t Ns, int64_t Nq,
             int32_t *ret_idx, float *ret_dist, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Consumers of the KNN result (the callers either side of s3d_knn).
+ *
+ * s3d_knn_interpolate_fwd / _bwd replace the body of knn_linear_interpolation
+ * (Swin3D/modules/swin3d_layers.py:53-73) after its KNN.apply call:
+ *     w_i = 1/(dist_i + 1e-8);  w_i /= sum_j w_j;  out[q,:] = sum_i src_feat[idx[q,i],:] * w_i
+ *  idx int32[Nq,K] and dist float[Nq,K] are KNN.apply's outputs (dist = sqrt of s3d_knn's
+ *  ret_dist); src_feat [Ns,C], out/dout [Nq,C] in `dtype` (S3D_F32 or S3D_F16); 1 <= K <= 64;
+ *  C a multiple of 4 (fp32) or 8 (fp16), rows 16-byte aligned.
+ *  fp32 results follow the reference's operation order exactly; for fp16 the running sum is
+ *  rounded to fp16 after every neighbour, as the reference's in-place += does.
+ *  _bwd writes dsrc float[Ns,C] = the gradient w.r.t. src_feat (cleared by the call, accumulated
+ *  in fp32); dist and the coordinates receive no gradient, as in the reference.
+ *
+ * s3d_knn_maxpool_fwd / _bwd replace gather + MaxPool1d(K) of GridKNNDownsample.forward
+ * (swin3d_layers.py:302-309; query_knn_feature :28-50).  LayerNorm and the bias-free Linear of
+ * that block act on each gathered row by itself, so the caller applies them once per SOURCE row
+ * (g = linear(norm(src_feat)), [Ns,C]) and this call finishes the job:
+ *     out[q,c] = max_i g[idx[q,i], c],   arg[q,c] = the source row that supplied it
+ *  (first maximum wins on ties, NaN propagates, as MaxPool1d).  _bwd: dg float[Ns,C] (cleared by
+ *  the call) receives dout[q,c] at row arg[q,c].
+ */
+int s3d_knn_interpolate_fwd(const int32_t *idx, const float *dist, const void *src_feat, void *out,
+                            int64_t Nq, int K, int C, int dtype, void *stream);
+int s3d_knn_interpolate_bwd(const int32_t *idx, const float *dist, const void *dout, float *dsrc,
+                            int64_t Nq, int64_t Ns, int K, int C, int dtype, void *stream);
+int s3d_knn_maxpool_fwd(const int32_t *idx, const void *g, void *out, int32_t *arg,
+                        int64_t Nq, int K, int C, int dtype, void *stream);
+int s3d_knn_maxpool_bwd(const int32_t *arg, const void *dout, float *dg,
+                        int64_t Nq, int64_t Ns, int C, int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -168,3 +168,68 @@ def window_offsets(w_sizes):
     x_off = w2n[m2w] + m_off // w[m2w]
     y_off = w2n[m2w] + m_off % w[m2w]
     return x_off, y_off, m2w, w, w2n, w2m
+
+
+# ---- consumers of the KNN result -----------------------------------------------------------------
+
+def knn_interpolate(idx, dist, src_feat):
+    """numpy restatement of knn_linear_interpolation after its KNN.apply call
+    (swin3d_layers.py:64-72), operation by operation: weights in fp32; per neighbour one rounded
+    product (fp32) and one add whose result is rounded to the feature dtype (the reference's
+    in-place ``query_feat += ...`` on a tensor of src_feat's dtype)."""
+    idx = np.asarray(idx, dtype=np.int64)
+    dist = np.asarray(dist, dtype=np.float32)
+    src_feat = np.asarray(src_feat)
+    dt = src_feat.dtype
+    weight = (np.float32(1.0) / (dist + np.float32(1e-8))).astype(np.float32)
+    norm = np.zeros((dist.shape[0], 1), dtype=np.float32)
+    for i in range(dist.shape[1]):                      # sequential sum over the K neighbours
+        norm[:, 0] = norm[:, 0] + weight[:, i]
+    weight = (weight / norm).astype(np.float32)
+    out = np.zeros((idx.shape[0], src_feat.shape[1]), dtype=dt)
+    for i in range(idx.shape[1]):
+        prod = src_feat[idx[:, i]].astype(np.float32) * weight[:, i:i + 1]
+        out = (out.astype(np.float32) + prod).astype(dt)
+    return out
+
+
+def knn_interpolate_weights(dist):
+    dist = np.asarray(dist, dtype=np.float32)
+    weight = (np.float32(1.0) / (dist + np.float32(1e-8))).astype(np.float32)
+    norm = np.zeros((dist.shape[0], 1), dtype=np.float32)
+    for i in range(dist.shape[1]):
+        norm[:, 0] = norm[:, 0] + weight[:, i]
+    return (weight / norm).astype(np.float32)
+
+
+def knn_interpolate_bwd(idx, dist, dout, n_src):
+    """Gradient w.r.t. src_feat of knn_interpolate (autograd of the indexing + multiply,
+    swin3d_layers.py:70-72), accumulated in fp64 and returned as float32 [n_src, C]."""
+    idx = np.asarray(idx, dtype=np.int64)
+    w = knn_interpolate_weights(dist).astype(np.float64)
+    dout = np.asarray(dout).astype(np.float64)
+    dsrc = np.zeros((n_src, dout.shape[1]), dtype=np.float64)
+    for i in range(idx.shape[1]):
+        np.add.at(dsrc, idx[:, i], dout * w[:, i:i + 1])
+    return dsrc.astype(np.float32)
+
+
+def knn_maxpool(idx, g):
+    """max over the K neighbours of g[idx] per channel = MaxPool1d(K) over the gathered rows
+    (swin3d_layers.py:302-309); -> (out, arg = source row of the first maximum)."""
+    idx = np.asarray(idx, dtype=np.int64)
+    g = np.asarray(g)
+    gathered = g[idx]                                    # [Nq, K, C]
+    first = np.argmax(gathered.astype(np.float32), axis=1)      # first maximum along K
+    out = np.take_along_axis(gathered, first[:, None, :], axis=1)[:, 0, :]
+    arg = np.take_along_axis(np.broadcast_to(idx[:, :, None], gathered.shape), first[:, None, :], axis=1)[:, 0, :]
+    return out, arg.astype(np.int32)
+
+
+def knn_maxpool_bwd(arg, dout, n_src):
+    arg = np.asarray(arg, dtype=np.int64)
+    dout = np.asarray(dout).astype(np.float64)
+    dg = np.zeros((n_src, dout.shape[1]), dtype=np.float64)
+    cols = np.broadcast_to(np.arange(dout.shape[1])[None, :], dout.shape)
+    np.add.at(dg, (arg, cols), dout)
+    return dg.astype(np.float32)

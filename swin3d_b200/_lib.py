@@ -34,6 +34,10 @@ SIGNATURES = {
                                 [_c_void_p] * 5 + [_c_void_p]),
     "s3d_knn": (_i32, [_i32, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _i32, _i64, _i64,
                        _c_void_p, _c_void_p, _c_void_p]),
+    "s3d_knn_interpolate_fwd": (_i32, [_c_void_p] * 4 + [_i64, _i32, _i32, _i32, _c_void_p]),
+    "s3d_knn_interpolate_bwd": (_i32, [_c_void_p] * 4 + [_i64, _i64, _i32, _i32, _i32, _c_void_p]),
+    "s3d_knn_maxpool_fwd": (_i32, [_c_void_p] * 4 + [_i64, _i32, _i32, _i32, _c_void_p]),
+    "s3d_knn_maxpool_bwd": (_i32, [_c_void_p] * 3 + [_i64, _i64, _i32, _i32, _c_void_p]),
 }
 
 

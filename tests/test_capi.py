@@ -19,7 +19,8 @@ def test_header_declares_entry_points():
     syms = declared_symbols()
     for s in ("s3d_attn_fwd", "s3d_attn_bwd", "s3d_window_build", "s3d_knn",
               "s3d_window_build_workspace_bytes", "s3d_status_string", "s3d_version",
-              "s3d_debug_crse_indices"):
+              "s3d_debug_crse_indices", "s3d_knn_interpolate_fwd", "s3d_knn_interpolate_bwd",
+              "s3d_knn_maxpool_fwd", "s3d_knn_maxpool_bwd"):
         assert s in syms
 
 
