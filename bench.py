@@ -118,7 +118,8 @@ def cpu_baseline_attention(sample_rooms=1, voxels=None, threads=0, steps=1, warm
     rng = np.random.default_rng(0)
     q, k, v, g = (rng.standard_normal((N, c["H"], c["hd"])).astype(np.float32) for _ in range(4))
     q *= c["hd"] ** -0.5
-    nthreads = threads or O.max_threads()
+    # every core this process may run on; torchrun exports OMP_NUM_THREADS=1, which the explicit count overrides
+    nthreads = threads or len(os.sched_getaffinity(0))
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
