@@ -1,6 +1,6 @@
 """Generates tests/golden/offsets_reference.npz by running the reference's own Python code.
 
-Needs a checkout of microsoft/Swin3D (default /root/reference); MinkowskiEngine, timm and the two
+Needs a checkout of microsoft/Swin3D (path as first argument); MinkowskiEngine, timm and the two
 CUDA extensions are replaced by empty stub modules, which is enough to import
 Swin3D.modules.swin3d_layers and to run, on CPU tensors,
   * sparse_self_attention(protocol="v2")      (swin3d_layers.py:76-150)

@@ -1,6 +1,6 @@
 """Runs the reference's own compiled CUDA kernels (oracle/_ref/ref_swin3d_cuda.so, built by
 oracle/build_ref.py from the sources of microsoft/Swin3D) on seeded inputs on a GPU and writes
-their outputs to gpurun_out/ref_gpu_golden.npz.  A copy of that file is committed as
+their outputs to ref_gpu_golden.npz in the run's output folder.  A copy of that file is committed as
 tests/golden/ref_gpu_golden.npz and pins the CPU oracle (tests/test_golden_ref_gpu.py).
 
 Only shapes for which the reference forward kernel stays inside its 32-entry shared staging

@@ -23,7 +23,7 @@ def test_window_offsets_match_reference(case):
         assert np.array_equal(got, exp), name
 
 
-def test_known_answer_from_survey_probe():
+def test_known_answer_three_windows():
     x, y, m2w, ws, w2n, w2m = O.window_offsets([2, 3, 1])
     assert w2n.tolist() == [0, 2, 5]
     assert w2m.tolist() == [0, 4, 13]
