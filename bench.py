@@ -400,6 +400,67 @@ def run_attention(args):
     return 0
 
 
+def run_attention_split(args):
+    """Secondary workload: ONE 8-room batch split over the ranks by window ranges (strong scaling):
+    every rank computes its windows, per-voxel outputs and gradients are all-gathered (NCCL), table
+    gradients all-reduced.  Device-resident timing, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from swin3d_b200 import synthetic as S
+    from swin3d_b200.dist import sharded_attention
+    from swin3d_b200.window import build_windows
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    c = CFG
+    H, hd, ws, quant, crse = c["H"], c["hd"], c["ws"], c["quant"], c["crse"]
+    sc = make_batch(0, args.rooms or c["rooms"], c["voxels_per_room"])      # the same batch on every rank
+    N = sc.coords.shape[0]
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    sizes = S.table_sizes(ws, quant, H, hd, crse)
+    wi = build_windows(dev(sc.coords), dev(S.signal_feats(sc, crse)), ws, 0)
+    ncr = wi.n_coords.clone()
+    ncr[:, :3] *= quant
+    ncr[:, 3:] *= 2 * quant
+    gen = torch.Generator(device="cuda").manual_seed(1234)
+    rnd = lambda: torch.randn((N, H, hd), device="cuda", generator=gen, dtype=torch.float32)
+    q = (rnd() * hd ** -0.5).half()
+    k, v, g = rnd().half(), rnd().half(), rnd().half()
+    tabs = [dev(t).half() for t in S.make_tables(1, sizes)]
+
+    def step():
+        return sharded_attention(q, k, v, *tabs, sizes, wi.w_sizes, wi.w2n, wi.n2n, ncr, dout=g)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        step()
+    t1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([t0.elapsed_time(t1) / args.steps], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(json.dumps({"metric": "attn fwd+bwd voxels/sec @Swin3D-L stage1, one batch split over the GPUs",
+                          "value": N / (float(ms[0]) * 1e-3), "unit": "voxels/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": float(ms[0]),
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                          "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+                          "config": workload_config(), "voxels_total": N,
+                          "exchange": "all-gather of out, dq, dk, dv rows (4 x N x 160 B) + all-reduce of 3 table gradients"}))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def run_knn(args):
     """Secondary workload: KNN stress (200k queries x 50k sources per scene, 8 scenes, K=16 and 3)."""
     import torch
@@ -480,7 +541,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="attn", choices=["attn", "knn"])
+    ap.add_argument("--workload", default="attn", choices=["attn", "knn", "attn-split"])
     ap.add_argument("--rooms", type=int, default=0, help="rooms per GPU (default 8)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -488,6 +549,8 @@ def main():
         return run_reference_arm(args)
     if args.workload == "knn":
         return run_knn(args)
+    if args.workload == "attn-split":
+        return run_attention_split(args)
     return run_attention(args)
 
 

@@ -9,7 +9,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from oracle import oracle as O
-from swin3d_b200.dist import allreduce_table_grads, shard_voxel_range, shard_windows
+from swin3d_b200.dist import all_gather_window_rows, allreduce_table_grads, shard_voxel_range, shard_windows
 from tests.helpers import make_problem
 
 
@@ -74,6 +74,55 @@ def test_two_rank_window_sharding_reproduces_single_rank_gradients():
                           out, s, mx, p.g)
     for a, b in zip(got, ref):
         assert np.allclose(a, b, rtol=1e-12, atol=1e-14)
+
+
+def _rank_gather(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    p = make_problem(seed=72, n_voxels=700, grid=22, H=2, hd=8, crse="XYZ_RGB")
+    parts = shard_windows(p.w_sizes, world)
+    ranges = [shard_voxel_range(p.w_sizes, p.w2n, a, b) for a, b in parts]
+    a, b = parts[rank]
+    lo, hi = ranges[rank]
+    # forward of this rank's windows only; rows of other voxels stay whatever the buffer held
+    out, s, mx = O.attn_forward(p.q, p.k, p.v, p.tq, p.tk, p.tv, p.sizes, p.w_sizes[a:b], p.w2n[a:b],
+                                p.n2n, p.n_crse)
+    n2n = torch.from_numpy(p.n2n)
+    mine = n2n[lo:hi].long()
+    out_t = torch.from_numpy(out)
+    out_t[torch.ones(out_t.shape[0], dtype=torch.bool).index_fill_(0, mine, False)] = float("nan")
+    full = all_gather_window_rows(out_t[mine], ranges, n2n)
+    q.put((rank, full.numpy()))
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("world", [2, 3])
+def test_all_gather_of_window_shards_reassembles_the_output(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_gather, args=(r, world, port, q)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    got = dict(q.get(timeout=240) for _ in range(world))
+    for pr in procs:
+        pr.join(60)
+        assert pr.exitcode == 0
+    p = make_problem(seed=72, n_voxels=700, grid=22, H=2, hd=8, crse="XYZ_RGB")
+    ref, _, _ = O.attn_forward(p.q, p.k, p.v, p.tq, p.tk, p.tv, p.sizes, p.w_sizes, p.w2n, p.n2n, p.n_crse)
+    for r in range(world):                  # every rank ends with the full, identical array
+        assert np.array_equal(got[r], ref)
+
+
+def test_all_gather_window_rows_single_process_unpermutes():
+    n2n = torch.tensor([2, 0, 3, 1])
+    rows = torch.arange(8.0).view(4, 2)
+    full = all_gather_window_rows(rows, [(0, 4)], n2n)
+    assert torch.equal(full[n2n], rows)
+    with pytest.raises(ValueError):
+        all_gather_window_rows(rows[:3], [(0, 4)], n2n)
 
 
 def test_compat_aliases_resolve_reference_import_paths():

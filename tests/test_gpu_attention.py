@@ -275,3 +275,28 @@ def test_fp16_head_dim_16_tensor_core_path(crse, H, ws, shift):
     assert rel_err(out, o_ref) < FP16_TOL
     for name, a, b in zip("dq dk dv dtq dtk dtv".split(), grads, g_ref):
         assert rel_err(a, b) < FP16_TOL, name
+
+
+def test_sharded_attention_single_rank_equals_plain_call():
+    """swin3d_b200.dist.sharded_attention without a process group: the window range is the whole
+    list, the all-gather degenerates to the un-permutation through n2n."""
+    import torch
+    from swin3d_b200.dist import sharded_attention
+    from swin3d_b200.sparse_dl.attn import attn_coff as C
+    p = make_problem(seed=31, n_voxels=3000, grid=40, H=4, hd=8, crse="XYZ_RGB_NORM")
+    dev = lambda a, dt=None: (torch.from_numpy(np.ascontiguousarray(a)).cuda() if dt is None
+                              else torch.from_numpy(np.ascontiguousarray(a)).cuda().to(dt))
+    h = torch.float16
+    q, k, v, g = (dev(x, h) for x in (p.q, p.k, p.v, p.g))
+    tabs = [dev(x, h) for x in (p.tq, p.tk, p.tv)]
+    ws, w2n, n2n = (dev(x.astype(np.int32)) for x in (p.w_sizes, p.w2n, p.n2n))
+    ncr = dev(p.n_crse.astype(np.float32))
+    sizes = [int(x) for x in p.sizes]
+    out, dq, dk, dv, tg = sharded_attention(q, k, v, *tabs, sizes, ws, w2n, n2n, ncr, dout=g)
+    o2, lse = C.attn_forward_raw(q, k, v, *tabs, sizes, ws, w2n, n2n, ncr)
+    g2 = C.attn_backward_raw(q, k, v, *tabs, sizes, ws, w2n, n2n, ncr, o2, lse, g)
+    assert torch.equal(out, o2)
+    for a, b in zip((dq, dk, dv), g2[:3]):
+        assert torch.equal(a, b)
+    for a, b in zip(tg, g2[3:]):      # fp32 atomics: the order of the block flushes differs run to run
+        assert float((a - b).abs().max()) <= 1e-5 * max(float(b.abs().max()), 1e-6)
