@@ -300,3 +300,63 @@ def test_sharded_attention_single_rank_equals_plain_call():
         assert torch.equal(a, b)
     for a, b in zip(tg, g2[3:]):      # fp32 atomics: the order of the block flushes differs run to run
         assert float((a - b).abs().max()) <= 1e-5 * max(float(b.abs().max()), 1e-6)
+
+
+def test_full_benchmark_size_properties():
+    """The benchmark's full size (8 synthetic rooms, ~1 M voxels, 10 heads x 8, fp16), checked through
+    properties that need no reference result:
+      * value path is linear: out(v1 + v2) = out(v1) + out(v2), and with all value tables and v
+        constant the output is that constant (probabilities sum to one);
+      * the result does not depend on the order in which voxels are stored (a permutation of the
+        rows, with n2n mapped accordingly, permutes the output rows);
+      * dV sums: sum_k dV_k = sum_q dO_q when the value tables are zero (each row of p sums to one);
+      * a sample of windows agrees with the CPU oracle."""
+    import bench
+    from swin3d_b200.window import build_windows
+    from swin3d_b200.sparse_dl.attn import attn_coff as C
+    c = bench.CFG
+    H, hd, ws, quant, crse = c["H"], c["hd"], c["ws"], c["quant"], c["crse"]
+    sc = bench.make_batch(0, c["rooms"], c["voxels_per_room"])
+    N = sc.coords.shape[0]
+    assert N > 900_000
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    wi = build_windows(dev(sc.coords), dev(S.signal_feats(sc, crse)), ws, 0)
+    ncr = wi.n_coords.clone()
+    ncr[:, :3] *= quant
+    ncr[:, 3:] *= 2 * quant
+    sizes = S.table_sizes(ws, quant, H, hd, crse)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    rnd = lambda: torch.randn((N, H, hd), device="cuda", generator=gen).half()
+    q, k, v1, v2, g = rnd() * hd ** -0.5, rnd(), rnd(), rnd(), rnd()
+    tq, tk, tv = (dev(t).half() for t in S.make_tables(3, sizes))
+    fwd = lambda vv, tvv, n2n=wi.n2n, qq=q, kk=k: C.attn_forward_raw(qq, kk, vv, tq, tk, tvv, sizes, wi.w_sizes, wi.w2n, n2n, ncr)
+    zero_tv = torch.zeros_like(tv)
+    o1, lse = fwd(v1, zero_tv)
+    o2, _ = fwd(v2, zero_tv)
+    o12, _ = fwd((v1.float() + v2.float()).half(), zero_tv)
+    assert torch.isfinite(o1).all() and torch.isfinite(lse).all()
+    lin = (o12.float() - o1.float() - o2.float()).abs().max().item()
+    assert lin < 2e-2 * o12.float().abs().max().item()          # fp16 tolerance of the suite
+    ones, _ = fwd(torch.full_like(v1, 0.5), zero_tv)
+    assert (ones.float() - 0.5).abs().max().item() < 2e-3
+    # storage-order independence
+    perm = torch.randperm(N, device="cuda", generator=gen)
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(N, device="cuda")
+    n2n_p = inv[wi.n2n.long()].int()                             # sorted position -> row in the permuted arrays
+    op, _ = C.attn_forward_raw(q[perm], k[perm], v1[perm], tq, tk, tv, sizes, wi.w_sizes, wi.w2n, n2n_p, ncr)
+    of, lse_f = fwd(v1, tv)
+    assert torch.equal(op, of[perm])
+    # backward: column sums of p are carried by dV
+    grads = C.attn_backward_raw(q, k, v1, tq, tk, zero_tv, sizes, wi.w_sizes, wi.w2n, wi.n2n, ncr, o1, lse, g)
+    dv_sum, g_sum = grads[2].double().sum(0), g.double().sum(0)
+    assert (dv_sum - g_sum).abs().max().item() < 2e-3 * g.double().abs().sum(0).max().item()
+    assert all(torch.isfinite(x).all() for x in grads)
+    # a sample of windows against the oracle (the same rows, fp64 arithmetic)
+    w_sizes, w2n, n2n = (x.cpu().numpy() for x in (wi.w_sizes, wi.w2n, wi.n2n))
+    pick = np.linspace(0, len(w_sizes) - 1, 40).astype(np.int64)
+    f64 = lambda t: t.double().cpu().numpy()
+    o_ref, _, _ = O.attn_forward(f64(q), f64(k), f64(v1), f64(tq), f64(tk), f64(tv), sizes, w_sizes[pick],
+                                 w2n[pick], n2n, ncr.cpu().numpy(), dtype=np.float64)
+    rows = np.concatenate([n2n[w2n[w]:w2n[w] + w_sizes[w]] for w in pick])
+    assert rel_err(f64(of)[rows], o_ref[rows]) < FP16_TOL
