@@ -461,6 +461,78 @@ def run_attention_split(args):
     return 0
 
 
+def run_stages(args):
+    """Secondary workload: the cRSE attention of every stage of the Swin3D-L backbone on one batch
+    (channels 80/160/320/640/640, heads 10/10/20/40/40, window 5/7/7/7/7, quant 4, XYZ_RGB_NORM,
+    fp16), the voxel set coarsened by 2 per stage as the backbone's pooling does.  The whole
+    backbone needs MinkowskiEngine, which is not available; these per-stage times, weighted by the
+    block counts 2/4/9/4/4, are its attention share."""
+    import torch
+    from swin3d_b200 import synthetic as S
+    from swin3d_b200.sparse_dl.attn import attn_coff as C
+    from swin3d_b200.window import build_windows
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    c = CFG
+    quant, crse = c["quant"], c["crse"]
+    base = make_batch(0, args.rooms or c["rooms"], c["voxels_per_room"])
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    peak, peak_src = load_peaks()
+    stages = []
+    total = 0.0
+    for s, (Cc, H, ws, depth) in enumerate(zip((80, 160, 320, 640, 640), (10, 10, 20, 40, 40),
+                                               (5, 7, 7, 7, 7), (2, 4, 9, 4, 4))):
+        hd, stride = Cc // H, 2 ** s
+        sc = S.downsample_scene(base, stride)
+        N = sc.coords.shape[0]
+        sizes = S.table_sizes(ws, quant, H, hd, crse)
+        wins = []
+        for shift in (0, ws // 2):
+            wi = build_windows(dev(sc.coords), dev(S.signal_feats(sc, crse)), ws, shift, stride)
+            ncr = wi.n_coords.clone()
+            ncr[:, :3] *= quant
+            ncr[:, 3:] *= 2 * quant
+            wins.append((wi, ncr.contiguous()))
+        gen = torch.Generator(device="cuda").manual_seed(77 + s)
+        rnd = lambda: torch.randn((N, H, hd), device="cuda", generator=gen).half()
+        q, k, v, g = rnd() * hd ** -0.5, rnd(), rnd(), rnd()
+        tabs = [dev(t).half() for t in S.make_tables(1, sizes)]
+
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+
+        def step(i, ev=None):
+            wi, ncr = wins[i % 2]
+            if ev:
+                ev[0].record()
+            out, lse = C.attn_forward_raw(q, k, v, *tabs, sizes, wi.w_sizes, wi.w2n, wi.n2n, ncr)
+            if ev:
+                ev[1].record()
+            C.attn_backward_raw(q, k, v, *tabs, sizes, wi.w_sizes, wi.w2n, wi.n2n, ncr, out, lse, g)
+            if ev:
+                ev[2].record()
+
+        for i in range(max(args.warmup, 3)):
+            step(i)
+        torch.cuda.synchronize()
+        for i in range(args.steps):
+            step(i, evs[i])
+        torch.cuda.synchronize()
+        fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
+        bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+        ms = evs[0][0].elapsed_time(evs[-1][2]) / args.steps
+        byt = bytes_fwd(Cc, 2, len(sizes), H) + bytes_bwd(Cc, 2, len(sizes), H)
+        gbs = N * byt / (ms * 1e-3) / 1e9
+        stages.append({"stage": s + 1, "channels": Cc, "heads": H, "head_dim": hd, "window": ws,
+                       "voxels": N, "pairs": [w.num_pairs for w, _ in wins], "max_window": wins[0][0].max_window,
+                       "ms_fwd_bwd": ms, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "voxels_per_s": N / (ms * 1e-3), "blocks": depth,
+                       "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / peak})
+        total += depth * ms
+    print(json.dumps({"metric": "cRSE attention fwd+bwd per Swin3D-L backbone pass (sum over stages x blocks)",
+                      "value": total, "unit": "ms", "higher_is_better": False, "n_gpus": 1,
+                      "steps": args.steps, "warmup": max(args.warmup, 3), "data": "synthetic",
+                      "dtype": "f16 storage, f32 accumulate", "peak_source": peak_src, "stages": stages}))
+    return 0
+
+
 def run_knn(args):
     """Secondary workload: KNN stress (200k queries x 50k sources per scene, 8 scenes, K=16 and 3)."""
     import torch
@@ -541,7 +613,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="attn", choices=["attn", "knn", "attn-split"])
+    ap.add_argument("--workload", default="attn", choices=["attn", "knn", "attn-split", "stages"])
     ap.add_argument("--rooms", type=int, default=0, help="rooms per GPU (default 8)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -551,6 +623,8 @@ def main():
         return run_knn(args)
     if args.workload == "attn-split":
         return run_attention_split(args)
+    if args.workload == "stages":
+        return run_stages(args)
     return run_attention(args)
 
 

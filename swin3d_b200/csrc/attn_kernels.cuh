@@ -30,6 +30,7 @@ int crse_indices_dump(const float *n_coords, const CrseMeta &meta, int first_pos
 // Tensor-core path (attn_tc_fwd.cu): fp16 storage, head_dim 8, even head count.
 bool attn_tc_supported(const AttnArgs &a);
 int attn_tc_forward(const AttnArgs &a, cudaStream_t st);
+int attn_tc_head_mode(const AttnArgs &a);                      // HDM_* of attn_tc.cuh for this call
 bool attn_tc_fwd_small_supported(const AttnArgs &a);          // attn_tc_fwd_small.cu: windows <= 32 voxels
 int attn_tc_forward_small(const AttnArgs &a, cudaStream_t st);
 bool attn_tc_bwd_supported(const AttnArgs &a);

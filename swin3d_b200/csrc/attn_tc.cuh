@@ -60,6 +60,15 @@ __device__ __forceinline__ void mma_k16_h(uint32_t &d0, uint32_t &d1, uint32_t a
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
 }
 
+// The same with the accumulators carried in (second plane of a head-dim-16 head pair).
+__device__ __forceinline__ void mma_k16_ha(uint32_t &d0, uint32_t &d1, uint32_t a0, uint32_t a1,
+                                           uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f16.f16.f16.f16 {%0,%1}, {%2,%3,%4,%5}, {%6,%7}, {%0,%1};\n"
+                 : "+r"(d0), "+r"(d1)
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // Same shape, fp32 accumulators, C = 0.
 __device__ __forceinline__ void mma_k16_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                           uint32_t a3, uint32_t b0, uint32_t b1)
@@ -116,6 +125,53 @@ __device__ __forceinline__ int table_row(const CrseMeta &im, int r)
     return r < im.R ? r - n : -1;
 }
 
+// Head modes of the tiled kernels.  A thread block always works on two "slots" packed as half2:
+//   HDM_PAIR8   head_dim 8 : slots = heads 2hp, 2hp+1, 8 channels each, one plane
+//   HDM_SINGLE16 head_dim 16: slots = the two 8-channel halves of head hp (partial scores are summed)
+//   HDM_PAIR16  head_dim 16: slots = heads 2hp, 2hp+1; their 16 channels are split into two PLANES of
+//               8; contractions over channels accumulate over the planes, products whose result
+//               is per channel are made once per plane.  Per-pair work (look-ups, histograms) is
+//               that of one head_dim-8 pair, i.e. half of two HDM_SINGLE16 blocks.
+constexpr int HDM_PAIR8 = 0, HDM_SINGLE16 = 1, HDM_PAIR16 = 2;
+
+// Offset (in halves, inside a voxel or table row of H*hd channels) of the 8 channels of slot h, plane s.
+template <int HDM>
+__device__ __forceinline__ int slot_offset(int hp, int h, int s)
+{
+    return HDM == HDM_PAIR16 ? hp * 32 + h * 16 + s * 8 : hp * 16 + h * 8;
+}
+
+// A-operand fragment (16 table rows of tile mt x the 16 (slot, channel) of one plane).
+template <int HDM>
+__device__ __forceinline__ void load_table_a_frag(uint32_t (&a)[2][2], const __half *tab, const CrseMeta &im, int HC,
+                                                  int hp, int s, int mt, int g, int t)
+{
+    const int r0 = table_row(im, mt * 16 + g), r1 = table_row(im, mt * 16 + g + 8);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int o = slot_offset<HDM>(hp, h, s) + 2 * t;
+        a[h][0] = r0 >= 0 ? *reinterpret_cast<const uint32_t *>(tab + (int64_t)r0 * HC + o) : 0u;
+        a[h][1] = r1 >= 0 ? *reinterpret_cast<const uint32_t *>(tab + (int64_t)r1 * HC + o) : 0u;
+    }
+}
+
+// B-operand fragment (k = the 16 table rows of k-step ks, n = the 8 channels of slot h, plane s).
+template <int HDM>
+__device__ __forceinline__ void load_table_b_frag(uint32_t (&b)[2][2], const __half *tab, const CrseMeta &im, int HC,
+                                                  int hp, int s, int ks, int g, int t)
+{
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int ra = table_row(im, ks * 16 + 2 * t + 8 * half), rb = table_row(im, ks * 16 + 2 * t + 8 * half + 1);
+            const int o = slot_offset<HDM>(hp, h, s) + g;
+            const __half lo = ra >= 0 ? tab[(int64_t)ra * HC + o] : __float2half(0.f);
+            const __half hi = rb >= 0 ? tab[(int64_t)rb * HC + o] : __float2half(0.f);
+            b[h][half] = h2_as_u32(__halves2half2(lo, hi));
+        }
+}
+
 // Histogram update  hist[a][row_j] += v[a][j]  for four voxels j of a tile at once, for NDIM signal
 // dimensions (disjoint row ranges) and NARR histograms sharing the row index.  All loads are issued
 // before any store, so the shared-memory latency is paid once per group instead of once per voxel;
@@ -165,7 +221,7 @@ struct SmemLayout {
     int off_pq, off_hist, off_pk, off_s, off_idx, off_kv, off_kc, off_misc, total;
 };
 
-__host__ __device__ inline SmemLayout make_layout(int R, int n_rowq_arrays)
+__host__ __device__ inline SmemLayout make_layout(int R, int n_rowq_arrays, int n_planes = 1)
 {
     SmemLayout L;
     L.R16 = (R + 15) / 16 * 16;
@@ -177,7 +233,7 @@ __host__ __device__ inline SmemLayout make_layout(int R, int n_rowq_arrays)
     L.off_pk = off;   off += (KT * L.Rp * 4 > 18432) ? KT * L.Rp * 4 : 18432;
     L.off_s = off;    off += KT * QT * 8;                      // float2 scores / half2 probabilities
     L.off_idx = off;  off += KT * 2 * QT * 4;                  // packed cRSE indices
-    L.off_kv = off;   off += 2 * KT * 16 * 2;                  // key and value rows of the tile
+    L.off_kv = off;   off += n_planes * 2 * KT * 16 * 2;       // key and value rows of the tile, per plane
     L.off_kc = off;   off += KT * 12 * 4;                      // key coordinates, padded to 12
     L.off_misc = off; off += 1024;
     L.total = off;

@@ -17,7 +17,7 @@
 namespace s3d {
 namespace tc {
 
-template <int D, int MTW, bool HD16>
+template <int D, int MTW, int HDM>
 __global__ void __launch_bounds__(NTHREADS, 2)
 attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                    const __half *__restrict__ v, const __half *__restrict__ tq,
@@ -27,52 +27,44 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                    const float *__restrict__ n_coords, int64_t W, int H, int skip_upto,
                    __half *__restrict__ out, float *__restrict__ lse)
 {
+    constexpr bool HD16 = HDM == HDM_SINGLE16;       // the two slots are halves of one head
+    constexpr bool PAIR16 = HDM == HDM_PAIR16;       // two heads of 16 channels, two planes
+    constexpr int NPL = PAIR16 ? 2 : 1;
+    constexpr int MTP = PAIR16 ? 1 : MTW;            // resident table fragments only with one plane
     extern __shared__ __align__(16) unsigned char smem[];
-    const SmemLayout L = make_layout(meta.R, 1);
+    const SmemLayout L = make_layout(meta.R, 1, NPL);
     uint32_t *s_pq = reinterpret_cast<uint32_t *>(smem + L.off_pq);      // [R16][32] half2
     uint32_t *s_hist = reinterpret_cast<uint32_t *>(smem + L.off_hist);  // [R16][32] half2
     uint32_t *s_pk = reinterpret_cast<uint32_t *>(smem + L.off_pk);      // [KT][Rp] half2
-    float2 *s_s = reinterpret_cast<float2 *>(smem + L.off_s);            // [KT][32] (h0,h1)
+    float2 *s_s = reinterpret_cast<float2 *>(smem + L.off_s);            // [KT][32] (slot 0, slot 1)
     uint32_t *s_idx = reinterpret_cast<uint32_t *>(smem + L.off_idx);    // [KT][2][32]
-    __half *s_k = reinterpret_cast<__half *>(smem + L.off_kv);           // [KT][16]
-    __half *s_v = s_k + KT * 16;                                         // [KT][16]
+    __half *s_k = reinterpret_cast<__half *>(smem + L.off_kv);           // [plane][KT][16]
+    __half *s_v = s_k + NPL * KT * 16;                                   // [plane][KT][16]
     float *s_kc = reinterpret_cast<float *>(smem + L.off_kc);            // [KT][12]
     float *s_mtile = reinterpret_cast<float *>(smem + L.off_misc);       // [32][2]
     float *s_alpha = s_mtile + 64;                                       // [32][2]
     int *s_qrow = reinterpret_cast<int *>(s_alpha + 64);                 // [32]
-    __half *s_q = reinterpret_cast<__half *>(smem + L.off_s);            // [32][16], aliases s_s
+    __half *s_q = reinterpret_cast<__half *>(smem + L.off_s);            // [plane][32][16], aliases s_s
     float *s_red = reinterpret_cast<float *>(smem + L.off_pk);           // [8][32][16], aliases s_pk
     float *s_lsum = s_red + NWARP * QT * 16;                             // [8][32][2]
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int hp = blockIdx.y;
-    // head_dim 8: the block serves heads 2hp, 2hp+1.  head_dim 16: it serves head hp, whose two
-    // 8-channel halves take the place of the two heads (their partial scores are summed).
-    const int HC = H * (HD16 ? 16 : 8), co = hp * 16;
+    const int HC = H * (HDM == HDM_PAIR8 ? 8 : 16);
     const int n_mt = L.R16 / 16, Rp = L.Rp;
     const int mypos = qpos(lane);
     constexpr float LOG2E = 1.4426950408889634f;
 
-    // ---- this head pair's tables as mma fragments, resident in registers -----------------------
-    uint32_t tqA[MTW][2][2], tkA[MTW][2][2], tvB[MTW][2][2];
+    // ---- one-plane modes: this block's table slices as mma fragments, resident in registers --------
+    uint32_t tqA[MTP][2][2], tkA[MTP][2][2], tvB[MTP][2][2];
+    if (!PAIR16) {
 #pragma unroll
-    for (int i = 0; i < MTW; ++i) {
-        const int mt = wid + NWARP * i;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int t0 = table_row(meta, mt * 16 + g), t1 = table_row(meta, mt * 16 + g + 8);
-            tqA[i][h][0] = t0 >= 0 ? *reinterpret_cast<const uint32_t *>(tq + (int64_t)t0 * HC + co + h * 8 + 2 * t) : 0u;
-            tqA[i][h][1] = t1 >= 0 ? *reinterpret_cast<const uint32_t *>(tq + (int64_t)t1 * HC + co + h * 8 + 2 * t) : 0u;
-            tkA[i][h][0] = t0 >= 0 ? *reinterpret_cast<const uint32_t *>(tk + (int64_t)t0 * HC + co + h * 8 + 2 * t) : 0u;
-            tkA[i][h][1] = t1 >= 0 ? *reinterpret_cast<const uint32_t *>(tk + (int64_t)t1 * HC + co + h * 8 + 2 * t) : 0u;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int ra = table_row(meta, mt * 16 + 2 * t + 8 * half), rb = table_row(meta, mt * 16 + 2 * t + 8 * half + 1);
-                const __half lo = ra >= 0 ? tv[(int64_t)ra * HC + co + h * 8 + g] : __float2half(0.f);
-                const __half hi = rb >= 0 ? tv[(int64_t)rb * HC + co + h * 8 + g] : __float2half(0.f);
-                tvB[i][h][half] = h2_as_u32(__halves2half2(lo, hi));
-            }
+        for (int i = 0; i < MTP; ++i) {
+            const int mt = wid + NWARP * i;
+            load_table_a_frag<HDM>(tqA[i], tq, meta, HC, hp, 0, mt, g, t);
+            load_table_a_frag<HDM>(tkA[i], tk, meta, HC, hp, 0, mt, g, t);
+            load_table_b_frag<HDM>(tvB[i], tv, meta, HC, hp, 0, mt, g, t);
         }
     }
 
@@ -88,42 +80,55 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
 #pragma unroll
             for (int d = 0; d < D; ++d)
                 cq[d] = lane < nq ? __ldg(n_coords + (int64_t)(base + q0 + lane) * D + d) : 0.f;
-            if (tid < 64) {
-                const int qi = tid >> 1, hf = tid & 1;
+            if (tid < 64 * NPL) {
+                const int qi = (tid >> 1) & 31, hf = tid & 1, pl = tid >> 6;
                 uint4 val = make_uint4(0, 0, 0, 0);
                 if (qi < nq) {
                     const int row = __ldg(n2n + base + q0 + qi);
-                    if (hf == 0) s_qrow[qi] = row;
-                    val = __ldg(reinterpret_cast<const uint4 *>(q + (int64_t)row * HC + co + hf * 8));
+                    if (hf == 0 && pl == 0) s_qrow[qi] = row;
+                    val = __ldg(reinterpret_cast<const uint4 *>(q + (int64_t)row * HC + slot_offset<HDM>(hp, hf, pl)));
                 }
-                *reinterpret_cast<uint4 *>(s_q + qi * 16 + hf * 8) = val;
+                *reinterpret_cast<uint4 *>(s_q + pl * 512 + qi * 16 + hf * 8) = val;
             }
             for (int i = tid; i < L.R16 * QT / 4; i += NTHREADS)
                 reinterpret_cast<uint4 *>(s_hist)[i] = make_uint4(0, 0, 0, 0);
             __syncthreads();
-            // block-diagonal B fragments of Q^T: n-tile j <-> (queries 4j..4j+3) x (head 0, head 1)
-            uint32_t qB[8][2];
+            // block-diagonal B fragments of Q^T: n-tile j <-> (queries 4j..4j+3) x (slot 0, slot 1)
+            uint32_t qB[NPL][8][2];
+            uint32_t qS[NPL][2];   // the n-tile of Q^T this warp multiplies with K for the plain q.k scores
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const uint32_t wq = *reinterpret_cast<const uint32_t *>(s_q + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
-                qB[j][0] = (g & 1) ? 0u : wq;
-                qB[j][1] = (g & 1) ? wq : 0u;
+            for (int pl = 0; pl < NPL; ++pl) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t wq = *reinterpret_cast<const uint32_t *>(s_q + pl * 512 + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+                    qB[pl][j][0] = (g & 1) ? 0u : wq;
+                    qB[pl][j][1] = (g & 1) ? wq : 0u;
+                }
+                const uint32_t wq = *reinterpret_cast<const uint32_t *>(s_q + pl * 512 + (4 * wid + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+                qS[pl][0] = (g & 1) ? 0u : wq;
+                qS[pl][1] = (g & 1) ? wq : 0u;
             }
-            uint32_t qS[2];   // the n-tile of Q^T this warp multiplies with K for the plain q.k scores
-            {
-                const uint32_t wq = *reinterpret_cast<const uint32_t *>(s_q + (4 * wid + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
-                qS[0] = (g & 1) ? 0u : wq;
-                qS[1] = (g & 1) ? wq : 0u;
-            }
-            // P_q^T[row][(q, head)] = Tq . Q^T, fp16 accumulate, stored as it comes out
+            // P_q^T[row][(q, slot)] = Tq . Q^T, fp16 accumulate, stored as it comes out
 #pragma unroll
             for (int i = 0; i < MTW; ++i) {
                 const int mt = wid + NWARP * i;
                 if (mt < n_mt) {
                     uint32_t d0[8], d1[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        mma_k16_h(d0[j], d1[j], tqA[i][0][0], tqA[i][0][1], tqA[i][1][0], tqA[i][1][1], qB[j][0], qB[j][1]);
+                    for (int pl = 0; pl < NPL; ++pl) {
+                        uint32_t af[2][2];
+                        if (PAIR16) {
+                            load_table_a_frag<HDM>(af, tq, meta, HC, hp, pl, mt, g, t);
+                        } else {
+                            af[0][0] = tqA[i % MTP][0][0]; af[0][1] = tqA[i % MTP][0][1];
+                            af[1][0] = tqA[i % MTP][1][0]; af[1][1] = tqA[i % MTP][1][1];
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (pl == 0) mma_k16_h(d0[j], d1[j], af[0][0], af[0][1], af[1][0], af[1][1], qB[pl][j][0], qB[pl][j][1]);
+                            else mma_k16_ha(d0[j], d1[j], af[0][0], af[0][1], af[1][0], af[1][1], qB[pl][j][0], qB[pl][j][1]);
+                        }
+                    }
                     // query 4j+t sits in column 4t + j/2 (j even) or 16 + 4t + j/2 (j odd)
                     uint32_t *r0 = s_pq + (mt * 16 + g) * QT + 4 * t;
                     *reinterpret_cast<uint4 *>(r0) = make_uint4(d0[0], d0[2], d0[4], d0[6]);
@@ -134,58 +139,90 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
             }
             float m_run[2] = {-INFINITY, -INFINITY};
             float l_part[2] = {0.f, 0.f};
-            float oacc[2][2][4];  // [head][m-tile][c-frag]; meaningful in warp 7 only
+            // P.V accumulators [slot][m-tile][c-frag]; meaningful in warp 7 (plane 0) and, with two
+            // planes, warp 6 (plane 1)
+            float oacc[2][2][4];
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
                 for (int i = 0; i < 2; ++i) oacc[h][i][0] = oacc[h][i][1] = oacc[h][i][2] = oacc[h][i][3] = 0.f;
+            const bool pv_warp = wid == NWARP - 1 || (PAIR16 && wid == NWARP - 2);
+            const int pv_plane = NWARP - 1 - wid;
 
             for (int k0 = 0; k0 < n; k0 += KT) {
                 const int nk = min(KT, n - k0);
                 __syncthreads();  // P_q stored / previous key tile fully consumed
                 // ---- stage the key tile -----------------------------------------------------------
-                if (tid < 64) {
-                    const int ki = tid >> 2, which = (tid >> 1) & 1, hf = tid & 1;
+                if (tid < 64 * NPL) {
+                    const int ki = (tid >> 2) & 15, which = (tid >> 1) & 1, hf = tid & 1, pl = tid >> 6;
                     uint4 val = make_uint4(0, 0, 0, 0);
                     if (ki < nk) {
                         const int row = __ldg(n2n + base + k0 + ki);
                         const __half *src = which ? v : k;
-                        val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)row * HC + co + hf * 8));
+                        val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)row * HC + slot_offset<HDM>(hp, hf, pl)));
                     }
-                    *reinterpret_cast<uint4 *>((which ? s_v : s_k) + ki * 16 + hf * 8) = val;
-                } else if (tid < 64 + KT * D) {
-                    const int e = tid - 64, ki = e / D, d = e - ki * D;
+                    *reinterpret_cast<uint4 *>((which ? s_v : s_k) + pl * KT * 16 + ki * 16 + hf * 8) = val;
+                }
+                if (tid >= NTHREADS - 32) {
+                    s_mtile[(tid - (NTHREADS - 32)) * 2] = -INFINITY;
+                    s_mtile[(tid - (NTHREADS - 32)) * 2 + 1] = -INFINITY;
+                }
+                for (int e = (tid + 128) % NTHREADS; e < KT * D; e += NTHREADS) {   // threads 128.. first: they stage no rows
+                    const int ki = e / D, d = e - ki * D;
                     s_kc[ki * 12 + d] = ki < nk ? __ldg(n_coords + (int64_t)(base + k0 + ki) * D + d) : 0.f;
-                } else if (tid >= 224) {
-                    s_mtile[(tid - 224) * 2] = -INFINITY;
-                    s_mtile[(tid - 224) * 2 + 1] = -INFINITY;
                 }
                 __syncthreads();
-                // ---- P_k^T[row][(key, head)] = Tk . K^T -> s_pk[key][row];  S0^T[key][(q, head)] = K . Q^T ----
+                // ---- P_k^T[row][(key, slot)] = Tk . K^T -> s_pk[key][row];  S0^T[key][(q, slot)] = K . Q^T ----
                 {
+                    uint32_t kf[MTW][NPL][2][2];
+                    if (PAIR16) {
+#pragma unroll
+                        for (int i = 0; i < MTW; ++i)
+#pragma unroll
+                            for (int pl = 0; pl < NPL; ++pl)
+                                load_table_a_frag<HDM>(kf[i][pl], tk, meta, HC, hp, pl, wid + NWARP * i, g, t);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < MTW; ++i) {
+                            kf[i][0][0][0] = tkA[i % MTP][0][0]; kf[i][0][0][1] = tkA[i % MTP][0][1];
+                            kf[i][0][1][0] = tkA[i % MTP][1][0]; kf[i][0][1][1] = tkA[i % MTP][1][1];
+                        }
+                    }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const uint32_t wk = *reinterpret_cast<const uint32_t *>(s_k + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
-                        const uint32_t b0 = (g & 1) ? 0u : wk, b1 = (g & 1) ? wk : 0u;
+                        uint32_t b0[NPL], b1[NPL];
+#pragma unroll
+                        for (int pl = 0; pl < NPL; ++pl) {
+                            const uint32_t wk = *reinterpret_cast<const uint32_t *>(s_k + pl * KT * 16 + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+                            b0[pl] = (g & 1) ? 0u : wk;
+                            b1[pl] = (g & 1) ? wk : 0u;
+                        }
 #pragma unroll
                         for (int i = 0; i < MTW; ++i) {
                             const int mt = wid + NWARP * i;
                             if (mt < n_mt) {
                                 uint32_t d0, d1;
-                                mma_k16_h(d0, d1, tkA[i][0][0], tkA[i][0][1], tkA[i][1][0], tkA[i][1][1], b0, b1);
+                                mma_k16_h(d0, d1, kf[i][0][0][0], kf[i][0][0][1], kf[i][0][1][0], kf[i][0][1][1], b0[0], b1[0]);
+                                if (PAIR16)
+                                    mma_k16_ha(d0, d1, kf[i][NPL - 1][0][0], kf[i][NPL - 1][0][1], kf[i][NPL - 1][1][0], kf[i][NPL - 1][1][1], b0[NPL - 1], b1[NPL - 1]);
                                 uint32_t *dst = s_pk + (4 * j + t) * Rp + mt * 16 + g;
                                 dst[0] = d0;
                                 dst[8] = d1;
                             }
                         }
                     }
-                    {   // one n-tile (4 queries x 2 heads) of S0 per warp
-                        const uint32_t a0 = *reinterpret_cast<const uint32_t *>(s_k + g * 16 + 2 * t);
-                        const uint32_t a1 = *reinterpret_cast<const uint32_t *>(s_k + (g + 8) * 16 + 2 * t);
-                        const uint32_t a2 = *reinterpret_cast<const uint32_t *>(s_k + g * 16 + 8 + 2 * t);
-                        const uint32_t a3 = *reinterpret_cast<const uint32_t *>(s_k + (g + 8) * 16 + 8 + 2 * t);
+                    {   // one n-tile (4 queries x 2 slots) of S0 per warp
                         float c[4];
-                        mma_k16_z(c, a0, a1, a2, a3, qS[0], qS[1]);
+#pragma unroll
+                        for (int pl = 0; pl < NPL; ++pl) {
+                            const __half *kp = s_k + pl * KT * 16;
+                            const uint32_t a0 = *reinterpret_cast<const uint32_t *>(kp + g * 16 + 2 * t);
+                            const uint32_t a1 = *reinterpret_cast<const uint32_t *>(kp + (g + 8) * 16 + 2 * t);
+                            const uint32_t a2 = *reinterpret_cast<const uint32_t *>(kp + g * 16 + 8 + 2 * t);
+                            const uint32_t a3 = *reinterpret_cast<const uint32_t *>(kp + (g + 8) * 16 + 8 + 2 * t);
+                            if (pl == 0) mma_k16_z(c, a0, a1, a2, a3, qS[pl][0], qS[pl][1]);
+                            else mma_k16(c, a0, a1, a2, a3, qS[pl][0], qS[pl][1]);
+                        }
                         s_s[g * QT + 4 * wid + t] = make_float2(c[0], c[1]);
                         s_s[(g + 8) * QT + 4 * wid + t] = make_float2(c[2], c[3]);
                     }
@@ -270,7 +307,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                         x.w = h2_as_u32(__hmul2(u32_as_h2(x.w), a[3]));
                         *reinterpret_cast<uint4 *>(s_hist + r * QT + 4 * c4) = x;
                     }
-                    if (wid == NWARP - 1) {
+                    if (pv_warp) {
 #pragma unroll
                         for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -285,7 +322,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                 // ---- phase 2: histogram update; a warp owns one or two signal dimensions ----------------
                 {
                     int dA = -1, dB = -1;
-                    if (D <= NWARP - 1) {
+                    if (D <= NWARP - 2) {
                         if (wid < D) dA = wid;
                     } else if (wid < D - 5) {
                         dA = wid; dB = wid + 5;     // one index field from each packed word
@@ -319,9 +356,10 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                         }
                     }
                 }
-                // ---- O += P.V on the tensor cores (warp 7) --------------------------------------------
-                if (wid == NWARP - 1) {
-                    uint32_t pa[2][2][4];  // [head][m-tile][a0..a3]
+                // ---- O += P.V on the tensor cores (warp 7; with two planes also warp 6) -----------------
+                if (pv_warp) {
+                    const __half *vp = s_v + pv_plane * KT * 16;
+                    uint32_t pa[2][2][4];  // [slot][m-tile][a0..a3]
 #pragma unroll
                     for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -340,7 +378,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
 #pragma unroll
                         for (int kh = 0; kh < 2; ++kh) {
                             const int ka = 2 * t + 8 * kh;
-                            vb[kh] = h2_as_u32(__halves2half2(s_v[ka * 16 + h * 8 + g], s_v[(ka + 1) * 16 + h * 8 + g]));
+                            vb[kh] = h2_as_u32(__halves2half2(vp[ka * 16 + h * 8 + g], vp[(ka + 1) * 16 + h * 8 + g]));
                         }
 #pragma unroll
                         for (int i = 0; i < 2; ++i)
@@ -349,91 +387,108 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                 }
             }  // key tiles
             __syncthreads();
-            // ---- O += hist . Tv, K split over the warps, then reduce, normalise and store --------------
-            float part[2][2][4];
+            // ---- per plane: O += hist . Tv (K split over the warps), reduce, normalise and store ------------
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int pl = 0; pl < NPL; ++pl) {
+                float part[2][2][4];
 #pragma unroll
-                for (int i = 0; i < 2; ++i)
+                for (int h = 0; h < 2; ++h)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) part[h][i][e] = (wid == NWARP - 1) ? oacc[h][i][e] : 0.f;
+                    for (int i = 0; i < 2; ++i)
 #pragma unroll
-            for (int i = 0; i < MTW; ++i) {
-                const int ks = wid + NWARP * i;
-                if (ks < n_mt) {
-                    // rows 2t, 2t+1, 2t+8, 2t+9 of this k-step; columns = queries {g, g+8, g+16, g+24}
-                    uint32_t x0[4], x1[4], x2[4], x3[4];
-                    {
-                        const uint4 y0 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t) * QT + 4 * g);
-                        const uint4 y1 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t + 1) * QT + 4 * g);
-                        const uint4 y2 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t + 8) * QT + 4 * g);
-                        const uint4 y3 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t + 9) * QT + 4 * g);
-                        x0[0] = y0.x; x0[1] = y0.y; x0[2] = y0.z; x0[3] = y0.w;
-                        x1[0] = y1.x; x1[1] = y1.y; x1[2] = y1.z; x1[3] = y1.w;
-                        x2[0] = y2.x; x2[1] = y2.y; x2[2] = y2.z; x2[3] = y2.w;
-                        x3[0] = y3.x; x3[1] = y3.y; x3[2] = y3.z; x3[3] = y3.w;
-                    }
+                        for (int e = 0; e < 4; ++e) part[h][i][e] = (wid == NWARP - 1 - pl) ? oacc[h][i][e] : 0.f;
 #pragma unroll
-                    for (int mtile = 0; mtile < 2; ++mtile) {
-                        const int ja = 2 * mtile, jb = 2 * mtile + 1;   // queries g+16m and g+16m+8
-                        mma_k16(part[0][mtile], pack_lo(x0[ja], x1[ja]), pack_lo(x0[jb], x1[jb]),
-                                pack_lo(x2[ja], x3[ja]), pack_lo(x2[jb], x3[jb]), tvB[i][0][0], tvB[i][0][1]);
-                        mma_k16(part[1][mtile], pack_hi(x0[ja], x1[ja]), pack_hi(x0[jb], x1[jb]),
-                                pack_hi(x2[ja], x3[ja]), pack_hi(x2[jb], x3[jb]), tvB[i][1][0], tvB[i][1][1]);
-                    }
-                }
-            }
-            // s_red aliases s_pk, which nobody reads after the last phase 1 (a barrier ago)
+                for (int i = 0; i < MTW; ++i) {
+                    const int ks = wid + NWARP * i;
+                    if (ks < n_mt) {
+                        uint32_t bf[2][2];
+                        if (PAIR16) {
+                            load_table_b_frag<HDM>(bf, tv, meta, HC, hp, pl, ks, g, t);
+                        } else {
+                            bf[0][0] = tvB[i % MTP][0][0]; bf[0][1] = tvB[i % MTP][0][1];
+                            bf[1][0] = tvB[i % MTP][1][0]; bf[1][1] = tvB[i % MTP][1][1];
+                        }
+                        // rows 2t, 2t+1, 2t+8, 2t+9 of this k-step; columns = queries {g, g+8, g+16, g+24}
+                        uint32_t x0[4], x1[4], x2[4], x3[4];
+                        {
+                            const uint4 y0 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t) * QT + 4 * g);
+                            const uint4 y1 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t + 1) * QT + 4 * g);
+                            const uint4 y2 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t + 8) * QT + 4 * g);
+                            const uint4 y3 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t + 9) * QT + 4 * g);
+                            x0[0] = y0.x; x0[1] = y0.y; x0[2] = y0.z; x0[3] = y0.w;
+                            x1[0] = y1.x; x1[1] = y1.y; x1[2] = y1.z; x1[3] = y1.w;
+                            x2[0] = y2.x; x2[1] = y2.y; x2[2] = y2.z; x2[3] = y2.w;
+                            x3[0] = y3.x; x3[1] = y3.y; x3[2] = y3.z; x3[3] = y3.w;
+                        }
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int i = 0; i < 2; ++i)
-#pragma unroll
-                    for (int rr = 0; rr < 2; ++rr) {
-                        const int qq = 16 * i + g + 8 * rr;
-                        *reinterpret_cast<float2 *>(s_red + (wid * QT + qq) * 16 + h * 8 + 2 * t) =
-                            make_float2(part[h][i][2 * rr], part[h][i][2 * rr + 1]);
-                    }
-            s_lsum[(wid * QT + lane) * 2] = l_part[0];
-            s_lsum[(wid * QT + lane) * 2 + 1] = l_part[1];
-            if (wid == 0) {   // final maxima for the log-sum-exp
-                s_mtile[lane * 2] = m_run[0];
-                s_mtile[lane * 2 + 1] = m_run[1];
-            }
-            __syncthreads();
-            {
-                const int qq = tid >> 3, ch = (tid & 7) * 2, h = ch >> 3;
-                if (qq < nq) {
-                    float a = 0.f, b = 0.f, ls = 0.f;
-#pragma unroll
-                    for (int ww = 0; ww < NWARP; ++ww) {
-                        const float2 pr = *reinterpret_cast<const float2 *>(s_red + (ww * QT + qq) * 16 + ch);
-                        a += pr.x;
-                        b += pr.y;
-                        ls += s_lsum[(ww * QT + qq) * 2 + h];
-                    }
-                    const float inv = 1.f / ls;
-                    const int64_t row = s_qrow[qq];
-                    *reinterpret_cast<__half2 *>(out + row * HC + co + ch) = __floats2half2_rn(a * inv, b * inv);
-                    if (HD16) {
-                        if (ch == 0) lse[row * H + hp] = s_mtile[qq * 2] + __logf(ls);
-                    } else if ((ch & 7) == 0) {
-                        lse[row * H + 2 * hp + h] = s_mtile[qq * 2 + h] + __logf(ls);
+                        for (int mtile = 0; mtile < 2; ++mtile) {
+                            const int ja = 2 * mtile, jb = 2 * mtile + 1;   // queries g+16m and g+16m+8
+                            mma_k16(part[0][mtile], pack_lo(x0[ja], x1[ja]), pack_lo(x0[jb], x1[jb]),
+                                    pack_lo(x2[ja], x3[ja]), pack_lo(x2[jb], x3[jb]), bf[0][0], bf[0][1]);
+                            mma_k16(part[1][mtile], pack_hi(x0[ja], x1[ja]), pack_hi(x0[jb], x1[jb]),
+                                    pack_hi(x2[ja], x3[ja]), pack_hi(x2[jb], x3[jb]), bf[1][0], bf[1][1]);
+                        }
                     }
                 }
-            }
+                // s_red aliases s_pk, which nobody reads after the last phase 1 (a barrier ago); the
+                // second plane waits until the first one's reduction has been read
+                if (pl > 0) __syncthreads();
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i)
+#pragma unroll
+                        for (int rr = 0; rr < 2; ++rr) {
+                            const int qq = 16 * i + g + 8 * rr;
+                            *reinterpret_cast<float2 *>(s_red + (wid * QT + qq) * 16 + h * 8 + 2 * t) =
+                                make_float2(part[h][i][2 * rr], part[h][i][2 * rr + 1]);
+                        }
+                if (pl == 0) {
+                    s_lsum[(wid * QT + lane) * 2] = l_part[0];
+                    s_lsum[(wid * QT + lane) * 2 + 1] = l_part[1];
+                    if (wid == 0) {   // final maxima for the log-sum-exp
+                        s_mtile[lane * 2] = m_run[0];
+                        s_mtile[lane * 2 + 1] = m_run[1];
+                    }
+                }
+                __syncthreads();
+                {
+                    const int qq = tid >> 3, ch = (tid & 7) * 2, h = ch >> 3;
+                    if (qq < nq) {
+                        float a = 0.f, b = 0.f, ls = 0.f;
+#pragma unroll
+                        for (int ww = 0; ww < NWARP; ++ww) {
+                            const float2 pr = *reinterpret_cast<const float2 *>(s_red + (ww * QT + qq) * 16 + ch);
+                            a += pr.x;
+                            b += pr.y;
+                            ls += s_lsum[(ww * QT + qq) * 2 + h];
+                        }
+                        const float inv = 1.f / ls;
+                        const int64_t row = s_qrow[qq];
+                        *reinterpret_cast<__half2 *>(out + row * HC + slot_offset<HDM>(hp, h, pl) + (ch & 7)) =
+                            __floats2half2_rn(a * inv, b * inv);
+                        if (pl == 0) {
+                            if (HD16) {
+                                if (ch == 0) lse[row * H + hp] = s_mtile[qq * 2] + __logf(ls);
+                            } else if ((ch & 7) == 0) {
+                                lse[row * H + 2 * hp + h] = s_mtile[qq * 2 + h] + __logf(ls);
+                            }
+                        }
+                    }
+                }
+            }  // planes
         }  // query tiles
     }      // windows
 }
 
-template <int D, int MTW, bool HD16>
+template <int D, int MTW, int HDM>
 static int launch(const AttnArgs &a, int skip_upto, cudaStream_t st)
 {
-    const SmemLayout L = make_layout(a.meta.R, 1);
-    auto kern = attn_fwd_tc_kernel<D, MTW, HD16>;
+    const SmemLayout L = make_layout(a.meta.R, 1, HDM == HDM_PAIR16 ? 2 : 1);
+    auto kern = attn_fwd_tc_kernel<D, MTW, HDM>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total) != cudaSuccess)
         return S3D_ERR_LAUNCH;
-    const int hp = HD16 ? a.H : a.H / 2;
+    const int hp = HDM == HDM_SINGLE16 ? a.H : a.H / 2;
     int dev = 0, sms = 148, per_sm = 1;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -451,7 +506,24 @@ static int launch(const AttnArgs &a, int skip_upto, cudaStream_t st)
     return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
 }
 
+template <int D, int MTW>
+static int launch_mode(const AttnArgs &a, int hdm, int skip_upto, cudaStream_t st)
+{
+    switch (hdm) {
+        case HDM_PAIR8: return launch<D, MTW, HDM_PAIR8>(a, skip_upto, st);
+        case HDM_SINGLE16: return launch<D, MTW, HDM_SINGLE16>(a, skip_upto, st);
+        default: return launch<D, MTW, HDM_PAIR16>(a, skip_upto, st);
+    }
+}
+
 }  // namespace tc
+
+// Head mode of the tiled kernels for a call (see attn_tc.cuh).
+int attn_tc_head_mode(const AttnArgs &a)
+{
+    if (a.hd == 8) return tc::HDM_PAIR8;
+    return (a.H & 1) ? tc::HDM_SINGLE16 : tc::HDM_PAIR16;
+}
 
 bool attn_tc_supported(const AttnArgs &a)
 {
@@ -461,7 +533,7 @@ bool attn_tc_supported(const AttnArgs &a)
     if (Rint > 16 * tc::NWARP * 3) return false;
     for (int d = 0; d < a.meta.D; ++d)
         if (a.meta.L[d] >= (1 << tc::IDX_BITS)) return false;   // idx may reach L
-    if (tc::make_layout(Rint, 1).total > 227 * 1024) return false;
+    if (tc::make_layout(Rint, 1, 2).total > 227 * 1024) return false;
     return true;
 }
 
@@ -470,8 +542,10 @@ int attn_tc_forward(const AttnArgs &a0, cudaStream_t st)
     if (a0.W == 0) return S3D_OK;
     AttnArgs a = a0;
     a.meta = tc::internal_meta(a0.meta);   // kernels work in the internal row numbering
+    const int hdm = attn_tc_head_mode(a0);
     int skip_upto = 0;
-    if (attn_tc_fwd_small_supported(a0)) {
+    // the single-tile kernel serves head pairs of 8 channels and single heads of 16
+    if (hdm != tc::HDM_PAIR16 && attn_tc_fwd_small_supported(a0)) {
         const int rc = attn_tc_forward_small(a0, st);
         if (rc != S3D_OK) return rc;
         skip_upto = tc::QT;
@@ -480,9 +554,9 @@ int attn_tc_forward(const AttnArgs &a0, cudaStream_t st)
     const int mtw = (n_mt + tc::NWARP - 1) / tc::NWARP;
 #define S3D_TC_FWD(DD)                                            \
     switch (mtw) {                                                \
-        case 1: return a.hd == 16 ? tc::launch<DD, 1, true>(a, skip_upto, st) : tc::launch<DD, 1, false>(a, skip_upto, st); \
-        case 2: return a.hd == 16 ? tc::launch<DD, 2, true>(a, skip_upto, st) : tc::launch<DD, 2, false>(a, skip_upto, st); \
-        case 3: return a.hd == 16 ? tc::launch<DD, 3, true>(a, skip_upto, st) : tc::launch<DD, 3, false>(a, skip_upto, st); \
+        case 1: return tc::launch_mode<DD, 1>(a, hdm, skip_upto, st); \
+        case 2: return tc::launch_mode<DD, 2>(a, hdm, skip_upto, st); \
+        case 3: return tc::launch_mode<DD, 3>(a, hdm, skip_upto, st); \
         default: return S3D_ERR_UNSUPPORTED;                      \
     }
     switch (a.meta.D) {

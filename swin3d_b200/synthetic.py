@@ -147,6 +147,20 @@ def concat_scenes(scenes: List[Scene]) -> Scene:
                  np.concatenate([s.rgb for s in scenes]), np.concatenate([s.normal for s in scenes]))
 
 
+def downsample_scene(scene: Scene, stride: int) -> Scene:
+    """The scene as a later backbone stage sees it: voxels merged on a grid `stride` times coarser
+    (coordinates become multiples of `stride`, the tensor stride of that stage, as after
+    MinkowskiEngine pooling, microsoft/Swin3D Swin3D/modules/swin3d_layers.py:188-231); each coarse
+    voxel keeps the signals of its first member."""
+    if stride == 1:
+        return scene
+    c = scene.coords.astype(np.int64).copy()
+    c[:, 1:] = np.floor_divide(c[:, 1:], stride) * stride
+    _, first = np.unique(c, axis=0, return_index=True)
+    first.sort()
+    return Scene(c[first].astype(np.int32), scene.local[first], scene.rgb[first], scene.normal[first])
+
+
 def signal_feats(scene: Scene, crse: str = "XYZ_RGB_NORM") -> np.ndarray:
     """float32 [N,F]: in-voxel position, then colour, then normal, as the cRSE mode asks."""
     cols = [scene.local]

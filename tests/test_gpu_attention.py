@@ -256,10 +256,12 @@ def test_fp16_index_equal_to_L_alias_rows_and_determinism():
         assert rel_err(a[2][i], b[2][i]) < 1e-4
 
 
-@pytest.mark.parametrize("crse,H,ws,shift", [("XYZ_RGB_NORM", 5, 5, 2), ("XYZ_RGB", 3, 5, 0), ("XYZ", 2, 7, 3)])
+@pytest.mark.parametrize("crse,H,ws,shift", [("XYZ_RGB_NORM", 5, 5, 2), ("XYZ_RGB", 3, 5, 0), ("XYZ", 2, 7, 3),
+                                             ("XYZ_RGB_NORM", 4, 7, 0), ("XYZ_RGB_NORM", 10, 7, 3), ("XYZ_RGB", 6, 5, 2)])
 def test_fp16_head_dim_16_tensor_core_path(crse, H, ws, shift):
-    """head_dim 16 (every stage but the first of the reference models): a block serves one head
-    as two 8-channel halves.  Any head count, small and large windows."""
+    """head_dim 16 (every stage but the first of the reference models).  Odd head counts: a block
+    serves one head as two 8-channel halves; even head counts: a block serves two heads, their 16
+    channels split into two planes.  Small and large windows."""
     from tests.gpu_helpers import cuda_fwd_bwd
     p = make_problem(seed=81, n_voxels=1500, grid=26, ws=ws, shift=shift, H=H, hd=16, crse=crse,
                      round_fp16=True)
