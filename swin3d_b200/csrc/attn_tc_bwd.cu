@@ -29,7 +29,7 @@ struct BwdSmem {
     int off_px, px_stride, off_hx, off_py, py_stride, off_s, off_dp, off_idx, off_yt, off_yc, off_misc, total;
 };
 
-__host__ __device__ inline BwdSmem make_bwd_layout(int R, int npx, int nh, int npy, int BKT)
+__host__ __device__ inline BwdSmem make_bwd_layout(int R, int npx, int nh, int npy, int BKT, int n_planes = 1)
 {
     BwdSmem L;
     L.R16 = (R + 15) / 16 * 16;
@@ -44,15 +44,15 @@ __host__ __device__ inline BwdSmem make_bwd_layout(int R, int npx, int nh, int n
     L.off_s = off;  off += BKT * QT * 8;     // float2 scores, then (p, ds) half2 pairs
     L.off_dp = off; off += BKT * QT * 8;     // float2 dO.v
     L.off_idx = off; off += BKT * 2 * QT * 4;
-    L.off_yt = off; off += 2 * BKT * 16 * 2;
+    L.off_yt = off; off += n_planes * 2 * BKT * 16 * 2;
     L.off_yc = off; off += BKT * 12 * 4;
-    L.off_misc = off; off += 1536;
+    L.off_misc = off; off += 2048;
     L.total = off;
     return L;
 }
 
 struct BwdParams {
-    const __half *x0, *x1, *y0, *y1;   // feature rows [N][H][8]: SIDE 0: q, dout, k, v ; SIDE 1: k, v, q, dout
+    const __half *x0, *x1, *y0, *y1;   // feature rows [N][H][hd]: SIDE 0: q, dout, k, v ; SIDE 1: k, v, q, dout
     const __half *o;                   // forward output (for delta)
     const float *lse;
     const __half *t_px0, *t_px1, *t_py0, *t_py1;   // tables of the x / y projections
@@ -65,49 +65,50 @@ struct BwdParams {
     int skip_upto;   // windows with at most this many voxels are left to the single-sweep kernel
 };
 
-// A-operand fragments (m16 x k16, both heads on K) of a table slice for the row tiles this warp owns.
-template <int MTW>
-__device__ __forceinline__ void load_table_a(const __half *tab, const CrseMeta &im, int HC, int co, int wid, int g, int t,
-                                             uint32_t (&a)[MTW][2][2])
-{
-#pragma unroll
-    for (int i = 0; i < MTW; ++i) {
-        const int mt = wid + BW_NWARP * i;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int r0 = table_row(im, mt * 16 + g), r1 = table_row(im, mt * 16 + g + 8);
-            a[i][h][0] = r0 >= 0 ? *reinterpret_cast<const uint32_t *>(tab + (int64_t)r0 * HC + co + h * 8 + 2 * t) : 0u;
-            a[i][h][1] = r1 >= 0 ? *reinterpret_cast<const uint32_t *>(tab + (int64_t)r1 * HC + co + h * 8 + 2 * t) : 0u;
-        }
-    }
-}
-
-// Projection GEMM  P^T[row][(voxel, head)] = T . F^T  for NT n-tiles of 4 voxels, written either in the
-// lane-major layout [row][32] (column = qpos(voxel)) or in the tile layout [voxel][Rp].
-template <int MTW, bool LANE_MAJOR>
-__device__ __forceinline__ void project(const uint32_t (&ta)[MTW][2][2], const __half *feat /*[32][16]*/,
-                                        uint32_t *dst, int n_mt, int Rp, int nvalid, int wid, int g, int t)
+// Projection GEMM  P^T[row][(voxel, slot)] = T . F^T  for 8 n-tiles of 4 voxels, written either in the
+// lane-major layout [row][32] (column = qpos(voxel)) or in the tile layout [voxel][Rp].  `feat` holds
+// the staged rows plane by plane ([plane][plane_rows][16]); with two planes the channel contraction
+// accumulates over them.  RESIDENT: the table fragments come from registers (`ta`, [unit][plane]);
+// otherwise they are fetched from `tab` as they are needed.
+template <int MTW, bool LANE_MAJOR, int HDM, bool RESIDENT, int MTA, int NPA>
+__device__ __forceinline__ void project(const uint32_t (&ta)[MTA][NPA][2][2], const __half *tab, const CrseMeta &meta,
+                                        int HC, int hp, const __half *feat, int plane_rows, uint32_t *dst,
+                                        int n_mt, int Rp, int nvalid, int wid, int g, int t)
 {
     constexpr int NT = 8;
-    uint32_t b[NT][2];
+    constexpr int NPL = HDM == HDM_PAIR16 ? 2 : 1;
+    uint32_t b[NPL][NT][2];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-        const uint32_t wv = 4 * j < nvalid ? *reinterpret_cast<const uint32_t *>(feat + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t) : 0u;
-        b[j][0] = (g & 1) ? 0u : wv;
-        b[j][1] = (g & 1) ? wv : 0u;
-    }
+    for (int pl = 0; pl < NPL; ++pl)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const uint32_t wv = 4 * j < nvalid ? *reinterpret_cast<const uint32_t *>(feat + pl * plane_rows * 16 + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t) : 0u;
+            b[pl][j][0] = (g & 1) ? 0u : wv;
+            b[pl][j][1] = (g & 1) ? wv : 0u;
+        }
 #pragma unroll
     for (int i = 0; i < MTW; ++i) {
         const int mt = wid + BW_NWARP * i;
         if (mt < n_mt) {
             uint32_t d0[NT], d1[NT];
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                if (4 * j < nvalid) {   // n-tiles made of padding voxels only are not computed
-                    mma_k16_h(d0[j], d1[j], ta[i][0][0], ta[i][0][1], ta[i][1][0], ta[i][1][1], b[j][0], b[j][1]);
+            for (int pl = 0; pl < NPL; ++pl) {
+                uint32_t af[2][2];
+                if (!RESIDENT) {
+                    load_table_a_frag<HDM>(af, tab, meta, HC, hp, pl, mt, g, t);
                 } else {
-                    d0[j] = 0u;
-                    d1[j] = 0u;
+                    af[0][0] = ta[i % MTA][pl % NPA][0][0]; af[0][1] = ta[i % MTA][pl % NPA][0][1];
+                    af[1][0] = ta[i % MTA][pl % NPA][1][0]; af[1][1] = ta[i % MTA][pl % NPA][1][1];
+                }
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    if (4 * j < nvalid) {   // n-tiles made of padding voxels only are not computed
+                        if (pl == 0) mma_k16_h(d0[j], d1[j], af[0][0], af[0][1], af[1][0], af[1][1], b[pl][j][0], b[pl][j][1]);
+                        else mma_k16_ha(d0[j], d1[j], af[0][0], af[0][1], af[1][0], af[1][1], b[pl][j][0], b[pl][j][1]);
+                    } else if (pl == 0) {
+                        d0[j] = 0u;
+                        d1[j] = 0u;
+                    }
                 }
             }
             if (LANE_MAJOR) {
@@ -163,16 +164,20 @@ __device__ __forceinline__ void dx_gemm(float (&acc)[2][2][4], const uint2 *s_pd
     }
 }
 
-template <int D, int MTW, int SIDE, bool HD16>
+template <int D, int MTW, int SIDE, int HDM>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
 {
+    constexpr bool HD16 = HDM == HDM_SINGLE16;     // the two slots are halves of one head
+    constexpr bool PAIR16 = HDM == HDM_PAIR16;     // two heads of 16 channels, two planes
+    constexpr int NPL = PAIR16 ? 2 : 1;
+    constexpr int MTP = PAIR16 ? 1 : MTW;          // resident table fragments only with one plane
     constexpr int BKT = bkt_of(SIDE);
     constexpr int NPX = SIDE == 0 ? 2 : 1;   // x-side projections: (P_q, dB) | (P_k)
     constexpr int NH = SIDE == 0 ? 2 : 1;    // x-side histograms:  (ds, p)   | (ds)
     constexpr int NPY = SIDE == 0 ? 1 : 2;   // y-side projections: (P_k)     | (P_q, dB)
     extern __shared__ __align__(16) unsigned char smem[];
-    const BwdSmem L = make_bwd_layout(meta.R, NPX, NH, NPY, BKT);
+    const BwdSmem L = make_bwd_layout(meta.R, NPX, NH, NPY, BKT, NPL);
     uint32_t *s_px = reinterpret_cast<uint32_t *>(smem + L.off_px);   // [NPX][R16][32]
     uint32_t *s_hx = reinterpret_cast<uint32_t *>(smem + L.off_hx);   // [NH][R16][32]
     uint32_t *s_py = reinterpret_cast<uint32_t *>(smem + L.off_py);   // [NPY][KT][Rp]
@@ -180,58 +185,66 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
     uint2 *s_pd = reinterpret_cast<uint2 *>(smem + L.off_s);          // same storage: (p, ds) half2 pairs
     float2 *s_dp = reinterpret_cast<float2 *>(smem + L.off_dp);       // [BKT][32]
     uint32_t *s_idx = reinterpret_cast<uint32_t *>(smem + L.off_idx); // [BKT][2][32]
-    __half *s_y0 = reinterpret_cast<__half *>(smem + L.off_yt);       // [BKT][16]
-    __half *s_y1 = s_y0 + BKT * 16;
+    __half *s_y0 = reinterpret_cast<__half *>(smem + L.off_yt);       // [plane][BKT][16]
+    __half *s_y1 = s_y0 + NPL * BKT * 16;                             // [plane][BKT][16]
     float *s_yc = reinterpret_cast<float *>(smem + L.off_yc);         // [BKT][12]
-    float *s_ylse = reinterpret_cast<float *>(smem + L.off_misc);     // [BKT][2]  (SIDE 1)
-    float *s_ydel = s_ylse + 2 * BKT;                                 // [BKT][2]  (SIDE 1)
-    float *s_xlse = s_ydel + 2 * BKT;                                  // [32][2]   (SIDE 0)
-    float *s_xdel = s_xlse + 64;                                      // [32][2]   (SIDE 0)
-    int *s_xrow = reinterpret_cast<int *>(s_xdel + 64);               // [32]
-    __half *s_x0 = reinterpret_cast<__half *>(smem + L.off_s);        // [32][16] aliases s_s (set-up only)
-    __half *s_x1 = reinterpret_cast<__half *>(smem + L.off_dp);       // [32][16] aliases s_dp (set-up only)
+    float *s_ylse = reinterpret_cast<float *>(smem + L.off_misc);     // [BKT][2]          (SIDE 1)
+    float *s_ydel = s_ylse + 2 * BKT;                                 // [plane][BKT][2]   (SIDE 1)
+    float *s_xlse = s_ydel + 2 * 2 * BKT;                             // [32][2]           (SIDE 0)
+    float *s_xdel = s_xlse + 64;                                      // [plane][32][2]    (SIDE 0)
+    int *s_xrow = reinterpret_cast<int *>(s_xdel + 128);              // [32]
+    __half *s_x0 = reinterpret_cast<__half *>(smem + L.off_s);        // [plane][32][16] aliases s_s (set-up, table gradients)
+    __half *s_x1 = reinterpret_cast<__half *>(smem + L.off_dp);       // [plane][32][16] aliases s_dp
     float *s_red = reinterpret_cast<float *>(smem + L.off_px);        // [16][32][16] aliases s_px (epilogue)
     float *s_red2 = s_red + BW_NWARP * QT * 16;                       // [32][16]
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int hp = blockIdx.y, H = P.H;
-    // head_dim 16: the block serves head hp; its two 8-channel halves stand in for the two heads
-    const int HC = H * (HD16 ? 16 : 8), co = hp * 16;
+    const int HC = H * (HDM == HDM_PAIR8 ? 8 : 16);
     const int n_mt = L.R16 / 16, Rp = L.Rp;
     const int pxw = L.px_stride / 4, pyw = L.py_stride / 4;
     const int mypos = qpos(lane);
     constexpr float LOG2E = 1.4426950408889634f;
 
-    // ---- resident table fragments --------------------------------------------------------------------
-    uint32_t ta_px0[MTW][2][2], ta_px1[MTW][2][2], ta_py0[MTW][2][2], ta_py1[MTW][2][2];
-    load_table_a<MTW>(P.t_px0, meta, HC, co, wid, g, t, ta_px0);
-    load_table_a<MTW>(P.t_py0, meta, HC, co, wid, g, t, ta_py0);
-    if (SIDE == 0) load_table_a<MTW>(P.t_px1, meta, HC, co, wid, g, t, ta_px1);
-    else load_table_a<MTW>(P.t_py1, meta, HC, co, wid, g, t, ta_py1);
-    // B fragments (k = row, n = channel) of T0 for dX += H0 . T0
-    uint32_t t0B[MTW][2][2];
+    // ---- resident table fragments: those of the y side (used once per y tile) in every mode, those of
+    //      the x side (used once per item) only with one plane --------------------------------------------
+    uint32_t ta_py0[MTW][NPL][2][2], ta_py1[SIDE == 1 ? MTW : 1][NPL][2][2];
+    uint32_t ta_px0[MTP][1][2][2], ta_px1[MTP][1][2][2];
+    uint32_t t0B[MTP][2][2];   // B fragments (k = row, n = channel) of T0 for dX += H0 . T0
 #pragma unroll
-    for (int i = 0; i < MTW; ++i) {
-        const int ks = wid + BW_NWARP * i;
+    for (int i = 0; i < MTW; ++i)
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+        for (int pl = 0; pl < NPL; ++pl) {
+            const int mt = wid + BW_NWARP * i;
+            load_table_a_frag<HDM>(ta_py0[i][pl], P.t_py0, meta, HC, hp, pl, mt, g, t);
+            if (SIDE == 1) load_table_a_frag<HDM>(ta_py1[i % (SIDE == 1 ? MTW : 1)][pl], P.t_py1, meta, HC, hp, pl, mt, g, t);
+        }
+    if (!PAIR16) {
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int ra = table_row(meta, ks * 16 + 2 * t + 8 * half), rb = table_row(meta, ks * 16 + 2 * t + 8 * half + 1);
-                const __half lo = ra >= 0 ? P.t_px0[(int64_t)ra * HC + co + h * 8 + g] : __float2half(0.f);
-                const __half hi = rb >= 0 ? P.t_px0[(int64_t)rb * HC + co + h * 8 + g] : __float2half(0.f);
-                t0B[i][h][half] = h2_as_u32(__halves2half2(lo, hi));
-            }
+        for (int i = 0; i < MTP; ++i) {
+            const int mt = wid + BW_NWARP * i;
+            load_table_a_frag<HDM>(ta_px0[i][0], P.t_px0, meta, HC, hp, 0, mt, g, t);
+            if (SIDE == 0) load_table_a_frag<HDM>(ta_px1[i][0], P.t_px1, meta, HC, hp, 0, mt, g, t);
+            load_table_b_frag<HDM>(t0B[i], P.t_px0, meta, HC, hp, 0, mt, g, t);
+        }
     }
-    // table-gradient accumulators: [hist][row tile of this warp][head][c-frag]
-    float dt_acc[NH][MTW][2][4];
+    // table-gradient accumulators: [plane][hist][row tile of this warp][slot][c-frag]
+    float dt_acc[NPL][NH][MTW][2][4];
 #pragma unroll
-    for (int a = 0; a < NH; ++a)
+    for (int pl = 0; pl < NPL; ++pl)
 #pragma unroll
-        for (int i = 0; i < MTW; ++i)
+        for (int a = 0; a < NH; ++a)
 #pragma unroll
-            for (int h = 0; h < 2; ++h) dt_acc[a][i][h][0] = dt_acc[a][i][h][1] = dt_acc[a][i][h][2] = dt_acc[a][i][h][3] = 0.f;
+            for (int i = 0; i < MTW; ++i)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    dt_acc[pl][a][i][h][0] = dt_acc[pl][a][i][h][1] = dt_acc[pl][a][i][h][2] = dt_acc[pl][a][i][h][3] = 0.f;
+    // pair GEMMs dX += E^T . Y run in otherwise idle warps, one (product, plane) each:
+    //   warp 15: ds . Y0 plane 0   warp 14: p . Y1 plane 0 (SIDE 1)   warps 13 / 12: the same for plane 1
+    const int dx_which = (wid & 1) ? 0 : 1;
+    const int dx_plane = wid >= BW_NWARP - 2 ? 0 : 1;
+    const bool dx_warp = wid >= BW_NWARP - (PAIR16 ? 4 : 2) && (SIDE == 1 || dx_which == 0);
 
     for (int64_t w = blockIdx.x; w < P.W; w += gridDim.x) {
         const int n = __ldg(P.w_sizes + w);
@@ -245,17 +258,18 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
 #pragma unroll
             for (int d = 0; d < D; ++d)
                 cx[d] = lane < nx ? __ldg(P.n_coords + (int64_t)(base + x0 + lane) * D + d) : 0.f;
-            if (tid < 128) {
-                const int xi = tid >> 2, which = (tid >> 1) & 1, hf = tid & 1;
+            if (tid < 128 * NPL) {
+                const int xi = (tid >> 2) & 31, which = (tid >> 1) & 1, hf = tid & 1, pl = tid >> 7;
                 uint4 val = make_uint4(0, 0, 0, 0);
                 if (xi < nx) {
                     const int row = __ldg(P.n2n + base + x0 + xi);
-                    if (which == 0 && hf == 0) s_xrow[xi] = row;
+                    if (which == 0 && hf == 0 && pl == 0) s_xrow[xi] = row;
                     const __half *src = which ? P.x1 : P.x0;
-                    val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)row * HC + co + hf * 8));
+                    const int64_t goff = (int64_t)row * HC + slot_offset<HDM>(hp, hf, pl);
+                    val = __ldg(reinterpret_cast<const uint4 *>(src + goff));
                     if (SIDE == 0 && which == 1) {
-                        // delta[x][head hf] = sum_c dO . O ; lse
-                        const uint4 ov = __ldg(reinterpret_cast<const uint4 *>(P.o + (int64_t)row * HC + co + hf * 8));
+                        // delta[x][slot hf] = sum_c dO . O (this plane's 8 channels) ; lse
+                        const uint4 ov = __ldg(reinterpret_cast<const uint4 *>(P.o + goff));
                         const __half2 *a2 = reinterpret_cast<const __half2 *>(&val);
                         const __half2 *b2 = reinterpret_cast<const __half2 *>(&ov);
                         float acc = 0.f;
@@ -264,14 +278,14 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                             const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
                             acc += fa.x * fb.x + fa.y * fb.y;
                         }
-                        s_xdel[xi * 2 + hf] = acc;
-                        s_xlse[xi * 2 + hf] = __ldg(P.lse + (int64_t)row * H + (HD16 ? hp : 2 * hp + hf));
+                        s_xdel[pl * 64 + xi * 2 + hf] = acc;
+                        if (pl == 0) s_xlse[xi * 2 + hf] = __ldg(P.lse + (int64_t)row * H + (HD16 ? hp : 2 * hp + hf));
                     }
                 } else if (SIDE == 0 && which == 1) {
-                    s_xdel[xi * 2 + hf] = 0.f;
-                    s_xlse[xi * 2 + hf] = 0.f;
+                    s_xdel[pl * 64 + xi * 2 + hf] = 0.f;
+                    if (pl == 0) s_xlse[xi * 2 + hf] = 0.f;
                 }
-                *reinterpret_cast<uint4 *>((which ? s_x1 : s_x0) + xi * 16 + hf * 8) = val;
+                *reinterpret_cast<uint4 *>((which ? s_x1 : s_x0) + pl * 512 + xi * 16 + hf * 8) = val;
             }
             for (int i = tid; i < NH * L.R16 * QT / 4; i += BW_THREADS)
                 reinterpret_cast<uint4 *>(s_hx)[i] = make_uint4(0, 0, 0, 0);
@@ -280,60 +294,67 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
             if (SIDE == 0) {
                 xlse[0] = s_xlse[lane * 2]; xlse[1] = s_xlse[lane * 2 + 1];
                 xdel[0] = s_xdel[lane * 2]; xdel[1] = s_xdel[lane * 2 + 1];
+                if (PAIR16) { xdel[0] += s_xdel[64 + lane * 2]; xdel[1] += s_xdel[64 + lane * 2 + 1]; }
                 if (HD16) xdel[0] = xdel[1] = xdel[0] + xdel[1];   // delta of the whole head
             }
             // block-diagonal B fragments of X0^T / X1^T for the n-tile this warp multiplies in S0 / dPV0
-            uint32_t xS[2][2];   // [X0 | X1][b0, b1] for n-tile wid % 8
-#pragma unroll
-            for (int a = 0; a < 2; ++a) {
-                const __half *src = a == 0 ? s_x0 : s_x1;
-                const int j = wid & 7;
-                const uint32_t wv = *reinterpret_cast<const uint32_t *>(src + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
-                xS[a][0] = (g & 1) ? 0u : wv;
-                xS[a][1] = (g & 1) ? wv : 0u;
-            }
-            // B fragments (k = position, n = channel) of X0 / X1 for the table-gradient GEMMs
-            uint32_t xTB[NH][2][2][2];   // [hist][k-step][head][b0,b1]
-#pragma unroll
-            for (int a = 0; a < NH; ++a) {
-                // SIDE 0: hist 0 (ds) pairs with X0 = Q, hist 1 (p) with X1 = dO ; SIDE 1: hist 0 with X0 = K
-                const __half *src = a == 0 ? s_x0 : s_x1;
-#pragma unroll
-                for (int ks = 0; ks < 2; ++ks)
-#pragma unroll
-                    for (int h = 0; h < 2; ++h)
-#pragma unroll
-                        for (int half = 0; half < 2; ++half) {
-                            const int p0 = 16 * ks + 4 * t + 2 * half, p1 = p0 + 1;
-                            const int xa = (p0 >> 2) + 8 * (p0 & 3), xb = (p1 >> 2) + 8 * (p1 & 3);
-                            xTB[a][ks][h][half] = h2_as_u32(__halves2half2(src[xa * 16 + h * 8 + g], src[xb * 16 + h * 8 + g]));
-                        }
-            }
-            project<MTW, true>(ta_px0, s_x0, s_px, n_mt, Rp, nx, wid, g, t);
-            if (SIDE == 0) project<MTW, true>(ta_px1, s_x1, s_px + pxw, n_mt, Rp, nx, wid, g, t);
-
-            float dxacc[2][2][2][4];   // [which: ds.Y0 | p.Y1][head][m-tile][c-frag], warps 15 / 14
+            uint32_t xS[2][NPL][2];   // [X0 | X1][plane][b0, b1] for n-tile wid % 8
 #pragma unroll
             for (int a = 0; a < 2; ++a)
 #pragma unroll
-                for (int h = 0; h < 2; ++h)
+                for (int pl = 0; pl < NPL; ++pl) {
+                    const __half *src = (a == 0 ? s_x0 : s_x1) + pl * 512;
+                    const int j = wid & 7;
+                    const uint32_t wv = *reinterpret_cast<const uint32_t *>(src + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+                    xS[a][pl][0] = (g & 1) ? 0u : wv;
+                    xS[a][pl][1] = (g & 1) ? wv : 0u;
+                }
+            // one-plane modes: B fragments (k = position, n = channel) of X0 / X1 for the table-gradient
+            // GEMMs, kept in registers over the y loop (the staged rows are overwritten by it); with two
+            // planes the rows are staged again after the loop instead
+            constexpr int NHP = PAIR16 ? 1 : NH;
+            uint32_t xTB[NHP][2][2][2];   // [hist][k-step][slot][b0,b1]
+            if (!PAIR16) {
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) dxacc[a][h][i][0] = dxacc[a][h][i][1] = dxacc[a][h][i][2] = dxacc[a][h][i][3] = 0.f;
+                for (int a = 0; a < NHP; ++a) {
+                    // SIDE 0: hist 0 (ds) pairs with X0 = Q, hist 1 (p) with X1 = dO ; SIDE 1: hist 0 with X0 = K
+                    const __half *src = a == 0 ? s_x0 : s_x1;
+#pragma unroll
+                    for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+#pragma unroll
+                            for (int half = 0; half < 2; ++half) {
+                                const int p0 = 16 * ks + 4 * t + 2 * half, p1 = p0 + 1;
+                                const int xa = (p0 >> 2) + 8 * (p0 & 3), xb = (p1 >> 2) + 8 * (p1 & 3);
+                                xTB[a][ks][h][half] = h2_as_u32(__halves2half2(src[xa * 16 + h * 8 + g], src[xb * 16 + h * 8 + g]));
+                            }
+                }
+            }
+            project<MTW, true, HDM, !PAIR16>(ta_px0, P.t_px0, meta, HC, hp, s_x0, 32, s_px, n_mt, Rp, nx, wid, g, t);
+            if (SIDE == 0) project<MTW, true, HDM, !PAIR16>(ta_px1, P.t_px1, meta, HC, hp, s_x1, 32, s_px + pxw, n_mt, Rp, nx, wid, g, t);
+
+            float dxa[2][2][4];   // [slot][m-tile][c-frag] of this warp's pair GEMM (see dx_warp)
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) dxa[h][i][0] = dxa[h][i][1] = dxa[h][i][2] = dxa[h][i][3] = 0.f;
 
             for (int y0 = 0; y0 < n; y0 += BKT) {
                 const int ny = min(BKT, n - y0);
                 __syncthreads();
                 // ---- stage the y tile ---------------------------------------------------------------
-                if (tid < 4 * BKT) {
-                    const int yi = tid >> 2, which = (tid >> 1) & 1, hf = tid & 1;
+                if (tid < 4 * BKT * NPL) {
+                    const int yi = (tid >> 2) % BKT, which = (tid >> 1) & 1, hf = tid & 1, pl = tid / (4 * BKT);
                     uint4 val = make_uint4(0, 0, 0, 0);
                     float del = 0.f, ls = 0.f;
                     if (yi < ny) {
                         const int row = __ldg(P.n2n + base + y0 + yi);
                         const __half *src = which ? P.y1 : P.y0;
-                        val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)row * HC + co + hf * 8));
+                        const int64_t goff = (int64_t)row * HC + slot_offset<HDM>(hp, hf, pl);
+                        val = __ldg(reinterpret_cast<const uint4 *>(src + goff));
                         if (SIDE == 1 && which == 1) {
-                            const uint4 ov = __ldg(reinterpret_cast<const uint4 *>(P.o + (int64_t)row * HC + co + hf * 8));
+                            const uint4 ov = __ldg(reinterpret_cast<const uint4 *>(P.o + goff));
                             const __half2 *a2 = reinterpret_cast<const __half2 *>(&val);
                             const __half2 *b2 = reinterpret_cast<const __half2 *>(&ov);
 #pragma unroll
@@ -341,22 +362,23 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                                 const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
                                 del += fa.x * fb.x + fa.y * fb.y;
                             }
-                            ls = __ldg(P.lse + (int64_t)row * H + (HD16 ? hp : 2 * hp + hf));
+                            if (pl == 0) ls = __ldg(P.lse + (int64_t)row * H + (HD16 ? hp : 2 * hp + hf));
                         }
                     }
                     if (SIDE == 1 && which == 1) {
-                        s_ydel[yi * 2 + hf] = del;
-                        s_ylse[yi * 2 + hf] = ls;
+                        s_ydel[pl * 2 * BKT + yi * 2 + hf] = del;
+                        if (pl == 0) s_ylse[yi * 2 + hf] = ls;
                     }
-                    *reinterpret_cast<uint4 *>((which ? s_y1 : s_y0) + yi * 16 + hf * 8) = val;
-                } else if (tid < 4 * BKT + BKT * D) {
-                    const int e = tid - 4 * BKT, yi = e / D, d = e - yi * D;
+                    *reinterpret_cast<uint4 *>((which ? s_y1 : s_y0) + pl * BKT * 16 + yi * 16 + hf * 8) = val;
+                }
+                for (int e = (tid + BW_THREADS / 2) % BW_THREADS; e < BKT * D; e += BW_THREADS) {   // upper half first: it stages no rows
+                    const int yi = e / D, d = e - yi * D;
                     s_yc[yi * 12 + d] = yi < ny ? __ldg(P.n_coords + (int64_t)(base + y0 + yi) * D + d) : 0.f;
                 }
                 __syncthreads();
                 // ---- y-side projections; S0 = Y0 . X0^T and dPV0 = Y1 . X1^T, one (m-tile, n-tile) per warp ----
-                project<MTW, false>(ta_py0, s_y0, s_py, n_mt, Rp, ny, wid, g, t);
-                if (SIDE == 1) project<MTW, false>(ta_py1, s_y1, s_py + pyw, n_mt, Rp, ny, wid, g, t);
+                project<MTW, false, HDM, true>(ta_py0, P.t_py0, meta, HC, hp, s_y0, BKT, s_py, n_mt, Rp, ny, wid, g, t);
+                if (SIDE == 1) project<MTW, false, HDM, true>(ta_py1, P.t_py1, meta, HC, hp, s_y1, BKT, s_py + pyw, n_mt, Rp, ny, wid, g, t);
                 {
                     constexpr int PER = (BKT / 16) * 8;     // (m-tile, n-tile) units per product
 #pragma unroll
@@ -364,14 +386,18 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                         const int u = u0 + wid;
                         const int a = u / PER, r = u % PER, mt = r >> 3, j = r & 7;   // y rows 16mt.., x columns 4j..
                         if (16 * mt < ny && 4 * j < nx) {
-                            const __half *ysrc = (a == 0 ? s_y0 : s_y1) + mt * 16 * 16;
-                            const uint32_t a0 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 2 * t);
-                            const uint32_t a1 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 2 * t);
-                            const uint32_t a2 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 8 + 2 * t);
-                            const uint32_t a3 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 8 + 2 * t);
                             float c[4];
-                            if (a == 0) mma_k16_z(c, a0, a1, a2, a3, xS[0][0], xS[0][1]);
-                            else mma_k16_z(c, a0, a1, a2, a3, xS[1][0], xS[1][1]);
+#pragma unroll
+                            for (int pl = 0; pl < NPL; ++pl) {
+                                const __half *ysrc = (a == 0 ? s_y0 : s_y1) + pl * BKT * 16 + mt * 16 * 16;
+                                const uint32_t a0 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 2 * t);
+                                const uint32_t a1 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 2 * t);
+                                const uint32_t a2 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 8 + 2 * t);
+                                const uint32_t a3 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 8 + 2 * t);
+                                const uint32_t b0 = a == 0 ? xS[0][pl][0] : xS[1][pl][0], b1 = a == 0 ? xS[0][pl][1] : xS[1][pl][1];
+                                if (pl == 0) mma_k16_z(c, a0, a1, a2, a3, b0, b1);
+                                else mma_k16(c, a0, a1, a2, a3, b0, b1);
+                            }
                             float2 *dst = (a == 0 ? s_s : s_dp) + mt * 16 * QT;
                             dst[g * QT + 4 * j + t] = make_float2(c[0], c[1]);
                             dst[(g + 8) * QT + 4 * j + t] = make_float2(c[2], c[3]);
@@ -407,8 +433,12 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                         const float2 s0 = s_s[yy * QT + lane];
                         const float2 dp0 = s_dp[yy * QT + lane];
                         float ls0, ls1, de0, de1;
-                        if (SIDE == 0) { ls0 = xlse[0]; ls1 = xlse[1]; de0 = xdel[0]; de1 = xdel[1]; }
-                        else { ls0 = s_ylse[yy * 2]; ls1 = s_ylse[yy * 2 + 1]; de0 = s_ydel[yy * 2]; de1 = s_ydel[yy * 2 + 1]; }
+                        if (SIDE == 0) {
+                            ls0 = xlse[0]; ls1 = xlse[1]; de0 = xdel[0]; de1 = xdel[1];
+                        } else {
+                            ls0 = s_ylse[yy * 2]; ls1 = s_ylse[yy * 2 + 1]; de0 = s_ydel[yy * 2]; de1 = s_ydel[yy * 2 + 1];
+                            if (PAIR16) { de0 += s_ydel[2 * BKT + yy * 2]; de1 += s_ydel[2 * BKT + yy * 2 + 1]; }
+                        }
                         if (HD16 && SIDE == 1) de0 = de1 = de0 + de1;
                         float sc0 = s0.x + bs.x, sc1 = s0.y + bs.y, dq0 = dp0.x + bd.x, dq1 = dp0.y + bd.y;
                         if (HD16) { sc0 = sc1 = sc0 + sc1; dq0 = dq1 = dq0 + dq1; }   // halves of one head add up
@@ -444,17 +474,33 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                         hist_add4<1, NH>(cell, pxw, off, vals, ny - y4);
                     }
                 }
-                // ---- dX += dS^T-tile . Y0 (warp 15) ; SIDE 1: dX1 += P^T-tile . Y1 (warp 14), tensor cores ----
-                if (wid == BW_NWARP - 1) {
-                    dx_gemm<0>(dxacc[0], s_pd, s_y0, 0, g, t);
-                    if (BKT > 16 && ny > 16) dx_gemm<0>(dxacc[0], s_pd, s_y0, 16, g, t);
-                }
-                if (SIDE == 1 && wid == BW_NWARP - 2) {
-                    dx_gemm<1>(dxacc[1], s_pd, s_y1, 0, g, t);
-                    if (BKT > 16 && ny > 16) dx_gemm<1>(dxacc[1], s_pd, s_y1, 16, g, t);
+                // ---- pair GEMMs on the tensor cores: dX += dS^T-tile . Y0 ; SIDE 1: dX1 += P^T-tile . Y1 ------
+                if (dx_warp) {
+                    if (dx_which == 0) {
+                        const __half *ysrc = s_y0 + dx_plane * BKT * 16;
+                        dx_gemm<0>(dxa, s_pd, ysrc, 0, g, t);
+                        if (BKT > 16 && ny > 16) dx_gemm<0>(dxa, s_pd, ysrc, 16, g, t);
+                    } else {
+                        const __half *ysrc = s_y1 + dx_plane * BKT * 16;
+                        dx_gemm<1>(dxa, s_pd, ysrc, 0, g, t);
+                        if (BKT > 16 && ny > 16) dx_gemm<1>(dxa, s_pd, ysrc, 16, g, t);
+                    }
                 }
             }  // y tiles
             __syncthreads();
+            if (PAIR16) {
+                // the pair arrays are dead: stage the x rows again for the table-gradient GEMMs
+                if (tid < 128 * NPL) {
+                    const int xi = (tid >> 2) & 31, which = (tid >> 1) & 1, hf = tid & 1, pl = tid >> 7;
+                    uint4 val = make_uint4(0, 0, 0, 0);
+                    if (xi < nx && (which == 0 || NH == 2)) {
+                        const __half *src = which ? P.x1 : P.x0;
+                        val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)s_xrow[xi] * HC + slot_offset<HDM>(hp, hf, pl)));
+                    }
+                    *reinterpret_cast<uint4 *>((which ? s_x1 : s_x0) + pl * 512 + xi * 16 + hf * 8) = val;
+                }
+                __syncthreads();
+            }
             // ---- table gradients: dT[a][row][c] += sum_x H_a[row][x] X_a[x][c] --------------------------------
 #pragma unroll
             for (int i = 0; i < MTW; ++i) {
@@ -467,92 +513,126 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                             // lane (g,t): rows g and g+8 of the tile, positions 16ks+4t .. +3  <->  k = 2t, 2t+1, 2t+8, 2t+9
                             const uint4 u = *reinterpret_cast<const uint4 *>(s_hx + a * pxw + (mt * 16 + g) * QT + 16 * ks + 4 * t);
                             const uint4 v2 = *reinterpret_cast<const uint4 *>(s_hx + a * pxw + (mt * 16 + g + 8) * QT + 16 * ks + 4 * t);
-                            mma_k16(dt_acc[a][i][0], pack_lo(u.x, u.y), pack_lo(v2.x, v2.y), pack_lo(u.z, u.w), pack_lo(v2.z, v2.w),
-                                    xTB[a][ks][0][0], xTB[a][ks][0][1]);
-                            mma_k16(dt_acc[a][i][1], pack_hi(u.x, u.y), pack_hi(v2.x, v2.y), pack_hi(u.z, u.w), pack_hi(v2.z, v2.w),
-                                    xTB[a][ks][1][0], xTB[a][ks][1][1]);
+#pragma unroll
+                            for (int pl = 0; pl < NPL; ++pl) {
+                                uint32_t bf[2][2];
+                                if (PAIR16) {
+                                    const __half *src = (a == 0 ? s_x0 : s_x1) + pl * 512;
+#pragma unroll
+                                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                                        for (int half = 0; half < 2; ++half) {
+                                            const int p0 = 16 * ks + 4 * t + 2 * half, p1 = p0 + 1;
+                                            const int xa = (p0 >> 2) + 8 * (p0 & 3), xb = (p1 >> 2) + 8 * (p1 & 3);
+                                            bf[h][half] = h2_as_u32(__halves2half2(src[xa * 16 + h * 8 + g], src[xb * 16 + h * 8 + g]));
+                                        }
+                                } else {
+                                    bf[0][0] = xTB[a % NHP][ks][0][0]; bf[0][1] = xTB[a % NHP][ks][0][1];
+                                    bf[1][0] = xTB[a % NHP][ks][1][0]; bf[1][1] = xTB[a % NHP][ks][1][1];
+                                }
+                                mma_k16(dt_acc[pl][a][i][0], pack_lo(u.x, u.y), pack_lo(v2.x, v2.y), pack_lo(u.z, u.w), pack_lo(v2.z, v2.w),
+                                        bf[0][0], bf[0][1]);
+                                mma_k16(dt_acc[pl][a][i][1], pack_hi(u.x, u.y), pack_hi(v2.x, v2.y), pack_hi(u.z, u.w), pack_hi(v2.z, v2.w),
+                                        bf[1][0], bf[1][1]);
+                            }
                         }
                 }
             }
-            // ---- dX += H0 . T0 (row range split over the warps), reduce, store ---------------------------------
-            float part[2][2][4];
+            // ---- per plane: dX += H0 . T0 (row range split over the warps), reduce, store ------------------------
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int pl = 0; pl < NPL; ++pl) {
+                const int own0 = BW_NWARP - 1 - 2 * pl, own1 = BW_NWARP - 2 - 2 * pl;   // warps holding ds.Y0 / p.Y1 of this plane
+                float part[2][2][4];
 #pragma unroll
-                for (int i = 0; i < 2; ++i)
+                for (int h = 0; h < 2; ++h)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) part[h][i][e] = (wid == BW_NWARP - 1) ? dxacc[0][h][i][e] : 0.f;
+                    for (int i = 0; i < 2; ++i)
 #pragma unroll
-            for (int i = 0; i < MTW; ++i) {
-                const int ks = wid + BW_NWARP * i;
-                if (ks < n_mt) {
-                    const uint4 y0v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t) * QT + 4 * g);
-                    const uint4 y1v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t + 1) * QT + 4 * g);
-                    const uint4 y2v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t + 8) * QT + 4 * g);
-                    const uint4 y3v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t + 9) * QT + 4 * g);
-                    // m-tile 0: queries g, g+8 (columns .x, .y) ; m-tile 1: queries g+16, g+24 (.z, .w)
-                    mma_k16(part[0][0], pack_lo(y0v.x, y1v.x), pack_lo(y0v.y, y1v.y), pack_lo(y2v.x, y3v.x), pack_lo(y2v.y, y3v.y), t0B[i][0][0], t0B[i][0][1]);
-                    mma_k16(part[1][0], pack_hi(y0v.x, y1v.x), pack_hi(y0v.y, y1v.y), pack_hi(y2v.x, y3v.x), pack_hi(y2v.y, y3v.y), t0B[i][1][0], t0B[i][1][1]);
-                    mma_k16(part[0][1], pack_lo(y0v.z, y1v.z), pack_lo(y0v.w, y1v.w), pack_lo(y2v.z, y3v.z), pack_lo(y2v.w, y3v.w), t0B[i][0][0], t0B[i][0][1]);
-                    mma_k16(part[1][1], pack_hi(y0v.z, y1v.z), pack_hi(y0v.w, y1v.w), pack_hi(y2v.z, y3v.z), pack_hi(y2v.w, y3v.w), t0B[i][1][0], t0B[i][1][1]);
-                }
-            }
-            __syncthreads();   // every warp is done with s_px (phase 1 look-ups) before it becomes s_red
+                        for (int e = 0; e < 4; ++e) part[h][i][e] = (wid == own0) ? dxa[h][i][e] : 0.f;
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int i = 0; i < 2; ++i)
-#pragma unroll
-                    for (int rr = 0; rr < 2; ++rr) {
-                        const int xx = 16 * i + g + 8 * rr;
-                        *reinterpret_cast<float2 *>(s_red + (wid * QT + xx) * 16 + h * 8 + 2 * t) =
-                            make_float2(part[h][i][2 * rr], part[h][i][2 * rr + 1]);
-                        if (SIDE == 1 && wid == BW_NWARP - 2)
-                            *reinterpret_cast<float2 *>(s_red2 + xx * 16 + h * 8 + 2 * t) =
-                                make_float2(dxacc[1][h][i][2 * rr], dxacc[1][h][i][2 * rr + 1]);
+                for (int i = 0; i < MTW; ++i) {
+                    const int ks = wid + BW_NWARP * i;
+                    if (ks < n_mt) {
+                        uint32_t bf[2][2];
+                        if (PAIR16) {
+                            load_table_b_frag<HDM>(bf, P.t_px0, meta, HC, hp, pl, ks, g, t);
+                        } else {
+                            bf[0][0] = t0B[i % MTP][0][0]; bf[0][1] = t0B[i % MTP][0][1];
+                            bf[1][0] = t0B[i % MTP][1][0]; bf[1][1] = t0B[i % MTP][1][1];
+                        }
+                        const uint4 y0v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t) * QT + 4 * g);
+                        const uint4 y1v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t + 1) * QT + 4 * g);
+                        const uint4 y2v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t + 8) * QT + 4 * g);
+                        const uint4 y3v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t + 9) * QT + 4 * g);
+                        // m-tile 0: queries g, g+8 (columns .x, .y) ; m-tile 1: queries g+16, g+24 (.z, .w)
+                        mma_k16(part[0][0], pack_lo(y0v.x, y1v.x), pack_lo(y0v.y, y1v.y), pack_lo(y2v.x, y3v.x), pack_lo(y2v.y, y3v.y), bf[0][0], bf[0][1]);
+                        mma_k16(part[1][0], pack_hi(y0v.x, y1v.x), pack_hi(y0v.y, y1v.y), pack_hi(y2v.x, y3v.x), pack_hi(y2v.y, y3v.y), bf[1][0], bf[1][1]);
+                        mma_k16(part[0][1], pack_lo(y0v.z, y1v.z), pack_lo(y0v.w, y1v.w), pack_lo(y2v.z, y3v.z), pack_lo(y2v.w, y3v.w), bf[0][0], bf[0][1]);
+                        mma_k16(part[1][1], pack_hi(y0v.z, y1v.z), pack_hi(y0v.w, y1v.w), pack_hi(y2v.z, y3v.z), pack_hi(y2v.w, y3v.w), bf[1][0], bf[1][1]);
                     }
-            __syncthreads();
-            {
-                const int xx = tid >> 4, ch = tid & 15;
-                if (xx < nx) {
-                    float a = 0.f;
-#pragma unroll
-                    for (int ww = 0; ww < BW_NWARP; ++ww) a += s_red[(ww * QT + xx) * 16 + ch];
-                    const int64_t row = s_xrow[xx];
-                    P.dx0[row * HC + co + ch] = __float2half_rn(a);
-                    if (SIDE == 1) P.dx1[row * HC + co + ch] = __float2half_rn(s_red2[xx * 16 + ch]);
                 }
-            }
+                // every warp is done with s_px (phase 1 look-ups) before it becomes s_red, and with the
+                // previous plane's reduction
+                __syncthreads();
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i)
+#pragma unroll
+                        for (int rr = 0; rr < 2; ++rr) {
+                            const int xx = 16 * i + g + 8 * rr;
+                            *reinterpret_cast<float2 *>(s_red + (wid * QT + xx) * 16 + h * 8 + 2 * t) =
+                                make_float2(part[h][i][2 * rr], part[h][i][2 * rr + 1]);
+                            if (SIDE == 1 && wid == own1)
+                                *reinterpret_cast<float2 *>(s_red2 + xx * 16 + h * 8 + 2 * t) =
+                                    make_float2(dxa[h][i][2 * rr], dxa[h][i][2 * rr + 1]);
+                        }
+                __syncthreads();
+                {
+                    const int xx = tid >> 4, ch = tid & 15;
+                    if (xx < nx) {
+                        float a = 0.f;
+#pragma unroll
+                        for (int ww = 0; ww < BW_NWARP; ++ww) a += s_red[(ww * QT + xx) * 16 + ch];
+                        const int64_t o = (int64_t)s_xrow[xx] * HC + slot_offset<HDM>(hp, ch >> 3, pl) + (ch & 7);
+                        P.dx0[o] = __float2half_rn(a);
+                        if (SIDE == 1) P.dx1[o] = __float2half_rn(s_red2[xx * 16 + ch]);
+                    }
+                }
+            }  // planes
         }  // x tiles
     }      // windows
 
     // ---- flush the table gradients of this block ---------------------------------------------------------------
 #pragma unroll
-    for (int a = 0; a < NH; ++a) {
-        float *dst = a == 0 ? P.dt0 : P.dt1;
+    for (int pl = 0; pl < NPL; ++pl)
 #pragma unroll
-        for (int i = 0; i < MTW; ++i) {
-            const int mt = wid + BW_NWARP * i;
+        for (int a = 0; a < NH; ++a) {
+            float *dst = a == 0 ? P.dt0 : P.dt1;
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int i = 0; i < MTW; ++i) {
+                const int mt = wid + BW_NWARP * i;
 #pragma unroll
-                for (int rr = 0; rr < 2; ++rr) {
-                    const int row = table_row(meta, mt * 16 + g + 8 * rr);   // aliases flush into the row they stand for
-                    if (mt < n_mt && row >= 0) {
-                        float *p = dst + (int64_t)row * HC + co + h * 8 + 2 * t;
-                        atomicAdd(p, dt_acc[a][i][h][2 * rr]);
-                        atomicAdd(p + 1, dt_acc[a][i][h][2 * rr + 1]);
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const int row = table_row(meta, mt * 16 + g + 8 * rr);   // aliases flush into the row they stand for
+                        if (mt < n_mt && row >= 0) {
+                            float *p = dst + (int64_t)row * HC + slot_offset<HDM>(hp, h, pl) + 2 * t;
+                            atomicAdd(p, dt_acc[pl][a][i][h][2 * rr]);
+                            atomicAdd(p + 1, dt_acc[pl][a][i][h][2 * rr + 1]);
+                        }
                     }
-                }
+            }
         }
-    }
 }
 
-template <int D, int MTW, int SIDE, bool HD16>
+template <int D, int MTW, int SIDE, int HDM>
 static int launch_side(const BwdParams &p, const CrseMeta &meta, cudaStream_t st)
 {
-    const BwdSmem L = make_bwd_layout(meta.R, SIDE == 0 ? 2 : 1, SIDE == 0 ? 2 : 1, SIDE == 0 ? 1 : 2, bkt_of(SIDE));
-    auto kern = attn_bwd_tc_kernel<D, MTW, SIDE, HD16>;
+    const BwdSmem L = make_bwd_layout(meta.R, SIDE == 0 ? 2 : 1, SIDE == 0 ? 2 : 1, SIDE == 0 ? 1 : 2, bkt_of(SIDE),
+                                      HDM == HDM_PAIR16 ? 2 : 1);
+    auto kern = attn_bwd_tc_kernel<D, MTW, SIDE, HDM>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total) != cudaSuccess)
         return S3D_ERR_LAUNCH;
     int dev = 0, sms = 148, per_sm = 1;
@@ -560,7 +640,7 @@ static int launch_side(const BwdParams &p, const CrseMeta &meta, cudaStream_t st
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, BW_THREADS, L.total) != cudaSuccess || per_sm < 1)
         return S3D_ERR_LAUNCH;
-    const int hp = HD16 ? p.H : p.H / 2;
+    const int hp = HDM == HDM_SINGLE16 ? p.H : p.H / 2;
     int gx = sms * per_sm / hp;
     if (gx > p.W) gx = (int)p.W;
     if (gx < 1) gx = 1;
@@ -569,7 +649,7 @@ static int launch_side(const BwdParams &p, const CrseMeta &meta, cudaStream_t st
     return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
 }
 
-template <int D, int MTW, bool HD16>
+template <int D, int MTW, int HDM>
 static int launch_both(const AttnArgs &a, int skip_upto, cudaStream_t st)
 {
     BwdParams pq{};
@@ -583,7 +663,7 @@ static int launch_both(const AttnArgs &a, int skip_upto, cudaStream_t st)
     pq.dt0 = a.dtq; pq.dt1 = a.dtv;
     pq.w_sizes = a.w_sizes; pq.w2n = a.w2n; pq.n2n = a.n2n; pq.n_coords = a.n_coords;
     pq.W = a.W; pq.H = a.H;
-    int rc = launch_side<D, MTW, 0, HD16>(pq, a.meta, st);
+    int rc = launch_side<D, MTW, 0, HDM>(pq, a.meta, st);
     if (rc != S3D_OK) return rc;
     BwdParams pk = pq;
     pk.x0 = (const __half *)a.k;   pk.x1 = (const __half *)a.v;
@@ -592,7 +672,17 @@ static int launch_both(const AttnArgs &a, int skip_upto, cudaStream_t st)
     pk.t_py0 = (const __half *)a.tq; pk.t_py1 = (const __half *)a.tv;
     pk.dx0 = (__half *)a.dk; pk.dx1 = (__half *)a.dv;
     pk.dt0 = a.dtk; pk.dt1 = nullptr;
-    return launch_side<D, MTW, 1, HD16>(pk, a.meta, st);
+    return launch_side<D, MTW, 1, HDM>(pk, a.meta, st);
+}
+
+template <int D, int MTW>
+static int launch_mode(const AttnArgs &a, int hdm, int skip_upto, cudaStream_t st)
+{
+    switch (hdm) {
+        case HDM_PAIR8: return launch_both<D, MTW, HDM_PAIR8>(a, skip_upto, st);
+        case HDM_SINGLE16: return launch_both<D, MTW, HDM_SINGLE16>(a, skip_upto, st);
+        default: return launch_both<D, MTW, HDM_PAIR16>(a, skip_upto, st);
+    }
 }
 
 }  // namespace tc
@@ -605,8 +695,9 @@ bool attn_tc_bwd_supported(const AttnArgs &a)
     if (Rint > 16 * tc::BW_NWARP * 2) return false;
     for (int d = 0; d < a.meta.D; ++d)
         if (a.meta.L[d] >= (1 << tc::IDX_BITS)) return false;
-    if (tc::make_bwd_layout(Rint, 2, 2, 1, tc::bkt_of(0)).total > 227 * 1024) return false;
-    if (tc::make_bwd_layout(Rint, 1, 1, 2, tc::bkt_of(1)).total > 227 * 1024) return false;
+    const int planes = attn_tc_head_mode(a) == tc::HDM_PAIR16 ? 2 : 1;
+    if (tc::make_bwd_layout(Rint, 2, 2, 1, tc::bkt_of(0), planes).total > 227 * 1024) return false;
+    if (tc::make_bwd_layout(Rint, 1, 1, 2, tc::bkt_of(1), planes).total > 227 * 1024) return false;
     return true;
 }
 
@@ -616,8 +707,10 @@ int attn_tc_backward(const AttnArgs &a0, cudaStream_t st)
     if (a0.W == 0) return S3D_OK;
     AttnArgs a = a0;
     a.meta = tc::internal_meta(a0.meta);   // kernels work in the internal row numbering
+    const int hdm = attn_tc_head_mode(a0);
     int skip_upto = 0;
-    if (attn_tc_bwd_small_supported(a0)) {
+    // the single-sweep kernel serves head pairs of 8 channels and single heads of 16
+    if (hdm != tc::HDM_PAIR16 && attn_tc_bwd_small_supported(a0)) {
         const int rc = attn_tc_backward_small(a0, st);
         if (rc != S3D_OK) return rc;
         skip_upto = tc::QT;
@@ -626,8 +719,8 @@ int attn_tc_backward(const AttnArgs &a0, cudaStream_t st)
     const int mtw = (n_mt + tc::BW_NWARP - 1) / tc::BW_NWARP;
 #define S3D_TC_BWD(DD)                                            \
     switch (mtw) {                                                \
-        case 1: return a.hd == 16 ? tc::launch_both<DD, 1, true>(a, skip_upto, st) : tc::launch_both<DD, 1, false>(a, skip_upto, st); \
-        case 2: return a.hd == 16 ? tc::launch_both<DD, 2, true>(a, skip_upto, st) : tc::launch_both<DD, 2, false>(a, skip_upto, st); \
+        case 1: return tc::launch_mode<DD, 1>(a, hdm, skip_upto, st); \
+        case 2: return tc::launch_mode<DD, 2>(a, hdm, skip_upto, st); \
         default: return S3D_ERR_UNSUPPORTED;                      \
     }
     switch (a.meta.D) {

@@ -56,14 +56,18 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
     const int mypos = qpos(lane);
     constexpr float LOG2E = 1.4426950408889634f;
 
-    // ---- one-plane modes: this block's table slices as mma fragments, resident in registers --------
-    uint32_t tqA[MTP][2][2], tkA[MTP][2][2], tvB[MTP][2][2];
+    // ---- this block's table slices as mma fragments, resident in registers: Tk (used once per key
+    //      tile) in every mode, Tq and Tv (used once per item) only with one plane -----------------------
+    uint32_t tqA[MTP][2][2], tvB[MTP][2][2], tkA[MTW][NPL][2][2];
+#pragma unroll
+    for (int i = 0; i < MTW; ++i)
+#pragma unroll
+        for (int pl = 0; pl < NPL; ++pl) load_table_a_frag<HDM>(tkA[i][pl], tk, meta, HC, hp, pl, wid + NWARP * i, g, t);
     if (!PAIR16) {
 #pragma unroll
         for (int i = 0; i < MTP; ++i) {
             const int mt = wid + NWARP * i;
             load_table_a_frag<HDM>(tqA[i], tq, meta, HC, hp, 0, mt, g, t);
-            load_table_a_frag<HDM>(tkA[i], tk, meta, HC, hp, 0, mt, g, t);
             load_table_b_frag<HDM>(tvB[i], tv, meta, HC, hp, 0, mt, g, t);
         }
     }
@@ -174,20 +178,6 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                 __syncthreads();
                 // ---- P_k^T[row][(key, slot)] = Tk . K^T -> s_pk[key][row];  S0^T[key][(q, slot)] = K . Q^T ----
                 {
-                    uint32_t kf[MTW][NPL][2][2];
-                    if (PAIR16) {
-#pragma unroll
-                        for (int i = 0; i < MTW; ++i)
-#pragma unroll
-                            for (int pl = 0; pl < NPL; ++pl)
-                                load_table_a_frag<HDM>(kf[i][pl], tk, meta, HC, hp, pl, wid + NWARP * i, g, t);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < MTW; ++i) {
-                            kf[i][0][0][0] = tkA[i % MTP][0][0]; kf[i][0][0][1] = tkA[i % MTP][0][1];
-                            kf[i][0][1][0] = tkA[i % MTP][1][0]; kf[i][0][1][1] = tkA[i % MTP][1][1];
-                        }
-                    }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         uint32_t b0[NPL], b1[NPL];
@@ -202,9 +192,9 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                             const int mt = wid + NWARP * i;
                             if (mt < n_mt) {
                                 uint32_t d0, d1;
-                                mma_k16_h(d0, d1, kf[i][0][0][0], kf[i][0][0][1], kf[i][0][1][0], kf[i][0][1][1], b0[0], b1[0]);
+                                mma_k16_h(d0, d1, tkA[i][0][0][0], tkA[i][0][0][1], tkA[i][0][1][0], tkA[i][0][1][1], b0[0], b1[0]);
                                 if (PAIR16)
-                                    mma_k16_ha(d0, d1, kf[i][NPL - 1][0][0], kf[i][NPL - 1][0][1], kf[i][NPL - 1][1][0], kf[i][NPL - 1][1][1], b0[NPL - 1], b1[NPL - 1]);
+                                    mma_k16_ha(d0, d1, tkA[i][NPL - 1][0][0], tkA[i][NPL - 1][0][1], tkA[i][NPL - 1][1][0], tkA[i][NPL - 1][1][1], b0[NPL - 1], b1[NPL - 1]);
                                 uint32_t *dst = s_pk + (4 * j + t) * Rp + mt * 16 + g;
                                 dst[0] = d0;
                                 dst[8] = d1;
