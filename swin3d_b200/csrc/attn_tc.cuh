@@ -221,20 +221,22 @@ struct SmemLayout {
     int off_pq, off_hist, off_pk, off_s, off_idx, off_kv, off_kc, off_misc, total;
 };
 
-__host__ __device__ inline SmemLayout make_layout(int R, int n_rowq_arrays, int n_planes = 1)
+__host__ __device__ inline SmemLayout make_layout(int R, int n_rowq_arrays, int n_planes = 1, int n_warps = NWARP)
 {
+    const int kt = 2 * n_warps;                                  // keys per tile: two per warp
     SmemLayout L;
     L.R16 = (R + 15) / 16 * 16;
     L.Rp = (L.R16 + 31) / 32 * 32 + 8;
     int off = 0;
     L.off_pq = off;   off += n_rowq_arrays * L.R16 * QT * 4;   // P_q (and dB in the backward)
     L.off_hist = off; off += n_rowq_arrays * L.R16 * QT * 4;   // histograms
-    // the per-key array doubles as the cross-warp reduction buffer of the epilogue (18 KB)
-    L.off_pk = off;   off += (KT * L.Rp * 4 > 18432) ? KT * L.Rp * 4 : 18432;
-    L.off_s = off;    off += KT * QT * 8;                      // float2 scores / half2 probabilities
-    L.off_idx = off;  off += KT * 2 * QT * 4;                  // packed cRSE indices
-    L.off_kv = off;   off += n_planes * 2 * KT * 16 * 2;       // key and value rows of the tile, per plane
-    L.off_kc = off;   off += KT * 12 * 4;                      // key coordinates, padded to 12
+    // the per-key array doubles as the cross-warp reduction buffer of the epilogue (2.25 KB per warp)
+    const int red = n_warps * (QT * 16 + QT * 2) * 4;
+    L.off_pk = off;   off += (kt * L.Rp * 4 > red) ? kt * L.Rp * 4 : red;
+    L.off_s = off;    off += kt * QT * 8;                      // float2 scores / half2 probabilities
+    L.off_idx = off;  off += kt * 2 * QT * 4;                  // packed cRSE indices
+    L.off_kv = off;   off += n_planes * 2 * kt * 16 * 2;       // key and value rows of the tile, per plane
+    L.off_kc = off;   off += kt * 12 * 4;                      // key coordinates, padded to 12
     L.off_misc = off; off += 1024;
     L.total = off;
     return L;

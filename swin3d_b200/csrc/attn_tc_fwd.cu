@@ -17,8 +17,8 @@
 namespace s3d {
 namespace tc {
 
-template <int D, int MTW, int HDM>
-__global__ void __launch_bounds__(NTHREADS, 2)
+template <int D, int MTW, int HDM, int NW>
+__global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1)
 attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                    const __half *__restrict__ v, const __half *__restrict__ tq,
                    const __half *__restrict__ tk, const __half *__restrict__ tv,
@@ -31,8 +31,11 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
     constexpr bool PAIR16 = HDM == HDM_PAIR16;       // two heads of 16 channels, two planes
     constexpr int NPL = PAIR16 ? 2 : 1;
     constexpr int MTP = PAIR16 ? 1 : MTW;            // resident table fragments only with one plane
+    // NW warps per block: 8 (two blocks per SM) or, when the tables are too large for that, 16 (one
+    // block per SM); a key tile holds two keys per warp
+    constexpr int NWARP = NW, NTHREADS = NW * 32, KT = 2 * NW;
     extern __shared__ __align__(16) unsigned char smem[];
-    const SmemLayout L = make_layout(meta.R, 1, NPL);
+    const SmemLayout L = make_layout(meta.R, 1, NPL, NW);
     uint32_t *s_pq = reinterpret_cast<uint32_t *>(smem + L.off_pq);      // [R16][32] half2
     uint32_t *s_hist = reinterpret_cast<uint32_t *>(smem + L.off_hist);  // [R16][32] half2
     uint32_t *s_pk = reinterpret_cast<uint32_t *>(smem + L.off_pk);      // [KT][Rp] half2
@@ -45,8 +48,8 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
     float *s_alpha = s_mtile + 64;                                       // [32][2]
     int *s_qrow = reinterpret_cast<int *>(s_alpha + 64);                 // [32]
     __half *s_q = reinterpret_cast<__half *>(smem + L.off_s);            // [plane][32][16], aliases s_s
-    float *s_red = reinterpret_cast<float *>(smem + L.off_pk);           // [8][32][16], aliases s_pk
-    float *s_lsum = s_red + NWARP * QT * 16;                             // [8][32][2]
+    float *s_red = reinterpret_cast<float *>(smem + L.off_pk);           // [NW][32][16], aliases s_pk
+    float *s_lsum = s_red + NWARP * QT * 16;                             // [NW][32][2]
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -108,7 +111,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                     qB[pl][j][0] = (g & 1) ? 0u : wq;
                     qB[pl][j][1] = (g & 1) ? wq : 0u;
                 }
-                const uint32_t wq = *reinterpret_cast<const uint32_t *>(s_q + pl * 512 + (4 * wid + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+                const uint32_t wq = *reinterpret_cast<const uint32_t *>(s_q + pl * 512 + (4 * (wid & 7) + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
                 qS[pl][0] = (g & 1) ? 0u : wq;
                 qS[pl][1] = (g & 1) ? wq : 0u;
             }
@@ -157,8 +160,8 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                 const int nk = min(KT, n - k0);
                 __syncthreads();  // P_q stored / previous key tile fully consumed
                 // ---- stage the key tile -----------------------------------------------------------
-                if (tid < 64 * NPL) {
-                    const int ki = (tid >> 2) & 15, which = (tid >> 1) & 1, hf = tid & 1, pl = tid >> 6;
+                if (tid < 4 * KT * NPL) {
+                    const int ki = (tid >> 2) % KT, which = (tid >> 1) & 1, hf = tid & 1, pl = tid / (4 * KT);
                     uint4 val = make_uint4(0, 0, 0, 0);
                     if (ki < nk) {
                         const int row = __ldg(n2n + base + k0 + ki);
@@ -171,7 +174,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                     s_mtile[(tid - (NTHREADS - 32)) * 2] = -INFINITY;
                     s_mtile[(tid - (NTHREADS - 32)) * 2 + 1] = -INFINITY;
                 }
-                for (int e = (tid + 128) % NTHREADS; e < KT * D; e += NTHREADS) {   // threads 128.. first: they stage no rows
+                for (int e = (tid + NTHREADS / 2) % NTHREADS; e < KT * D; e += NTHREADS) {   // upper half first: it stages no rows
                     const int ki = e / D, d = e - ki * D;
                     s_kc[ki * 12 + d] = ki < nk ? __ldg(n_coords + (int64_t)(base + k0 + ki) * D + d) : 0.f;
                 }
@@ -179,7 +182,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                 // ---- P_k^T[row][(key, slot)] = Tk . K^T -> s_pk[key][row];  S0^T[key][(q, slot)] = K . Q^T ----
                 {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int j = 0; j < KT / 4; ++j) {
                         uint32_t b0[NPL], b1[NPL];
 #pragma unroll
                         for (int pl = 0; pl < NPL; ++pl) {
@@ -201,11 +204,12 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                             }
                         }
                     }
-                    {   // one n-tile (4 queries x 2 slots) of S0 per warp
+                    {   // one (16 keys, 4 queries x 2 slots) tile of S0 per warp
+                        const int smt = wid >> 3, sj = wid & 7;
                         float c[4];
 #pragma unroll
                         for (int pl = 0; pl < NPL; ++pl) {
-                            const __half *kp = s_k + pl * KT * 16;
+                            const __half *kp = s_k + pl * KT * 16 + smt * 256;
                             const uint32_t a0 = *reinterpret_cast<const uint32_t *>(kp + g * 16 + 2 * t);
                             const uint32_t a1 = *reinterpret_cast<const uint32_t *>(kp + (g + 8) * 16 + 2 * t);
                             const uint32_t a2 = *reinterpret_cast<const uint32_t *>(kp + g * 16 + 8 + 2 * t);
@@ -213,8 +217,8 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                             if (pl == 0) mma_k16_z(c, a0, a1, a2, a3, qS[pl][0], qS[pl][1]);
                             else mma_k16(c, a0, a1, a2, a3, qS[pl][0], qS[pl][1]);
                         }
-                        s_s[g * QT + 4 * wid + t] = make_float2(c[0], c[1]);
-                        s_s[(g + 8) * QT + 4 * wid + t] = make_float2(c[2], c[3]);
+                        s_s[(16 * smt + g) * QT + 4 * sj + t] = make_float2(c[0], c[1]);
+                        s_s[(16 * smt + g + 8) * QT + 4 * sj + t] = make_float2(c[2], c[3]);
                     }
                 }
                 __syncthreads();
@@ -349,30 +353,35 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                 // ---- O += P.V on the tensor cores (warp 7; with two planes also warp 6) -----------------
                 if (pv_warp) {
                     const __half *vp = s_v + pv_plane * KT * 16;
-                    uint32_t pa[2][2][4];  // [slot][m-tile][a0..a3]
 #pragma unroll
-                    for (int i = 0; i < 2; ++i)
+                    for (int ks = 0; ks < KT / 16; ++ks) {
+                        if (16 * ks < nk) {
+                            uint32_t pa[2][2][4];  // [slot][m-tile][a0..a3]
 #pragma unroll
-                        for (int kh = 0; kh < 2; ++kh)      // keys 2t.. / keys 2t+8..
+                            for (int i = 0; i < 2; ++i)
 #pragma unroll
-                            for (int rr = 0; rr < 2; ++rr) { // query 16i+g / 16i+g+8
-                                const int qq = 16 * i + g + 8 * rr, ka = 2 * t + 8 * kh;
-                                const uint32_t x = reinterpret_cast<const uint32_t *>(s_s + ka * QT + qq)[0];
-                                const uint32_t y = reinterpret_cast<const uint32_t *>(s_s + (ka + 1) * QT + qq)[0];
-                                pa[0][i][2 * kh + rr] = pack_lo(x, y);
-                                pa[1][i][2 * kh + rr] = pack_hi(x, y);
+                                for (int kh = 0; kh < 2; ++kh)      // keys 2t.. / keys 2t+8..
+#pragma unroll
+                                    for (int rr = 0; rr < 2; ++rr) { // query 16i+g / 16i+g+8
+                                        const int qq = 16 * i + g + 8 * rr, ka = 16 * ks + 2 * t + 8 * kh;
+                                        const uint32_t x = reinterpret_cast<const uint32_t *>(s_s + ka * QT + qq)[0];
+                                        const uint32_t y = reinterpret_cast<const uint32_t *>(s_s + (ka + 1) * QT + qq)[0];
+                                        pa[0][i][2 * kh + rr] = pack_lo(x, y);
+                                        pa[1][i][2 * kh + rr] = pack_hi(x, y);
+                                    }
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                uint32_t vb[2];
+#pragma unroll
+                                for (int kh = 0; kh < 2; ++kh) {
+                                    const int ka = 16 * ks + 2 * t + 8 * kh;
+                                    vb[kh] = h2_as_u32(__halves2half2(vp[ka * 16 + h * 8 + g], vp[(ka + 1) * 16 + h * 8 + g]));
+                                }
+#pragma unroll
+                                for (int i = 0; i < 2; ++i)
+                                    mma_k16(oacc[h][i], pa[h][i][0], pa[h][i][1], pa[h][i][2], pa[h][i][3], vb[0], vb[1]);
                             }
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        uint32_t vb[2];
-#pragma unroll
-                        for (int kh = 0; kh < 2; ++kh) {
-                            const int ka = 2 * t + 8 * kh;
-                            vb[kh] = h2_as_u32(__halves2half2(vp[ka * 16 + h * 8 + g], vp[(ka + 1) * 16 + h * 8 + g]));
                         }
-#pragma unroll
-                        for (int i = 0; i < 2; ++i)
-                            mma_k16(oacc[h][i], pa[h][i][0], pa[h][i][1], pa[h][i][2], pa[h][i][3], vb[0], vb[1]);
                     }
                 }
             }  // key tiles
@@ -444,7 +453,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                 __syncthreads();
                 {
                     const int qq = tid >> 3, ch = (tid & 7) * 2, h = ch >> 3;
-                    if (qq < nq) {
+                    if (qq < nq) {          // qq >= 32 (warps 8..15 of a 16-warp block) never passes: nq <= 32
                         float a = 0.f, b = 0.f, ls = 0.f;
 #pragma unroll
                         for (int ww = 0; ww < NWARP; ++ww) {
@@ -471,11 +480,12 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
     }      // windows
 }
 
-template <int D, int MTW, int HDM>
+template <int D, int MTW, int HDM, int NW>
 static int launch(const AttnArgs &a, int skip_upto, cudaStream_t st)
 {
-    const SmemLayout L = make_layout(a.meta.R, 1, HDM == HDM_PAIR16 ? 2 : 1);
-    auto kern = attn_fwd_tc_kernel<D, MTW, HDM>;
+    constexpr int NTHREADS = NW * 32;
+    const SmemLayout L = make_layout(a.meta.R, 1, HDM == HDM_PAIR16 ? 2 : 1, NW);
+    auto kern = attn_fwd_tc_kernel<D, MTW, HDM, NW>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total) != cudaSuccess)
         return S3D_ERR_LAUNCH;
     const int hp = HDM == HDM_SINGLE16 ? a.H : a.H / 2;
@@ -496,14 +506,21 @@ static int launch(const AttnArgs &a, int skip_upto, cudaStream_t st)
     return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
 }
 
-template <int D, int MTW>
+template <int D, int MTW, int NW>
 static int launch_mode(const AttnArgs &a, int hdm, int skip_upto, cudaStream_t st)
 {
     switch (hdm) {
-        case HDM_PAIR8: return launch<D, MTW, HDM_PAIR8>(a, skip_upto, st);
-        case HDM_SINGLE16: return launch<D, MTW, HDM_SINGLE16>(a, skip_upto, st);
-        default: return launch<D, MTW, HDM_PAIR16>(a, skip_upto, st);
+        case HDM_PAIR8: return launch<D, MTW, HDM_PAIR8, NW>(a, skip_upto, st);
+        case HDM_SINGLE16: return launch<D, MTW, HDM_SINGLE16, NW>(a, skip_upto, st);
+        default: return launch<D, MTW, HDM_PAIR16, NW>(a, skip_upto, st);
     }
+}
+
+// Warps per block for a table of R (internal) rows: 8 while two such blocks fit on an SM, else 16.
+static int warps_per_block(int R, int planes)
+{
+    const bool two_fit = 2 * (make_layout(R, 1, planes, 8).total + 1024) <= 228 * 1024;
+    return (two_fit || make_layout(R, 1, planes, 16).total > 227 * 1024) ? 8 : 16;
 }
 
 }  // namespace tc
@@ -523,7 +540,7 @@ bool attn_tc_supported(const AttnArgs &a)
     if (Rint > 16 * tc::NWARP * 3) return false;
     for (int d = 0; d < a.meta.D; ++d)
         if (a.meta.L[d] >= (1 << tc::IDX_BITS)) return false;   // idx may reach L
-    if (tc::make_layout(Rint, 1, 2).total > 227 * 1024) return false;
+    if (tc::make_layout(Rint, 1, 2, 8).total > 227 * 1024) return false;
     return true;
 }
 
@@ -541,12 +558,15 @@ int attn_tc_forward(const AttnArgs &a0, cudaStream_t st)
         skip_upto = tc::QT;
     }
     const int n_mt = (a.meta.R + 15) / 16;
-    const int mtw = (n_mt + tc::NWARP - 1) / tc::NWARP;
+    const int nw = tc::warps_per_block(a.meta.R, hdm == tc::HDM_PAIR16 ? 2 : 1);
+    const int mtw = (n_mt + nw - 1) / nw;
 #define S3D_TC_FWD(DD)                                            \
-    switch (mtw) {                                                \
-        case 1: return tc::launch_mode<DD, 1>(a, hdm, skip_upto, st); \
-        case 2: return tc::launch_mode<DD, 2>(a, hdm, skip_upto, st); \
-        case 3: return tc::launch_mode<DD, 3>(a, hdm, skip_upto, st); \
+    switch (nw == 8 ? mtw : 10 + mtw) {                           \
+        case 1: return tc::launch_mode<DD, 1, 8>(a, hdm, skip_upto, st); \
+        case 2: return tc::launch_mode<DD, 2, 8>(a, hdm, skip_upto, st); \
+        case 3: return tc::launch_mode<DD, 3, 8>(a, hdm, skip_upto, st); \
+        case 11: return tc::launch_mode<DD, 1, 16>(a, hdm, skip_upto, st); \
+        case 12: return tc::launch_mode<DD, 2, 16>(a, hdm, skip_upto, st); \
         default: return S3D_ERR_UNSUPPORTED;                      \
     }
     switch (a.meta.D) {
