@@ -10,14 +10,20 @@
 // What differs is the data path: a block of queries streams its scene's source points through
 // shared memory in tiles (one coalesced global read per point per block instead of one per
 // thread), candidates are read back as one broadcast 16-byte shared load, and the heap root is
-// held in a register so the common "not closer" case costs one compare.
+// held in a register so the common "not closer" case costs one compare.  Candidates that beat the
+// (possibly stale) root are parked in a small per-thread queue in shared memory and offered to the
+// heap later, in index order and against the then current root, by all lanes of the warp at the
+// same time: the heap sees exactly the reference's sequence of replacements (a parked candidate
+// that no longer beats the root is dropped, as it would have been in its turn), but the divergent
+// sift-downs of different lanes overlap instead of running one after the other.
 #include "common.cuh"
 #include "knn_kernels.cuh"
 
 namespace s3d {
 
 constexpr int KNN_THREADS = 256;
-constexpr int KNN_TILE = 1024;
+constexpr int KNN_TILE = 768;
+constexpr int KNN_QCAP = 12;   // parked candidates per thread; drained when a batch of 8 may not fit
 
 __device__ __forceinline__ void knn_sift_down(float *heap, int *idx, int start, int end)
 {
@@ -49,7 +55,8 @@ knn_kernel(int K, const float *__restrict__ src, const float *__restrict__ query
            const int32_t *__restrict__ src_offset, const int32_t *__restrict__ query_offset,
            int B, int64_t Nq, int32_t *__restrict__ ret_idx, float *__restrict__ ret_dist)
 {
-    __shared__ float4 s_pts[KNN_TILE];
+    __shared__ float4 s_pts[KNN_TILE + 8];         // a step of eight may read past the last point
+    __shared__ int s_qi[KNN_QCAP * KNN_THREADS];   // parked candidates (source rows), [slot][thread]
     __shared__ int s_lo, s_hi;
 
     const int64_t g = (int64_t)blockIdx.x * KNN_THREADS + threadIdx.x;
@@ -85,6 +92,28 @@ knn_kernel(int K, const float *__restrict__ src, const float *__restrict__ query
     __syncthreads();
     const int lo = s_lo, hi = s_hi;
     float top = heap[0];
+    int qn = 0;                                   // parked candidates of this thread
+    int *qi = s_qi + threadIdx.x;                 // this thread's column of the queue
+
+    // offer the parked candidates to the heap, oldest first; every lane of the warp takes part
+    auto drain = [&]() {
+        const int most = __reduce_max_sync(0xffffffffu, qn);
+        for (int e = 0; e < most; ++e) {
+            if (e < qn) {
+                // the distance is evaluated again from the source row (same expression, same bits)
+                const int si = qi[e * KNN_THREADS];
+                const float *p = src + (int64_t)si * 3;
+                const float d = knn_dist2(__ldg(p) - qx, __ldg(p + 1) - qy, __ldg(p + 2) - qz);
+                if (d < heap[0]) {
+                    heap[0] = d;
+                    hidx[0] = si;
+                    knn_sift_down(heap, hidx, 0, K);
+                }
+            }
+        }
+        qn = 0;
+        top = heap[0];
+    };
 
     for (int t0 = lo; t0 < hi; t0 += KNN_TILE) {
         const int cnt = min(KNN_TILE, hi - t0);
@@ -96,40 +125,41 @@ knn_kernel(int K, const float *__restrict__ src, const float *__restrict__ query
         __syncthreads();
         // clip the tile to this thread's own scene
         const int jb = max(s0 - t0, 0), je = min(s1 - t0, cnt);
-        int j = jb;
+        // every lane walks the same number of steps (lanes of other scenes idle) so that the warp can
+        // drain together
+        const int jb_w = __reduce_min_sync(0xffffffffu, jb), je_w = __reduce_max_sync(0xffffffffu, je);
         // eight candidates per step: one test for "none is closer than the heap root" (the common
-        // case); otherwise the eight are offered to the heap one by one, in index order
-        for (; j + 8 <= je; j += 8) {
+        // case); the others are parked
+        for (int j = jb_w; j < je_w; j += 8) {
             float dd[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const float4 p = s_pts[j + u];
                 dd[u] = knn_dist2(p.x - qx, p.y - qy, p.z - qz);
             }
-            const float m = fminf(fminf(fminf(dd[0], dd[1]), fminf(dd[2], dd[3])),
-                                  fminf(fminf(dd[4], dd[5]), fminf(dd[6], dd[7])));
-            if (m < top) {
+            if (j >= jb && j + 8 <= je) {           // the whole step lies in this thread's scene (the common case)
+                const float m = fminf(fminf(fminf(dd[0], dd[1]), fminf(dd[2], dd[3])),
+                                      fminf(fminf(dd[4], dd[5]), fminf(dd[6], dd[7])));
+                if (m < top) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (dd[u] < top) {
+                            qi[qn * KNN_THREADS] = t0 + j + u;
+                            ++qn;
+                        }
+                }
+            } else {
 #pragma unroll
                 for (int u = 0; u < 8; ++u)
-                    if (dd[u] < top) {
-                        heap[0] = dd[u];
-                        hidx[0] = t0 + j + u;
-                        knn_sift_down(heap, hidx, 0, K);
-                        top = heap[0];
+                    if (j + u >= jb && j + u < je && dd[u] < top) {
+                        qi[qn * KNN_THREADS] = t0 + j + u;
+                        ++qn;
                     }
             }
-        }
-        for (; j < je; ++j) {
-            const float4 p = s_pts[j];
-            const float d = knn_dist2(p.x - qx, p.y - qy, p.z - qz);
-            if (d < top) {
-                heap[0] = d;
-                hidx[0] = t0 + j;
-                knn_sift_down(heap, hidx, 0, K);
-                top = heap[0];
-            }
+            if (__any_sync(0xffffffffu, qn > KNN_QCAP - 8)) drain();
         }
     }
+    drain();
     if (!active) return;
     for (int i = K - 1; i > 0; --i) {
         const float tf = heap[0]; heap[0] = heap[i]; heap[i] = tf;
