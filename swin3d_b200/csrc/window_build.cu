@@ -9,8 +9,12 @@
 // Windows come out in lexicographic (batch, wx, wy, wz) order.
 //
 // All kernels are plain integer/byte work bound by HBM bandwidth: keys are read and written
-// with coalesced accesses, digit ranking uses warp match + shared counters, and radix passes
-// whose digit is identical for every key are skipped on the device (no host round trip).
+// with coalesced accesses, digit ranking uses warp match + shared counters.  The batch and window
+// fields of the key are packed as tightly as the batch at hand allows (a reduction finds their
+// ranges first), so a typical batch sorts in four 8-bit passes instead of seven; the passes above
+// the highest used bit exit at once, and passes whose digit is identical for every key are skipped
+// on the device (no host round trip).
+#include <climits>
 #include <mutex>
 
 #include "common.cuh"
@@ -32,28 +36,93 @@ constexpr int NPASS = 8;
 __device__ __forceinline__ int floor_div(int a, int b) { int q = a / b; return (a % b != 0 && ((a < 0) != (b < 0))) ? q - 1 : q; }
 
 // ---- keys ------------------------------------------------------------------------------------
-__global__ void wb_keys_kernel(const int32_t *__restrict__ coords, int64_t N, int stride, int ws,
-                               int shift, uint64_t *__restrict__ keys, uint32_t *__restrict__ vals,
-                               int64_t *__restrict__ counts)
+struct VoxelWindow {
+    int b, wx, wy, wz, cell;
+};
+
+__device__ __forceinline__ VoxelWindow voxel_window(const int32_t *__restrict__ coords, int64_t i, int stride, int ws, int shift)
 {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N) return;
     const int4 c = __ldg(reinterpret_cast<const int4 *>(coords) + i);  // b, x, y, z
     const int wstride = ws * stride;
     const int sx = c.y + shift * stride, sy = c.z + shift * stride, sz = c.w + shift * stride;
-    const int wx = floor_div(sx, wstride), wy = floor_div(sy, wstride), wz = floor_div(sz, wstride);
-    const int cx = (sx - wx * wstride) / stride, cy = (sy - wy * wstride) / stride,
-              cz = (sz - wz * wstride) / stride;
-    const int cell = (cx * ws + cy) * ws + cz;
-    const int bx = wx + W_BIAS, by = wy + W_BIAS, bz = wz + W_BIAS;
-    if (c.x < 0 || c.x >= (1 << B_BITS) || bx < 0 || bx >= (1 << W_BITS) || by < 0 ||
-        by >= (1 << W_BITS) || bz < 0 || bz >= (1 << W_BITS) || cell >= (1 << CELL_BITS))
-        counts[3] = 1;  // coordinate outside the representable range
-    uint64_t key = (uint64_t)(uint32_t)c.x;
-    key = (key << W_BITS) | (uint32_t)(bx & ((1 << W_BITS) - 1));
-    key = (key << W_BITS) | (uint32_t)(by & ((1 << W_BITS) - 1));
-    key = (key << W_BITS) | (uint32_t)(bz & ((1 << W_BITS) - 1));
-    key = (key << CELL_BITS) | (uint32_t)(cell & ((1 << CELL_BITS) - 1));
+    VoxelWindow v;
+    v.b = c.x;
+    v.wx = floor_div(sx, wstride); v.wy = floor_div(sy, wstride); v.wz = floor_div(sz, wstride);
+    const int cx = (sx - v.wx * wstride) / stride, cy = (sy - v.wy * wstride) / stride,
+              cz = (sz - v.wz * wstride) / stride;
+    v.cell = (cx * ws + cy) * ws + cz;
+    return v;
+}
+
+// range[0..3] = min of (batch, wx, wy, wz), range[4..7] = max; also flags coordinates outside the
+// supported range (batch < 2^10, |window index| < 2^14, cell id < 2^9)
+__global__ void wb_range_kernel(const int32_t *__restrict__ coords, int64_t N, int stride, int ws, int shift,
+                                int *__restrict__ range, int64_t *__restrict__ counts)
+{
+    int lo[4] = {INT_MAX, INT_MAX, INT_MAX, INT_MAX}, hi[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+    bool bad = false;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < N; i += (int64_t)gridDim.x * blockDim.x) {
+        const VoxelWindow v = voxel_window(coords, i, stride, ws, shift);
+        const int f[4] = {v.b, v.wx, v.wy, v.wz};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            lo[k] = min(lo[k], f[k]);
+            hi[k] = max(hi[k], f[k]);
+        }
+        const int bx = v.wx + W_BIAS, by = v.wy + W_BIAS, bz = v.wz + W_BIAS;
+        bad = bad || v.b < 0 || v.b >= (1 << B_BITS) || bx < 0 || bx >= (1 << W_BITS) || by < 0 ||
+              by >= (1 << W_BITS) || bz < 0 || bz >= (1 << W_BITS) || v.cell >= (1 << CELL_BITS);
+    }
+    // warp, then block, then one set of atomics per block
+    __shared__ int s_lo[4], s_hi[4];
+    if (threadIdx.x < 4) {
+        s_lo[threadIdx.x] = INT_MAX;
+        s_hi[threadIdx.x] = INT_MIN;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        lo[k] = __reduce_min_sync(0xffffffffu, lo[k]);
+        hi[k] = __reduce_max_sync(0xffffffffu, hi[k]);
+    }
+    if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            atomicMin(s_lo + k, lo[k]);
+            atomicMax(s_hi + k, hi[k]);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < 4) {
+        atomicMin(range + threadIdx.x, s_lo[threadIdx.x]);
+        atomicMax(range + 4 + threadIdx.x, s_hi[threadIdx.x]);
+    }
+    if (bad) counts[3] = 1;  // coordinate outside the representable range
+}
+
+__device__ __forceinline__ int bits_for(int span) { return span > 0 ? 32 - __clz(span) : 0; }
+
+// key = (batch - min | wx - min | wy - min | wz - min | cell), the first four fields as wide as their
+// spans need.  live[p] = 1 for the radix passes that cover a used bit.
+__global__ void wb_keys_kernel(const int32_t *__restrict__ coords, int64_t N, int stride, int ws,
+                               int shift, const int *__restrict__ range, uint64_t *__restrict__ keys,
+                               uint32_t *__restrict__ vals, int *__restrict__ live)
+{
+    const int wbx = bits_for(range[5] - range[1]), wby = bits_for(range[6] - range[2]), wbz = bits_for(range[7] - range[3]);
+    const int wbb = bits_for(range[4] - range[0]);
+    if (blockIdx.x == 0 && threadIdx.x < NPASS) {
+        // spans are clamped by the range check (10 + 3*15 + 9 = 64 bits at most)
+        const int total = min(64, wbb + wbx + wby + wbz + CELL_BITS);
+        live[threadIdx.x] = 8 * threadIdx.x < total ? 1 : 0;
+    }
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const VoxelWindow v = voxel_window(coords, i, stride, ws, shift);
+    uint64_t key = (uint64_t)(uint32_t)(v.b - range[0]) & ((1ull << B_BITS) - 1);
+    key = (key << wbx) | ((uint64_t)(uint32_t)(v.wx - range[1]) & ((1ull << W_BITS) - 1));
+    key = (key << wby) | ((uint64_t)(uint32_t)(v.wy - range[2]) & ((1ull << W_BITS) - 1));
+    key = (key << wbz) | ((uint64_t)(uint32_t)(v.wz - range[3]) & ((1ull << W_BITS) - 1));
+    key = (key << CELL_BITS) | (uint32_t)(v.cell & ((1 << CELL_BITS) - 1));
     keys[i] = key;
     vals[i] = (uint32_t)i;
 }
@@ -85,9 +154,12 @@ __device__ __forceinline__ uint32_t block_scan_incl(uint32_t x, uint32_t *s_warp
     return x + prefix;
 }
 
+// `gate`: optional flag in device memory; the kernel does nothing when it is zero (a radix pass that
+// is known to have nothing to sort)
 __global__ void __launch_bounds__(SCAN_THREADS)
-scan_tile_sums_kernel(const uint32_t *__restrict__ in, int64_t n, uint32_t *__restrict__ sums)
+scan_tile_sums_kernel(const uint32_t *__restrict__ in, int64_t n, uint32_t *__restrict__ sums, const int *__restrict__ gate)
 {
+    if (gate && !*gate) return;
     __shared__ uint32_t s_warp[SCAN_THREADS / 32];
     const int64_t base = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
     uint32_t t = 0;
@@ -101,8 +173,9 @@ scan_tile_sums_kernel(const uint32_t *__restrict__ in, int64_t n, uint32_t *__re
 
 // single block: exclusive scan of sums[0..m) in place; sums[m] receives the grand total
 __global__ void __launch_bounds__(SCAN_THREADS)
-scan_sums_kernel(uint32_t *__restrict__ sums, int64_t m)
+scan_sums_kernel(uint32_t *__restrict__ sums, int64_t m, const int *__restrict__ gate)
 {
+    if (gate && !*gate) return;
     __shared__ uint32_t s_warp[SCAN_THREADS / 32];
     uint32_t carry = 0;
     for (int64_t b0 = 0; b0 < m; b0 += SCAN_THREADS) {
@@ -118,8 +191,9 @@ scan_sums_kernel(uint32_t *__restrict__ sums, int64_t m)
 
 __global__ void __launch_bounds__(SCAN_THREADS)
 scan_apply_kernel(const uint32_t *__restrict__ in, int64_t n, const uint32_t *__restrict__ sums,
-                  uint32_t *__restrict__ out_excl)
+                  uint32_t *__restrict__ out_excl, const int *__restrict__ gate)
 {
+    if (gate && !*gate) return;
     __shared__ uint32_t s_warp[SCAN_THREADS / 32];
     const int64_t base = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
     uint32_t x[SCAN_ITEMS], t = 0;
@@ -138,12 +212,13 @@ scan_apply_kernel(const uint32_t *__restrict__ in, int64_t n, const uint32_t *__
     }
 }
 
-static void scan_excl_u32(const uint32_t *in, uint32_t *out, int64_t n, uint32_t *sums, cudaStream_t st)
+static void scan_excl_u32(const uint32_t *in, uint32_t *out, int64_t n, uint32_t *sums, cudaStream_t st,
+                          const int *gate = nullptr)
 {
     const int64_t tiles = (n + SCAN_TILE - 1) / SCAN_TILE;
-    scan_tile_sums_kernel<<<(unsigned)tiles, SCAN_THREADS, 0, st>>>(in, n, sums);
-    scan_sums_kernel<<<1, SCAN_THREADS, 0, st>>>(sums, tiles);
-    scan_apply_kernel<<<(unsigned)tiles, SCAN_THREADS, 0, st>>>(in, n, sums, out);
+    scan_tile_sums_kernel<<<(unsigned)tiles, SCAN_THREADS, 0, st>>>(in, n, sums, gate);
+    scan_sums_kernel<<<1, SCAN_THREADS, 0, st>>>(sums, tiles, gate);
+    scan_apply_kernel<<<(unsigned)tiles, SCAN_THREADS, 0, st>>>(in, n, sums, out, gate);
 }
 
 // ---- radix sort passes ---------------------------------------------------------------------------
@@ -154,8 +229,9 @@ struct SortBufs {
 };
 
 __global__ void __launch_bounds__(WB_THREADS)
-radix_hist_kernel(SortBufs b, int pass, int64_t N, int nblk, uint32_t *__restrict__ hist)
+radix_hist_kernel(SortBufs b, int pass, int64_t N, int nblk, uint32_t *__restrict__ hist, const int *__restrict__ live)
 {
+    if (!live[pass]) return;
     __shared__ uint32_t s_h[256];
     s_h[threadIdx.x] = 0;
     __syncthreads();
@@ -173,8 +249,16 @@ radix_hist_kernel(SortBufs b, int pass, int64_t N, int nblk, uint32_t *__restric
 // Decide whether pass `pass` permutes anything: if one digit value holds all N keys the pass is
 // the identity (the sort is stable) and is skipped.
 __global__ void radix_decide_kernel(SortBufs b, int pass, int64_t N, int nblk,
-                                    const uint32_t *__restrict__ excl, int *__restrict__ skip)
+                                    const uint32_t *__restrict__ excl, int *__restrict__ skip,
+                                    const int *__restrict__ live)
 {
+    if (!live[pass]) {          // no used bit in this digit: nothing was counted, nothing moves
+        if (threadIdx.x == 0) {
+            skip[pass] = 1;
+            b.cur[pass + 1] = b.cur[pass];
+        }
+        return;
+    }
     __shared__ int s_uniform;
     if (threadIdx.x == 0) s_uniform = 0;
     __syncthreads();
@@ -293,9 +377,13 @@ __global__ void wb_sizes_kernel(const int32_t *__restrict__ w2n, int64_t N,
     }
 }
 
-__global__ void wb_init_kernel(int64_t *counts, int *cur)
+__global__ void wb_init_kernel(int64_t *counts, int *cur, int *range)
 {
-    if (threadIdx.x < 4) counts[threadIdx.x] = 0;
+    if (threadIdx.x < 4) {
+        counts[threadIdx.x] = 0;
+        range[threadIdx.x] = INT_MAX;
+        range[4 + threadIdx.x] = INT_MIN;
+    }
     if (threadIdx.x == 0) cur[0] = 0;
 }
 
@@ -351,14 +439,17 @@ int window_build_launch(const int32_t *coords, const float *feats, int64_t N, in
     uint32_t *flags = reinterpret_cast<uint32_t *>(ws_ptr + L.flags);
     int *skip = reinterpret_cast<int *>(ws_ptr + L.skip);
 
-    wb_init_kernel<<<1, 32, 0, st>>>(counts, b.cur);
+    // the small arrays share one 256-byte slot of the workspace: cur[NPASS+1], range[8], live[NPASS]
+    int *range = b.cur + 16, *live = b.cur + 24;
+    wb_init_kernel<<<1, 32, 0, st>>>(counts, b.cur, range);
     if (N == 0) return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
     const unsigned nb = (unsigned)((N + 255) / 256);
-    wb_keys_kernel<<<nb, 256, 0, st>>>(coords, N, stride, ws, shift, b.keys[0], b.vals[0], counts);
+    wb_range_kernel<<<nb < 148u * 8u ? nb : 148u * 8u, 256, 0, st>>>(coords, N, stride, ws, shift, range, counts);
+    wb_keys_kernel<<<nb, 256, 0, st>>>(coords, N, stride, ws, shift, range, b.keys[0], b.vals[0], live);
     for (int pass = 0; pass < NPASS; ++pass) {
-        radix_hist_kernel<<<L.nblk, WB_THREADS, 0, st>>>(b, pass, N, L.nblk, hist);
-        scan_excl_u32(hist, excl, (int64_t)256 * L.nblk, sums, st);
-        radix_decide_kernel<<<1, 256, 0, st>>>(b, pass, N, L.nblk, excl, skip);
+        radix_hist_kernel<<<L.nblk, WB_THREADS, 0, st>>>(b, pass, N, L.nblk, hist, live);
+        scan_excl_u32(hist, excl, (int64_t)256 * L.nblk, sums, st, live + pass);
+        radix_decide_kernel<<<1, 256, 0, st>>>(b, pass, N, L.nblk, excl, skip, live);
         radix_scatter_kernel<<<L.nblk, WB_THREADS, 0, st>>>(b, pass, N, L.nblk, excl, skip);
     }
     wb_flags_kernel<<<nb, 256, 0, st>>>(b, N, ws, F, feats, flags, n2n, n_coords);
