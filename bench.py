@@ -278,11 +278,13 @@ def run_attention(args):
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
 
     # ---- end to end through the public autograd Function, host buffers in and out ------------
-    # Rooms are independent (windows never cross rooms), so the batch is cut into chunks of whole
-    # rooms: 1 room first (its host->device copy is the only one nothing can hide), then half of
-    # what is left, and so on, ending with 1 room (whose device->host copy is the exposed tail).
-    # All host->device copies are queued in room order on their own stream; a chunk starts as soon
-    # as its rooms have arrived, and its results go back on a third stream while the next computes.
+    # A step copies its q, k, v, dOut from pinned host memory, runs forward + backward through
+    # SelfAttnAIOFunction and copies out, dq, dk, dv (and the table gradients) back.  Copies run on
+    # their own streams and the device inputs are double-buffered, so the copy-in of step i+1 and
+    # the copy-out of step i-1 overlap the compute of step i.  Rooms are independent (windows never
+    # cross rooms): the first timed step works in room chunks of growing size (1, 1, 2, 4) so that
+    # compute starts after one room has arrived, the last one in shrinking chunks (4, 2, 1, 1) so
+    # that little is left to copy out when compute ends, the steps between take the whole batch.
     x_pin = [t.cpu().pin_memory() for t in (q, k, v, g)]
     out_pin = [torch.empty((N, H, hd), dtype=torch.float16).pin_memory() for _ in range(4)]
     tg_pin = torch.empty((3, sum(sizes)), dtype=torch.float32).pin_memory()
@@ -291,83 +293,116 @@ def run_attention(args):
     room_of = sc.coords[:, 0]
     bounds = [0] + [int(x) for x in np.cumsum(np.bincount(room_of))]
     n_rooms = len(bounds) - 1
-    plan, left = [1], n_rooms - 1
-    while left > 0:
-        plan.append((left + 1) // 2)
-        left -= plan[-1]
-    chunks, r0 = [], 0          # (lo, hi, [index list per shift])
-    for cnt in plan:
-        lo, hi = bounds[r0], bounds[r0 + cnt]
-        r0 += cnt
-        per_shift = []
-        for shift in (0, ws // 2):
-            wi_r = build_windows(coords_d[lo:hi].contiguous(), feats_d[lo:hi].contiguous(), ws, shift)
-            ncr_r = wi_r.n_coords.clone()
-            ncr_r[:, :3] *= quant
-            ncr_r[:, 3:] *= 2 * quant
-            per_shift.append(wi_r.reference_indices(ncr_r.contiguous()))
-        chunks.append((lo, hi, per_shift))
+
+    def split(counts):
+        counts = [c for c in counts if c > 0]
+        out, r0 = [], 0
+        for c in counts:
+            out.append((r0, r0 + c))
+            r0 += c
+        assert r0 == n_rooms
+        return out
+
+    ramp = [1, 1, n_rooms // 4, 0] if n_rooms >= 8 else [1, 0]
+    ramp[-1] = n_rooms - sum(ramp[:-1])                       # 8 rooms: 1, 1, 2, 4
+    mid = max(n_rooms - 2, 0)
+    only = [1, (mid + 1) // 2, mid - (mid + 1) // 2, 1] if n_rooms > 3 else [1] * n_rooms
+    plans = {"first": split(ramp), "mid": split([n_rooms]), "last": split(ramp[::-1]), "only": split(only)}
+    chunk_idx = {}      # (first room, end room) -> [index list per shift]
+    for plan in plans.values():
+        for ra, rb in plan:
+            if (ra, rb) in chunk_idx:
+                continue
+            lo, hi = bounds[ra], bounds[rb]
+            per_shift = []
+            for shift in (0, ws // 2):
+                wi_r = build_windows(coords_d[lo:hi].contiguous(), feats_d[lo:hi].contiguous(), ws, shift)
+                ncr_r = wi_r.n_coords.clone()
+                ncr_r[:, :3] *= quant
+                ncr_r[:, 3:] *= 2 * quant
+                per_shift.append(wi_r.reference_indices(ncr_r.contiguous()))
+            chunk_idx[(ra, rb)] = per_shift
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     comp = torch.cuda.current_stream()
+    dev_in = [[torch.empty((N, H, hd), dtype=torch.float16, device="cuda") for _ in range(4)] for _ in range(2)]
+    set_free = [None, None]     # event: the compute that last read this buffer set has finished
 
-    def e2e_step(i):
+    def e2e_step(i, plan):
+        bufs = dev_in[i % 2]
         for p in tab_params:
             p.grad = None
-        staged = []
+        arrived = []
         with torch.cuda.stream(s_in):
-            s_in.wait_stream(comp)      # the previous step's device buffers are free again
-            for lo, hi, _ in chunks:
-                bufs = [x[lo:hi].cuda(non_blocking=True) for x in x_pin]
-                ev_in = torch.cuda.Event()
-                ev_in.record(s_in)
-                staged.append((bufs, ev_in))
-        keep = []
-        for (lo, hi, idx), (bufs, ev_in) in zip(chunks, staged):
+            if set_free[i % 2] is not None:
+                s_in.wait_event(set_free[i % 2])
+            for ra, rb in plan:
+                lo, hi = bounds[ra], bounds[rb]
+                for dst, src in zip(bufs, x_pin):
+                    dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(s_in)
+                arrived.append(ev)
+        for (ra, rb), ev_in in zip(plan, arrived):
+            lo, hi = bounds[ra], bounds[rb]
             comp.wait_event(ev_in)
-            dq_, dk_, dv_, dg_ = bufs
-            dq_.requires_grad_()
-            dk_.requires_grad_()
-            dv_.requires_grad_()
+            dq_, dk_, dv_ = (bufs[j][lo:hi].requires_grad_() for j in range(3))
+            dg_ = bufs[3][lo:hi]
             with torch.autocast("cuda", dtype=torch.float16):
-                o = C.SelfAttnAIOFunction.apply(dq_, dk_, dv_, *tab_params, offsets_cpu, idx[i % 2],
+                o = C.SelfAttnAIOFunction.apply(dq_, dk_, dv_, *tab_params, offsets_cpu, chunk_idx[(ra, rb)][i % 2],
                                                 C.PosEmb.SEPARATE, C.TableDims.D0, C.IndexMode.INDIRECT,
                                                 C.PrecisionMode.HALF_ALL)
             ev_f = torch.cuda.Event()
             ev_f.record(comp)
+            od = o.detach()
+            od.record_stream(s_out)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_f)          # the output goes back while the backward runs
-                out_pin[0][lo:hi].copy_(o.detach(), non_blocking=True)
+                out_pin[0][lo:hi].copy_(od, non_blocking=True)
             o.backward(dg_)
             ev_c = torch.cuda.Event()
             ev_c.record(comp)
+            grads = (dq_.grad, dk_.grad, dv_.grad)
+            for t in grads:
+                t.record_stream(s_out)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_c)
-                out_pin[1][lo:hi].copy_(dq_.grad, non_blocking=True)
-                out_pin[2][lo:hi].copy_(dk_.grad, non_blocking=True)
-                out_pin[3][lo:hi].copy_(dv_.grad, non_blocking=True)
-            keep.append((dq_, dk_, dv_, dg_, o))
+                for j, t in enumerate(grads):
+                    out_pin[1 + j][lo:hi].copy_(t, non_blocking=True)
         tgs = torch.stack([p.grad for p in tab_params])
         if world > 1:
             dist.all_reduce(tgs)
-        tg_pin.copy_(tgs, non_blocking=True)
-        ev_o = torch.cuda.Event()
-        ev_o.record(s_out)
-        comp.wait_event(ev_o)       # the step ends when the last result has reached the host buffer
-        return keep
+        ev_t = torch.cuda.Event()
+        ev_t.record(comp)
+        set_free[i % 2] = ev_t
+        tgs.record_stream(s_out)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_t)
+            tg_pin.copy_(tgs, non_blocking=True)
 
-    e2e_steps = max(2, min(args.steps, 5))
-    held = []
-    for i in range(3):              # warm-up; `held` keeps the previous step's buffers alive as the
-        held = e2e_step(i)          # timed loop does, so both buffer sets exist before timing starts
-        torch.cuda.synchronize()
+    def e2e_run(nsteps):
+        for i in range(nsteps):
+            name = "only" if nsteps == 1 else ("first" if i == 0 else ("last" if i == nsteps - 1 else "mid"))
+            e2e_step(i, plans[name])
+        comp.wait_stream(s_out)     # the run ends when the last result has reached the host buffer
+
+    e2e_steps = max(2, min(args.steps, 10))
+    e2e_run(3)                      # warm-up: allocator pools of all three streams, index caches
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     t0.record()
-    for i in range(e2e_steps):
-        held = e2e_step(i)          # tensors of the previous step are released once the next is queued
+    e2e_run(e2e_steps)
     t1.record()
     torch.cuda.synchronize()
     e2e_ms = t0.elapsed_time(t1) / e2e_steps
+    # the host buffers now hold the results of the last timed step: they must equal the device-resident
+    # path on the same window set (windows are independent and the kernels are deterministic in out, dq, dk, dv)
+    ref_out, ref_grads = step(e2e_steps - 1)
+    torch.cuda.synchronize()
+    for name, got, want in (("out", out_pin[0], ref_out), ("dq", out_pin[1], ref_grads[0]),
+                            ("dk", out_pin[2], ref_grads[1]), ("dv", out_pin[3], ref_grads[2])):
+        if not torch.equal(got, want.cpu()):
+            raise RuntimeError(f"end-to-end pipeline: {name} differs from the device-resident result")
 
     stats = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e_ms, float(N)], dtype=torch.float64, device="cuda")
     if world > 1:
