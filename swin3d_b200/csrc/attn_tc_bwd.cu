@@ -1,4 +1,4 @@
-// Fused backward of the cRSE window attention, tensor-core path (fp16 storage, head_dim 8).
+// Fused backward of the cRSE window attention, tensor-core path (fp16 storage, head_dim 8 or 16).
 //
 // One templated kernel, launched twice per call:
 //   SIDE 0  lanes = queries (x = q, y = k):  dQ, dTq, dTv
@@ -12,7 +12,11 @@
 //   dTv    += H1^T . dO               (SIDE 0)
 // Table gradients are accumulated in registers over every window a block processes and reach
 // global memory once per block (atomicAdd of fp32), instead of once per pair, head and channel.
-// grid = (x, H/2); one block per SM (16 warps); shared-memory layouts as in attn_tc.cuh.
+// grid = (x, head pairs or heads: head modes of attn_tc.cuh); one block per SM (16 warps).  With two
+// planes (two heads of 16 channels per block) contractions over channels accumulate over the planes,
+// per-channel products (dX, dT) are made once per plane; the y-side table fragments, used once per
+// y tile, stay in registers, the x-side ones are fetched per item, and the x rows are staged a second
+// time for the table-gradient GEMMs instead of being held in registers across the y loop.
 #include "attn_kernels.cuh"
 #include "attn_tc.cuh"
 

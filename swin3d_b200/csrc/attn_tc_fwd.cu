@@ -1,16 +1,19 @@
-// Fused forward of the cRSE window attention, tensor-core path (fp16 storage, head_dim 8).
+// Fused forward of the cRSE window attention, tensor-core path (fp16 storage, head_dim 8 or 16).
 //
-// grid = (x, H/2): a block serves one pair of heads for the windows x, x+gridDim.x, ... and keeps
-// that head pair's table slices as mma fragments in registers for its whole life.  Work item =
-// (window, tile of 32 queries); keys are streamed in tiles of 16 with an online softmax whose
-// rescale happens once per key tile.  Per key tile:
+// grid = (x, head pairs or heads, see the head modes in attn_tc.cuh): a block serves its two slots
+// for the windows x, x+gridDim.x, ...  Work item = (window, tile of 32 queries); keys are streamed in
+// tiles of two per warp (32 with 16 warps, 16 with 8) with an online softmax whose rescale happens
+// once per key tile.  Per key tile:
 //   GEMM    P_k = K.Tk^T (this tile's keys), S0 = K.Q^T                          [tensor cores]
 //   phase 1 lane = query, each warp two keys: cRSE indices, 2*D look-ups, score, running max
 //   phase 1.5 probabilities p = exp(s - m), row sums
-//   phase 2 one or two signal dimensions per warp: hist[row][q] += p, four keys per step (no atomics:
-//           rows of different dimensions are disjoint, a warp owns its dimensions) | warp 7: O += P.V [tc]
-// and per item:  P_q = Q.Tq^T before, O += hist.Tv after                        [tensor cores]
-// See attn_tc.cuh for the factorisation and the shared-memory layouts.
+//   phase 2 one signal dimension per warp (two with 8 warps): hist[row][q] += p, four keys per step
+//           (no atomics: rows of different dimensions are disjoint, a warp owns its dimensions)
+//           | last warp (and, with two planes, the one before it): O += P.V           [tensor cores]
+// and per item:  P_q = Q.Tq^T before, O += hist.Tv after (once per plane)         [tensor cores]
+// The Tk fragments (used once per key tile) stay in registers; Tq and Tv (used once per item) do
+// too when the head mode has one plane and are fetched through L1/L2 otherwise.
+// See attn_tc.cuh for the factorisation, the head modes and the shared-memory layouts.
 #include "attn_kernels.cuh"
 #include "attn_tc.cuh"
 
