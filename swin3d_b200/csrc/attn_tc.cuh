@@ -155,7 +155,13 @@ __device__ __forceinline__ void load_table_a_frag(uint32_t (&a)[2][2], const __h
     }
 }
 
-// B-operand fragment (k = the 16 table rows of k-step ks, n = the 8 channels of slot h, plane s).
+// Table row (within a 16-row k-step) that k-slot (2t + 8*half + second) of an mma lane stands for in
+// the hist . T products: slots {2t, 2t+1, 2t+8, 2t+9} <-> rows {t, t+4, t+8, t+12}.  This is the order
+// in which the conflict-free histogram loads of ht_unit (attn_tc_small.cuh) deliver the rows.
+__device__ __forceinline__ int ht_krow(int t, int half, int second) { return t + 8 * half + 4 * second; }
+
+// B-operand fragment (k = the 16 table rows of k-step ks in ht_krow order, n = the 8 channels of
+// slot h, plane s).
 template <int HDM>
 __device__ __forceinline__ void load_table_b_frag(uint32_t (&b)[2][2], const __half *tab, const CrseMeta &im, int HC,
                                                   int hp, int s, int ks, int g, int t)
@@ -164,7 +170,7 @@ __device__ __forceinline__ void load_table_b_frag(uint32_t (&b)[2][2], const __h
     for (int h = 0; h < 2; ++h)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-            const int ra = table_row(im, ks * 16 + 2 * t + 8 * half), rb = table_row(im, ks * 16 + 2 * t + 8 * half + 1);
+            const int ra = table_row(im, ks * 16 + ht_krow(t, half, 0)), rb = table_row(im, ks * 16 + ht_krow(t, half, 1));
             const int o = slot_offset<HDM>(hp, h, s) + g;
             const __half lo = ra >= 0 ? tab[(int64_t)ra * HC + o] : __float2half(0.f);
             const __half hi = rb >= 0 ? tab[(int64_t)rb * HC + o] : __float2half(0.f);

@@ -19,6 +19,7 @@
 // time for the table-gradient GEMMs instead of being held in registers across the y loop.
 #include "attn_kernels.cuh"
 #include "attn_tc.cuh"
+#include "attn_tc_small.cuh"
 
 namespace s3d {
 namespace tc {
@@ -116,11 +117,16 @@ __device__ __forceinline__ void project(const uint32_t (&ta)[MTA][NPA][2][2], co
                 }
             }
             if (LANE_MAJOR) {
+                // odd rows of a quarter warp store their upper half first: the eight lanes cover all banks
                 uint32_t *r0 = dst + (mt * 16 + g) * QT + 4 * t;
-                *reinterpret_cast<uint4 *>(r0) = make_uint4(d0[0], d0[2], d0[4], d0[6]);
-                *reinterpret_cast<uint4 *>(r0 + 16) = make_uint4(d0[1], d0[3], d0[5], d0[7]);
-                *reinterpret_cast<uint4 *>(r0 + 8 * QT) = make_uint4(d1[0], d1[2], d1[4], d1[6]);
-                *reinterpret_cast<uint4 *>(r0 + 8 * QT + 16) = make_uint4(d1[1], d1[3], d1[5], d1[7]);
+                const bool od = g & 1;
+                const int o0 = od ? 16 : 0, o1 = 16 - o0;
+                const uint4 a0 = make_uint4(d0[0], d0[2], d0[4], d0[6]), a1 = make_uint4(d0[1], d0[3], d0[5], d0[7]);
+                const uint4 b0 = make_uint4(d1[0], d1[2], d1[4], d1[6]), b1 = make_uint4(d1[1], d1[3], d1[5], d1[7]);
+                *reinterpret_cast<uint4 *>(r0 + o0) = od ? a1 : a0;
+                *reinterpret_cast<uint4 *>(r0 + o1) = od ? a0 : a1;
+                *reinterpret_cast<uint4 *>(r0 + 8 * QT + o0) = od ? b1 : b0;
+                *reinterpret_cast<uint4 *>(r0 + 8 * QT + o1) = od ? b0 : b1;
             } else {
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
@@ -513,13 +519,10 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
 #pragma unroll
                     for (int a = 0; a < NH; ++a)
 #pragma unroll
-                        for (int ks = 0; ks < 2; ++ks) {
-                            // lane (g,t): rows g and g+8 of the tile, positions 16ks+4t .. +3  <->  k = 2t, 2t+1, 2t+8, 2t+9
-                            const uint4 u = *reinterpret_cast<const uint4 *>(s_hx + a * pxw + (mt * 16 + g) * QT + 16 * ks + 4 * t);
-                            const uint4 v2 = *reinterpret_cast<const uint4 *>(s_hx + a * pxw + (mt * 16 + g + 8) * QT + 16 * ks + 4 * t);
+                        for (int pl = 0; pl < NPL; ++pl) {
+                            uint32_t bf[2][2][2];   // [k-step][slot][b0, b1]
 #pragma unroll
-                            for (int pl = 0; pl < NPL; ++pl) {
-                                uint32_t bf[2][2];
+                            for (int ks = 0; ks < 2; ++ks) {
                                 if (PAIR16) {
                                     const __half *src = (a == 0 ? s_x0 : s_x1) + pl * 512;
 #pragma unroll
@@ -528,17 +531,14 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                                         for (int half = 0; half < 2; ++half) {
                                             const int p0 = 16 * ks + 4 * t + 2 * half, p1 = p0 + 1;
                                             const int xa = (p0 >> 2) + 8 * (p0 & 3), xb = (p1 >> 2) + 8 * (p1 & 3);
-                                            bf[h][half] = h2_as_u32(__halves2half2(src[xa * 16 + h * 8 + g], src[xb * 16 + h * 8 + g]));
+                                            bf[ks][h][half] = h2_as_u32(__halves2half2(src[xa * 16 + h * 8 + g], src[xb * 16 + h * 8 + g]));
                                         }
                                 } else {
-                                    bf[0][0] = xTB[a % NHP][ks][0][0]; bf[0][1] = xTB[a % NHP][ks][0][1];
-                                    bf[1][0] = xTB[a % NHP][ks][1][0]; bf[1][1] = xTB[a % NHP][ks][1][1];
+                                    bf[ks][0][0] = xTB[a % NHP][ks][0][0]; bf[ks][0][1] = xTB[a % NHP][ks][0][1];
+                                    bf[ks][1][0] = xTB[a % NHP][ks][1][0]; bf[ks][1][1] = xTB[a % NHP][ks][1][1];
                                 }
-                                mma_k16(dt_acc[pl][a][i][0], pack_lo(u.x, u.y), pack_lo(v2.x, v2.y), pack_lo(u.z, u.w), pack_lo(v2.z, v2.w),
-                                        bf[0][0], bf[0][1]);
-                                mma_k16(dt_acc[pl][a][i][1], pack_hi(u.x, u.y), pack_hi(v2.x, v2.y), pack_hi(u.z, u.w), pack_hi(v2.z, v2.w),
-                                        bf[1][0], bf[1][1]);
                             }
+                            dt_unit_b(dt_acc[pl][a][i], s_hx + a * pxw, bf, mt, g, t);
                         }
                 }
             }
@@ -564,15 +564,7 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                             bf[0][0] = t0B[i % MTP][0][0]; bf[0][1] = t0B[i % MTP][0][1];
                             bf[1][0] = t0B[i % MTP][1][0]; bf[1][1] = t0B[i % MTP][1][1];
                         }
-                        const uint4 y0v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t) * QT + 4 * g);
-                        const uint4 y1v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t + 1) * QT + 4 * g);
-                        const uint4 y2v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t + 8) * QT + 4 * g);
-                        const uint4 y3v = *reinterpret_cast<const uint4 *>(s_hx + (ks * 16 + 2 * t + 9) * QT + 4 * g);
-                        // m-tile 0: queries g, g+8 (columns .x, .y) ; m-tile 1: queries g+16, g+24 (.z, .w)
-                        mma_k16(part[0][0], pack_lo(y0v.x, y1v.x), pack_lo(y0v.y, y1v.y), pack_lo(y2v.x, y3v.x), pack_lo(y2v.y, y3v.y), bf[0][0], bf[0][1]);
-                        mma_k16(part[1][0], pack_hi(y0v.x, y1v.x), pack_hi(y0v.y, y1v.y), pack_hi(y2v.x, y3v.x), pack_hi(y2v.y, y3v.y), bf[1][0], bf[1][1]);
-                        mma_k16(part[0][1], pack_lo(y0v.z, y1v.z), pack_lo(y0v.w, y1v.w), pack_lo(y2v.z, y3v.z), pack_lo(y2v.w, y3v.w), bf[0][0], bf[0][1]);
-                        mma_k16(part[1][1], pack_hi(y0v.z, y1v.z), pack_hi(y0v.w, y1v.w), pack_hi(y2v.z, y3v.z), pack_hi(y2v.w, y3v.w), bf[1][0], bf[1][1]);
+                        ht_unit(part, s_hx, bf, ks, g, t);
                     }
                 }
                 // every warp is done with s_px (phase 1 look-ups) before it becomes s_red, and with the

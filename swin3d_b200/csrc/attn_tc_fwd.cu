@@ -16,6 +16,7 @@
 // See attn_tc.cuh for the factorisation, the head modes and the shared-memory layouts.
 #include "attn_kernels.cuh"
 #include "attn_tc.cuh"
+#include "attn_tc_small.cuh"
 
 namespace s3d {
 namespace tc {
@@ -139,12 +140,17 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                             else mma_k16_ha(d0[j], d1[j], af[0][0], af[0][1], af[1][0], af[1][1], qB[pl][j][0], qB[pl][j][1]);
                         }
                     }
-                    // query 4j+t sits in column 4t + j/2 (j even) or 16 + 4t + j/2 (j odd)
+                    // query 4j+t sits in column 4t + j/2 (j even) or 16 + 4t + j/2 (j odd); odd rows of a
+                    // quarter warp store their upper half first so that the eight lanes cover all banks
                     uint32_t *r0 = s_pq + (mt * 16 + g) * QT + 4 * t;
-                    *reinterpret_cast<uint4 *>(r0) = make_uint4(d0[0], d0[2], d0[4], d0[6]);
-                    *reinterpret_cast<uint4 *>(r0 + 16) = make_uint4(d0[1], d0[3], d0[5], d0[7]);
-                    *reinterpret_cast<uint4 *>(r0 + 8 * QT) = make_uint4(d1[0], d1[2], d1[4], d1[6]);
-                    *reinterpret_cast<uint4 *>(r0 + 8 * QT + 16) = make_uint4(d1[1], d1[3], d1[5], d1[7]);
+                    const bool od = g & 1;
+                    const int o0 = od ? 16 : 0, o1 = 16 - o0;
+                    const uint4 a0 = make_uint4(d0[0], d0[2], d0[4], d0[6]), a1 = make_uint4(d0[1], d0[3], d0[5], d0[7]);
+                    const uint4 b0 = make_uint4(d1[0], d1[2], d1[4], d1[6]), b1 = make_uint4(d1[1], d1[3], d1[5], d1[7]);
+                    *reinterpret_cast<uint4 *>(r0 + o0) = od ? a1 : a0;
+                    *reinterpret_cast<uint4 *>(r0 + o1) = od ? a0 : a1;
+                    *reinterpret_cast<uint4 *>(r0 + 8 * QT + o0) = od ? b1 : b0;
+                    *reinterpret_cast<uint4 *>(r0 + 8 * QT + o1) = od ? b0 : b1;
                 }
             }
             float m_run[2] = {-INFINITY, -INFINITY};
@@ -410,26 +416,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                             bf[0][0] = tvB[i % MTP][0][0]; bf[0][1] = tvB[i % MTP][0][1];
                             bf[1][0] = tvB[i % MTP][1][0]; bf[1][1] = tvB[i % MTP][1][1];
                         }
-                        // rows 2t, 2t+1, 2t+8, 2t+9 of this k-step; columns = queries {g, g+8, g+16, g+24}
-                        uint32_t x0[4], x1[4], x2[4], x3[4];
-                        {
-                            const uint4 y0 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t) * QT + 4 * g);
-                            const uint4 y1 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t + 1) * QT + 4 * g);
-                            const uint4 y2 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t + 8) * QT + 4 * g);
-                            const uint4 y3 = *reinterpret_cast<const uint4 *>(s_hist + (ks * 16 + 2 * t + 9) * QT + 4 * g);
-                            x0[0] = y0.x; x0[1] = y0.y; x0[2] = y0.z; x0[3] = y0.w;
-                            x1[0] = y1.x; x1[1] = y1.y; x1[2] = y1.z; x1[3] = y1.w;
-                            x2[0] = y2.x; x2[1] = y2.y; x2[2] = y2.z; x2[3] = y2.w;
-                            x3[0] = y3.x; x3[1] = y3.y; x3[2] = y3.z; x3[3] = y3.w;
-                        }
-#pragma unroll
-                        for (int mtile = 0; mtile < 2; ++mtile) {
-                            const int ja = 2 * mtile, jb = 2 * mtile + 1;   // queries g+16m and g+16m+8
-                            mma_k16(part[0][mtile], pack_lo(x0[ja], x1[ja]), pack_lo(x0[jb], x1[jb]),
-                                    pack_lo(x2[ja], x3[ja]), pack_lo(x2[jb], x3[jb]), bf[0][0], bf[0][1]);
-                            mma_k16(part[1][mtile], pack_hi(x0[ja], x1[ja]), pack_hi(x0[jb], x1[jb]),
-                                    pack_hi(x2[ja], x3[ja]), pack_hi(x2[jb], x3[jb]), bf[1][0], bf[1][1]);
-                        }
+                        ht_unit(part, s_hist, bf, ks, g, t);
                     }
                 }
                 // s_red aliases s_pk, which nobody reads after the last phase 1 (a barrier ago); the

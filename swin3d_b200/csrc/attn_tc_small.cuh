@@ -1,5 +1,5 @@
-// Warp-level GEMM building blocks shared by the single-tile (window of at most 32 voxels) kernels:
-// one projection unit, the pair-array GEMMs, one table-gradient unit, one hist.T unit.
+// Warp-level GEMM building blocks: one projection unit and the pair-array GEMMs of the single-tile
+// (window of at most 32 voxels) kernels, one table-gradient unit and one hist.T unit for all kernels.
 #pragma once
 #include "attn_tc.cuh"
 
@@ -115,10 +115,21 @@ __device__ __forceinline__ void dt_unit(float (&acc)[2][4], const uint32_t *hist
     }
 }
 
-// Table row (within a 16-row k-step) that k-slot (2t + 8*half + second) of an mma lane stands for in
-// ht_unit: slots {2t, 2t+1, 2t+8, 2t+9} <-> rows {t, t+4, t+8, t+12}.  The B fragments (table rows)
-// must be loaded with the same permutation.
-__device__ __forceinline__ int ht_krow(int t, int half, int second) { return t + 8 * half + 4 * second; }
+// The same with the B fragments (k = voxel, n = channel; [k-step][slot][b0, b1]) supplied by the caller.
+__device__ __forceinline__ void dt_unit_b(float (&acc)[2][4], const uint32_t *hist, const uint32_t (&b)[2][2][2], int mt, int g, int t)
+{
+    const bool od = g & 1;
+    const uint32_t *hu = hist + (mt * 16 + g) * QT + 4 * t, *hw = hu + 8 * QT;
+    const uint4 ua = *reinterpret_cast<const uint4 *>(hu + (od ? 16 : 0)), ub = *reinterpret_cast<const uint4 *>(hu + (od ? 0 : 16));
+    const uint4 wa = *reinterpret_cast<const uint4 *>(hw + (od ? 16 : 0)), wb = *reinterpret_cast<const uint4 *>(hw + (od ? 0 : 16));
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+        const bool first = (ks == 0) != od;
+        const uint4 u = first ? ua : ub, w = first ? wa : wb;
+        mma_k16(acc[0], pack_lo(u.x, u.y), pack_lo(w.x, w.y), pack_lo(u.z, u.w), pack_lo(w.z, w.w), b[ks][0][0], b[ks][0][1]);
+        mma_k16(acc[1], pack_hi(u.x, u.y), pack_hi(w.x, w.y), pack_hi(u.z, u.w), pack_hi(w.z, w.w), b[ks][1][0], b[ks][1][1]);
+    }
+}
 
 // part[head][m-tile] += hist(16 rows of k-step ks) . T(16 rows)  for the 32 voxels (m) of the window.
 // The fragment an mma lane (g,t) needs (four rows, one 16-byte column chunk g) would make the four
