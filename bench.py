@@ -49,6 +49,30 @@ def load_peaks():
     return 6650.0, "fallback"
 
 
+def bind_to_gpu_numa_node(local_rank: int) -> None:
+    """Runs this rank on the CPU cores next to its GPU (as NVML reports them), so that the pinned host
+    buffers it allocates afterwards are on that socket and the copies do not cross the inter-socket
+    link.  Only this process's own CPU affinity is touched; nothing is done if NVML or the cores are
+    not available."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:        # the CUDA ordinal need not be the NVML index: go through the PCI address
+            import torch
+            pr = torch.cuda.get_device_properties(local_rank)
+            handle = pynvml.nvmlDeviceGetHandleByPciBusId(
+                f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0".encode())
+        except Exception:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        near = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        cpus = near & os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+    except Exception:
+        pass
+
+
 def make_batch(rank: int, rooms: int, voxels_per_room: int):
     from swin3d_b200 import synthetic as S
     scenes = [S.make_room(1000 * rank + s, target_voxels=voxels_per_room, batch_index=s)
@@ -176,6 +200,7 @@ def run_attention(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
+        bind_to_gpu_numa_node(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     c = CFG
     H, hd, ws, quant, crse = c["H"], c["hd"], c["ws"], c["quant"], c["crse"]
