@@ -140,35 +140,40 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
             cx[d] = lane < n ? __ldg(P.n_coords + (int64_t)(base + lane) * D + d) : 0.f;
             if (wid == 0) s_c[lane * 12 + d] = cx[d];
         }
-        if (tid < 256) {
-            const int i = tid >> 3, arr = (tid >> 1) & 3, hf = tid & 1;
-            uint4 val = make_uint4(0, 0, 0, 0);
-            if (i < n) {
-                const int row = __ldg(P.n2n + base + i);
-                if (arr == 0 && hf == 0) s_row[i] = row;
-                const __half *src = arr == 0 ? P.q : (arr == 1 ? P.k : (arr == 2 ? P.v : P.dout));
-                val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)row * HC + co + hf * 8));
-                if (arr == 3) {
-                    const uint4 ov = __ldg(reinterpret_cast<const uint4 *>(P.o + (int64_t)row * HC + co + hf * 8));
-                    const __half2 *a2 = reinterpret_cast<const __half2 *>(&val);
-                    const __half2 *b2 = reinterpret_cast<const __half2 *>(&ov);
-                    float acc = 0.f;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
-                        acc += fa.x * fb.x + fa.y * fb.y;
-                    }
-                    s_del[i * 2 + hf] = acc;
-                    s_lse[i * 2 + hf] = __ldg(P.lse + (int64_t)row * H + (HD16 ? hp : 2 * hp + hf));
-                }
-            } else if (arr == 3) {
-                s_del[i * 2 + hf] = 0.f;
-                s_lse[i * 2 + hf] = 0.f;
+        // the global loads are issued first and consumed after the histograms have been cleared, so
+        // that their latency overlaps the clearing
+        const int st_i = tid >> 3, st_arr = (tid >> 1) & 3, st_hf = tid & 1;
+        const bool st_act = tid < 256 && st_i < n;
+        uint4 st_val = make_uint4(0, 0, 0, 0), st_o = make_uint4(0, 0, 0, 0);
+        float st_lse = 0.f;
+        int st_row = 0;
+        if (st_act) {
+            st_row = __ldg(P.n2n + base + st_i);
+            const __half *src = st_arr == 0 ? P.q : (st_arr == 1 ? P.k : (st_arr == 2 ? P.v : P.dout));
+            st_val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)st_row * HC + co + st_hf * 8));
+            if (st_arr == 3) {
+                st_o = __ldg(reinterpret_cast<const uint4 *>(P.o + (int64_t)st_row * HC + co + st_hf * 8));
+                st_lse = __ldg(P.lse + (int64_t)st_row * H + (HD16 ? hp : 2 * hp + st_hf));
             }
-            *reinterpret_cast<uint4 *>(s_q + arr * 512 + i * 16 + hf * 8) = val;
         }
         for (int i = tid; i < 2 * L.R16 * QT / 4; i += SM_THREADS)
             reinterpret_cast<uint4 *>(s_hq)[i] = make_uint4(0, 0, 0, 0);     // histQ and histV are adjacent
+        if (tid < 256) {
+            if (st_act && st_arr == 0 && st_hf == 0) s_row[st_i] = st_row;
+            if (st_arr == 3) {
+                const __half2 *a2 = reinterpret_cast<const __half2 *>(&st_val);
+                const __half2 *b2 = reinterpret_cast<const __half2 *>(&st_o);
+                float acc = 0.f;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
+                    acc += fa.x * fb.x + fa.y * fb.y;
+                }
+                s_del[st_i * 2 + st_hf] = acc;         // zero beyond the window (both rows are zero there)
+                s_lse[st_i * 2 + st_hf] = st_lse;
+            }
+            *reinterpret_cast<uint4 *>(s_q + st_arr * 512 + st_i * 16 + st_hf * 8) = st_val;
+        }
         __syncthreads();
         const float xlse0 = s_lse[lane * 2], xlse1 = s_lse[lane * 2 + 1];
         float xdel0 = s_del[lane * 2], xdel1 = s_del[lane * 2 + 1];
