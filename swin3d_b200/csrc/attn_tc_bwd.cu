@@ -268,37 +268,42 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
 #pragma unroll
             for (int d = 0; d < D; ++d)
                 cx[d] = lane < nx ? __ldg(P.n_coords + (int64_t)(base + x0 + lane) * D + d) : 0.f;
-            if (tid < 128 * NPL) {
-                const int xi = (tid >> 2) & 31, which = (tid >> 1) & 1, hf = tid & 1, pl = tid >> 7;
-                uint4 val = make_uint4(0, 0, 0, 0);
-                if (xi < nx) {
-                    const int row = __ldg(P.n2n + base + x0 + xi);
-                    if (which == 0 && hf == 0 && pl == 0) s_xrow[xi] = row;
-                    const __half *src = which ? P.x1 : P.x0;
-                    const int64_t goff = (int64_t)row * HC + slot_offset<HDM>(hp, hf, pl);
-                    val = __ldg(reinterpret_cast<const uint4 *>(src + goff));
-                    if (SIDE == 0 && which == 1) {
-                        // delta[x][slot hf] = sum_c dO . O (this plane's 8 channels) ; lse
-                        const uint4 ov = __ldg(reinterpret_cast<const uint4 *>(P.o + goff));
-                        const __half2 *a2 = reinterpret_cast<const __half2 *>(&val);
-                        const __half2 *b2 = reinterpret_cast<const __half2 *>(&ov);
-                        float acc = 0.f;
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
-                            acc += fa.x * fb.x + fa.y * fb.y;
-                        }
-                        s_xdel[pl * 64 + xi * 2 + hf] = acc;
-                        if (pl == 0) s_xlse[xi * 2 + hf] = __ldg(P.lse + (int64_t)row * H + (HD16 ? hp : 2 * hp + hf));
-                    }
-                } else if (SIDE == 0 && which == 1) {
-                    s_xdel[pl * 64 + xi * 2 + hf] = 0.f;
-                    if (pl == 0) s_xlse[xi * 2 + hf] = 0.f;
+            // the global loads are issued first and consumed after the histograms have been cleared, so
+            // that their latency overlaps the clearing
+            const int st_xi = (tid >> 2) & 31, st_which = (tid >> 1) & 1, st_hf = tid & 1, st_pl = tid >> 7;
+            const bool st_stage = tid < 128 * NPL, st_act = st_stage && st_xi < nx;
+            uint4 st_val = make_uint4(0, 0, 0, 0), st_o = make_uint4(0, 0, 0, 0);
+            float st_lse = 0.f;
+            int st_row = 0;
+            if (st_act) {
+                st_row = __ldg(P.n2n + base + x0 + st_xi);
+                const __half *src = st_which ? P.x1 : P.x0;
+                const int64_t goff = (int64_t)st_row * HC + slot_offset<HDM>(hp, st_hf, st_pl);
+                st_val = __ldg(reinterpret_cast<const uint4 *>(src + goff));
+                if (SIDE == 0 && st_which == 1) {
+                    st_o = __ldg(reinterpret_cast<const uint4 *>(P.o + goff));
+                    if (st_pl == 0) st_lse = __ldg(P.lse + (int64_t)st_row * H + (HD16 ? hp : 2 * hp + st_hf));
                 }
-                *reinterpret_cast<uint4 *>((which ? s_x1 : s_x0) + pl * 512 + xi * 16 + hf * 8) = val;
             }
             for (int i = tid; i < NH * L.R16 * QT / 4; i += BW_THREADS)
                 reinterpret_cast<uint4 *>(s_hx)[i] = make_uint4(0, 0, 0, 0);
+            if (st_stage) {
+                if (st_act && st_which == 0 && st_hf == 0 && st_pl == 0) s_xrow[st_xi] = st_row;
+                if (SIDE == 0 && st_which == 1) {
+                    // delta[x][slot hf] = sum_c dO . O (this plane's 8 channels; zero beyond the tile) ; lse
+                    const __half2 *a2 = reinterpret_cast<const __half2 *>(&st_val);
+                    const __half2 *b2 = reinterpret_cast<const __half2 *>(&st_o);
+                    float acc = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
+                        acc += fa.x * fb.x + fa.y * fb.y;
+                    }
+                    s_xdel[st_pl * 64 + st_xi * 2 + st_hf] = acc;
+                    if (st_pl == 0) s_xlse[st_xi * 2 + st_hf] = st_lse;
+                }
+                *reinterpret_cast<uint4 *>((st_which ? s_x1 : s_x0) + st_pl * 512 + st_xi * 16 + st_hf * 8) = st_val;
+            }
             __syncthreads();
             float xlse[2] = {0.f, 0.f}, xdel[2] = {0.f, 0.f};
             if (SIDE == 0) {

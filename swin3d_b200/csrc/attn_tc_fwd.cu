@@ -91,18 +91,22 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
 #pragma unroll
             for (int d = 0; d < D; ++d)
                 cq[d] = lane < nq ? __ldg(n_coords + (int64_t)(base + q0 + lane) * D + d) : 0.f;
-            if (tid < 64 * NPL) {
-                const int qi = (tid >> 1) & 31, hf = tid & 1, pl = tid >> 6;
-                uint4 val = make_uint4(0, 0, 0, 0);
-                if (qi < nq) {
-                    const int row = __ldg(n2n + base + q0 + qi);
-                    if (hf == 0 && pl == 0) s_qrow[qi] = row;
-                    val = __ldg(reinterpret_cast<const uint4 *>(q + (int64_t)row * HC + slot_offset<HDM>(hp, hf, pl)));
-                }
-                *reinterpret_cast<uint4 *>(s_q + pl * 512 + qi * 16 + hf * 8) = val;
+            // the row loads are issued first and stored after the histogram has been cleared, so that
+            // their latency overlaps the clearing
+            const int st_qi = (tid >> 1) & 31, st_hf = tid & 1, st_pl = tid >> 6;
+            const bool st_stage = tid < 64 * NPL;
+            uint4 st_val = make_uint4(0, 0, 0, 0);
+            int st_row = 0;
+            if (st_stage && st_qi < nq) {
+                st_row = __ldg(n2n + base + q0 + st_qi);
+                st_val = __ldg(reinterpret_cast<const uint4 *>(q + (int64_t)st_row * HC + slot_offset<HDM>(hp, st_hf, st_pl)));
             }
             for (int i = tid; i < L.R16 * QT / 4; i += NTHREADS)
                 reinterpret_cast<uint4 *>(s_hist)[i] = make_uint4(0, 0, 0, 0);
+            if (st_stage) {
+                if (st_qi < nq && st_hf == 0 && st_pl == 0) s_qrow[st_qi] = st_row;
+                *reinterpret_cast<uint4 *>(s_q + st_pl * 512 + st_qi * 16 + st_hf * 8) = st_val;
+            }
             __syncthreads();
             // block-diagonal B fragments of Q^T: n-tile j <-> (queries 4j..4j+3) x (slot 0, slot 1)
             uint32_t qB[NPL][8][2];
