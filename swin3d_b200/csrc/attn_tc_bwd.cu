@@ -268,6 +268,35 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
 #pragma unroll
             for (int d = 0; d < D; ++d)
                 cx[d] = lane < nx ? __ldg(P.n_coords + (int64_t)(base + x0 + lane) * D + d) : 0.f;
+            // y tiles are fetched into registers one tile ahead: row pieces (and, SIDE 1, the forward
+            // output and lse of the rows) by the first 4*BKT*NPL threads, y coordinates one element per
+            // thread starting from the upper half
+            uint4 pf_val = make_uint4(0, 0, 0, 0), pf_o = make_uint4(0, 0, 0, 0);
+            float pf_c = 0.f, pf_ls = 0.f;
+            const int pf_e = (tid + BW_THREADS / 2) % BW_THREADS;
+            static_assert(BKT * D <= BW_THREADS, "one y coordinate per thread");
+            auto fetch_tile = [&](int yb) {
+                const int nyb = min(BKT, n - yb);
+                pf_val = make_uint4(0, 0, 0, 0);
+                pf_o = make_uint4(0, 0, 0, 0);
+                pf_c = 0.f;
+                pf_ls = 0.f;
+                if (tid < 4 * BKT * NPL) {
+                    const int yi = (tid >> 2) % BKT, which = (tid >> 1) & 1, hf = tid & 1, pl = tid / (4 * BKT);
+                    if (yi < nyb) {
+                        const int row = __ldg(P.n2n + base + yb + yi);
+                        const __half *src = which ? P.y1 : P.y0;
+                        const int64_t goff = (int64_t)row * HC + slot_offset<HDM>(hp, hf, pl);
+                        pf_val = __ldg(reinterpret_cast<const uint4 *>(src + goff));
+                        if (SIDE == 1 && which == 1) {
+                            pf_o = __ldg(reinterpret_cast<const uint4 *>(P.o + goff));
+                            if (pl == 0) pf_ls = __ldg(P.lse + (int64_t)row * H + (HD16 ? hp : 2 * hp + hf));
+                        }
+                    }
+                }
+                if (pf_e < BKT * D && pf_e / D < nyb) pf_c = __ldg(P.n_coords + (int64_t)(base + yb + pf_e / D) * D + pf_e % D);
+            };
+            fetch_tile(0);
             // the global loads are issued first and consumed after the histograms have been cleared, so
             // that their latency overlaps the clearing
             const int st_xi = (tid >> 2) & 31, st_which = (tid >> 1) & 1, st_hf = tid & 1, st_pl = tid >> 7;
@@ -358,39 +387,26 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
             for (int y0 = 0; y0 < n; y0 += BKT) {
                 const int ny = min(BKT, n - y0);
                 __syncthreads();
-                // ---- stage the y tile ---------------------------------------------------------------
+                // ---- stage the y tile (fetched into registers one tile ahead) ----------------------------
                 if (tid < 4 * BKT * NPL) {
                     const int yi = (tid >> 2) % BKT, which = (tid >> 1) & 1, hf = tid & 1, pl = tid / (4 * BKT);
-                    uint4 val = make_uint4(0, 0, 0, 0);
-                    float del = 0.f, ls = 0.f;
-                    if (yi < ny) {
-                        const int row = __ldg(P.n2n + base + y0 + yi);
-                        const __half *src = which ? P.y1 : P.y0;
-                        const int64_t goff = (int64_t)row * HC + slot_offset<HDM>(hp, hf, pl);
-                        val = __ldg(reinterpret_cast<const uint4 *>(src + goff));
-                        if (SIDE == 1 && which == 1) {
-                            const uint4 ov = __ldg(reinterpret_cast<const uint4 *>(P.o + goff));
-                            const __half2 *a2 = reinterpret_cast<const __half2 *>(&val);
-                            const __half2 *b2 = reinterpret_cast<const __half2 *>(&ov);
-#pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
-                                del += fa.x * fb.x + fa.y * fb.y;
-                            }
-                            if (pl == 0) ls = __ldg(P.lse + (int64_t)row * H + (HD16 ? hp : 2 * hp + hf));
-                        }
-                    }
                     if (SIDE == 1 && which == 1) {
-                        s_ydel[pl * 2 * BKT + yi * 2 + hf] = del;
-                        if (pl == 0) s_ylse[yi * 2 + hf] = ls;
+                        const __half2 *a2 = reinterpret_cast<const __half2 *>(&pf_val);
+                        const __half2 *b2 = reinterpret_cast<const __half2 *>(&pf_o);
+                        float del = 0.f;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
+                            del += fa.x * fb.x + fa.y * fb.y;
+                        }
+                        s_ydel[pl * 2 * BKT + yi * 2 + hf] = del;      // zero beyond the tile (both rows are zero there)
+                        if (pl == 0) s_ylse[yi * 2 + hf] = pf_ls;
                     }
-                    *reinterpret_cast<uint4 *>((which ? s_y1 : s_y0) + pl * BKT * 16 + yi * 16 + hf * 8) = val;
+                    *reinterpret_cast<uint4 *>((which ? s_y1 : s_y0) + pl * BKT * 16 + yi * 16 + hf * 8) = pf_val;
                 }
-                for (int e = (tid + BW_THREADS / 2) % BW_THREADS; e < BKT * D; e += BW_THREADS) {   // upper half first: it stages no rows
-                    const int yi = e / D, d = e - yi * D;
-                    s_yc[yi * 12 + d] = yi < ny ? __ldg(P.n_coords + (int64_t)(base + y0 + yi) * D + d) : 0.f;
-                }
+                if (pf_e < BKT * D) s_yc[(pf_e / D) * 12 + pf_e % D] = pf_c;
                 __syncthreads();
+                if (y0 + BKT < n) fetch_tile(y0 + BKT);      // in flight while this tile is worked on
                 // ---- y-side projections; S0 = Y0 . X0^T and dPV0 = Y1 . X1^T, one (m-tile, n-tile) per warp ----
                 project<MTW, false, HDM, true>(ta_py0, P.t_py0, meta, HC, hp, s_y0, BKT, s_py, n_mt, Rp, ny, wid, g, t);
                 if (SIDE == 1) project<MTW, false, HDM, true>(ta_py1, P.t_py1, meta, HC, hp, s_y1, BKT, s_py + pyw, n_mt, Rp, ny, wid, g, t);

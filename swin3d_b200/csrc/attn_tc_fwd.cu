@@ -91,6 +91,27 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
 #pragma unroll
             for (int d = 0; d < D; ++d)
                 cq[d] = lane < nq ? __ldg(n_coords + (int64_t)(base + q0 + lane) * D + d) : 0.f;
+            // key tiles are fetched into registers one tile ahead: K/V row pieces by the first
+            // 4*KT*NPL threads, key coordinates one element per thread starting from the upper half
+            uint4 pf_val = make_uint4(0, 0, 0, 0);
+            float pf_c = 0.f;
+            const int pf_e = (tid + NTHREADS / 2) % NTHREADS;
+            static_assert(KT * D <= NTHREADS, "one key coordinate per thread");
+            auto fetch_tile = [&](int kb) {
+                const int nkb = min(KT, n - kb);
+                pf_val = make_uint4(0, 0, 0, 0);
+                pf_c = 0.f;
+                if (tid < 4 * KT * NPL) {
+                    const int ki = (tid >> 2) % KT, which = (tid >> 1) & 1, hf = tid & 1, pl = tid / (4 * KT);
+                    if (ki < nkb) {
+                        const int row = __ldg(n2n + base + kb + ki);
+                        const __half *src = which ? v : k;
+                        pf_val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)row * HC + slot_offset<HDM>(hp, hf, pl)));
+                    }
+                }
+                if (pf_e < KT * D && pf_e / D < nkb) pf_c = __ldg(n_coords + (int64_t)(base + kb + pf_e / D) * D + pf_e % D);
+            };
+            fetch_tile(0);
             // the row loads are issued first and stored after the histogram has been cleared, so that
             // their latency overlaps the clearing
             const int st_qi = (tid >> 1) & 31, st_hf = tid & 1, st_pl = tid >> 6;
@@ -172,26 +193,18 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
             for (int k0 = 0; k0 < n; k0 += KT) {
                 const int nk = min(KT, n - k0);
                 __syncthreads();  // P_q stored / previous key tile fully consumed
-                // ---- stage the key tile -----------------------------------------------------------
+                // ---- stage the key tile (fetched into registers one tile ahead) ------------------------
                 if (tid < 4 * KT * NPL) {
                     const int ki = (tid >> 2) % KT, which = (tid >> 1) & 1, hf = tid & 1, pl = tid / (4 * KT);
-                    uint4 val = make_uint4(0, 0, 0, 0);
-                    if (ki < nk) {
-                        const int row = __ldg(n2n + base + k0 + ki);
-                        const __half *src = which ? v : k;
-                        val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)row * HC + slot_offset<HDM>(hp, hf, pl)));
-                    }
-                    *reinterpret_cast<uint4 *>((which ? s_v : s_k) + pl * KT * 16 + ki * 16 + hf * 8) = val;
+                    *reinterpret_cast<uint4 *>((which ? s_v : s_k) + pl * KT * 16 + ki * 16 + hf * 8) = pf_val;
                 }
                 if (tid >= NTHREADS - 32) {
                     s_mtile[(tid - (NTHREADS - 32)) * 2] = -INFINITY;
                     s_mtile[(tid - (NTHREADS - 32)) * 2 + 1] = -INFINITY;
                 }
-                for (int e = (tid + NTHREADS / 2) % NTHREADS; e < KT * D; e += NTHREADS) {   // upper half first: it stages no rows
-                    const int ki = e / D, d = e - ki * D;
-                    s_kc[ki * 12 + d] = ki < nk ? __ldg(n_coords + (int64_t)(base + k0 + ki) * D + d) : 0.f;
-                }
+                if (pf_e < KT * D) s_kc[(pf_e / D) * 12 + pf_e % D] = pf_c;
                 __syncthreads();
+                if (k0 + KT < n) fetch_tile(k0 + KT);      // in flight while this tile is worked on
                 // ---- P_k^T[row][(key, slot)] = Tk . K^T -> s_pk[key][row];  S0^T[key][(q, slot)] = K . Q^T ----
                 {
 #pragma unroll
