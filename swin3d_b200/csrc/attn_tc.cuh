@@ -88,6 +88,19 @@ __device__ __forceinline__ int crse_index_fast(float cq, float ck, int L, bool l
     return (int)min(u, (unsigned)(last_dim ? L - 1 : L));
 }
 
+// The coordinates of one staged voxel (rows of 12 floats, 16-byte aligned) as three broadcast
+// 16-byte loads instead of one 4-byte load per signal dimension.
+template <int D>
+__device__ __forceinline__ void load_coords12(const float *row, float (&c)[D])
+{
+    float tmp[12];
+    *reinterpret_cast<float4 *>(tmp) = *reinterpret_cast<const float4 *>(row);
+    if (D > 4) *reinterpret_cast<float4 *>(tmp + 4) = *reinterpret_cast<const float4 *>(row + 4);
+    if (D > 8) *reinterpret_cast<float4 *>(tmp + 8) = *reinterpret_cast<const float4 *>(row + 8);
+#pragma unroll
+    for (int d = 0; d < D; ++d) c[d] = tmp[d];
+}
+
 __device__ __forceinline__ uint32_t pack_lo(uint32_t x, uint32_t y) { return __byte_perm(x, y, 0x5410); }
 __device__ __forceinline__ uint32_t pack_hi(uint32_t x, uint32_t y) { return __byte_perm(x, y, 0x7632); }
 

@@ -444,9 +444,11 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                     if (yy < ny) {
                         __half2 b0 = __float2half2_rn(0.f), b1 = b0, b2 = b0;
                         uint32_t w0 = 0, w1 = 0;
+                        float cyv[D];
+                        load_coords12<D>(s_yc + yy * 12, cyv);
 #pragma unroll
                         for (int d = 0; d < D; ++d) {
-                            const float cy = s_yc[yy * 12 + d];
+                            const float cy = cyv[d];
                             const int idx = SIDE == 0 ? crse_index_fast(cx[d], cy, meta.L[d], d == D - 1)
                                                       : crse_index_fast(cy, cx[d], meta.L[d], d == D - 1);
                             const int row = meta.rowbase[d] + idx;

@@ -217,9 +217,11 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
             if (kk < n) {
                 __half2 b0 = __float2half2_rn(0.f), b1 = b0, b2 = b0;
                 uint32_t w0 = 0, w1 = 0;
+                float ckv[D];
+                load_coords12<D>(s_c + kk * 12, ckv);
 #pragma unroll
                 for (int d = 0; d < D; ++d) {
-                    const int idx = crse_index_fast(cx[d], s_c[kk * 12 + d], meta.L[d], d == D - 1);
+                    const int idx = crse_index_fast(cx[d], ckv[d], meta.L[d], d == D - 1);
                     const int row = meta.rowbase[d] + idx;
                     b0 = __hadd2(b0, u32_as_h2(s_pq[row * QT + mypos]));
                     b1 = __hadd2(b1, u32_as_h2(s_pk[kk * Rp + row]));
