@@ -233,6 +233,84 @@ __device__ __forceinline__ void hist_add4(uint32_t *cell, int arr_stride, const 
                 if (j < cnt) cell[a * arr_stride + off[d][j]] = c[d][a][j];
 }
 
+// Work distribution of the tiled kernels.  A work item is (window, tile of 32 voxels); tile t of window w
+// belongs to block (w + t) mod gridDim.x of its head pair, which spreads the tiles of large windows
+// over the blocks (whole windows per block left the blocks 15-30 % out of balance where windows are
+// few and of very different sizes).  The blocks find their items without any global bookkeeping:
+// window sizes are read in chunks of WL_CHUNK, every thread of the first WL_CHUNK/32 warps looks at one
+// window and the warp appends its items to its own segment of a list in shared memory, in window
+// order (deterministic).  Entry: (window - chunk start) << 8 | tile.  A chunk whose items do not fit
+// the list (windows of thousands of voxels) is walked directly instead (WorkItems::next).
+constexpr int WL_CHUNK = 256, WL_SEG = 64;      // windows per chunk; list entries per warp segment
+constexpr int WL_NSEG = WL_CHUNK / 32;
+constexpr int WL_BYTES = WL_NSEG * WL_SEG * 2 + 64;
+
+// s_list: uint16 [WL_NSEG][WL_SEG], s_cnt: int [WL_NSEG + 1] (the last entry: overflow flag, cleared by
+// the caller before).  All threads of the block call this between two __syncthreads().  Windows of at
+// most `skip_upto` voxels are left out.
+__device__ __forceinline__ void build_work_list(const int32_t *__restrict__ w_sizes, int64_t W, int64_t c0,
+                                                int skip_upto, uint16_t *s_list, int *s_cnt)
+{
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    if (tid >= WL_CHUNK) return;
+    const int nb = gridDim.x, b = blockIdx.x;
+    const int64_t w = c0 + tid;
+    const int n = w < W ? __ldg(w_sizes + w) : 0;
+    const int tiles = n > skip_upto ? (n + QT - 1) / QT : 0;
+    int t = (int)(((int64_t)b - w) % nb);
+    if (t < 0) t += nb;
+    int pos = 0;
+    bool over = tiles > 256;
+    while (__any_sync(0xffffffffu, t < tiles)) {
+        const bool mine = t < tiles;
+        const unsigned m = __ballot_sync(0xffffffffu, mine);
+        if (mine) {
+            const int at = pos + __popc(m & ((1u << lane) - 1u));
+            if (at < WL_SEG) s_list[wid * WL_SEG + at] = (uint16_t)((tid << 8) | (t & 255));
+        }
+        pos += __popc(m);
+        t += nb;
+    }
+    over = over || pos > WL_SEG;
+    if (__any_sync(0xffffffffu, over) && lane == 0) s_cnt[WL_NSEG] = 1;
+    if (lane == 0) s_cnt[wid] = pos;
+}
+
+// Next item of this block in the current chunk (every thread holds the same state: list position
+// pos = segment * WL_SEG + index, or, when the list overflowed, the window and tile of a direct walk).
+// -> true and (window, first voxel of the tile), false at the end of the chunk.
+__device__ __forceinline__ bool next_work_item(const uint16_t *list, const int *cnt, const int32_t *__restrict__ w_sizes,
+                                               int64_t W, int64_t c0, int skip_upto, int &pos, int &dw, int &dt,
+                                               int64_t &win, int &x0)
+{
+    if (cnt[WL_NSEG] == 0) {
+        while (pos < WL_NSEG * WL_SEG && (pos & (WL_SEG - 1)) >= cnt[pos / WL_SEG]) pos = (pos | (WL_SEG - 1)) + 1;
+        if (pos >= WL_NSEG * WL_SEG) return false;
+        const int e = list[pos++];
+        win = c0 + (e >> 8);
+        x0 = (e & 255) * QT;
+        return true;
+    }
+    // direct walk: dw = window offset in the chunk, dt = next tile of that window for this block (-1: none yet)
+    const int nb = gridDim.x, b = blockIdx.x;
+    for (;;) {
+        if (dw >= 0 && dw < WL_CHUNK && c0 + dw < W && dt >= 0) {
+            const int n = __ldg(w_sizes + c0 + dw);
+            const int tiles = n > skip_upto ? (n + QT - 1) / QT : 0;
+            if (dt < tiles) {
+                win = c0 + dw;
+                x0 = dt * QT;
+                dt += nb;
+                return true;
+            }
+        }
+        ++dw;
+        if (dw >= WL_CHUNK || c0 + dw >= W) return false;
+        dt = (int)(((int64_t)b - (c0 + dw)) % nb);
+        if (dt < 0) dt += nb;
+    }
+}
+
 // Shared-memory carve-up (byte offsets) for a table of R rows.
 struct SmemLayout {
     int R16;      // rows rounded up to a multiple of 16
@@ -256,7 +334,7 @@ __host__ __device__ inline SmemLayout make_layout(int R, int n_rowq_arrays, int 
     L.off_idx = off;  off += kt * 2 * QT * 4;                  // packed cRSE indices
     L.off_kv = off;   off += n_planes * 2 * kt * 16 * 2;       // key and value rows of the tile, per plane
     L.off_kc = off;   off += kt * 12 * 4;                      // key coordinates, padded to 12
-    L.off_misc = off; off += 1024;
+    L.off_misc = off; off += 1024 + WL_BYTES;
     L.total = off;
     return L;
 }

@@ -51,7 +51,7 @@ __host__ __device__ inline BwdSmem make_bwd_layout(int R, int npx, int nh, int n
     L.off_idx = off; off += BKT * 2 * QT * 4;
     L.off_yt = off; off += n_planes * 2 * BKT * 16 * 2;
     L.off_yc = off; off += BKT * 12 * 4;
-    L.off_misc = off; off += 2048;
+    L.off_misc = off; off += 2048 + WL_BYTES;
     L.total = off;
     return L;
 }
@@ -203,6 +203,8 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
     float *s_xlse = s_ydel + 2 * 2 * BKT;                             // [32][2]           (SIDE 0)
     float *s_xdel = s_xlse + 64;                                      // [plane][32][2]    (SIDE 0)
     int *s_xrow = reinterpret_cast<int *>(s_xdel + 128);              // [32]
+    uint16_t *s_wlist = reinterpret_cast<uint16_t *>(smem + L.off_misc + 2048);   // work list of the chunk
+    int *s_wcnt = reinterpret_cast<int *>(s_wlist + WL_NSEG * WL_SEG);
     __half *s_x0 = reinterpret_cast<__half *>(smem + L.off_s);        // [plane][32][16] aliases s_s (set-up, table gradients)
     __half *s_x1 = reinterpret_cast<__half *>(smem + L.off_dp);       // [plane][32][16] aliases s_dp
     float *s_red = reinterpret_cast<float *>(smem + L.off_px);        // [16][32][16] aliases s_px (epilogue)
@@ -256,11 +258,17 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
     const int dx_plane = wid >= BW_NWARP - 2 ? 0 : 1;
     const bool dx_warp = wid >= BW_NWARP - (PAIR16 ? 4 : 2) && (SIDE == 1 || dx_which == 0);
 
-    for (int64_t w = blockIdx.x; w < P.W; w += gridDim.x) {
-        const int n = __ldg(P.w_sizes + w);
-        if (n <= P.skip_upto) continue;
-        const int base = __ldg(P.w2n + w);
-        for (int x0 = 0; x0 < n; x0 += QT) {
+    for (int64_t c0 = 0; c0 < P.W; c0 += WL_CHUNK) {
+        __syncthreads();            // every warp has left the item loop of the previous chunk
+        if (tid == 0) s_wcnt[WL_NSEG] = 0;
+        __syncthreads();
+        build_work_list(P.w_sizes, P.W, c0, P.skip_upto, s_wlist, s_wcnt);
+        __syncthreads();
+        int it_pos = 0, it_dw = -1, it_dt = -1;
+        int64_t w;
+        int x0;
+        while (next_work_item(s_wlist, s_wcnt, P.w_sizes, P.W, c0, P.skip_upto, it_pos, it_dw, it_dt, w, x0)) {
+            const int n = __ldg(P.w_sizes + w), base = __ldg(P.w2n + w);
             const int nx = min(QT, n - x0);
             // ---- item set-up: x rows, x coordinates, projections of the x side, empty histograms --------
             __syncthreads();
@@ -619,8 +627,8 @@ attn_bwd_tc_kernel(const BwdParams P, const CrseMeta meta)
                     }
                 }
             }  // planes
-        }  // x tiles
-    }      // windows
+        }  // items
+    }      // chunks of windows
 
     // ---- flush the table gradients of this block ---------------------------------------------------------------
 #pragma unroll
