@@ -51,6 +51,8 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
     float *s_mtile = reinterpret_cast<float *>(smem + L.off_misc);       // [32][2]
     float *s_alpha = s_mtile + 64;                                       // [32][2]
     int *s_qrow = reinterpret_cast<int *>(s_alpha + 64);                 // [32]
+    uint16_t *s_wlist = reinterpret_cast<uint16_t *>(smem + L.off_misc + 1024);   // work list of the chunk
+    int *s_wcnt = reinterpret_cast<int *>(s_wlist + WL_NSEG * WL_SEG);
     __half *s_q = reinterpret_cast<__half *>(smem + L.off_s);            // [plane][32][16], aliases s_s
     float *s_red = reinterpret_cast<float *>(smem + L.off_pk);           // [NW][32][16], aliases s_pk
     float *s_lsum = s_red + NWARP * QT * 16;                             // [NW][32][2]
@@ -79,11 +81,17 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
         }
     }
 
-    for (int64_t w = blockIdx.x; w < W; w += gridDim.x) {
-        const int n = __ldg(w_sizes + w);
-        if (n <= skip_upto) continue;       // left to the single-tile kernel
-        const int base = __ldg(w2n + w);
-        for (int q0 = 0; q0 < n; q0 += QT) {
+    for (int64_t c0 = 0; c0 < W; c0 += WL_CHUNK) {
+        __syncthreads();            // every warp has left the item loop of the previous chunk
+        if (tid == 0) s_wcnt[WL_NSEG] = 0;
+        __syncthreads();
+        build_work_list(w_sizes, W, c0, skip_upto, s_wlist, s_wcnt);   // windows up to skip_upto: single-tile kernel
+        __syncthreads();
+        int it_pos = 0, it_dw = -1, it_dt = -1;
+        int64_t w;
+        int q0;
+        while (next_work_item(s_wlist, s_wcnt, w_sizes, W, c0, skip_upto, it_pos, it_dw, it_dt, w, q0)) {
+            const int n = __ldg(w_sizes + w), base = __ldg(w2n + w);
             const int nq = min(QT, n - q0);
             // ---- item set-up -------------------------------------------------------------------
             __syncthreads();  // previous item's epilogue has finished with s_red / s_qrow
@@ -483,8 +491,8 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                     }
                 }
             }  // planes
-        }  // query tiles
-    }      // windows
+        }  // items
+    }      // chunks of windows
 }
 
 template <int D, int MTW, int HDM, int NW>

@@ -403,3 +403,28 @@ def test_c_abi_calls_can_be_captured_in_a_cuda_graph():
         assert torch.equal(a, b), name
     for a, b in zip(replayed[5:], direct[5:]):      # table gradients: fp32 atomics, order differs
         assert float((a - b).abs().max()) <= 1e-5 * max(float(b.abs().max()), 1e-6)
+
+
+def test_tiled_kernels_work_list_overflow_falls_back_to_a_direct_walk():
+    """150 heads leave one block per head pair, which then owns every tile of every window; nine
+    dense 343-voxel windows give its first warp 99 work items, more than a list segment holds, so the
+    kernels walk the chunk's windows directly.  Checked against the generic kernels of the library."""
+    import os
+    from tests.gpu_helpers import cuda_fwd_bwd
+    g = np.stack(np.meshgrid(np.arange(21), np.arange(21), np.arange(7), indexing="ij"), -1).reshape(-1, 3)
+    n = len(g)
+    rng = np.random.default_rng(8)
+    sc = S.Scene(np.concatenate([np.zeros((n, 1)), g], 1).astype(np.int32),
+                 rng.random((n, 3), dtype=np.float32) * 0.999, rng.random((n, 3), dtype=np.float32),
+                 np.tile(np.array([[0, 0, 1]], dtype=np.float32), (n, 1)))
+    p = make_problem(seed=3, ws=7, H=150, hd=8, crse="XYZ", scene=sc, round_fp16=True)
+    assert p.w_sizes.max() == 343 and len(p.w_sizes) == 9
+    fast = cuda_fwd_bwd(p, torch.float16)
+    os.environ["S3D_FORCE_SCALAR"] = "1"
+    try:
+        slow = cuda_fwd_bwd(p, torch.float16)
+    finally:
+        os.environ.pop("S3D_FORCE_SCALAR")
+    assert rel_err(fast[0], slow[0]) < 5e-3
+    for a, b in zip(fast[2], slow[2]):
+        assert rel_err(a, b) < 1.5e-2
