@@ -693,13 +693,159 @@ def run_knn(args):
     return 0
 
 
+def load_reference_kernels():
+    """The reference's own CUDA kernels as compiled by oracle/build_ref.py (a torch extension module
+    exposing cal_max_coffs, self_attn_forward, cal_exp_sum_grads, self_attn_indir_backward,
+    knn_cuda), or None when that build is not present."""
+    import importlib.machinery
+    import importlib.util
+    so = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "_ref", "ref_swin3d_cuda.so")
+    if not os.path.exists(so):
+        return None
+    import torch  # noqa: F401  (the extension links against torch)
+    loader = importlib.machinery.ExtensionFileLoader("ref_swin3d_cuda", so)
+    spec = importlib.util.spec_from_loader("ref_swin3d_cuda", loader)
+    mod = importlib.util.module_from_spec(spec)
+    loader.exec_module(mod)
+    return mod
+
+
+def run_reference_gpu(args):
+    """Secondary workload: the reference's own CUDA kernels (compiled for this GPU from its sources,
+    unchanged but for the torch dispatch macro argument) timed beside this library on the same
+    device and inputs.  Attention: the stage-2 shape of Swin3D-L (C = 160, 10 heads x 16, window 7,
+    XYZ_RGB_NORM) on a 2-room batch coarsened by 2, because the reference forward kernel indexes its
+    32-entry shared staging array out of bounds for head_dim < 16 in fp32 (< 32 in fp16) and is not
+    run on such shapes; the call sequence is that of SelfAttnAIOFunction.forward/backward
+    (sparse_dl/attn/attn_coff.py:180-184, 219-224).  KNN: the 8-scene stress case."""
+    import torch
+    from swin3d_b200 import synthetic as S
+    from swin3d_b200.sparse_dl.attn import attn_coff as C
+    from swin3d_b200.sparse_dl.knn.knn import knn_raw
+    from swin3d_b200.window import build_windows
+    ref = load_reference_kernels()
+    if ref is None:
+        print(json.dumps({"workload": "reference-gpu", "unavailable": "oracle/_ref/ref_swin3d_cuda.so is not built"}))
+        return 0
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    c = CFG
+    quant, crse = c["quant"], c["crse"]
+    Cc, H, ws, stride = 160, 10, 7, 2
+    hd = Cc // H
+    sc = S.downsample_scene(make_batch(0, args.rooms or 2, c["voxels_per_room"]), stride)
+    N = sc.coords.shape[0]
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    sizes = S.table_sizes(ws, quant, H, hd, crse)
+    wi = build_windows(dev(sc.coords), dev(S.signal_feats(sc, crse)), ws, 0, stride)
+    ncr = wi.n_coords.clone()
+    ncr[:, :3] *= quant
+    ncr[:, 3:] *= 2 * quant
+    ncr = ncr.contiguous()
+    gen = torch.Generator(device="cuda").manual_seed(91)
+    rnd = lambda: torch.randn((N, H, hd), device="cuda", generator=gen)
+    q, k, v, g = rnd() * hd ** -0.5, rnd(), rnd(), rnd()
+    q, k, v, g = (t.half().float() for t in (q, k, v, g))       # fp16-representable: same inputs for every arm
+    tabs = [dev(t).half().float() for t in S.make_tables(1, sizes)]
+
+    # the reference's index list (swin3d_layers.py:76-150, protocol v2): pair -> window, window sizes,
+    # window -> first pair, window -> first voxel, voxel permutation, scaled signal coordinates
+    w64 = wi.w_sizes.to(torch.int64)
+    w2 = w64 * w64
+    m2w = torch.repeat_interleave(torch.arange(w64.numel(), device="cuda"), w2)
+    w2m = torch.cumsum(w2, 0) - w2
+    idx = [m2w, w64, w2m, wi.w2n.to(torch.int64), wi.n2n.to(torch.int64), ncr.float()]
+    offs = torch.tensor(list(sizes), dtype=torch.int32, device="cuda")
+    qkv = [q, k, v]
+
+    def ref_step(keep=None):
+        mx = ref.cal_max_coffs(qkv, tabs, offs, idx, 2, 3)
+        raw, sm = ref.self_attn_forward(qkv, tabs, mx, offs, idx, 2, 3)
+        norm = raw / sm
+        raw2 = norm * sm
+        dS = ref.cal_exp_sum_grads(g, raw2, sm, v, tabs[2])
+        grads = ref.self_attn_indir_backward(g, dS, raw2, sm, mx, q, k, v, *tabs, offs, idx, 2, 3)
+        if keep is not None:
+            keep.extend([norm, *grads[:6]])
+
+    def our_step(dt, keep=None):
+        a = [t.to(dt) for t in (q, k, v)]
+        tb = [t.to(dt) for t in tabs]
+        gg = g.to(dt)
+
+        def fn(keep=keep):
+            out, lse = C.attn_forward_raw(*a, *tb, sizes, wi.w_sizes, wi.w2n, wi.n2n, ncr)
+            gr = C.attn_backward_raw(*a, *tb, sizes, wi.w_sizes, wi.w2n, wi.n2n, ncr, out, lse, gg)
+            if keep is not None:
+                keep.extend([out, *gr])
+        return fn
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 3))
+    keep_ref, keep16, keep32 = [], [], []
+    ref_step(keep_ref)
+    our_step(torch.float16, keep16)()
+    our_step(torch.float32, keep32)()
+    torch.cuda.synchronize()
+    rel = lambda a, b: float((a.float() - b.float()).abs().max() / b.float().abs().max())
+    names = ("out", "dq", "dk", "dv", "dtq", "dtk", "dtv")
+    err16 = {n: rel(a.reshape(b.shape), b) for n, a, b in zip(names, keep16, keep_ref)}
+    err32 = {n: rel(a.reshape(b.shape), b) for n, a, b in zip(names, keep32, keep_ref)}
+    del keep_ref, keep16, keep32
+    ms_ref = timed(ref_step, steps, warm)
+    ms_16 = timed(our_step(torch.float16), steps, warm)
+    ms_32 = timed(our_step(torch.float32), steps, warm)
+    attn = {"shape": {"voxels": N, "pairs": wi.num_pairs, "channels": Cc, "heads": H, "head_dim": hd, "window": ws,
+                      "cRSE": crse, "max_window": wi.max_window},
+            "reference_f32_ms": ms_ref, "ours_f16_ms": ms_16, "ours_f32_ms": ms_32,
+            "speedup_f16_vs_reference_f32": ms_ref / ms_16, "speedup_f32_vs_reference_f32": ms_ref / ms_32,
+            "max_rel_diff_ours_f16_vs_reference": err16, "max_rel_diff_ours_f32_vs_reference": err32}
+
+    # ---- KNN -------------------------------------------------------------------------------------
+    scenes = [S.make_knn_scene(s, 200_000, 50_000) for s in range(8)]
+    src = torch.from_numpy(np.concatenate([s for s, _ in scenes])).cuda()
+    qry = torch.from_numpy(np.concatenate([qq for _, qq in scenes])).cuda()
+    so = torch.arange(1, 9, dtype=torch.int32, device="cuda") * 50_000
+    qo = torch.arange(1, 9, dtype=torch.int32, device="cuda") * 200_000
+    knn = {}
+    for K in (3, 16):
+        ridx = torch.zeros((qry.shape[0], K), dtype=torch.int32, device="cuda")
+        rd2 = torch.full((qry.shape[0], K), 1e10, dtype=torch.float32, device="cuda")
+
+        def ref_knn():
+            ridx.zero_()
+            rd2.fill_(1e10)
+            ref.knn_cuda(K, src, qry, so, qo, ridx, rd2)
+
+        ms_r = timed(ref_knn, steps, 1)
+        ms_o = timed(lambda: knn_raw(K, src, qry, so, qo), steps, 1)
+        oi, od = knn_raw(K, src, qry, so, qo)
+        knn[f"K{K}"] = {"reference_ms": ms_r, "ours_ms": ms_o, "speedup": ms_r / ms_o,
+                        "indices_equal": bool(torch.equal(oi, ridx)),
+                        "distance_bits_equal": bool(torch.equal(od.view(torch.int32), rd2.view(torch.int32)))}
+    print(json.dumps({"workload": "reference-gpu", "metric": "reference CUDA kernels vs this library, same GPU and inputs",
+                      "unit": "ms", "n_gpus": 1, "steps": steps, "warmup": warm, "data": "synthetic",
+                      "attention_fwd_bwd": attn, "knn_8x200k_x_50k": knn}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="attn", choices=["attn", "knn", "attn-split", "stages"])
+    ap.add_argument("--workload", default="attn", choices=["attn", "knn", "attn-split", "stages", "reference-gpu"])
     ap.add_argument("--rooms", type=int, default=0, help="rooms per GPU (default 8)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -711,6 +857,8 @@ def main():
         return run_attention_split(args)
     if args.workload == "stages":
         return run_stages(args)
+    if args.workload == "reference-gpu":
+        return run_reference_gpu(args)
     return run_attention(args)
 
 
