@@ -5,108 +5,129 @@
 // (Swin3D/src/attn/self_attn_aio_fwd.cu:16-52,111-188, self_attn_aio_bwd.cu:14-113):
 //   s_qk = sum_c ( q_c k_c + q_c * sum_n Tq[n,idx_n,h,c] + k_c * sum_n Tk[n,idx_n,h,c] )
 //   out_q = sum_k softmax_k(s_qk) * ( v_k + sum_n Tv[n,idx_n,h,:] )
-// but the structure is different: one warp owns a whole window, one lane owns one
-// (query, head) row, the softmax is online, outputs are written once (no atomics), and the
-// backward keeps the per-head table gradients in shared memory until the block retires.
+// but the structure is different: a group of head_dim lanes (lane = channel) owns one
+// (voxel, head) row, so rows of q, k, v and of the tables are read as coalesced pieces; the
+// softmax is online, outputs are written once (no atomics), and the backward keeps the per-head
+// table gradients in shared memory until the block retires.
 #include "attn_kernels.cuh"
 #include "common.cuh"
 
 namespace s3d {
 
-template <int D>
-__device__ __forceinline__ void pair_rows(const float *cq, const float *__restrict__ ck,
-                                          const CrseMeta &m, int *rows)
+template <typename T> __device__ __forceinline__ float ldf(const T *p);
+template <> __device__ __forceinline__ float ldf<float>(const float *p) { return __ldg(p); }
+template <> __device__ __forceinline__ float ldf<__half>(const __half *p) { return __half2float(__ldg(p)); }
+template <typename T> __device__ __forceinline__ void stf(T *p, float x);
+template <> __device__ __forceinline__ void stf<float>(float *p, float x) { *p = x; }
+template <> __device__ __forceinline__ void stf<__half>(__half *p, float x) { *p = __float2half_rn(x); }
+
+// Window that holds position p of the window-sorted voxel list: the last w with w2n[w] <= p.
+__device__ __forceinline__ int64_t window_of(const int32_t *__restrict__ w2n, int64_t W, int p)
 {
-#pragma unroll
-    for (int n = 0; n < D; ++n)
-        rows[n] = m.rowbase[n] + crse_index(cq[n], __ldg(ck + n), m.L[n], n == D - 1);
+    int64_t lo = 0, hi = W - 1;
+    while (lo < hi) {
+        const int64_t mid = (lo + hi + 1) >> 1;
+        if (__ldg(w2n + mid) <= p) lo = mid;
+        else hi = mid - 1;
+    }
+    return lo;
 }
 
-// ---------------------------------------------------------------------------------------------
-// Forward: warp per window, lane per (query, head).
-template <typename T, int HD, int D>
-__global__ void __launch_bounds__(128)
-attn_fwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
-                       const T *__restrict__ tq, const T *__restrict__ tk, const T *__restrict__ tv,
-                       const CrseMeta meta, const int32_t *__restrict__ w_sizes,
-                       const int32_t *__restrict__ w2n, const int32_t *__restrict__ n2n,
-                       const float *__restrict__ n_coords, int64_t W, int H,
-                       T *__restrict__ out, float *__restrict__ lse)
+// Sum over the HD lanes of a group (groups are aligned, so xor offsets below HD stay inside).
+template <int HD>
+__device__ __forceinline__ float group_sum(float x, unsigned gmask)
 {
-    const int lane = threadIdx.x & 31;
-    const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
-    const int HC = H * HD;
+#pragma unroll
+    for (int o = HD / 2; o > 0; o >>= 1) x += __shfl_xor_sync(gmask, x, o);
+    return x;
+}
 
-    for (int64_t w = warp0; w < W; w += nwarps) {
-        const int n = __ldg(w_sizes + w);
-        const int base = __ldg(w2n + w);
-        for (int item = lane; item < n * H; item += 32) {
-            const int qi = item / H, h = item - qi * H;
-            const int64_t qrow = __ldg(n2n + base + qi);
-            float qv[HD], cq[D], acc[HD];
-            load_vec<T, HD>(q + qrow * HC + h * HD, qv);
+// Table rows of the pair (query coordinates cq, key coordinates at ck) and the three sums of
+// this lane's channel over the D looked-up rows.
+template <typename T, int D>
+__device__ __forceinline__ void pair_tables(const float *cq, const float *ck, const CrseMeta &m,
+                                            const T *__restrict__ tq, const T *__restrict__ tk,
+                                            const T *__restrict__ tv, int HC, int hc, int *rows,
+                                            float &bq, float &bk, float &bv)
+{
+    bq = bk = bv = 0.f;
 #pragma unroll
-            for (int d = 0; d < D; ++d) cq[d] = __ldg(n_coords + (int64_t)(base + qi) * D + d);
-#pragma unroll
-            for (int c = 0; c < HD; ++c) acc[c] = 0.f;
-            float mx = -INFINITY, l = 0.f;
-            for (int kj = 0; kj < n; ++kj) {
-                const int64_t krow = __ldg(n2n + base + kj);
-                int rows[D];
-                pair_rows<D>(cq, n_coords + (int64_t)(base + kj) * D, meta, rows);
-                float kv[HD], bq[HD], bk[HD], bv[HD];
-                load_vec<T, HD>(k + krow * HC + h * HD, kv);
-#pragma unroll
-                for (int c = 0; c < HD; ++c) bq[c] = bk[c] = bv[c] = 0.f;
-#pragma unroll
-                for (int d = 0; d < D; ++d) {
-                    float t[HD];
-                    const int64_t off = (int64_t)rows[d] * HC + h * HD;
-                    load_vec<T, HD>(tq + off, t);
-#pragma unroll
-                    for (int c = 0; c < HD; ++c) bq[c] += t[c];
-                    load_vec<T, HD>(tk + off, t);
-#pragma unroll
-                    for (int c = 0; c < HD; ++c) bk[c] += t[c];
-                    load_vec<T, HD>(tv + off, t);
-#pragma unroll
-                    for (int c = 0; c < HD; ++c) bv[c] += t[c];
-                }
-                float s = 0.f;
-#pragma unroll
-                for (int c = 0; c < HD; ++c) s += qv[c] * (kv[c] + bq[c]) + kv[c] * bk[c];
-                float vv[HD];
-                load_vec<T, HD>(v + krow * HC + h * HD, vv);
-                const float mnew = fmaxf(mx, s);
-                const float scale = __expf(mx - mnew);
-                const float p = __expf(s - mnew);
-                l = l * scale + p;
-#pragma unroll
-                for (int c = 0; c < HD; ++c) acc[c] = acc[c] * scale + p * (vv[c] + bv[c]);
-                mx = mnew;
-            }
-            const float inv = 1.f / l;
-#pragma unroll
-            for (int c = 0; c < HD; ++c) acc[c] *= inv;
-            store_vec<T, HD>(out + qrow * HC + h * HD, acc);
-            lse[qrow * H + h] = mx + __logf(l);
-        }
+    for (int d = 0; d < D; ++d) {
+        rows[d] = m.rowbase[d] + crse_index(cq[d], ck[d], m.L[d], d == D - 1);
+        const int64_t off = (int64_t)rows[d] * HC + hc;
+        bq += ldf(tq + off);
+        bk += ldf(tk + off);
+        bv += ldf(tv + off);
     }
 }
 
 // ---------------------------------------------------------------------------------------------
-// Backward.  grid = (window chunks, H); one block works on one head so the three per-head
-// table-gradient slices (3 * R * HD floats) fit in shared memory.  Inside a block every warp
-// takes windows of the chunk; pass A runs with lane = query (dQ, dTq, dTv), pass B with
-// lane = key (dK, dV, dTk).  Every quantity is recomputed from q,k,v,tables,lse.
+// Forward: a group of HD lanes (lane = channel) owns one (query, head) row and walks the keys of
+// the query's window; every row of q, k, v and of the tables is read as one coalesced piece.
 template <typename T, int HD, int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
+attn_fwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
+                       const T *__restrict__ tq, const T *__restrict__ tk, const T *__restrict__ tv,
+                       const CrseMeta meta, const int32_t *__restrict__ w_sizes,
+                       const int32_t *__restrict__ w2n, const int32_t *__restrict__ n2n,
+                       const float *__restrict__ n_coords, int64_t N, int64_t W, int H,
+                       T *__restrict__ out, float *__restrict__ lse)
+{
+    constexpr int G = 32 / HD;
+    const int lane = threadIdx.x & 31, c = lane % HD, gi = lane / HD;
+    const unsigned gmask = HD == 32 ? 0xffffffffu : (((1u << (HD & 31)) - 1u) << (gi * HD));
+    const int HC = H * HD;
+    const int64_t group0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * G + gi;
+    const int64_t ngroups = (int64_t)gridDim.x * (blockDim.x >> 5) * G;
+
+    for (int64_t item = group0; item < N * H; item += ngroups) {
+        const int p = (int)(item / H), h = (int)(item - (int64_t)p * H);
+        const int64_t w = window_of(w2n, W, p);
+        const int n = __ldg(w_sizes + w), base = __ldg(w2n + w);
+        const int64_t qrow = __ldg(n2n + p);
+        const int hc = h * HD + c;
+        const float qc = ldf(q + qrow * HC + hc);
+        float cq[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) cq[d] = __ldg(n_coords + (int64_t)p * D + d);
+        float acc = 0.f, mx = -INFINITY, l = 0.f;
+        for (int kj = 0; kj < n; ++kj) {
+            const int64_t krow = __ldg(n2n + base + kj);
+            float ck[D];
+#pragma unroll
+            for (int d = 0; d < D; ++d) ck[d] = __ldg(n_coords + (int64_t)(base + kj) * D + d);
+            const float kc = ldf(k + krow * HC + hc), vc = ldf(v + krow * HC + hc);
+            int rows[D];
+            float bq, bk, bv;
+            pair_tables<T, D>(cq, ck, meta, tq, tk, tv, HC, hc, rows, bq, bk, bv);
+            const float s = group_sum<HD>(qc * (kc + bq) + kc * bk, gmask);
+            const float mnew = fmaxf(mx, s);
+            const float scale = __expf(mx - mnew);
+            const float pr = __expf(s - mnew);
+            l = l * scale + pr;
+            acc = acc * scale + pr * (vc + bv);
+            mx = mnew;
+        }
+        stf(out + qrow * HC + hc, acc / l);
+        if (c == 0) lse[qrow * H + h] = mx + __logf(l);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward.  grid = (position chunks, H); one block works on one head so the three per-head
+// table-gradient slices (3 * R * HD floats) fit in shared memory.  A group of HD lanes (lane =
+// channel) takes one position of the window-sorted voxel list, first as a query (dQ, dTq, dTv over
+// the keys of its window), then as a key (dK, dV, dTk over the queries).  Every quantity is
+// recomputed from q, k, v, tables, out and lse; dP - delta is one sum, sum_c dO_c (v_c + B_c - o_c).
+// The shared-memory adds of a group hit HD consecutive words, so they do not collide.
+template <typename T, int HD, int D>
+__global__ void __launch_bounds__(256)
 attn_bwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
                        const T *__restrict__ tq, const T *__restrict__ tk, const T *__restrict__ tv,
                        const CrseMeta meta, const int32_t *__restrict__ w_sizes,
                        const int32_t *__restrict__ w2n, const int32_t *__restrict__ n2n,
-                       const float *__restrict__ n_coords, int64_t W, int H, int windows_per_block,
+                       const float *__restrict__ n_coords, int64_t N, int64_t W, int H,
+                       int positions_per_block,
                        const T *__restrict__ o, const float *__restrict__ lse,
                        const T *__restrict__ dout, T *__restrict__ dq, T *__restrict__ dk,
                        T *__restrict__ dv, float *__restrict__ dtq, float *__restrict__ dtk,
@@ -118,151 +139,90 @@ attn_bwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T
     __syncthreads();
     float *s_dtq = s_dt, *s_dtk = s_dt + RH, *s_dtv = s_dt + 2 * RH;
 
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    constexpr int G = 32 / HD;
+    const int lane = threadIdx.x & 31, c = lane % HD, gi = lane / HD;
+    const unsigned gmask = HD == 32 ? 0xffffffffu : (((1u << (HD & 31)) - 1u) << (gi * HD));
     const int h = blockIdx.y;
-    const int HC = H * HD;
-    const int64_t wbeg = (int64_t)blockIdx.x * windows_per_block;
-    const int64_t wend = min(W, wbeg + (int64_t)windows_per_block);
+    const int HC = H * HD, hc = h * HD + c;
+    const int group = (threadIdx.x >> 5) * G + gi, ngroup = (blockDim.x >> 5) * G;
+    const int64_t pbeg = (int64_t)blockIdx.x * positions_per_block;
+    const int64_t pend = min(N, pbeg + (int64_t)positions_per_block);
 
-    for (int64_t w = wbeg + warp; w < wend; w += nwarp) {
-        const int n = __ldg(w_sizes + w);
-        const int base = __ldg(w2n + w);
-        // ---- pass A: lane = query ------------------------------------------------------------
-        for (int qi = lane; qi < n; qi += 32) {
-            const int64_t qrow = __ldg(n2n + base + qi);
-            float qv[HD], gv[HD], cq[D], dqa[HD];
-            load_vec<T, HD>(q + qrow * HC + h * HD, qv);
-            load_vec<T, HD>(dout + qrow * HC + h * HD, gv);
-            float delta = 0.f;
-            {
-                float ov[HD];
-                load_vec<T, HD>(o + qrow * HC + h * HD, ov);
+    for (int64_t pp = pbeg + group; pp < pend; pp += ngroup) {
+        const int p = (int)pp;
+        const int64_t w = window_of(w2n, W, p);
+        const int n = __ldg(w_sizes + w), base = __ldg(w2n + w);
+        const int64_t row = __ldg(n2n + p);
+        float cp[D];
 #pragma unroll
-                for (int c = 0; c < HD; ++c) delta += ov[c] * gv[c];
-            }
-            const float L = __ldg(lse + qrow * H + h);
-#pragma unroll
-            for (int d = 0; d < D; ++d) cq[d] = __ldg(n_coords + (int64_t)(base + qi) * D + d);
-#pragma unroll
-            for (int c = 0; c < HD; ++c) dqa[c] = 0.f;
+        for (int d = 0; d < D; ++d) cp[d] = __ldg(n_coords + (int64_t)p * D + d);
+        // ---- position p as a query ---------------------------------------------------------------
+        {
+            const float qc = ldf(q + row * HC + hc), gc = ldf(dout + row * HC + hc);
+            const float oc = ldf(o + row * HC + hc);
+            const float L = __ldg(lse + row * H + h);
+            float dqa = 0.f;
             for (int kj = 0; kj < n; ++kj) {
                 const int64_t krow = __ldg(n2n + base + kj);
+                float ck[D];
+#pragma unroll
+                for (int d = 0; d < D; ++d) ck[d] = __ldg(n_coords + (int64_t)(base + kj) * D + d);
+                const float kc = ldf(k + krow * HC + hc), vc = ldf(v + krow * HC + hc);
                 int rows[D];
-                pair_rows<D>(cq, n_coords + (int64_t)(base + kj) * D, meta, rows);
-                float kv[HD], vv[HD], bq[HD], bk[HD], bv[HD];
-                load_vec<T, HD>(k + krow * HC + h * HD, kv);
-                load_vec<T, HD>(v + krow * HC + h * HD, vv);
-#pragma unroll
-                for (int c = 0; c < HD; ++c) bq[c] = bk[c] = bv[c] = 0.f;
-#pragma unroll
-                for (int d = 0; d < D; ++d) {
-                    float t[HD];
-                    const int64_t off = (int64_t)rows[d] * HC + h * HD;
-                    load_vec<T, HD>(tq + off, t);
-#pragma unroll
-                    for (int c = 0; c < HD; ++c) bq[c] += t[c];
-                    load_vec<T, HD>(tk + off, t);
-#pragma unroll
-                    for (int c = 0; c < HD; ++c) bk[c] += t[c];
-                    load_vec<T, HD>(tv + off, t);
-#pragma unroll
-                    for (int c = 0; c < HD; ++c) bv[c] += t[c];
-                }
-                float s = 0.f, dp = 0.f;
-#pragma unroll
-                for (int c = 0; c < HD; ++c) {
-                    s += qv[c] * (kv[c] + bq[c]) + kv[c] * bk[c];
-                    dp += gv[c] * (vv[c] + bv[c]);
-                }
-                const float p = __expf(s - L);
-                const float ds = p * (dp - delta);
-#pragma unroll
-                for (int c = 0; c < HD; ++c) dqa[c] += ds * (kv[c] + bq[c]);
+                float bq, bk, bv;
+                pair_tables<T, D>(cp, ck, meta, tq, tk, tv, HC, hc, rows, bq, bk, bv);
+                const float s = group_sum<HD>(qc * (kc + bq) + kc * bk, gmask);
+                const float e = group_sum<HD>(gc * (vc + bv - oc), gmask);
+                const float pr = __expf(s - L);
+                const float ds = pr * e;
+                dqa += ds * (kc + bq);
+                const float aq = ds * qc, av = pr * gc;
 #pragma unroll
                 for (int d = 0; d < D; ++d) {
-                    const int ro = rows[d] * HD;
-#pragma unroll
-                    for (int c = 0; c < HD; ++c) {
-                        atomicAdd(s_dtq + ro + c, ds * qv[c]);
-                        atomicAdd(s_dtv + ro + c, p * gv[c]);
-                    }
+                    atomicAdd(s_dtq + rows[d] * HD + c, aq);
+                    atomicAdd(s_dtv + rows[d] * HD + c, av);
                 }
             }
-            store_vec<T, HD>(dq + qrow * HC + h * HD, dqa);
+            stf(dq + row * HC + hc, dqa);
         }
-        // ---- pass B: lane = key --------------------------------------------------------------
-        for (int kj = lane; kj < n; kj += 32) {
-            const int64_t krow = __ldg(n2n + base + kj);
-            float kv[HD], vv[HD], ck[D], dka[HD], dva[HD];
-            load_vec<T, HD>(k + krow * HC + h * HD, kv);
-            load_vec<T, HD>(v + krow * HC + h * HD, vv);
-#pragma unroll
-            for (int d = 0; d < D; ++d) ck[d] = __ldg(n_coords + (int64_t)(base + kj) * D + d);
-#pragma unroll
-            for (int c = 0; c < HD; ++c) dka[c] = dva[c] = 0.f;
+        // ---- position p as a key -----------------------------------------------------------------
+        {
+            const float kc = ldf(k + row * HC + hc), vc = ldf(v + row * HC + hc);
+            float dka = 0.f, dva = 0.f;
             for (int qi = 0; qi < n; ++qi) {
                 const int64_t qrow = __ldg(n2n + base + qi);
-                int rows[D];
+                float cq[D];
 #pragma unroll
-                for (int d = 0; d < D; ++d)
-                    rows[d] = meta.rowbase[d] +
-                              crse_index(__ldg(n_coords + (int64_t)(base + qi) * D + d), ck[d],
-                                         meta.L[d], d == D - 1);
-                float qv[HD], gv[HD], ov[HD], bq[HD], bk[HD], bv[HD];
-                load_vec<T, HD>(q + qrow * HC + h * HD, qv);
-                load_vec<T, HD>(dout + qrow * HC + h * HD, gv);
-                load_vec<T, HD>(o + qrow * HC + h * HD, ov);
+                for (int d = 0; d < D; ++d) cq[d] = __ldg(n_coords + (int64_t)(base + qi) * D + d);
+                const float qc = ldf(q + qrow * HC + hc), gc = ldf(dout + qrow * HC + hc);
+                const float oc = ldf(o + qrow * HC + hc);
                 const float L = __ldg(lse + qrow * H + h);
+                int rows[D];
+                float bq, bk, bv;
+                pair_tables<T, D>(cq, cp, meta, tq, tk, tv, HC, hc, rows, bq, bk, bv);
+                const float s = group_sum<HD>(qc * (kc + bq) + kc * bk, gmask);
+                const float e = group_sum<HD>(gc * (vc + bv - oc), gmask);
+                const float pr = __expf(s - L);
+                const float ds = pr * e;
+                dka += ds * (qc + bk);
+                dva += pr * gc;
+                const float ak = ds * kc;
 #pragma unroll
-                for (int c = 0; c < HD; ++c) bq[c] = bk[c] = bv[c] = 0.f;
-#pragma unroll
-                for (int d = 0; d < D; ++d) {
-                    float t[HD];
-                    const int64_t off = (int64_t)rows[d] * HC + h * HD;
-                    load_vec<T, HD>(tq + off, t);
-#pragma unroll
-                    for (int c = 0; c < HD; ++c) bq[c] += t[c];
-                    load_vec<T, HD>(tk + off, t);
-#pragma unroll
-                    for (int c = 0; c < HD; ++c) bk[c] += t[c];
-                    load_vec<T, HD>(tv + off, t);
-#pragma unroll
-                    for (int c = 0; c < HD; ++c) bv[c] += t[c];
-                }
-                float s = 0.f, dp = 0.f, delta = 0.f;
-#pragma unroll
-                for (int c = 0; c < HD; ++c) {
-                    s += qv[c] * (kv[c] + bq[c]) + kv[c] * bk[c];
-                    dp += gv[c] * (vv[c] + bv[c]);
-                    delta += ov[c] * gv[c];
-                }
-                const float p = __expf(s - L);
-                const float ds = p * (dp - delta);
-#pragma unroll
-                for (int c = 0; c < HD; ++c) {
-                    dka[c] += ds * (qv[c] + bk[c]);
-                    dva[c] += p * gv[c];
-                }
-#pragma unroll
-                for (int d = 0; d < D; ++d) {
-                    const int ro = rows[d] * HD;
-#pragma unroll
-                    for (int c = 0; c < HD; ++c) atomicAdd(s_dtk + ro + c, ds * kv[c]);
-                }
+                for (int d = 0; d < D; ++d) atomicAdd(s_dtk + rows[d] * HD + c, ak);
             }
-            store_vec<T, HD>(dk + krow * HC + h * HD, dka);
-            store_vec<T, HD>(dv + krow * HC + h * HD, dva);
+            stf(dk + row * HC + hc, dka);
+            stf(dv + row * HC + hc, dva);
         }
     }
     __syncthreads();
     // flush: element (row r, channel c) of this head lives at (r*H + h)*HD + c in the flat table
     for (int i = threadIdx.x; i < RH; i += blockDim.x) {
-        const int r = i / HD, c = i - r * HD;
-        const int64_t g = ((int64_t)r * H + h) * HD + c;
-        const float a = s_dtq[i], b = s_dtk[i], cc = s_dtv[i];
+        const int r = i / HD, cc = i - r * HD;
+        const int64_t g = ((int64_t)r * H + h) * HD + cc;
+        const float a = s_dtq[i], b = s_dtk[i], e = s_dtv[i];
         if (a != 0.f) atomicAdd(dtq + g, a);
         if (b != 0.f) atomicAdd(dtk + g, b);
-        if (cc != 0.f) atomicAdd(dtv + g, cc);
+        if (e != 0.f) atomicAdd(dtv + g, e);
     }
 }
 
@@ -285,21 +245,21 @@ __global__ void crse_indices_kernel(const float *__restrict__ n_coords, const Cr
 template <typename T, int HD, int D>
 static int launch_fwd(const AttnArgs &a, cudaStream_t st)
 {
-    if (a.W == 0) return S3D_OK;
-    const int warps_per_block = 4;
-    int64_t blocks = (a.W + warps_per_block - 1) / warps_per_block;
-    const int64_t cap = 148 * 16;
+    if (a.W == 0 || a.N == 0) return S3D_OK;
+    const int groups_per_block = 8 * (32 / HD);
+    int64_t blocks = (a.N * a.H + groups_per_block - 1) / groups_per_block;
+    const int64_t cap = 148 * 64;
     if (blocks > cap) blocks = cap;
-    attn_fwd_scalar_kernel<T, HD, D><<<(unsigned)blocks, warps_per_block * 32, 0, st>>>(
+    attn_fwd_scalar_kernel<T, HD, D><<<(unsigned)blocks, 256, 0, st>>>(
         (const T *)a.q, (const T *)a.k, (const T *)a.v, (const T *)a.tq, (const T *)a.tk,
-        (const T *)a.tv, a.meta, a.w_sizes, a.w2n, a.n2n, a.n_coords, a.W, a.H, (T *)a.out, a.lse);
+        (const T *)a.tv, a.meta, a.w_sizes, a.w2n, a.n2n, a.n_coords, a.N, a.W, a.H, (T *)a.out, a.lse);
     return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
 }
 
 template <typename T, int HD, int D>
 static int launch_bwd(const AttnArgs &a, cudaStream_t st)
 {
-    if (a.W == 0) return S3D_OK;
+    if (a.W == 0 || a.N == 0) return S3D_OK;
     const size_t smem = (size_t)3 * a.meta.R * HD * sizeof(float);
     if (smem > 200 * 1024) return S3D_ERR_UNSUPPORTED;
     auto kern = attn_bwd_scalar_kernel<T, HD, D>;
@@ -307,14 +267,15 @@ static int launch_bwd(const AttnArgs &a, cudaStream_t st)
         return S3D_ERR_LAUNCH;
     // enough blocks to fill the machine a few times over, few enough that the per-block flush
     // of the table gradients stays small
-    int64_t target_blocks = (148 * 8 + a.H - 1) / a.H;
-    int64_t wpb = (a.W + target_blocks - 1) / target_blocks;
-    if (wpb < 4) wpb = 4;
-    const int64_t chunks = (a.W + wpb - 1) / wpb;
+    const int64_t target_blocks = (148 * 8 + a.H - 1) / a.H;
+    int64_t ppb = (a.N + target_blocks - 1) / target_blocks;
+    const int groups_per_block = 8 * (32 / HD);
+    if (ppb < groups_per_block) ppb = groups_per_block;
+    const int64_t chunks = (a.N + ppb - 1) / ppb;
     dim3 grid((unsigned)chunks, (unsigned)a.H);
-    kern<<<grid, 128, smem, st>>>((const T *)a.q, (const T *)a.k, (const T *)a.v, (const T *)a.tq,
+    kern<<<grid, 256, smem, st>>>((const T *)a.q, (const T *)a.k, (const T *)a.v, (const T *)a.tq,
                                   (const T *)a.tk, (const T *)a.tv, a.meta, a.w_sizes, a.w2n, a.n2n,
-                                  a.n_coords, a.W, a.H, (int)wpb, (const T *)a.out, a.lse,
+                                  a.n_coords, a.N, a.W, a.H, (int)ppb, (const T *)a.out, a.lse,
                                   (const T *)a.dout, (T *)a.dq, (T *)a.dk, (T *)a.dv, a.dtq, a.dtk,
                                   a.dtv);
     return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
