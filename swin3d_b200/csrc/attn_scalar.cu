@@ -7,8 +7,9 @@
 //   out_q = sum_k softmax_k(s_qk) * ( v_k + sum_n Tv[n,idx_n,h,:] )
 // but the structure is different: a group of head_dim lanes (lane = channel) owns one
 // (voxel, head) row, so rows of q, k, v and of the tables are read as coalesced pieces; the
-// softmax is online, outputs are written once (no atomics), and the backward keeps the per-head
-// table gradients in shared memory until the block retires.
+// softmax is online, outputs are written once (no atomics), and the backward sums the scalar
+// weights of every looked-up table row in per-group histograms and touches the global table
+// gradient once per (voxel, head, touched row).
 #include "attn_kernels.cuh"
 #include "common.cuh"
 
@@ -42,19 +43,56 @@ __device__ __forceinline__ float group_sum(float x, unsigned gmask)
     return x;
 }
 
-// Table rows of the pair (query coordinates cq, key coordinates at ck) and the three sums of
-// this lane's channel over the D looked-up rows.
-template <typename T, int D>
-__device__ __forceinline__ void pair_tables(const float *cq, const float *ck, const CrseMeta &m,
+// The signal dimensions are dealt to the lanes of a group: lane c works out the table row of
+// dimensions c, c + HD, ... (one per lane, two for lane 0 of an 8-lane group with 9 dimensions)
+// and the group exchanges the rows by shuffles.
+template <int HD, int D>
+struct LaneDims {
+    static constexpr int NDL = (D + HD - 1) / HD;
+    float own[NDL];   // this voxel's coordinate in the lane's dimensions
+    int L[NDL], rb[NDL], dim[NDL];
+    bool last[NDL];
+
+    __device__ __forceinline__ void init(const CrseMeta &m, int c)
+    {
+#pragma unroll
+        for (int j = 0; j < NDL; ++j) {
+            const int d = c + j * HD;
+            const bool ok = d < D;
+            dim[j] = ok ? d : 0;
+            L[j] = m.L[dim[j]];
+            rb[j] = m.rowbase[dim[j]];
+            last[j] = d == D - 1;
+        }
+    }
+    __device__ __forceinline__ void load(const float *__restrict__ coords_row, float (&x)[NDL]) const
+    {
+#pragma unroll
+        for (int j = 0; j < NDL; ++j) x[j] = __ldg(coords_row + dim[j]);
+    }
+};
+
+// Table rows of a pair and the three sums of this lane's channel over the D looked-up rows.
+// oth: the other voxel's coordinate in this lane's dimensions; OWN_IS_QUERY says which side the
+// lane's own voxel is on.
+template <typename T, int HD, int D, bool OWN_IS_QUERY>
+__device__ __forceinline__ void pair_tables(const LaneDims<HD, D> &ld, const float (&oth)[LaneDims<HD, D>::NDL],
+                                            int gi, unsigned gmask,
                                             const T *__restrict__ tq, const T *__restrict__ tk,
-                                            const T *__restrict__ tv, int HC, int hc, int *rows,
+                                            const T *__restrict__ tv, int HC, int hc,
+                                            int (&mine)[LaneDims<HD, D>::NDL],
                                             float &bq, float &bk, float &bv)
 {
+    constexpr int NDL = LaneDims<HD, D>::NDL;
+#pragma unroll
+    for (int j = 0; j < NDL; ++j)
+        mine[j] = ld.rb[j] + (OWN_IS_QUERY ? crse_index(ld.own[j], oth[j], ld.L[j], ld.last[j])
+                                           : crse_index(oth[j], ld.own[j], ld.L[j], ld.last[j]));
     bq = bk = bv = 0.f;
 #pragma unroll
     for (int d = 0; d < D; ++d) {
-        rows[d] = m.rowbase[d] + crse_index(cq[d], ck[d], m.L[d], d == D - 1);
-        const int64_t off = (int64_t)rows[d] * HC + hc;
+        const int row = __shfl_sync(gmask, mine[d / HD], gi * HD + d % HD);
+        const int64_t off = (int64_t)row * HC + hc;
         bq += ldf(tq + off);
         bk += ldf(tk + off);
         bv += ldf(tv + off);
@@ -87,19 +125,26 @@ attn_fwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T
         const int64_t qrow = __ldg(n2n + p);
         const int hc = h * HD + c;
         const float qc = ldf(q + qrow * HC + hc);
-        float cq[D];
-#pragma unroll
-        for (int d = 0; d < D; ++d) cq[d] = __ldg(n_coords + (int64_t)p * D + d);
+        LaneDims<HD, D> ld;
+        ld.init(meta, c);
+        ld.load(n_coords + (int64_t)p * D, ld.own);
         float acc = 0.f, mx = -INFINITY, l = 0.f;
+        // the next key's row number and coordinates are fetched one iteration ahead
+        int64_t krow_n = __ldg(n2n + base);
+        float oth_n[LaneDims<HD, D>::NDL];
+        ld.load(n_coords + (int64_t)base * D, oth_n);
         for (int kj = 0; kj < n; ++kj) {
-            const int64_t krow = __ldg(n2n + base + kj);
-            float ck[D];
+            const int64_t krow = krow_n;
+            float oth[LaneDims<HD, D>::NDL];
 #pragma unroll
-            for (int d = 0; d < D; ++d) ck[d] = __ldg(n_coords + (int64_t)(base + kj) * D + d);
+            for (int j = 0; j < LaneDims<HD, D>::NDL; ++j) oth[j] = oth_n[j];
+            const int nx = base + min(kj + 1, n - 1);
+            krow_n = __ldg(n2n + nx);
+            ld.load(n_coords + (int64_t)nx * D, oth_n);
             const float kc = ldf(k + krow * HC + hc), vc = ldf(v + krow * HC + hc);
-            int rows[D];
+            int mine[LaneDims<HD, D>::NDL];
             float bq, bk, bv;
-            pair_tables<T, D>(cq, ck, meta, tq, tk, tv, HC, hc, rows, bq, bk, bv);
+            pair_tables<T, HD, D, true>(ld, oth, gi, gmask, tq, tk, tv, HC, hc, mine, bq, bk, bv);
             const float s = group_sum<HD>(qc * (kc + bq) + kc * bk, gmask);
             const float mnew = fmaxf(mx, s);
             const float scale = __expf(mx - mnew);
@@ -114,115 +159,174 @@ attn_fwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T
 }
 
 // ---------------------------------------------------------------------------------------------
-// Backward.  grid = (position chunks, H); one block works on one head so the three per-head
-// table-gradient slices (3 * R * HD floats) fit in shared memory.  A group of HD lanes (lane =
-// channel) takes one position of the window-sorted voxel list, first as a query (dQ, dTq, dTv over
-// the keys of its window), then as a key (dK, dV, dTk over the queries).  Every quantity is
-// recomputed from q, k, v, tables, out and lse; dP - delta is one sum, sum_c dO_c (v_c + B_c - o_c).
-// The shared-memory adds of a group hit HD consecutive words, so they do not collide.
+// Backward.  A group of HD lanes (lane = channel) takes one (position, head) of the window-sorted
+// voxel list, first as a query (dQ, dTq, dTv over the keys of its window), then as a key (dK, dV,
+// dTk over the queries).  Every quantity is recomputed from q, k, v, tables, out and lse;
+// dP - delta is one sum, sum_c dO_c (v_c + B_c - o_c).
+//
+// Table gradients: for a fixed query, dTq[r] = q * (sum of ds over the keys whose pair looks up
+// row r), and likewise dTv[r] = dO * (sum of p) and, for a fixed key, dTk[r] = k * (sum of ds).
+// So each group keeps two scalar histograms over the table rows in shared memory, updated by the
+// lane that owns the signal dimension with a plain read-modify-write, and after the sweep adds
+// (histogram entry) x (its row vector) to the global table gradient once per touched row.
+// Histogram rows use a numbering in which every dimension owns L + 1 rows (index L, which through
+// the reference's flat addressing names row 0 of the next dimension, gets a private slot), so lanes
+// of different dimensions never touch the same word.
+template <int D>
+__device__ __forceinline__ int flat_row_of_slot(const CrseMeta &m, int slot)
+{
+    int d = 0;
+#pragma unroll
+    for (int i = 1; i < D; ++i) d += (slot >= m.rowbase[i] + i) ? 1 : 0;
+    return slot - d;
+}
+
+// Adds x[slot] * (va, vb) to the rows of two global tables for every non-zero slot of the
+// group's two histograms, and clears the histograms.  ta/tb may be the same pointer pair twice.
+template <int HD, int D>
+__device__ __forceinline__ void flush_hists(float *ha, float *hb, int n_slots, const CrseMeta &m,
+                                            float *__restrict__ ta, float va,
+                                            float *__restrict__ tb, float vb, bool use_b,
+                                            int HC, int hc, int c, int gi, unsigned gmask)
+{
+    __syncwarp(gmask);
+    for (int s0 = 0; s0 < n_slots; s0 += HD) {
+        const int si = s0 + c;
+        float a = 0.f, b = 0.f;
+        if (si < n_slots) {
+            a = ha[si];
+            ha[si] = 0.f;
+            if (use_b) {
+                b = hb[si];
+                hb[si] = 0.f;
+            }
+        }
+        unsigned nz = __ballot_sync(gmask, a != 0.f || b != 0.f) >> (gi * HD);
+        if (HD < 32) nz &= (1u << (HD & 31)) - 1u;
+        while (nz) {
+            const int j = __ffs(nz) - 1;
+            nz &= nz - 1;
+            const float aj = __shfl_sync(gmask, a, gi * HD + j);
+            const float bj = __shfl_sync(gmask, b, gi * HD + j);
+            const int64_t off = (int64_t)flat_row_of_slot<D>(m, s0 + j) * HC + hc;
+            if (aj != 0.f) atomicAdd(ta + off, aj * va);
+            if (use_b && bj != 0.f) atomicAdd(tb + off, bj * vb);
+        }
+    }
+    __syncwarp(gmask);
+}
+
 template <typename T, int HD, int D>
 __global__ void __launch_bounds__(256)
 attn_bwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
                        const T *__restrict__ tq, const T *__restrict__ tk, const T *__restrict__ tv,
                        const CrseMeta meta, const int32_t *__restrict__ w_sizes,
                        const int32_t *__restrict__ w2n, const int32_t *__restrict__ n2n,
-                       const float *__restrict__ n_coords, int64_t N, int64_t W, int H,
-                       int positions_per_block,
+                       const float *__restrict__ n_coords, int64_t N, int64_t W, int H, int slots_padded,
                        const T *__restrict__ o, const float *__restrict__ lse,
                        const T *__restrict__ dout, T *__restrict__ dq, T *__restrict__ dk,
                        T *__restrict__ dv, float *__restrict__ dtq, float *__restrict__ dtk,
                        float *__restrict__ dtv)
 {
-    extern __shared__ float s_dt[];  // [3][R*HD]
-    const int RH = meta.R * HD;
-    for (int i = threadIdx.x; i < 3 * RH; i += blockDim.x) s_dt[i] = 0.f;
-    __syncthreads();
-    float *s_dtq = s_dt, *s_dtk = s_dt + RH, *s_dtv = s_dt + 2 * RH;
-
+    extern __shared__ float s_hist[];  // [groups of the block][2][slots_padded]
     constexpr int G = 32 / HD;
+    constexpr int NDL = LaneDims<HD, D>::NDL;
     const int lane = threadIdx.x & 31, c = lane % HD, gi = lane / HD;
     const unsigned gmask = HD == 32 ? 0xffffffffu : (((1u << (HD & 31)) - 1u) << (gi * HD));
-    const int h = blockIdx.y;
-    const int HC = H * HD, hc = h * HD + c;
-    const int group = (threadIdx.x >> 5) * G + gi, ngroup = (blockDim.x >> 5) * G;
-    const int64_t pbeg = (int64_t)blockIdx.x * positions_per_block;
-    const int64_t pend = min(N, pbeg + (int64_t)positions_per_block);
+    const int HC = H * HD;
+    const int n_slots = meta.R + D;
+    for (int i = threadIdx.x; i < (blockDim.x >> 5) * G * 2 * slots_padded; i += blockDim.x) s_hist[i] = 0.f;
+    __syncthreads();
+    float *ha = s_hist + (size_t)((threadIdx.x >> 5) * G + gi) * 2 * slots_padded;
+    float *hb = ha + slots_padded;
+    const int64_t group0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * G + gi;
+    const int64_t ngroups = (int64_t)gridDim.x * (blockDim.x >> 5) * G;
 
-    for (int64_t pp = pbeg + group; pp < pend; pp += ngroup) {
-        const int p = (int)pp;
+    LaneDims<HD, D> ld;
+    ld.init(meta, c);
+    bool mine_ok[NDL];
+#pragma unroll
+    for (int j = 0; j < NDL; ++j) mine_ok[j] = c + j * HD < D;
+
+    for (int64_t item = group0; item < N * H; item += ngroups) {
+        const int p = (int)(item / H), h = (int)(item - (int64_t)p * H);
+        const int hc = h * HD + c;
         const int64_t w = window_of(w2n, W, p);
         const int n = __ldg(w_sizes + w), base = __ldg(w2n + w);
         const int64_t row = __ldg(n2n + p);
-        float cp[D];
-#pragma unroll
-        for (int d = 0; d < D; ++d) cp[d] = __ldg(n_coords + (int64_t)p * D + d);
+        ld.load(n_coords + (int64_t)p * D, ld.own);
         // ---- position p as a query ---------------------------------------------------------------
         {
             const float qc = ldf(q + row * HC + hc), gc = ldf(dout + row * HC + hc);
             const float oc = ldf(o + row * HC + hc);
             const float L = __ldg(lse + row * H + h);
             float dqa = 0.f;
+            int64_t krow_n = __ldg(n2n + base);
+            float oth_n[NDL];
+            ld.load(n_coords + (int64_t)base * D, oth_n);
             for (int kj = 0; kj < n; ++kj) {
-                const int64_t krow = __ldg(n2n + base + kj);
-                float ck[D];
+                const int64_t krow = krow_n;
+                float oth[NDL];
 #pragma unroll
-                for (int d = 0; d < D; ++d) ck[d] = __ldg(n_coords + (int64_t)(base + kj) * D + d);
+                for (int j = 0; j < NDL; ++j) oth[j] = oth_n[j];
+                const int nx = base + min(kj + 1, n - 1);
+                krow_n = __ldg(n2n + nx);
+                ld.load(n_coords + (int64_t)nx * D, oth_n);
                 const float kc = ldf(k + krow * HC + hc), vc = ldf(v + krow * HC + hc);
-                int rows[D];
+                int mine[NDL];
                 float bq, bk, bv;
-                pair_tables<T, D>(cp, ck, meta, tq, tk, tv, HC, hc, rows, bq, bk, bv);
+                pair_tables<T, HD, D, true>(ld, oth, gi, gmask, tq, tk, tv, HC, hc, mine, bq, bk, bv);
                 const float s = group_sum<HD>(qc * (kc + bq) + kc * bk, gmask);
                 const float e = group_sum<HD>(gc * (vc + bv - oc), gmask);
                 const float pr = __expf(s - L);
                 const float ds = pr * e;
                 dqa += ds * (kc + bq);
-                const float aq = ds * qc, av = pr * gc;
 #pragma unroll
-                for (int d = 0; d < D; ++d) {
-                    atomicAdd(s_dtq + rows[d] * HD + c, aq);
-                    atomicAdd(s_dtv + rows[d] * HD + c, av);
-                }
+                for (int j = 0; j < NDL; ++j)
+                    if (mine_ok[j]) {
+                        const int slot = mine[j] + ld.dim[j];
+                        ha[slot] += ds;
+                        hb[slot] += pr;
+                    }
             }
             stf(dq + row * HC + hc, dqa);
+            flush_hists<HD, D>(ha, hb, n_slots, meta, dtq, qc, dtv, gc, true, HC, hc, c, gi, gmask);
         }
         // ---- position p as a key -----------------------------------------------------------------
         {
             const float kc = ldf(k + row * HC + hc), vc = ldf(v + row * HC + hc);
             float dka = 0.f, dva = 0.f;
+            int64_t qrow_n = __ldg(n2n + base);
+            float oth_n[NDL];
+            ld.load(n_coords + (int64_t)base * D, oth_n);
             for (int qi = 0; qi < n; ++qi) {
-                const int64_t qrow = __ldg(n2n + base + qi);
-                float cq[D];
+                const int64_t qrow = qrow_n;
+                float oth[NDL];
 #pragma unroll
-                for (int d = 0; d < D; ++d) cq[d] = __ldg(n_coords + (int64_t)(base + qi) * D + d);
+                for (int j = 0; j < NDL; ++j) oth[j] = oth_n[j];
+                const int nx = base + min(qi + 1, n - 1);
+                qrow_n = __ldg(n2n + nx);
+                ld.load(n_coords + (int64_t)nx * D, oth_n);
                 const float qc = ldf(q + qrow * HC + hc), gc = ldf(dout + qrow * HC + hc);
                 const float oc = ldf(o + qrow * HC + hc);
                 const float L = __ldg(lse + qrow * H + h);
-                int rows[D];
+                int mine[NDL];
                 float bq, bk, bv;
-                pair_tables<T, D>(cq, cp, meta, tq, tk, tv, HC, hc, rows, bq, bk, bv);
+                pair_tables<T, HD, D, false>(ld, oth, gi, gmask, tq, tk, tv, HC, hc, mine, bq, bk, bv);
                 const float s = group_sum<HD>(qc * (kc + bq) + kc * bk, gmask);
                 const float e = group_sum<HD>(gc * (vc + bv - oc), gmask);
                 const float pr = __expf(s - L);
                 const float ds = pr * e;
                 dka += ds * (qc + bk);
                 dva += pr * gc;
-                const float ak = ds * kc;
 #pragma unroll
-                for (int d = 0; d < D; ++d) atomicAdd(s_dtk + rows[d] * HD + c, ak);
+                for (int j = 0; j < NDL; ++j)
+                    if (mine_ok[j]) ha[mine[j] + ld.dim[j]] += ds;
             }
             stf(dk + row * HC + hc, dka);
             stf(dv + row * HC + hc, dva);
+            flush_hists<HD, D>(ha, hb, n_slots, meta, dtk, kc, dtk, 0.f, false, HC, hc, c, gi, gmask);
         }
-    }
-    __syncthreads();
-    // flush: element (row r, channel c) of this head lives at (r*H + h)*HD + c in the flat table
-    for (int i = threadIdx.x; i < RH; i += blockDim.x) {
-        const int r = i / HD, cc = i - r * HD;
-        const int64_t g = ((int64_t)r * H + h) * HD + cc;
-        const float a = s_dtq[i], b = s_dtk[i], e = s_dtv[i];
-        if (a != 0.f) atomicAdd(dtq + g, a);
-        if (b != 0.f) atomicAdd(dtk + g, b);
-        if (e != 0.f) atomicAdd(dtv + g, e);
     }
 }
 
@@ -260,22 +364,19 @@ template <typename T, int HD, int D>
 static int launch_bwd(const AttnArgs &a, cudaStream_t st)
 {
     if (a.W == 0 || a.N == 0) return S3D_OK;
-    const size_t smem = (size_t)3 * a.meta.R * HD * sizeof(float);
-    if (smem > 200 * 1024) return S3D_ERR_UNSUPPORTED;
+    const int groups_per_block = 8 * (32 / HD);
+    const int slots_padded = (a.meta.R + D + 31) / 32 * 32;
+    const size_t smem = (size_t)groups_per_block * 2 * slots_padded * sizeof(float);
+    if (smem > 227 * 1024) return S3D_ERR_UNSUPPORTED;
     auto kern = attn_bwd_scalar_kernel<T, HD, D>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return S3D_ERR_LAUNCH;
-    // enough blocks to fill the machine a few times over, few enough that the per-block flush
-    // of the table gradients stays small
-    const int64_t target_blocks = (148 * 8 + a.H - 1) / a.H;
-    int64_t ppb = (a.N + target_blocks - 1) / target_blocks;
-    const int groups_per_block = 8 * (32 / HD);
-    if (ppb < groups_per_block) ppb = groups_per_block;
-    const int64_t chunks = (a.N + ppb - 1) / ppb;
-    dim3 grid((unsigned)chunks, (unsigned)a.H);
-    kern<<<grid, 256, smem, st>>>((const T *)a.q, (const T *)a.k, (const T *)a.v, (const T *)a.tq,
+    int64_t blocks = (a.N * a.H + groups_per_block - 1) / groups_per_block;
+    const int64_t cap = 148 * 8;
+    if (blocks > cap) blocks = cap;
+    kern<<<(unsigned)blocks, 256, smem, st>>>((const T *)a.q, (const T *)a.k, (const T *)a.v, (const T *)a.tq,
                                   (const T *)a.tk, (const T *)a.tv, a.meta, a.w_sizes, a.w2n, a.n2n,
-                                  a.n_coords, a.N, a.W, a.H, (int)ppb, (const T *)a.out, a.lse,
+                                  a.n_coords, a.N, a.W, a.H, slots_padded, (const T *)a.out, a.lse,
                                   (const T *)a.dout, (T *)a.dq, (T *)a.dk, (T *)a.dv, a.dtq, a.dtk,
                                   a.dtv);
     return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
