@@ -15,12 +15,54 @@
 
 namespace s3d {
 
-template <typename T> __device__ __forceinline__ float ldf(const T *p);
-template <> __device__ __forceinline__ float ldf<float>(const float *p) { return __ldg(p); }
-template <> __device__ __forceinline__ float ldf<__half>(const __half *p) { return __half2float(__ldg(p)); }
-template <typename T> __device__ __forceinline__ void stf(T *p, float x);
-template <> __device__ __forceinline__ void stf<float>(float *p, float x) { *p = x; }
-template <> __device__ __forceinline__ void stf<__half>(__half *p, float x) { *p = __float2half_rn(x); }
+// VEC consecutive channels of a row as floats (one 4-, 8- or 16-byte access).
+template <typename T, int VEC> __device__ __forceinline__ void ldv(const T *p, float (&x)[VEC]);
+template <> __device__ __forceinline__ void ldv<float, 1>(const float *p, float (&x)[1]) { x[0] = __ldg(p); }
+template <> __device__ __forceinline__ void ldv<float, 2>(const float *p, float (&x)[2])
+{
+    const float2 a = __ldg(reinterpret_cast<const float2 *>(p));
+    x[0] = a.x; x[1] = a.y;
+}
+template <> __device__ __forceinline__ void ldv<float, 4>(const float *p, float (&x)[4])
+{
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(p));
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+}
+template <> __device__ __forceinline__ void ldv<__half, 1>(const __half *p, float (&x)[1]) { x[0] = __half2float(__ldg(p)); }
+template <> __device__ __forceinline__ void ldv<__half, 2>(const __half *p, float (&x)[2])
+{
+    const float2 a = __half22float2(__ldg(reinterpret_cast<const __half2 *>(p)));
+    x[0] = a.x; x[1] = a.y;
+}
+template <> __device__ __forceinline__ void ldv<__half, 4>(const __half *p, float (&x)[4])
+{
+    const uint2 r = __ldg(reinterpret_cast<const uint2 *>(p));
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&r.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+}
+template <typename T, int VEC> __device__ __forceinline__ void stv(T *p, const float (&x)[VEC]);
+template <> __device__ __forceinline__ void stv<float, 1>(float *p, const float (&x)[1]) { *p = x[0]; }
+template <> __device__ __forceinline__ void stv<float, 2>(float *p, const float (&x)[2])
+{
+    *reinterpret_cast<float2 *>(p) = make_float2(x[0], x[1]);
+}
+template <> __device__ __forceinline__ void stv<float, 4>(float *p, const float (&x)[4])
+{
+    *reinterpret_cast<float4 *>(p) = make_float4(x[0], x[1], x[2], x[3]);
+}
+template <> __device__ __forceinline__ void stv<__half, 1>(__half *p, const float (&x)[1]) { *p = __float2half_rn(x[0]); }
+template <> __device__ __forceinline__ void stv<__half, 2>(__half *p, const float (&x)[2])
+{
+    *reinterpret_cast<__half2 *>(p) = __floats2half2_rn(x[0], x[1]);
+}
+template <> __device__ __forceinline__ void stv<__half, 4>(__half *p, const float (&x)[4])
+{
+    uint2 r;
+    *reinterpret_cast<__half2 *>(&r.x) = __floats2half2_rn(x[0], x[1]);
+    *reinterpret_cast<__half2 *>(&r.y) = __floats2half2_rn(x[2], x[3]);
+    *reinterpret_cast<uint2 *>(p) = r;
+}
 
 // Window that holds position p of the window-sorted voxel list: the last w with w2n[w] <= p.
 __device__ __forceinline__ int64_t window_of(const int32_t *__restrict__ w2n, int64_t W, int p)
@@ -34,32 +76,37 @@ __device__ __forceinline__ int64_t window_of(const int32_t *__restrict__ w2n, in
     return lo;
 }
 
-// Sum over the HD lanes of a group (groups are aligned, so xor offsets below HD stay inside).
-template <int HD>
+// Sum over the LG lanes of a group (groups are aligned, so xor offsets below LG stay inside).
+template <int LG>
 __device__ __forceinline__ float group_sum(float x, unsigned gmask)
 {
 #pragma unroll
-    for (int o = HD / 2; o > 0; o >>= 1) x += __shfl_xor_sync(gmask, x, o);
+    for (int o = LG / 2; o > 0; o >>= 1) x += __shfl_xor_sync(gmask, x, o);
     return x;
 }
 
-// The signal dimensions are dealt to the lanes of a group: lane c works out the table row of
-// dimensions c, c + HD, ... (one per lane, two for lane 0 of an 8-lane group with 9 dimensions)
-// and the group exchanges the rows by shuffles.
-template <int HD, int D>
+template <int LG>
+__device__ __forceinline__ unsigned group_mask(int gi)
+{
+    return LG == 32 ? 0xffffffffu : (((1u << (LG & 31)) - 1u) << (gi * LG));
+}
+
+// The signal dimensions are dealt to the LG lanes of a group: lane c works out the table row of
+// dimensions c, c + LG, ... and the group exchanges the rows by shuffles.
+template <int LG, int D>
 struct LaneDims {
-    static constexpr int NDL = (D + HD - 1) / HD;
+    static constexpr int NDL = (D + LG - 1) / LG;
     float own[NDL];   // this voxel's coordinate in the lane's dimensions
     int L[NDL], rb[NDL], dim[NDL];
-    bool last[NDL];
+    bool last[NDL], ok[NDL];
 
     __device__ __forceinline__ void init(const CrseMeta &m, int c)
     {
 #pragma unroll
         for (int j = 0; j < NDL; ++j) {
-            const int d = c + j * HD;
-            const bool ok = d < D;
-            dim[j] = ok ? d : 0;
+            const int d = c + j * LG;
+            ok[j] = d < D;
+            dim[j] = ok[j] ? d : 0;
             L[j] = m.L[dim[j]];
             rb[j] = m.rowbase[dim[j]];
             last[j] = d == D - 1;
@@ -72,37 +119,46 @@ struct LaneDims {
     }
 };
 
-// Table rows of a pair and the three sums of this lane's channel over the D looked-up rows.
+// Table rows of a pair and the three sums of this lane's channels over the D looked-up rows.
 // oth: the other voxel's coordinate in this lane's dimensions; OWN_IS_QUERY says which side the
-// lane's own voxel is on.
-template <typename T, int HD, int D, bool OWN_IS_QUERY>
-__device__ __forceinline__ void pair_tables(const LaneDims<HD, D> &ld, const float (&oth)[LaneDims<HD, D>::NDL],
+// lane's own voxel is on.  mine: the rows of the lane's own dimensions.
+template <typename T, int LG, int D, int VEC, bool OWN_IS_QUERY>
+__device__ __forceinline__ void pair_tables(const LaneDims<LG, D> &ld, const float (&oth)[LaneDims<LG, D>::NDL],
                                             int gi, unsigned gmask,
                                             const T *__restrict__ tq, const T *__restrict__ tk,
                                             const T *__restrict__ tv, int HC, int hc,
-                                            int (&mine)[LaneDims<HD, D>::NDL],
-                                            float &bq, float &bk, float &bv)
+                                            int (&mine)[LaneDims<LG, D>::NDL],
+                                            float (&bq)[VEC], float (&bk)[VEC], float (&bv)[VEC])
 {
-    constexpr int NDL = LaneDims<HD, D>::NDL;
+    constexpr int NDL = LaneDims<LG, D>::NDL;
 #pragma unroll
     for (int j = 0; j < NDL; ++j)
         mine[j] = ld.rb[j] + (OWN_IS_QUERY ? crse_index(ld.own[j], oth[j], ld.L[j], ld.last[j])
                                            : crse_index(oth[j], ld.own[j], ld.L[j], ld.last[j]));
-    bq = bk = bv = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) bq[i] = bk[i] = bv[i] = 0.f;
 #pragma unroll
     for (int d = 0; d < D; ++d) {
-        const int row = __shfl_sync(gmask, mine[d / HD], gi * HD + d % HD);
+        const int row = __shfl_sync(gmask, mine[d / LG], gi * LG + d % LG);
         const int64_t off = (int64_t)row * HC + hc;
-        bq += ldf(tq + off);
-        bk += ldf(tk + off);
-        bv += ldf(tv + off);
+        float a[VEC], b[VEC], e[VEC];
+        ldv<T, VEC>(tq + off, a);
+        ldv<T, VEC>(tk + off, b);
+        ldv<T, VEC>(tv + off, e);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            bq[i] += a[i];
+            bk[i] += b[i];
+            bv[i] += e[i];
+        }
     }
 }
 
 // ---------------------------------------------------------------------------------------------
-// Forward: a group of HD lanes (lane = channel) owns one (query, head) row and walks the keys of
-// the query's window; every row of q, k, v and of the tables is read as one coalesced piece.
-template <typename T, int HD, int D>
+// Forward: a group of LG = HD / VEC lanes (a lane holds VEC consecutive channels) owns one
+// (query, head) row and walks the keys of the query's window; every row of q, k, v and of the
+// tables is read as one coalesced piece.
+template <typename T, int HD, int D, int VEC>
 __global__ void __launch_bounds__(256)
 attn_fwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
                        const T *__restrict__ tq, const T *__restrict__ tk, const T *__restrict__ tv,
@@ -111,55 +167,74 @@ attn_fwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T
                        const float *__restrict__ n_coords, int64_t N, int64_t W, int H,
                        T *__restrict__ out, float *__restrict__ lse)
 {
-    constexpr int G = 32 / HD;
-    const int lane = threadIdx.x & 31, c = lane % HD, gi = lane / HD;
-    const unsigned gmask = HD == 32 ? 0xffffffffu : (((1u << (HD & 31)) - 1u) << (gi * HD));
+    constexpr int LG = HD / VEC, G = 32 / LG;
+    constexpr int NDL = LaneDims<LG, D>::NDL;
+    const int lane = threadIdx.x & 31, c = lane % LG, gi = lane / LG;
+    const unsigned gmask = group_mask<LG>(gi);
     const int HC = H * HD;
     const int64_t group0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * G + gi;
     const int64_t ngroups = (int64_t)gridDim.x * (blockDim.x >> 5) * G;
+    LaneDims<LG, D> ld;
+    ld.init(meta, c);
 
-    for (int64_t item = group0; item < N * H; item += ngroups) {
+    // every lane of a warp runs the same number of items so that the warp stays together;
+    // groups past the end repeat the last item without storing
+    const int64_t items = N * H;
+    for (int64_t it0 = group0 - gi; it0 < items; it0 += ngroups) {
+        const bool live = it0 + gi < items;
+        const int64_t item = live ? it0 + gi : items - 1;
         const int p = (int)(item / H), h = (int)(item - (int64_t)p * H);
         const int64_t w = window_of(w2n, W, p);
         const int n = __ldg(w_sizes + w), base = __ldg(w2n + w);
         const int64_t qrow = __ldg(n2n + p);
-        const int hc = h * HD + c;
-        const float qc = ldf(q + qrow * HC + hc);
-        LaneDims<HD, D> ld;
-        ld.init(meta, c);
+        const int hc = h * HD + c * VEC;
+        float qc[VEC], acc[VEC];
+        ldv<T, VEC>(q + qrow * HC + hc, qc);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
         ld.load(n_coords + (int64_t)p * D, ld.own);
-        float acc = 0.f, mx = -INFINITY, l = 0.f;
+        float mx = -INFINITY, l = 0.f;
         // the next key's row number and coordinates are fetched one iteration ahead
         int64_t krow_n = __ldg(n2n + base);
-        float oth_n[LaneDims<HD, D>::NDL];
+        float oth_n[NDL];
         ld.load(n_coords + (int64_t)base * D, oth_n);
         for (int kj = 0; kj < n; ++kj) {
             const int64_t krow = krow_n;
-            float oth[LaneDims<HD, D>::NDL];
+            float oth[NDL];
 #pragma unroll
-            for (int j = 0; j < LaneDims<HD, D>::NDL; ++j) oth[j] = oth_n[j];
+            for (int j = 0; j < NDL; ++j) oth[j] = oth_n[j];
             const int nx = base + min(kj + 1, n - 1);
             krow_n = __ldg(n2n + nx);
             ld.load(n_coords + (int64_t)nx * D, oth_n);
-            const float kc = ldf(k + krow * HC + hc), vc = ldf(v + krow * HC + hc);
-            int mine[LaneDims<HD, D>::NDL];
-            float bq, bk, bv;
-            pair_tables<T, HD, D, true>(ld, oth, gi, gmask, tq, tk, tv, HC, hc, mine, bq, bk, bv);
-            const float s = group_sum<HD>(qc * (kc + bq) + kc * bk, gmask);
+            float kc[VEC], vc[VEC], bq[VEC], bk[VEC], bv[VEC];
+            ldv<T, VEC>(k + krow * HC + hc, kc);
+            ldv<T, VEC>(v + krow * HC + hc, vc);
+            int mine[NDL];
+            pair_tables<T, LG, D, VEC, true>(ld, oth, gi, gmask, tq, tk, tv, HC, hc, mine, bq, bk, bv);
+            float sp = 0.f;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) sp += qc[i] * (kc[i] + bq[i]) + kc[i] * bk[i];
+            const float s = group_sum<LG>(sp, gmask);
             const float mnew = fmaxf(mx, s);
             const float scale = __expf(mx - mnew);
             const float pr = __expf(s - mnew);
             l = l * scale + pr;
-            acc = acc * scale + pr * (vc + bv);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = acc[i] * scale + pr * (vc[i] + bv[i]);
             mx = mnew;
         }
-        stf(out + qrow * HC + hc, acc / l);
-        if (c == 0) lse[qrow * H + h] = mx + __logf(l);
+        if (live) {
+            const float inv = 1.f / l;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] *= inv;
+            stv<T, VEC>(out + qrow * HC + hc, acc);
+            if (c == 0) lse[qrow * H + h] = mx + __logf(l);
+        }
     }
 }
 
 // ---------------------------------------------------------------------------------------------
-// Backward.  A group of HD lanes (lane = channel) takes one (position, head) of the window-sorted
+// Backward.  A group of LG = HD / VEC lanes (a lane holds VEC consecutive channels) takes one (position, head) of the window-sorted
 // voxel list, first as a query (dQ, dTq, dTv over the keys of its window), then as a key (dK, dV,
 // dTk over the queries).  Every quantity is recomputed from q, k, v, tables, out and lse;
 // dP - delta is one sum, sum_c dO_c (v_c + B_c - o_c).
@@ -181,16 +256,16 @@ __device__ __forceinline__ int flat_row_of_slot(const CrseMeta &m, int slot)
     return slot - d;
 }
 
-// Adds x[slot] * (va, vb) to the rows of two global tables for every non-zero slot of the
-// group's two histograms, and clears the histograms.  ta/tb may be the same pointer pair twice.
-template <int HD, int D>
+// Adds hist[slot] * (row vector) to the rows of two global tables for every non-zero slot of the
+// group's two histograms, and clears the histograms.
+template <int LG, int D, int VEC>
 __device__ __forceinline__ void flush_hists(float *ha, float *hb, int n_slots, const CrseMeta &m,
-                                            float *__restrict__ ta, float va,
-                                            float *__restrict__ tb, float vb, bool use_b,
+                                            float *__restrict__ ta, const float (&va)[VEC],
+                                            float *__restrict__ tb, const float (&vb)[VEC], bool use_b,
                                             int HC, int hc, int c, int gi, unsigned gmask)
 {
     __syncwarp(gmask);
-    for (int s0 = 0; s0 < n_slots; s0 += HD) {
+    for (int s0 = 0; s0 < n_slots; s0 += LG) {
         const int si = s0 + c;
         float a = 0.f, b = 0.f;
         if (si < n_slots) {
@@ -201,22 +276,28 @@ __device__ __forceinline__ void flush_hists(float *ha, float *hb, int n_slots, c
                 hb[si] = 0.f;
             }
         }
-        unsigned nz = __ballot_sync(gmask, a != 0.f || b != 0.f) >> (gi * HD);
-        if (HD < 32) nz &= (1u << (HD & 31)) - 1u;
+        unsigned nz = __ballot_sync(gmask, a != 0.f || b != 0.f) >> (gi * LG);
+        if (LG < 32) nz &= (1u << (LG & 31)) - 1u;
         while (nz) {
             const int j = __ffs(nz) - 1;
             nz &= nz - 1;
-            const float aj = __shfl_sync(gmask, a, gi * HD + j);
-            const float bj = __shfl_sync(gmask, b, gi * HD + j);
+            const float aj = __shfl_sync(gmask, a, gi * LG + j);
+            const float bj = __shfl_sync(gmask, b, gi * LG + j);
             const int64_t off = (int64_t)flat_row_of_slot<D>(m, s0 + j) * HC + hc;
-            if (aj != 0.f) atomicAdd(ta + off, aj * va);
-            if (use_b && bj != 0.f) atomicAdd(tb + off, bj * vb);
+            if (aj != 0.f) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) atomicAdd(ta + off + i, aj * va[i]);
+            }
+            if (use_b && bj != 0.f) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) atomicAdd(tb + off + i, bj * vb[i]);
+            }
         }
     }
     __syncwarp(gmask);
 }
 
-template <typename T, int HD, int D>
+template <typename T, int HD, int D, int VEC>
 __global__ void __launch_bounds__(256)
 attn_bwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
                        const T *__restrict__ tq, const T *__restrict__ tk, const T *__restrict__ tv,
@@ -229,10 +310,10 @@ attn_bwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T
                        float *__restrict__ dtv)
 {
     extern __shared__ float s_hist[];  // [groups of the block][2][slots_padded]
-    constexpr int G = 32 / HD;
-    constexpr int NDL = LaneDims<HD, D>::NDL;
-    const int lane = threadIdx.x & 31, c = lane % HD, gi = lane / HD;
-    const unsigned gmask = HD == 32 ? 0xffffffffu : (((1u << (HD & 31)) - 1u) << (gi * HD));
+    constexpr int LG = HD / VEC, G = 32 / LG;
+    constexpr int NDL = LaneDims<LG, D>::NDL;
+    const int lane = threadIdx.x & 31, c = lane % LG, gi = lane / LG;
+    const unsigned gmask = group_mask<LG>(gi);
     const int HC = H * HD;
     const int n_slots = meta.R + D;
     for (int i = threadIdx.x; i < (blockDim.x >> 5) * G * 2 * slots_padded; i += blockDim.x) s_hist[i] = 0.f;
@@ -242,28 +323,34 @@ attn_bwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T
     const int64_t group0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * G + gi;
     const int64_t ngroups = (int64_t)gridDim.x * (blockDim.x >> 5) * G;
 
-    LaneDims<HD, D> ld;
+    LaneDims<LG, D> ld;
     ld.init(meta, c);
-    bool mine_ok[NDL];
-#pragma unroll
-    for (int j = 0; j < NDL; ++j) mine_ok[j] = c + j * HD < D;
 
-    for (int64_t item = group0; item < N * H; item += ngroups) {
+    // every lane of a warp runs the same number of items; groups past the end repeat the last item
+    // without storing or flushing
+    const int64_t items = N * H;
+    for (int64_t it0 = group0 - gi; it0 < items; it0 += ngroups) {
+        const bool live = it0 + gi < items;
+        const int64_t item = live ? it0 + gi : items - 1;
         const int p = (int)(item / H), h = (int)(item - (int64_t)p * H);
-        const int hc = h * HD + c;
+        const int hc = h * HD + c * VEC;
         const int64_t w = window_of(w2n, W, p);
         const int n = __ldg(w_sizes + w), base = __ldg(w2n + w);
         const int64_t row = __ldg(n2n + p);
         ld.load(n_coords + (int64_t)p * D, ld.own);
         // ---- position p as a query ---------------------------------------------------------------
         {
-            const float qc = ldf(q + row * HC + hc), gc = ldf(dout + row * HC + hc);
-            const float oc = ldf(o + row * HC + hc);
+            float qc[VEC], gc[VEC], oc[VEC], dqa[VEC];
+            ldv<T, VEC>(q + row * HC + hc, qc);
+            ldv<T, VEC>(dout + row * HC + hc, gc);
+            ldv<T, VEC>(o + row * HC + hc, oc);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) dqa[i] = 0.f;
             const float L = __ldg(lse + row * H + h);
-            float dqa = 0.f;
             int64_t krow_n = __ldg(n2n + base);
             float oth_n[NDL];
             ld.load(n_coords + (int64_t)base * D, oth_n);
+#pragma unroll(HD == 8 ? 2 : 1)
             for (int kj = 0; kj < n; ++kj) {
                 const int64_t krow = krow_n;
                 float oth[NDL];
@@ -272,33 +359,49 @@ attn_bwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T
                 const int nx = base + min(kj + 1, n - 1);
                 krow_n = __ldg(n2n + nx);
                 ld.load(n_coords + (int64_t)nx * D, oth_n);
-                const float kc = ldf(k + krow * HC + hc), vc = ldf(v + krow * HC + hc);
+                float kc[VEC], vc[VEC], bq[VEC], bk[VEC], bv[VEC];
+                ldv<T, VEC>(k + krow * HC + hc, kc);
+                ldv<T, VEC>(v + krow * HC + hc, vc);
                 int mine[NDL];
-                float bq, bk, bv;
-                pair_tables<T, HD, D, true>(ld, oth, gi, gmask, tq, tk, tv, HC, hc, mine, bq, bk, bv);
-                const float s = group_sum<HD>(qc * (kc + bq) + kc * bk, gmask);
-                const float e = group_sum<HD>(gc * (vc + bv - oc), gmask);
+                pair_tables<T, LG, D, VEC, true>(ld, oth, gi, gmask, tq, tk, tv, HC, hc, mine, bq, bk, bv);
+                float sp = 0.f, ep = 0.f;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    sp += qc[i] * (kc[i] + bq[i]) + kc[i] * bk[i];
+                    ep += gc[i] * (vc[i] + bv[i] - oc[i]);
+                }
+                const float s = group_sum<LG>(sp, gmask);
+                const float e = group_sum<LG>(ep, gmask);
                 const float pr = __expf(s - L);
                 const float ds = pr * e;
-                dqa += ds * (kc + bq);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) dqa[i] += ds * (kc[i] + bq[i]);
 #pragma unroll
                 for (int j = 0; j < NDL; ++j)
-                    if (mine_ok[j]) {
+                    if (ld.ok[j]) {
                         const int slot = mine[j] + ld.dim[j];
                         ha[slot] += ds;
                         hb[slot] += pr;
                     }
             }
-            stf(dq + row * HC + hc, dqa);
-            flush_hists<HD, D>(ha, hb, n_slots, meta, dtq, qc, dtv, gc, true, HC, hc, c, gi, gmask);
+            if (live) stv<T, VEC>(dq + row * HC + hc, dqa);
+            if (!live) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) qc[i] = gc[i] = 0.f;   // the repeated item adds zeros
+            }
+            flush_hists<LG, D, VEC>(ha, hb, n_slots, meta, dtq, qc, dtv, gc, true, HC, hc, c, gi, gmask);
         }
         // ---- position p as a key -----------------------------------------------------------------
         {
-            const float kc = ldf(k + row * HC + hc), vc = ldf(v + row * HC + hc);
-            float dka = 0.f, dva = 0.f;
+            float kc[VEC], vc[VEC], dka[VEC], dva[VEC];
+            ldv<T, VEC>(k + row * HC + hc, kc);
+            ldv<T, VEC>(v + row * HC + hc, vc);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) dka[i] = dva[i] = 0.f;
             int64_t qrow_n = __ldg(n2n + base);
             float oth_n[NDL];
             ld.load(n_coords + (int64_t)base * D, oth_n);
+#pragma unroll(HD == 8 ? 2 : 1)
             for (int qi = 0; qi < n; ++qi) {
                 const int64_t qrow = qrow_n;
                 float oth[NDL];
@@ -307,25 +410,40 @@ attn_bwd_scalar_kernel(const T *__restrict__ q, const T *__restrict__ k, const T
                 const int nx = base + min(qi + 1, n - 1);
                 qrow_n = __ldg(n2n + nx);
                 ld.load(n_coords + (int64_t)nx * D, oth_n);
-                const float qc = ldf(q + qrow * HC + hc), gc = ldf(dout + qrow * HC + hc);
-                const float oc = ldf(o + qrow * HC + hc);
+                float qc[VEC], gc[VEC], oc[VEC], bq[VEC], bk[VEC], bv[VEC];
+                ldv<T, VEC>(q + qrow * HC + hc, qc);
+                ldv<T, VEC>(dout + qrow * HC + hc, gc);
+                ldv<T, VEC>(o + qrow * HC + hc, oc);
                 const float L = __ldg(lse + qrow * H + h);
                 int mine[NDL];
-                float bq, bk, bv;
-                pair_tables<T, HD, D, false>(ld, oth, gi, gmask, tq, tk, tv, HC, hc, mine, bq, bk, bv);
-                const float s = group_sum<HD>(qc * (kc + bq) + kc * bk, gmask);
-                const float e = group_sum<HD>(gc * (vc + bv - oc), gmask);
+                pair_tables<T, LG, D, VEC, false>(ld, oth, gi, gmask, tq, tk, tv, HC, hc, mine, bq, bk, bv);
+                float sp = 0.f, ep = 0.f;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    sp += qc[i] * (kc[i] + bq[i]) + kc[i] * bk[i];
+                    ep += gc[i] * (vc[i] + bv[i] - oc[i]);
+                }
+                const float s = group_sum<LG>(sp, gmask);
+                const float e = group_sum<LG>(ep, gmask);
                 const float pr = __expf(s - L);
                 const float ds = pr * e;
-                dka += ds * (qc + bk);
-                dva += pr * gc;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    dka[i] += ds * (qc[i] + bk[i]);
+                    dva[i] += pr * gc[i];
+                }
 #pragma unroll
                 for (int j = 0; j < NDL; ++j)
-                    if (mine_ok[j]) ha[mine[j] + ld.dim[j]] += ds;
+                    if (ld.ok[j]) ha[mine[j] + ld.dim[j]] += ds;
             }
-            stf(dk + row * HC + hc, dka);
-            stf(dv + row * HC + hc, dva);
-            flush_hists<HD, D>(ha, hb, n_slots, meta, dtk, kc, dtk, 0.f, false, HC, hc, c, gi, gmask);
+            if (live) {
+                stv<T, VEC>(dk + row * HC + hc, dka);
+                stv<T, VEC>(dv + row * HC + hc, dva);
+            } else {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) kc[i] = 0.f;
+            }
+            flush_hists<LG, D, VEC>(ha, hb, n_slots, meta, dtk, kc, dtk, kc, false, HC, hc, c, gi, gmask);
         }
     }
 }
@@ -346,17 +464,58 @@ __global__ void crse_indices_kernel(const float *__restrict__ n_coords, const Cr
 }
 
 // ---------------------------------------------------------------------------------------------
+// Channels per lane, from measurements on a B200 (fp32, 9 signal dimensions): the forward is
+// fastest with groups of 2 (head_dim 8) or 8 lanes (head_dim 16 and 32); the backward, whose
+// histogram flush walks the table rows LG at a time, with groups of 8 or 16 lanes.
+template <int HD> struct ScalarVec;
+template <> struct ScalarVec<8> { static constexpr int FWD = 4, BWD = 1; };
+template <> struct ScalarVec<16> { static constexpr int FWD = 2, BWD = 1; };
+template <> struct ScalarVec<32> { static constexpr int FWD = 4, BWD = 4; };
+
+template <typename T, int HD, int D, int VEC>
+static int launch_fwd_v(const AttnArgs &a, cudaStream_t st)
+{
+    const int groups_per_block = 8 * (32 / (HD / VEC));
+    int64_t blocks = (a.N * a.H + groups_per_block - 1) / groups_per_block;
+    const int64_t cap = 148 * 64;
+    if (blocks > cap) blocks = cap;
+    attn_fwd_scalar_kernel<T, HD, D, VEC><<<(unsigned)blocks, 256, 0, st>>>(
+        (const T *)a.q, (const T *)a.k, (const T *)a.v, (const T *)a.tq, (const T *)a.tk,
+        (const T *)a.tv, a.meta, a.w_sizes, a.w2n, a.n2n, a.n_coords, a.N, a.W, a.H, (T *)a.out, a.lse);
+    return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
+}
+
 template <typename T, int HD, int D>
 static int launch_fwd(const AttnArgs &a, cudaStream_t st)
 {
     if (a.W == 0 || a.N == 0) return S3D_OK;
-    const int groups_per_block = 8 * (32 / HD);
+    return launch_fwd_v<T, HD, D, ScalarVec<HD>::FWD>(a, st);
+}
+
+template <typename T, int HD, int D, int VEC>
+static int launch_bwd_v(const AttnArgs &a, cudaStream_t st)
+{
+    constexpr int G = 32 / (HD / VEC);
+    const int slots_padded = (a.meta.R + D + 31) / 32 * 32;
+    const size_t per_group = (size_t)2 * slots_padded * sizeof(float);
+    // as many warps per block (at most 8) as keep the histograms of a block near 100 KB
+    int warps = (int)((100 * 1024) / (per_group * G));
+    if (warps > 8) warps = 8;
+    if (warps < 1) warps = 1;
+    const size_t smem = per_group * G * warps;
+    if (smem > 227 * 1024) return S3D_ERR_UNSUPPORTED;
+    auto kern = attn_bwd_scalar_kernel<T, HD, D, VEC>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return S3D_ERR_LAUNCH;
+    const int groups_per_block = warps * G;
     int64_t blocks = (a.N * a.H + groups_per_block - 1) / groups_per_block;
-    const int64_t cap = 148 * 64;
+    const int64_t cap = 148 * 8;
     if (blocks > cap) blocks = cap;
-    attn_fwd_scalar_kernel<T, HD, D><<<(unsigned)blocks, 256, 0, st>>>(
-        (const T *)a.q, (const T *)a.k, (const T *)a.v, (const T *)a.tq, (const T *)a.tk,
-        (const T *)a.tv, a.meta, a.w_sizes, a.w2n, a.n2n, a.n_coords, a.N, a.W, a.H, (T *)a.out, a.lse);
+    kern<<<(unsigned)blocks, warps * 32, smem, st>>>((const T *)a.q, (const T *)a.k, (const T *)a.v, (const T *)a.tq,
+                                  (const T *)a.tk, (const T *)a.tv, a.meta, a.w_sizes, a.w2n, a.n2n,
+                                  a.n_coords, a.N, a.W, a.H, slots_padded, (const T *)a.out, a.lse,
+                                  (const T *)a.dout, (T *)a.dq, (T *)a.dk, (T *)a.dv, a.dtq, a.dtk,
+                                  a.dtv);
     return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
 }
 
@@ -364,22 +523,7 @@ template <typename T, int HD, int D>
 static int launch_bwd(const AttnArgs &a, cudaStream_t st)
 {
     if (a.W == 0 || a.N == 0) return S3D_OK;
-    const int groups_per_block = 8 * (32 / HD);
-    const int slots_padded = (a.meta.R + D + 31) / 32 * 32;
-    const size_t smem = (size_t)groups_per_block * 2 * slots_padded * sizeof(float);
-    if (smem > 227 * 1024) return S3D_ERR_UNSUPPORTED;
-    auto kern = attn_bwd_scalar_kernel<T, HD, D>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return S3D_ERR_LAUNCH;
-    int64_t blocks = (a.N * a.H + groups_per_block - 1) / groups_per_block;
-    const int64_t cap = 148 * 8;
-    if (blocks > cap) blocks = cap;
-    kern<<<(unsigned)blocks, 256, smem, st>>>((const T *)a.q, (const T *)a.k, (const T *)a.v, (const T *)a.tq,
-                                  (const T *)a.tk, (const T *)a.tv, a.meta, a.w_sizes, a.w2n, a.n2n,
-                                  a.n_coords, a.N, a.W, a.H, slots_padded, (const T *)a.out, a.lse,
-                                  (const T *)a.dout, (T *)a.dq, (T *)a.dk, (T *)a.dv, a.dtq, a.dtk,
-                                  a.dtv);
-    return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
+    return launch_bwd_v<T, HD, D, ScalarVec<HD>::BWD>(a, st);
 }
 
 template <typename T, int HD>
