@@ -34,3 +34,18 @@ def install_as_swin3d(force: bool = False) -> None:
         parent, _, leaf = alias.rpartition(".")
         if parent in sys.modules:
             setattr(sys.modules[parent], leaf, mod)
+
+
+def patch_basic_layer(basic_layer_cls) -> None:
+    """Replaces ``BasicLayer.get_index01`` (Swin3D/modules/swin3d_layers.py:789-822) of the given
+    class by the window builder of this package, so that the two index constructions per stage
+    (:858-859) no longer enumerate window cells through MinkowskiEngine pooling.  The method keeps
+    its signature ``(self, sp, local_xyz, colors)`` and reads ``self.window_size``; the shifted
+    sparse tensor the caller passes for the odd blocks is grouped by its (already shifted)
+    coordinates."""
+    from . import window
+
+    def get_index01(self, sp, local_xyz, colors):
+        return window.get_index01(sp, local_xyz, colors, self.window_size)
+
+    basic_layer_cls.get_index01 = get_index01

@@ -67,3 +67,39 @@ def build_windows(coords: torch.Tensor, feats: torch.Tensor, window_size: int, s
         raise ValueError("s3d_window_build: a batch index or window coordinate is outside the "
                          "supported key range (batch < 1024, |window index| < 16384)")
     return WindowIndex(n2n, n_coords, w_sizes[:W], w2n[:W], M, mx)
+
+
+def _tensor_stride(sp) -> int:
+    """Tensor stride of a MinkowskiEngine-style sparse tensor (or of any object that mimics
+    ``sp.coordinate_map_key.get_tensor_stride()`` / ``sp.tensor_stride``)."""
+    key = getattr(sp, "coordinate_map_key", None)
+    if key is not None and hasattr(key, "get_tensor_stride"):
+        s = key.get_tensor_stride()
+    else:
+        s = getattr(sp, "tensor_stride", 1)
+    return int(s[0]) if isinstance(s, (list, tuple)) else int(s)
+
+
+def get_index01(sp, local_xyz: torch.Tensor, colors: torch.Tensor, window_size: int,
+                shift_size: int = 0):
+    """Call-compatible replacement of ``BasicLayer.get_index01`` (Swin3D/modules/swin3d_layers.py:
+    789-822) that does not go through MinkowskiEngine: ``sp`` only needs ``.C`` (int [N,4]: batch,
+    x, y, z) and its tensor stride.  Returns the same 8-tuple ``WindowAttention.forward``
+    (:490-500) unpacks:
+
+        (x_offset, y_offset, m2w_indices, w_sizes, w2n_indices, n2n_indices, w2m_indices, n_coords)
+
+    ``x_offset`` and ``y_offset`` are not read by ``WindowAttention`` and ``m2w_indices`` (one entry
+    per attention pair) is not read by the fused kernels: they are None / an empty tensor.  The
+    index tensors are int32, which ``SelfAttnAIOFunction`` takes as they are (the reference converts
+    int64 to int32 inside every call, self_attn_aio_fwd.cu:395-400).
+
+    ``shift_size`` (in voxels of this stage) may be given instead of building a shifted copy of
+    ``sp`` as ``BasicLayer.get_shifted_sp`` does; a shifted ``sp`` with ``shift_size=0`` groups
+    the same way."""
+    feats = torch.cat([local_xyz, colors], dim=1).float()
+    wi = build_windows(sp.C.int(), feats, window_size, shift_size, _tensor_stride(sp))
+    w2 = wi.w_sizes.to(torch.int64) ** 2
+    w2m = torch.cumsum(w2, 0) - w2
+    m2w = torch.empty(0, dtype=torch.int64, device=wi.n2n.device)
+    return (None, None, m2w, wi.w_sizes, wi.w2n, wi.n2n, w2m, wi.n_coords)

@@ -84,3 +84,21 @@ def test_python_wrappers_reject_cpu_tensors():
                                   TableDims.D0, IndexMode.DIRECT, PrecisionMode.HALF_NONE)
     with pytest.raises(RuntimeError, match="CUDA"):
         KNN.apply(3, torch.zeros(5, 3), torch.zeros(5, 3), torch.tensor([5]), torch.tensor([5]))
+
+
+def test_patch_basic_layer_replaces_get_index01_and_forwards_the_window_size(monkeypatch):
+    """compat.patch_basic_layer: the method keeps the reference's signature and hands the layer's
+    window size to the window builder (no GPU: the builder is replaced by a recorder)."""
+    from swin3d_b200 import compat, window
+
+    class BasicLayer:                      # stands in for Swin3D.modules.swin3d_layers.BasicLayer
+        window_size = 7
+
+        def get_index01(self, sp, local_xyz, colors):
+            raise AssertionError("the MinkowskiEngine path must not run")
+
+    seen = []
+    monkeypatch.setattr(window, "get_index01", lambda *a, **k: seen.append((a, k)) or "tuple")
+    compat.patch_basic_layer(BasicLayer)
+    assert BasicLayer().get_index01("sp", "xyz", "rgb") == "tuple"
+    assert seen == [(("sp", "xyz", "rgb", 7), {})]

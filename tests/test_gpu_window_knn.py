@@ -122,3 +122,59 @@ def test_knn_config5_scale_properties():
     sel = np.arange(0, 200_000, 997)
     ridx, rd2 = O.knn(16, src, qry[sel], [50_000], [len(sel)])
     assert np.array_equal(idx[sel], ridx) and np.array_equal(d2[sel], rd2)
+
+
+class _FakeMapKey:
+    def __init__(self, stride):
+        self._s = [stride] * 3
+
+    def get_tensor_stride(self):
+        return self._s
+
+
+class _FakeSparseTensor:
+    """What get_index01 reads of a MinkowskiEngine SparseTensor: .C and the tensor stride."""
+    def __init__(self, coords, stride=1):
+        self.C = coords
+        self.coordinate_map_key = _FakeMapKey(stride)
+
+
+@pytest.mark.parametrize("shift", [0, 2])
+def test_get_index01_drop_in_returns_the_tuple_window_attention_unpacks(shift):
+    """BasicLayer.get_index01 without MinkowskiEngine: the 8-tuple matches the numpy restatement of
+    the reference's grouping + offsets, whether the shift is passed or the sparse tensor is
+    already shifted (get_shifted_sp), and feeds SelfAttnAIOFunction like WindowAttention does."""
+    from swin3d_b200.window import get_index01
+    from swin3d_b200.sparse_dl.attn.attn_coff import (SelfAttnAIOFunction, PosEmb, TableDims,
+                                                      IndexMode, PrecisionMode)
+    from tests.helpers import make_problem, oracle_fwd_bwd, rel_err
+    sc = S.make_planes_and_boxes(5, 1500, 30)
+    p = make_problem(seed=41, scene=sc, ws=5, shift=shift, H=2, hd=16, crse="XYZ_RGB")
+    feats = S.signal_feats(sc, "XYZ_RGB")
+    local_xyz, colors = _dev(feats[:, :3]), _dev(feats[:, 3:])
+    shifted = sc.coords.copy()
+    shifted[:, 1:] += shift
+    tuples = [get_index01(_FakeSparseTensor(_dev(sc.coords)), local_xyz, colors, 5, shift_size=shift),
+              get_index01(_FakeSparseTensor(_dev(shifted)), local_xyz, colors, 5)]
+    ref = O.window_grouping(sc.coords, feats, 5, shift)
+    _, _, _, ws64, w2n64, w2m = O.window_offsets(ref[2])
+    for x_off, y_off, m2w, w_sizes, w2n, n2n, w2m_t, n_coords in tuples:
+        assert x_off is None and y_off is None and m2w.numel() == 0
+        assert np.array_equal(w_sizes.cpu().numpy(), ws64)
+        assert np.array_equal(w2n.cpu().numpy(), w2n64)
+        assert np.array_equal(w2m_t.cpu().numpy(), w2m)
+        assert np.array_equal(n2n.cpu().numpy(), ref[0])
+        assert np.array_equal(n_coords.cpu().numpy(), ref[1])
+    # the call WindowAttention.forward makes with that tuple
+    _, _, m2w, w_sizes, w2n, n2n, w2m_t, n_coords = tuples[1]
+    n_crse = torch.cat([n_coords[:, :3] * p.quant, n_coords[:, 3:6] * (2 * p.quant)], dim=1)
+    indices = [m2w, w_sizes, w2m_t, w2n, n2n, n_crse]
+    q, k, v = (_dev(a).requires_grad_() for a in (p.q, p.k, p.v))
+    tq, tk, tv = (_dev(a).requires_grad_() for a in (p.tq, p.tk, p.tv))
+    out = SelfAttnAIOFunction.apply(q, k, v, tq, tk, tv, torch.IntTensor(p.sizes).cuda(), indices,
+                                    PosEmb.SEPARATE, TableDims.D0, IndexMode.INDIRECT, PrecisionMode.HALF_NONE)
+    out.backward(_dev(p.g))
+    o_ref, _, g_ref = oracle_fwd_bwd(p, np.float64)
+    assert rel_err(out.detach().cpu().numpy(), o_ref) < 1e-4
+    for t, b in zip((q, k, v, tq, tk, tv), g_ref):
+        assert rel_err(t.grad.cpu().numpy(), b) < 1e-4
