@@ -54,6 +54,8 @@ int s3d_version(void);
  *  out          [N,H,hd] dtype `dtype`, original order: softmax-weighted values.
  *  lse          float[N,H], original order: log-sum-exp of each (voxel, head) score row.
  * Supported: hd in {8,16,32}; D in {3,6,9}; any H; any window size >= 1.
+ * q, k, v, out and the tables (and dout, dq, dk, dv, dtq, dtk, dtv of the backward) must be
+ * 16-byte aligned: S3D_ERR_BAD_ARG otherwise.
  */
 int s3d_attn_fwd(const void *q, const void *k, const void *v,
                  const void *tq, const void *tk, const void *tv,

@@ -1,6 +1,8 @@
 // extern "C" entry points of libswin3d_b200.so: argument validation and dispatch only.
 // The declarations, with the reference interfaces they replace, are in include/swin3d_b200.h.
 #include "attn_kernels.cuh"
+#include <cstdint>
+#include <initializer_list>
 #include "knn_kernels.cuh"
 #include "window_kernels.cuh"
 
@@ -39,13 +41,21 @@ int make_meta(const int32_t *table_sizes_host, int D, int H, int hd, CrseMeta &m
 
 }  // namespace
 
+// The kernels read and write rows with 16-byte vector accesses.
+static bool aligned16(std::initializer_list<const void *> ptrs)
+{
+    for (const void *p : ptrs)
+        if (reinterpret_cast<uintptr_t>(p) & 15) return false;
+    return true;
+}
+
 extern "C" {
 
 const char *s3d_status_string(int status)
 {
     switch (status) {
         case S3D_OK: return "ok";
-        case S3D_ERR_BAD_ARG: return "bad argument (null pointer, negative size, unknown dtype, or table size not a multiple of H*hd)";
+        case S3D_ERR_BAD_ARG: return "bad argument (null pointer, negative size, unknown dtype, table size not a multiple of H*hd, or a row/table pointer that is not 16-byte aligned)";
         case S3D_ERR_UNSUPPORTED: return "unsupported shape (head_dim must be 8, 16 or 32; signal dims 3, 6 or 9; K <= 64; window size <= 8)";
         case S3D_ERR_LAUNCH: return "CUDA launch error";
         case S3D_ERR_WORKSPACE: return "workspace too small";
@@ -68,6 +78,7 @@ int s3d_attn_fwd(const void *q, const void *k, const void *v, const void *tq, co
     if (N == 0 || W == 0) return S3D_OK;
     if (!q || !k || !v || !tq || !tk || !tv || !w_sizes || !w2n || !n2n || !n_coords || !out || !lse)
         return S3D_ERR_BAD_ARG;
+    if (!aligned16({q, k, v, tq, tk, tv, out})) return S3D_ERR_BAD_ARG;
     a.q = q; a.k = k; a.v = v; a.tq = tq; a.tk = tk; a.tv = tv;
     a.w_sizes = w_sizes; a.w2n = w2n; a.n2n = n2n; a.n_coords = n_coords;
     a.N = N; a.W = W; a.H = H; a.hd = hd; a.dtype = dtype;
@@ -96,6 +107,7 @@ int s3d_attn_bwd(const void *q, const void *k, const void *v, const void *tq, co
     if (!q || !k || !v || !tq || !tk || !tv || !w_sizes || !w2n || !n2n || !n_coords || !out || !lse ||
         !dout || !dq || !dk || !dv)
         return S3D_ERR_BAD_ARG;
+    if (!aligned16({q, k, v, tq, tk, tv, out, dout, dq, dk, dv, dtq, dtk, dtv})) return S3D_ERR_BAD_ARG;
     a.q = q; a.k = k; a.v = v; a.tq = tq; a.tk = tk; a.tv = tv;
     a.w_sizes = w_sizes; a.w2n = w2n; a.n2n = n2n; a.n_coords = n_coords;
     a.N = N; a.W = W; a.H = H; a.hd = hd; a.dtype = dtype;

@@ -84,9 +84,16 @@ def _check_inputs(q: Tensor, k: Tensor, v: Tensor, tables, indices):
                          "[m2w, w_sizes, w2m, w2n, n2n, n_coords]")
 
 
+def _aligned16(*tensors):
+    """The library wants 16-byte aligned rows and tables; a view that starts in the middle of a
+    storage (rare: torch allocations are 256-byte aligned) is copied."""
+    return [t if t.data_ptr() % 16 == 0 else t.clone(memory_format=torch.contiguous_format) for t in tensors]
+
+
 def attn_forward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n_coords):
     """One fused forward launch.  Tensors must already have the compute dtype.  -> (out, lse)."""
     import ctypes
+    q, k, v, tq, tk, tv = _aligned16(q, k, v, tq, tk, tv)
     N, H, hd = q.shape
     W = w_sizes.shape[0]
     D = len(sizes)
@@ -110,6 +117,7 @@ def attn_backward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, 
                       out, lse, dout):
     """One fused backward launch -> (dq, dk, dv, dtq, dtk, dtv); table grads are fp32."""
     import ctypes
+    q, k, v, tq, tk, tv, out, dout = _aligned16(q, k, v, tq, tk, tv, out, dout)
     N, H, hd = q.shape
     W = w_sizes.shape[0]
     D = len(sizes)

@@ -60,6 +60,12 @@ def test_argument_validation_without_device():
     # empty problem is a no-op
     assert L.s3d_attn_fwd(None, None, None, None, None, None, p, 3, None, None, None, None,
                           0, 0, 2, 8, 0, None, None, None) == 0
+    # a row or table pointer that is not 16-byte aligned is refused before any launch (the
+    # addresses are never dereferenced on this path)
+    ok, odd = 0x10000, 0x10004
+    assert L.s3d_attn_fwd(odd, ok, ok, ok, ok, ok, p, 3, ok, ok, ok, ok, 10, 1, 2, 8, 0, ok, ok, None) == 1
+    assert L.s3d_attn_fwd(ok, ok, ok, ok, odd, ok, p, 3, ok, ok, ok, ok, 10, 1, 2, 8, 0, ok, ok, None) == 1
+    assert L.s3d_attn_fwd(ok, ok, ok, ok, ok, ok, p, 3, ok, ok, ok, ok, 10, 1, 2, 8, 0, odd, ok, None) == 1
     assert L.s3d_knn(65, None, None, None, None, 1, 0, 0, None, None, None) == 2
     assert L.s3d_knn(0, None, None, None, None, 1, 0, 0, None, None, None) == 2
     assert L.s3d_knn(3, None, None, None, None, 1, 0, 0, None, None, None) == 0

@@ -449,3 +449,28 @@ def test_generic_kernels_with_item_counts_that_do_not_fill_the_last_warp(H, hd, 
         # of the stored output is left): measure against at least 1, the scale of the inputs
         for name, a, b in zip("dq dk dv dtq dtk dtv".split(), grads, g_ref):
             assert np.abs(a - b).max() / max(np.abs(b).max(), 1.0) < tol, name
+
+
+def test_views_that_are_not_16_byte_aligned_are_copied_by_the_wrapper_and_refused_by_the_c_abi():
+    import ctypes
+    from swin3d_b200 import _lib
+    from swin3d_b200.sparse_dl.attn import attn_coff as C
+    from tests.gpu_helpers import dev
+    p = make_problem(seed=51, n_voxels=400, grid=20, H=2, hd=8, crse="XYZ", round_fp16=True)
+    q, k, v, tq, tk, tv = (dev(a).half() for a in (p.q, p.k, p.v, p.tq, p.tk, p.tv))
+    idx = [dev(a) for a in (p.w_sizes.astype(np.int32), p.w2n.astype(np.int32), p.n2n.astype(np.int32))]
+    ncr = dev(p.n_crse)
+    out0, lse0 = C.attn_forward_raw(q, k, v, tq, tk, tv, list(p.sizes), *idx, ncr)
+    buf = torch.empty(q.numel() + 4, dtype=torch.float16, device="cuda")
+    q_odd = buf[4:].view(q.shape)                     # starts 8 bytes into its storage
+    q_odd.copy_(q)
+    assert q_odd.data_ptr() % 16 == 8
+    out1, lse1 = C.attn_forward_raw(q_odd, k, v, tq, tk, tv, list(p.sizes), *idx, ncr)
+    assert torch.equal(out0, out1) and torch.equal(lse0, lse1)
+    arr = (ctypes.c_int32 * 3)(*p.sizes)
+    rc = _lib.lib.s3d_attn_fwd(q_odd.data_ptr(), k.data_ptr(), v.data_ptr(), tq.data_ptr(), tk.data_ptr(),
+                               tv.data_ptr(), ctypes.cast(arr, ctypes.c_void_p), 3, idx[0].data_ptr(),
+                               idx[1].data_ptr(), idx[2].data_ptr(), ncr.data_ptr(), p.N, len(p.w_sizes),
+                               2, 8, _lib.S3D_F16, out1.data_ptr(),
+                               lse1.data_ptr(), None)
+    assert rc == 1
