@@ -5,8 +5,8 @@
 // (Swin3D/src/attn/self_attn_aio_fwd.cu:16-52,111-188, self_attn_aio_bwd.cu:14-113):
 //   s_qk = sum_c ( q_c k_c + q_c * sum_n Tq[n,idx_n,h,c] + k_c * sum_n Tk[n,idx_n,h,c] )
 //   out_q = sum_k softmax_k(s_qk) * ( v_k + sum_n Tv[n,idx_n,h,:] )
-// but the structure is different: a group of head_dim lanes (lane = channel) owns one
-// (voxel, head) row, so rows of q, k, v and of the tables are read as coalesced pieces; the
+// but the structure is different: a group of head_dim / VEC lanes (VEC consecutive channels per
+// lane) owns one (voxel, head) row, so rows of q, k, v and of the tables are read as coalesced pieces; the
 // softmax is online, outputs are written once (no atomics), and the backward sums the scalar
 // weights of every looked-up table row in per-group histograms and touches the global table
 // gradient once per (voxel, head, touched row).
