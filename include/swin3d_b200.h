@@ -89,6 +89,21 @@ int s3d_debug_crse_indices(const float *n_coords, const int32_t *table_sizes_hos
                            int H, int hd, int32_t first_pos, int32_t n, int32_t *idx_out,
                            void *stream);
 
+/* The same dump through the index function of one kernel family, so that the code the tensor-core
+ * kernels run is compared bit for bit too: variant 0 = generic kernels (as above), 1 = tiled
+ * tensor-core kernels, 2 = single-tile tensor-core kernels.  All three restate
+ * PositionEmbedding::set_qk_offset (Swin3D/src/attn/attn_utils.cuh:444-450).                 */
+int s3d_debug_crse_indices_variant(const float *n_coords, const int32_t *table_sizes_host, int D,
+                                   int H, int hd, int32_t first_pos, int32_t n, int variant,
+                                   int32_t *idx_out, void *stream);
+
+/* idx_out[i] = index of one signal dimension with L table rows for the coordinate pair
+ * (cq[i], ck[i]) (device arrays of n floats), through variant 0, 1 or 2; last_dim != 0 applies
+ * the clamp of the last signal dimension.  For sweeps over boundary values, NaN and infinities
+ * (Swin3D/src/attn/attn_utils.cuh:444-450).                                                   */
+int s3d_debug_crse_index_values(const float *cq, const float *ck, int64_t n, int L, int last_dim,
+                                int variant, int32_t *idx_out, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Window builder.  Replaces BasicLayer.get_map_pair / get_window_mapping / get_index01 and
  * sparse_self_attention (Swin3D/modules/swin3d_layers.py:713-822 and :76-150), i.e. the

@@ -26,6 +26,11 @@ int attn_scalar_forward(const AttnArgs &a, cudaStream_t st);
 int attn_scalar_backward(const AttnArgs &a, cudaStream_t st);
 int crse_indices_dump(const float *n_coords, const CrseMeta &meta, int first_pos, int n,
                       int32_t *out, cudaStream_t st);
+// crse_debug.cu: the index function of each kernel family (variant 0, 1, 2) on given inputs.
+int crse_indices_dump_variant(const float *n_coords, const CrseMeta &meta, int first_pos, int n, int variant,
+                              int32_t *out, cudaStream_t st);
+int crse_index_values(const float *cq, const float *ck, int64_t n, int L, int last, int variant, int32_t *out,
+                      cudaStream_t st);
 
 // Tensor-core path (attn_tc_fwd.cu): fp16 storage, head_dim 8, even head count.
 bool attn_tc_supported(const AttnArgs &a);

@@ -88,6 +88,38 @@ __device__ __forceinline__ int crse_index_fast(float cq, float ck, int L, bool l
     return (int)min(u, (unsigned)(last_dim ? L - 1 : L));
 }
 
+// The per-dimension constants of the cRSE index in the form the pair loops use them.  Passed as a
+// kernel parameter, so that they are constant-bank operands and cost no instruction:
+// half = (float)(L / 2), clamp = L (L - 1 for the last dimension, see crse_index in common.cuh).
+struct PairConsts {
+    float half[S3D_MAX_SIGNAL_DIMS];
+    uint32_t clamp[S3D_MAX_SIGNAL_DIMS];
+};
+
+__host__ inline PairConsts make_pair_consts(const CrseMeta &m)
+{
+    PairConsts pc{};
+    for (int d = 0; d < m.D; ++d) {
+        pc.half[d] = (float)(m.L[d] / 2);
+        pc.clamp[d] = (uint32_t)(d == m.D - 1 ? m.L[d] - 1 : m.L[d]);
+    }
+    return pc;
+}
+
+// crse_index_fast with the constants precomputed: same fp32 operations in the same order.
+__device__ __forceinline__ uint32_t crse_index_pc(float cq, float ck, float half, uint32_t clamp)
+{
+    return min(__float2uint_rz(__fadd_rn(__fsub_rn(cq, ck), half)), clamp);
+}
+
+// exp2 of a non-positive argument: one MUFU instruction (flushes results below 2^-126 to zero).
+__device__ __forceinline__ float ex2_approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // The coordinates of one staged voxel (rows of 12 floats, 16-byte aligned) as three broadcast
 // 16-byte loads instead of one 4-byte load per signal dimension.
 template <int D>

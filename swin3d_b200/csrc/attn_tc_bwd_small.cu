@@ -18,6 +18,20 @@
 namespace s3d {
 namespace tc {
 
+#ifdef S3D_PHASE_CLOCK
+__device__ unsigned int g_ablate_bwd;
+__device__ unsigned long long g_phase_cycles_bwd[16];
+#define S3D_KEEP(i) (!(ablate & (1u << (i))))
+#define S3D_PHASE_DECL long long ph_t = clock64(); unsigned long long ph_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define S3D_PHASE_MARK(i) if (threadIdx.x == 0) { const long long now = clock64(); ph_acc[i] += (unsigned long long)(now - ph_t); ph_t = now; }
+#define S3D_PHASE_FLUSH(base) if (threadIdx.x == 0) { for (int i = 0; i < 8; ++i) atomicAdd(&g_phase_cycles_bwd[(base) + i], ph_acc[i]); }
+#else
+#define S3D_KEEP(i) true
+#define S3D_PHASE_DECL
+#define S3D_PHASE_MARK(i)
+#define S3D_PHASE_FLUSH(base)
+#endif
+
 constexpr int SM_NWARP = 16;
 constexpr int SM_THREADS = SM_NWARP * 32;
 
@@ -128,11 +142,16 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
             }
     }
 
+    S3D_PHASE_DECL
+#ifdef S3D_PHASE_CLOCK
+    const unsigned ablate = g_ablate_bwd;
+#endif
     for (int64_t w = blockIdx.x; w < P.W; w += gridDim.x) {
         const int n = __ldg(P.w_sizes + w);
         if (n > QT) continue;                       // larger windows: two-sweep kernels
         const int base = __ldg(P.w2n + w);
         __syncthreads();
+        S3D_PHASE_MARK(0)
         // ---- stage the window: Q, K, V, dO rows, delta, lse, coordinates; clear the histograms ----------
         float cx[D];
 #pragma unroll
@@ -175,6 +194,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
             *reinterpret_cast<uint4 *>(s_q + st_arr * 512 + st_i * 16 + st_hf * 8) = st_val;
         }
         __syncthreads();
+        S3D_PHASE_MARK(1)
         const float xlse0 = s_lse[lane * 2], xlse1 = s_lse[lane * 2 + 1];
         float xdel0 = s_del[lane * 2], xdel1 = s_del[lane * 2 + 1];
         if (HD16) xdel0 = xdel1 = xdel0 + xdel1;   // delta of the whole head
@@ -183,13 +203,14 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
         for (int i = 0; i < NPU; ++i) {
             const int u = wid + SM_NWARP * i;
             const int tab = u / n_mt, mt = u - tab * n_mt;
+            if (!S3D_KEEP(0)) continue;
             if (tab == 0) project_unit<true>(ta[i], s_q, s_pq, mt, Rp, n, g, t);
             else if (tab == 1) project_unit<true>(ta[i], s_do, s_db, mt, Rp, n, g, t);
             else if (tab == 2) project_unit<false>(ta[i], s_k, s_pk, mt, Rp, n, g, t);
         }
         {
             const int mt = wid >> 3, j = wid & 7;     // key rows 16mt.., query columns 4j..
-            if (16 * mt < n && 4 * j < n) {
+            if (16 * mt < n && 4 * j < n && S3D_KEEP(1)) {
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
                     const __half *ysrc = (a == 0 ? s_k : s_v) + mt * 256;
@@ -209,12 +230,13 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
             }
         }
         __syncthreads();
+        S3D_PHASE_MARK(2)
         // ---- phase 1: two keys per warp, lane = query -----------------------------------------------------
 #pragma unroll
         for (int k2 = 0; k2 < 2; ++k2) {
             const int kk = 2 * wid + k2;
             uint4 ent = make_uint4(0u, 0u, 0u, 0u);
-            if (kk < n) {
+            if (kk < n && S3D_KEEP(2)) {
                 __half2 b0 = __float2half2_rn(0.f), b1 = b0, b2 = b0;
                 uint32_t w0 = 0, w1 = 0;
                 float ckv[D];
@@ -247,8 +269,9 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
             s_e[kk * ES + lane] = ent;
         }
         __syncthreads();
+        S3D_PHASE_MARK(3)
         // ---- phase 2 (lanes = queries): histQ += ds, histV += p ; warps 13-15: dK, dV, dQ pair GEMMs ----------
-        if (wid < D) {
+        if (wid < D && S3D_KEEP(3)) {
             const int d = wid;
             const int sh = IDX_BITS * (d % 5);
             const int rb = meta.rowbase[d];
@@ -272,15 +295,18 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
         for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int i = 0; i < 2; ++i) pg[h][i][0] = pg[h][i][1] = pg[h][i][2] = pg[h][i][3] = 0.f;
-        if (wid == 15) pair_gemm<1, false>(pg, s_e, s_k, n, g, t);        // dQ[q] += sum_k ds K[k]
+        if (!S3D_KEEP(4)) {}
+        else if (wid == 15) pair_gemm<1, false>(pg, s_e, s_k, n, g, t);        // dQ[q] += sum_k ds K[k]
         else if (wid == 14) pair_gemm<0, true>(pg, s_e, s_do, n, g, t);   // dV[k] += sum_q p  dO[q]
         else if (wid == 13) pair_gemm<1, true>(pg, s_e, s_q, n, g, t);    // dK[k] += sum_q ds Q[q]
         __syncthreads();
+        S3D_PHASE_MARK(4)
         // ---- query side: dTq, dTv ; dQ partials ; clear histK (= P_q storage) ------------------------------------
 #pragma unroll
         for (int i = 0; i < NPU; ++i) {
             const int u = wid + SM_NWARP * i;
             const int tab = u / n_mt, mt = u - tab * n_mt;
+            if (!S3D_KEEP(5)) continue;
             if (tab == 0) dt_unit(dt_acc[i], s_hq, s_q, mt, g, t);
             else if (tab == 1) dt_unit(dt_acc[i], s_hv, s_do, mt, g, t);
         }
@@ -292,7 +318,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
 #pragma unroll
         for (int i = 0; i < NHU; ++i) {
             const int v = wid + SM_NWARP * i;
-            if (v < n_mt) ht_unit(part, s_hq, tb[i], v, g, t);
+            if (v < n_mt && S3D_KEEP(6)) ht_unit(part, s_hq, tb[i], v, g, t);
         }
         for (int i = tid; i < L.R16 * QT / 4; i += SM_THREADS)
             reinterpret_cast<uint4 *>(s_hk)[i] = make_uint4(0, 0, 0, 0);
@@ -301,6 +327,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
         else if (wid == 14) store_part(s_red_dv, pg, g, t);
         else if (wid == 13) store_part(s_red_dk, pg, g, t);
         __syncthreads();
+        S3D_PHASE_MARK(5)
         {
             const int xx = tid >> 4, ch = tid & 15;
             if (xx < n) {
@@ -313,7 +340,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
             }
         }
         // ---- key side (lanes = keys): histK += ds, read column-wise from the pair array --------------------------
-        if (wid < D) {
+        if (wid < D && S3D_KEEP(7)) {
             const int d = wid;
             const int sh = IDX_BITS * (d % 5);
             const int rb = meta.rowbase[d];
@@ -333,12 +360,13 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
             }
         }
         __syncthreads();
+        S3D_PHASE_MARK(6)
         // ---- dTk ; dK partials ---------------------------------------------------------------------------------------
 #pragma unroll
         for (int i = 0; i < NPU; ++i) {
             const int u = wid + SM_NWARP * i;
             const int tab = u / n_mt, mt = u - tab * n_mt;
-            if (tab == 2) dt_unit(dt_acc[i], s_hk, s_k, mt, g, t);
+            if (tab == 2 && S3D_KEEP(5)) dt_unit(dt_acc[i], s_hk, s_k, mt, g, t);
         }
 #pragma unroll
         for (int h = 0; h < 2; ++h)
@@ -347,10 +375,11 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
 #pragma unroll
         for (int i = 0; i < NHU; ++i) {
             const int v = wid + SM_NWARP * i;
-            if (v >= n_mt && v < 2 * n_mt) ht_unit(part, s_hk, tb[i], v - n_mt, g, t);
+            if (v >= n_mt && v < 2 * n_mt && S3D_KEEP(6)) ht_unit(part, s_hk, tb[i], v - n_mt, g, t);
         }
         store_part(s_red + wid * 512, part, g, t);            // the previous contents were consumed before the last barrier
         __syncthreads();
+        S3D_PHASE_MARK(7)
         {
             const int xx = tid >> 4, ch = tid & 15;
             if (xx < n) {
@@ -361,6 +390,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
             }
         }
     }  // windows
+    S3D_PHASE_FLUSH(0)
 
     // ---- flush the table gradients of this block ---------------------------------------------------------------------
 #pragma unroll
@@ -404,6 +434,23 @@ static int launch_small(const SmallParams &p, const CrseMeta &meta, cudaStream_t
 }
 
 }  // namespace tc
+
+#ifdef S3D_PHASE_CLOCK
+extern "C" int s3d_debug_set_ablate_bwd(unsigned int mask)
+{
+    return cudaMemcpyToSymbol(tc::g_ablate_bwd, &mask, sizeof(mask)) == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
+}
+
+extern "C" int s3d_debug_phase_cycles_bwd(unsigned long long *out16, int reset)
+{
+    if (cudaMemcpyFromSymbol(out16, tc::g_phase_cycles_bwd, sizeof(unsigned long long) * 16) != cudaSuccess) return S3D_ERR_LAUNCH;
+    if (reset) {
+        unsigned long long z[16] = {0};
+        if (cudaMemcpyToSymbol(tc::g_phase_cycles_bwd, z, sizeof(z)) != cudaSuccess) return S3D_ERR_LAUNCH;
+    }
+    return S3D_OK;
+}
+#endif
 
 bool attn_tc_bwd_small_supported(const AttnArgs &a)
 {

@@ -48,6 +48,57 @@ __device__ __forceinline__ void project_unit(const uint32_t (&ta)[2][2], const _
     }
 }
 
+// Block-diagonal B fragments of a staged feature array ([32 voxels][16 halves] = two slots of 8
+// channels) for the both-slots-in-one-instruction projections: n-tile j covers voxels 4j..4j+3.
+// They depend on the window only, so a warp loads them once and uses them for all its units.
+__device__ __forceinline__ void load_feat_bfrag(uint32_t (&bf)[8][2], const __half *feat, int nvalid, int g, int t)
+{
+    const bool od = g & 1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t wv = 4 * j < nvalid
+            ? *reinterpret_cast<const uint32_t *>(feat + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t) : 0u;
+        bf[j][0] = od ? 0u : wv;
+        bf[j][1] = od ? wv : 0u;
+    }
+}
+
+// project_unit with the B fragments supplied by the caller.
+template <bool LANE_MAJOR>
+__device__ __forceinline__ void project_unit_b(const uint32_t (&ta)[2][2], const uint32_t (&bf)[8][2], uint32_t *dst,
+                                               int mt, int Rp, int nvalid, int g, int t)
+{
+    uint32_t d0[8], d1[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (4 * j < nvalid) {
+            mma_k16_h(d0[j], d1[j], ta[0][0], ta[0][1], ta[1][0], ta[1][1], bf[j][0], bf[j][1]);
+        } else {
+            d0[j] = 0u;
+            d1[j] = 0u;
+        }
+    }
+    if (LANE_MAJOR) {
+        uint32_t *r0 = dst + (mt * 16 + g) * QT + 4 * t;
+        const bool od = g & 1;
+        const int o0 = od ? 16 : 0, o1 = 16 - o0;
+        const uint4 a0 = make_uint4(d0[0], d0[2], d0[4], d0[6]), a1 = make_uint4(d0[1], d0[3], d0[5], d0[7]);
+        const uint4 b0 = make_uint4(d1[0], d1[2], d1[4], d1[6]), b1 = make_uint4(d1[1], d1[3], d1[5], d1[7]);
+        *reinterpret_cast<uint4 *>(r0 + o0) = od ? a1 : a0;
+        *reinterpret_cast<uint4 *>(r0 + o1) = od ? a0 : a1;
+        *reinterpret_cast<uint4 *>(r0 + 8 * QT + o0) = od ? b1 : b0;
+        *reinterpret_cast<uint4 *>(r0 + 8 * QT + o1) = od ? b0 : b1;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (4 * j < nvalid) {
+                uint32_t *p = dst + (4 * j + t) * Rp + mt * 16 + g;
+                p[0] = d0[j];
+                p[8] = d1[j];
+            }
+    }
+}
+
 // acc[head][m-tile] += A . B with A[m][kk] = field FIELD (0 = p, 1 = ds) of the pair entries and
 // B[kk][c] = rows[kk][head*8 + c].  TRANSPOSED = false: m = query, kk = key (entry [kk][m]);
 // TRANSPOSED = true: m = key, kk = query (entry [m][kk]).
@@ -68,6 +119,43 @@ __device__ __forceinline__ void pair_gemm(float (&acc)[2][2][4], const uint4 *s_
                         const int m = 16 * i + g + 8 * rr, ka = 16 * ks + 2 * t + 8 * kh;
                         const uint32_t u = TRANSPOSED ? e32[(m * ES + ka) * 4 + FIELD] : e32[(ka * ES + m) * 4 + FIELD];
                         const uint32_t w = TRANSPOSED ? e32[(m * ES + ka + 1) * 4 + FIELD] : e32[((ka + 1) * ES + m) * 4 + FIELD];
+                        fa[0][i][2 * kh + rr] = pack_lo(u, w);
+                        fa[1][i][2 * kh + rr] = pack_hi(u, w);
+                    }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t yb[2];
+#pragma unroll
+                for (int kh = 0; kh < 2; ++kh) {
+                    const int ka = 16 * ks + 2 * t + 8 * kh;
+                    yb[kh] = h2_as_u32(__halves2half2(rows[ka * 16 + h * 8 + g], rows[(ka + 1) * 16 + h * 8 + g]));
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+                    mma_k16(acc[h][i], fa[h][i][0], fa[h][i][1], fa[h][i][2], fa[h][i][3], yb[0], yb[1]);
+            }
+        }
+    }
+}
+
+// pair_gemm on a [32][ES] plane of 8-byte pair entries (two fields per entry).
+template <int FIELD, bool TRANSPOSED>
+__device__ __forceinline__ void pair_gemm2(float (&acc)[2][2][4], const uint2 *s_e, const __half *rows, int nk, int g, int t)
+{
+    const uint32_t *e32 = reinterpret_cast<const uint32_t *>(s_e);
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+        if (16 * ks < nk) {
+            uint32_t fa[2][2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int kh = 0; kh < 2; ++kh)
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const int m = 16 * i + g + 8 * rr, ka = 16 * ks + 2 * t + 8 * kh;
+                        const uint32_t u = TRANSPOSED ? e32[(m * ES + ka) * 2 + FIELD] : e32[(ka * ES + m) * 2 + FIELD];
+                        const uint32_t w = TRANSPOSED ? e32[(m * ES + ka + 1) * 2 + FIELD] : e32[((ka + 1) * ES + m) * 2 + FIELD];
                         fa[0][i][2 * kh + rr] = pack_lo(u, w);
                         fa[1][i][2 * kh + rr] = pack_hi(u, w);
                     }

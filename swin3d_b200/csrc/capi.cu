@@ -129,6 +129,28 @@ int s3d_debug_crse_indices(const float *n_coords, const int32_t *table_sizes_hos
     return crse_indices_dump(n_coords, m, first_pos, n, idx_out, static_cast<cudaStream_t>(stream));
 }
 
+int s3d_debug_crse_indices_variant(const float *n_coords, const int32_t *table_sizes_host, int D, int H,
+                                   int hd, int32_t first_pos, int32_t n, int variant, int32_t *idx_out,
+                                   void *stream)
+{
+    CrseMeta m;
+    const int rc = make_meta(table_sizes_host, D, H, hd, m);
+    if (rc != S3D_OK) return rc;
+    if (n < 0 || first_pos < 0 || variant < 0 || variant > 2) return S3D_ERR_BAD_ARG;
+    if (n == 0) return S3D_OK;
+    if (!n_coords || !idx_out) return S3D_ERR_BAD_ARG;
+    return crse_indices_dump_variant(n_coords, m, first_pos, n, variant, idx_out, static_cast<cudaStream_t>(stream));
+}
+
+int s3d_debug_crse_index_values(const float *cq, const float *ck, int64_t n, int L, int last_dim, int variant,
+                                int32_t *idx_out, void *stream)
+{
+    if (n < 0 || L < 1 || variant < 0 || variant > 2) return S3D_ERR_BAD_ARG;
+    if (n == 0) return S3D_OK;
+    if (!cq || !ck || !idx_out) return S3D_ERR_BAD_ARG;
+    return crse_index_values(cq, ck, n, L, last_dim, variant, idx_out, static_cast<cudaStream_t>(stream));
+}
+
 int64_t s3d_window_build_workspace_bytes(int64_t N) { return window_build_workspace_bytes(N); }
 
 int s3d_window_build(const int32_t *coords, const float *feats, int64_t N, int F, int stride, int ws,
