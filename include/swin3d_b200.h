@@ -39,6 +39,11 @@ const char *s3d_status_string(int status);
 /* Library/ABI version (major*1000 + minor). */
 int s3d_version(void);
 
+/* Text of the last CUDA runtime error behind an S3D_ERR_LAUNCH of the single-tile attention
+ * launchers ("no error" if none).  The reference reports launch errors through
+ * C10_CUDA_KERNEL_LAUNCH_CHECK (Swin3D/src/attn/self_attn_aio_fwd.cu:448).                   */
+const char *s3d_last_cuda_error_string(void);
+
 /* ---------------------------------------------------------------------------------------------
  * Fused cRSE window attention, forward.
  * Replaces the pair  attn_cuda.cal_max_coffs + attn_cuda.self_attn_forward  and the host-side

@@ -21,6 +21,7 @@ _i64 = ctypes.c_int64
 SIGNATURES = {
     "s3d_status_string": (ctypes.c_char_p, [_i32]),
     "s3d_version": (_i32, []),
+    "s3d_last_cuda_error_string": (ctypes.c_char_p, []),
     "s3d_attn_fwd": (_i32, [_c_void_p] * 6 + [_c_void_p, _i32] + [_c_void_p] * 4 +
                      [_i64, _i64, _i32, _i32, _i32, _c_void_p, _c_void_p, _c_void_p]),
     "s3d_attn_bwd": (_i32, [_c_void_p] * 6 + [_c_void_p, _i32] + [_c_void_p] * 4 +
@@ -70,4 +71,6 @@ def check(status: int, what: str):
         # shape/argument problems surface as ValueError, runtime problems as RuntimeError
         if status in (1, 2):
             raise ValueError(f"{what}: {msg}")
+        if status == 3:
+            msg += " (" + lib.s3d_last_cuda_error_string().decode() + ")"
         raise S3DError(f"{what}: {msg}")

@@ -21,6 +21,10 @@ struct AttnArgs {
     float *dtq, *dtk, *dtv;
 };
 
+// The last CUDA runtime error a launcher of this library ran into (cudaSuccess if none), for
+// s3d_last_cuda_error_string(); S3D_ERR_LAUNCH alone does not say which one it was.
+void note_cuda_error(cudaError_t e);
+
 // Generic path (attn_scalar.cu).
 int attn_scalar_forward(const AttnArgs &a, cudaStream_t st);
 int attn_scalar_backward(const AttnArgs &a, cudaStream_t st);

@@ -1,23 +1,37 @@
 // Backward of the cRSE window attention for windows of at most 32 voxels, tensor-core path
-// (fp16 storage, head_dim 8): ONE sweep per window instead of a query sweep plus a key sweep.
+// (fp16 storage): ONE sweep per window instead of a query sweep plus a key sweep.
 //
-// With the whole window in one 32 x 32 tile, the pair quantities (p, ds, packed cRSE indices) are
-// computed once (lanes = queries, 3*D look-ups per pair) and kept in shared memory as a
-// [key][query] array of 16-byte entries with a row stride of 33 entries, which can be read
-// conflict-free both by rows (lanes = queries) and by columns (lanes = keys).  The query-side
-// histograms (ds and p per query) are then built with lanes = queries, and the key-side histogram
-// (ds per key) with lanes = keys from the stored entries -- no second set of projections and
-// look-ups.  histK reuses the shared memory of the dead P_q projection, the cross-warp reduction
-// buffer that of dB.  All table products are GEMMs (mma.sync m16n8k16); the (table, row-tile) units
-// of the projection and table-gradient GEMMs are dealt round-robin to the 16 warps.
-// grid = (x, H/2), one block per SM.  Larger windows go through attn_tc_bwd.cu.
+// Block = 15 / 11 / 7 consumer warps (9 / 6 / 3 signal dimensions) + one producer warp, one block per SM, serving one head pair
+// (head_dim 8) or one head (head_dim 16) for the windows x, x + gridDim.x, ...  The producer walks
+// the block's windows ahead of the consumers: row numbers, coordinates and lse by plain loads, the
+// 32-byte Q, K, V, dO, O pieces of the voxels by the copy engine (cp.async.bulk) into the next
+// stage of shared memory; stages are handed over through "full" / "empty" mbarriers.
+// Per window (consumers, phases separated by a barrier among the consumer warps):
+//   GEMM    P_q = Tq.Q^T, dB = Tv.dO^T (lane-major), P_k = Tk.K^T (key-major); a warp owns consecutive
+//           (table, row tile) units, so it builds the B fragments of a feature array once per
+//           table; S0 = K.Q^T, dPV0 = V.dO^T                                        [tensor cores]
+//   scores  lane = query, keys dealt to the warps: D indices, 3*D look-ups, p = exp(s - lse),
+//           ds = p (dP - delta); written to four [key][query] planes (p, ds, idx 0-4, idx 5-8) with
+//           a row stride of 33, readable conflict-free by rows and by columns
+//   clear   the three histograms (they reuse the storage of P_q, dB, P_k)
+//   hist    warps 0..D-1: histQ += ds, histV += p for their dimension (lanes = queries);
+//           the next (D+1)/2 warps: histK += ds for two dimensions each (lanes = keys, planes read
+//           column-wise); one warp: dQ += dS.K, dK += dS^T.Q; one: dV = P^T.dO      [tensor cores]
+//   GEMM    dTq += histQ^T.Q, dTv += histV^T.dO, dTk += histK^T.K (accumulated in registers over
+//           all windows of the block), dQ += histQ.Tq, dK += histK.Tk                [tensor cores]
+//   store   reduce the partial dQ, dK over the warps, write dQ, dK, dV
+// grid = (x, H/2) or (x, H).  Larger windows go through attn_tc_bwd.cu.
 #include "attn_kernels.cuh"
 #include "attn_tc.cuh"
 #include "attn_tc_small.cuh"
+#include "async_stage.cuh"
 
 namespace s3d {
 namespace tc {
 
+// Debug build only (-DS3D_PHASE_CLOCK): cycles between the barriers of a window, summed over all
+// windows and blocks (s3d_debug_phase_cycles_bwd), and switches that skip pieces of the kernel so
+// that their cost can be measured (results are then wrong).  Compiled out otherwise.
 #ifdef S3D_PHASE_CLOCK
 __device__ unsigned int g_ablate_bwd;
 __device__ unsigned long long g_phase_cycles_bwd[16];
@@ -32,30 +46,41 @@ __device__ unsigned long long g_phase_cycles_bwd[16];
 #define S3D_PHASE_FLUSH(base)
 #endif
 
-constexpr int SM_NWARP = 16;
-constexpr int SM_THREADS = SM_NWARP * 32;
+constexpr int BS_STAGES = 2;
+
+// Consumer warps per block: D for the query-side histograms, (D+1)/2 for the key side, one or two
+// for the pair GEMMs, rounded so that consumers + producer fill whole groups of four warps (the
+// register file is split over the four schedulers of an SM).
+__host__ __device__ constexpr int bwd_small_warps(int D) { return D == 9 ? 15 : (D == 6 ? 11 : 7); }
 
 struct SmallSmem {
     int R16, Rp;
-    int off_pq, off_db, off_hq, off_hv, off_pk, off_e, off_rows, off_c, off_misc, total;
+    int off_pq, off_db, off_pk, off_s0, off_pl, off_rows, off_c, off_pg, off_ta, off_tb, off_misc, total;
 };
 
-__host__ __device__ inline SmallSmem make_small_layout(int R)
+__host__ __device__ inline SmallSmem make_small_layout(int R, int nw)
 {
     SmallSmem L;
     L.R16 = (R + 15) / 16 * 16;
     L.Rp = (L.R16 + 31) / 32 * 32 + 8;
     const int lane_arr = L.R16 * QT * 4;
     int off = 0;
-    L.off_pq = off; off += lane_arr;                               // P_q, later histK
-    L.off_db = off; off += lane_arr > 38912 ? lane_arr : 38912;    // dB, later the 38 KB reduction buffer
-    L.off_hq = off; off += lane_arr;
-    L.off_hv = off; off += lane_arr;
-    L.off_pk = off; off += 32 * L.Rp * 4;
-    L.off_e = off; off += 32 * ES * 16;
-    L.off_rows = off; off += 4 * 32 * 16 * 2;                      // Q, K, V, dO rows of the window
-    L.off_c = off; off += 32 * 12 * 4;
-    L.off_misc = off; off += 1024;
+    L.off_pq = off; off += lane_arr;                               // P_q, later histQ
+    L.off_db = off; off += lane_arr;                               // dB, later histV
+    const int pk = 32 * L.Rp * 4;
+    L.off_pk = off; off += pk > lane_arr ? pk : lane_arr;          // P_k, later histK
+    // S0/dPV0 and the planes are dead once the histograms exist; the partial dQ and dK of the hist.T
+    // warps (2 * (nw/2) * 2 KB) are written over them
+    const int part = 2 * (nw / 2) * 2048, s0pl = 32 * ES * 16 + 4 * 32 * ES * 4;
+    L.off_s0 = off; off += 32 * ES * 16;                           // S0 and dPV0 of every pair
+    L.off_pl = off; off += 4 * 32 * ES * 4;                        // planes p, ds, idx 0-4, idx 5-8
+    if (part > s0pl) off += part - s0pl;
+    L.off_rows = off; off += BS_STAGES * 5 * 32 * 16 * 2;          // Q, K, V, dO, O rows, per stage
+    L.off_c = off; off += BS_STAGES * 32 * 12 * 4;
+    L.off_pg = off; off += 3 * 2048;                               // dQ, dV, dK of the pair GEMMs
+    L.off_ta = off; off += 3 * (L.R16 / 16) * 512;                 // Tq, Tv, Tk as A fragments of the projections
+    L.off_tb = off; off += 2 * (L.R16 / 16) * 512;                 // Tq and Tk as B fragments of the hist.T products
+    L.off_misc = off; off += 2048;
     L.total = off;
     return L;
 }
@@ -72,344 +97,473 @@ struct SmallParams {
     int H;
 };
 
+// Set when a bounded wait of a kernel in this file ran out (it never should).
+__device__ int g_bwd_small_async_error;
+
 template <int D, int NPU /*projection + dT units per warp*/, int NHU /*hist.T units per warp*/, bool HD16>
-__global__ void __launch_bounds__(SM_THREADS, 1)
-attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
+__global__ void __launch_bounds__((bwd_small_warps(D) + 1) * 32, 1)
+attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts pc)
 {
+    constexpr int NW = bwd_small_warps(D);       // consumer warps
+    constexpr int NT = NW * 32;
+    constexpr int NKW = (D + 1) / 2;             // warps of the key-side histogram, two dimensions each
+    constexpr int GEMM_WARP = D + NKW;           // dQ and dK pair GEMMs
+    constexpr int DV_WARP = (D & 1) ? D + NKW - 1 : D + NKW + 1;   // dV: the key-side warp with one dimension, or a spare one
+    static_assert(DV_WARP < NW && GEMM_WARP < NW, "not enough warps");
+    constexpr int SG = NW / 2;                   // warps per hist.T side
+    constexpr int KPW = (QT + NW - 1) / NW;      // keys per warp in the score phase
     extern __shared__ __align__(16) unsigned char smem[];
-    const SmallSmem L = make_small_layout(meta.R);
+    const SmallSmem L = make_small_layout(meta.R, NW);
     uint32_t *s_pq = reinterpret_cast<uint32_t *>(smem + L.off_pq);
     uint32_t *s_db = reinterpret_cast<uint32_t *>(smem + L.off_db);
-    uint32_t *s_hq = reinterpret_cast<uint32_t *>(smem + L.off_hq);
-    uint32_t *s_hv = reinterpret_cast<uint32_t *>(smem + L.off_hv);
-    uint32_t *s_hk = s_pq;                                              // histK reuses P_q
     uint32_t *s_pk = reinterpret_cast<uint32_t *>(smem + L.off_pk);
-    uint4 *s_e = reinterpret_cast<uint4 *>(smem + L.off_e);             // [32][ES]
-    __half *s_q = reinterpret_cast<__half *>(smem + L.off_rows);        // [32][16] each
-    __half *s_k = s_q + 512, *s_v = s_q + 1024, *s_do = s_q + 1536;
-    float *s_c = reinterpret_cast<float *>(smem + L.off_c);             // [32][12]
-    float *s_lse = reinterpret_cast<float *>(smem + L.off_misc);        // [32][2]
-    float *s_del = s_lse + 64;                                          // [32][2]
-    int *s_row = reinterpret_cast<int *>(s_del + 64);                   // [32]
-    float *s_red = reinterpret_cast<float *>(smem + L.off_db);          // [16][32][16]  (dB is dead by then)
-    float *s_red_dk = s_red + SM_NWARP * 512;                           // [32][16]
-    float *s_red_dv = s_red_dk + 512;                                   // [32][16]
-    float *s_red_dq = s_red_dv + 512;                                   // [32][16]
+    uint32_t *s_hq = s_pq, *s_hv = s_db, *s_hk = s_pk;                  // the histograms reuse the projections
+    float4 *s_s0 = reinterpret_cast<float4 *>(smem + L.off_s0);         // [32][ES] (S0 h0, S0 h1, dPV0 h0, dPV0 h1)
+    uint32_t *s_P = reinterpret_cast<uint32_t *>(smem + L.off_pl);      // [32][ES] half2 p
+    uint32_t *s_DS = s_P + 32 * ES, *s_W0 = s_DS + 32 * ES, *s_W1 = s_W0 + 32 * ES;
+    __half *s_rows = reinterpret_cast<__half *>(smem + L.off_rows);     // [stage][Q,K,V,dO,O][32][16]
+    float *s_cs = reinterpret_cast<float *>(smem + L.off_c);            // [stage][32][12]
+    float *s_part = reinterpret_cast<float *>(smem + L.off_s0);         // [2][SG][32][16], over S0 and the planes
+    uint4 *s_ta = reinterpret_cast<uint4 *>(smem + L.off_ta);           // [Tq, Tv, Tk][row tile][lane]
+    float *s_pg = reinterpret_cast<float *>(smem + L.off_pg);           // [3][32][16]
+    uint4 *s_tb = reinterpret_cast<uint4 *>(smem + L.off_tb);           // [Tq, Tk][k-step][lane]
+    float *s_lses = reinterpret_cast<float *>(smem + L.off_misc);       // [stage][32][2]
+    float *s_del = s_lses + BS_STAGES * 64;                             // [32][2]
+    int *s_rowi = reinterpret_cast<int *>(s_del + 64);                  // [stage][32]
+    int *s_n = s_rowi + BS_STAGES * 32;                                 // [stage]
+    int *s_fail = s_n + BS_STAGES;
+    uint64_t *s_full = reinterpret_cast<uint64_t *>(smem + L.off_misc + 1536);   // [stage]
+    uint64_t *s_empty = s_full + BS_STAGES;
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
     const int hp = blockIdx.y, H = P.H;
     // head_dim 16: the block serves head hp; its two 8-channel halves stand in for the two heads
     const int HC = H * (HD16 ? 16 : 8), co = hp * 16;
+
+    if (tid == 0) {
+        for (int s = 0; s < BS_STAGES; ++s) {
+            mbar_init(s_full + s, 1);
+            mbar_init(s_empty + s, NW);
+        }
+        *s_fail = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    if (wid == NW) {
+        // ================================ producer warp ================================================
+        int64_t w = (int64_t)blockIdx.x - gridDim.x;
+        for (int it = 0;; ++it) {
+            int n = 0;
+            for (;;) {
+                const int64_t cand = w + (int64_t)(lane + 1) * gridDim.x;
+                const int nn = cand < P.W ? __ldg(P.w_sizes + cand) : 0;
+                const unsigned ok = __ballot_sync(0xffffffffu, nn >= 1 && nn <= QT);
+                if (ok) {
+                    const int j = __ffs(ok) - 1;
+                    w += (int64_t)(j + 1) * gridDim.x;
+                    n = __shfl_sync(0xffffffffu, nn, j);
+                    break;
+                }
+                w += (int64_t)32 * gridDim.x;
+                if (w + gridDim.x >= P.W) break;         // n stays 0: no more windows
+            }
+            int row = 0;
+            float c[D];
+            float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+            for (int d = 0; d < D; ++d) c[d] = 0.f;
+            if (n > 0) {
+                const int base = __ldg(P.w2n + w);
+                if (lane < n) {
+                    row = __ldg(P.n2n + base + lane);
+#pragma unroll
+                    for (int d = 0; d < D; ++d) c[d] = __ldg(P.n_coords + (int64_t)(base + lane) * D + d);
+                    if (HD16) {
+                        ls0 = ls1 = __ldg(P.lse + (int64_t)row * H + hp);
+                    } else {
+                        ls0 = __ldg(P.lse + (int64_t)row * H + 2 * hp);
+                        ls1 = __ldg(P.lse + (int64_t)row * H + 2 * hp + 1);
+                    }
+                }
+            }
+            const int s = it % BS_STAGES;
+            if (it >= BS_STAGES && !mbar_wait(s_empty + s, ((it / BS_STAGES) - 1) & 1)) {
+                g_bwd_small_async_error = 1;
+                n = 0;                                    // tell the consumers to stop
+            }
+            __half *rq = s_rows + s * 2560;
+            float *cs = s_cs + s * 384;
+#pragma unroll
+            for (int d = 0; d < D; ++d) cs[lane * 12 + d] = c[d];
+            s_rowi[s * 32 + lane] = row;
+            s_lses[s * 64 + lane * 2] = ls0;
+            s_lses[s * 64 + lane * 2 + 1] = ls1;
+            if (lane >= n) {                              // rows beyond the window are zero
+#pragma unroll
+                for (int a = 0; a < 5; ++a) {
+                    *reinterpret_cast<uint4 *>(rq + a * 512 + lane * 16) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4 *>(rq + a * 512 + lane * 16 + 8) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            if (lane == 0) s_n[s] = n;
+            async_proxy_fence();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_expect_tx(s_full + s, (unsigned)(n * 160));
+            __syncwarp();
+            if (lane < n) {
+                const int64_t off = (int64_t)row * HC + co;
+                bulk_copy_g2s(rq + lane * 16, P.q + off, 32, s_full + s);
+                bulk_copy_g2s(rq + 512 + lane * 16, P.k + off, 32, s_full + s);
+                bulk_copy_g2s(rq + 1024 + lane * 16, P.v + off, 32, s_full + s);
+                bulk_copy_g2s(rq + 1536 + lane * 16, P.dout + off, 32, s_full + s);
+                bulk_copy_g2s(rq + 2048 + lane * 16, P.o + off, 32, s_full + s);
+            }
+            if (n == 0) break;
+        }
+        return;
+    }
+
+    // ==================================== consumer warps ===============================================
+    const int g = lane >> 2, t = lane & 3;
     const int n_mt = L.R16 / 16, Rp = L.Rp;
     const int mypos = qpos(lane);
     constexpr float LOG2E = 1.4426950408889634f;
 
-    // ---- units of this warp: (table, row tile) for projections and table gradients -----------------
-    // unit u = wid + 16 i ; table = u / n_mt (0: Tq with Q, 1: Tv with dO, 2: Tk with K), tile = u % n_mt
-    uint32_t ta[NPU][2][2];
+    // (table, row tile) units of this warp, for the projections and the table gradients: u = wid NPU + i,
+    // table = u / n_mt: 0 = Tq with Q (-> P_q, dTq), 1 = Tv with dO (-> dB, dTv), 2 = Tk with K (-> P_k, dTk).
+    // Consecutive units mostly share their table, so the B fragments of a feature array are rebuilt
+    // only where the table changes.
+    // The A fragments of the table slices are built once per block and kept in shared memory (one
+    // 16-byte load per unit and window); the table-gradient accumulators stay in registers.
     float dt_acc[NPU][2][4];
 #pragma unroll
-    for (int i = 0; i < NPU; ++i) {
-        const int u = wid + SM_NWARP * i;
+    for (int i = 0; i < NPU; ++i)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) dt_acc[i][h][0] = dt_acc[i][h][1] = dt_acc[i][h][2] = dt_acc[i][h][3] = 0.f;
+    for (int u = wid; u < 3 * n_mt; u += NW) {
         const int tab = u / n_mt, mt = u - tab * n_mt;
         const __half *T = tab == 0 ? P.tq : (tab == 1 ? P.tv : P.tk);
+        const int r0 = table_row(meta, mt * 16 + g), r1 = table_row(meta, mt * 16 + g + 8);
+        uint32_t f[2][2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int r0 = table_row(meta, mt * 16 + g), r1 = table_row(meta, mt * 16 + g + 8);
-            const bool ok = tab < 3;
-            ta[i][h][0] = (ok && r0 >= 0) ? *reinterpret_cast<const uint32_t *>(T + (int64_t)r0 * HC + co + h * 8 + 2 * t) : 0u;
-            ta[i][h][1] = (ok && r1 >= 0) ? *reinterpret_cast<const uint32_t *>(T + (int64_t)r1 * HC + co + h * 8 + 2 * t) : 0u;
-            dt_acc[i][h][0] = dt_acc[i][h][1] = dt_acc[i][h][2] = dt_acc[i][h][3] = 0.f;
+            f[h][0] = r0 >= 0 ? *reinterpret_cast<const uint32_t *>(T + (int64_t)r0 * HC + co + h * 8 + 2 * t) : 0u;
+            f[h][1] = r1 >= 0 ? *reinterpret_cast<const uint32_t *>(T + (int64_t)r1 * HC + co + h * 8 + 2 * t) : 0u;
         }
+        s_ta[u * 32 + lane] = make_uint4(f[0][0], f[0][1], f[1][0], f[1][1]);
     }
-    // hist.T units: v = wid + 16 i ; side = v / n_mt (0: histQ.Tq -> dQ, 1: histK.Tk -> dK), k-step = v % n_mt
-    uint32_t tb[NHU][2][2];
-#pragma unroll
-    for (int i = 0; i < NHU; ++i) {
-        const int v = wid + SM_NWARP * i;
-        const int side = v / n_mt, ks = v - side * n_mt;
-        const __half *T = side == 0 ? P.tq : P.tk;
+    // hist.T side of this warp: 0 = histQ.Tq -> dQ (warps [0, SG)), 1 = histK.Tk -> dK (warps [SG, 2 SG));
+    // its k-steps are ws2 + SG i.  The B fragments of Tq and Tk for these products are built once per
+    // block and kept in shared memory (one 16-byte load per unit instead of resident registers).
+    const int side = wid / SG, ws2 = wid - side * SG;
+    for (int u = wid; u < 2 * n_mt; u += NW) {
+        const int sd = u / n_mt, ks = u - sd * n_mt;
+        const __half *T = sd == 0 ? P.tq : P.tk;
+        uint32_t f[2][2];
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const int ra = table_row(meta, ks * 16 + ht_krow(t, half, 0)), rb = table_row(meta, ks * 16 + ht_krow(t, half, 1));
-                const bool ok = side < 2;
-                const __half lo = (ok && ra >= 0) ? T[(int64_t)ra * HC + co + h * 8 + g] : __float2half(0.f);
-                const __half hi = (ok && rb >= 0) ? T[(int64_t)rb * HC + co + h * 8 + g] : __float2half(0.f);
-                tb[i][h][half] = h2_as_u32(__halves2half2(lo, hi));
+                const int ra = table_row(meta, ks * 16 + ht_krow(t, half, 0));
+                const int rb = table_row(meta, ks * 16 + ht_krow(t, half, 1));
+                const __half lo = ra >= 0 ? T[(int64_t)ra * HC + co + h * 8 + g] : __float2half(0.f);
+                const __half hi = rb >= 0 ? T[(int64_t)rb * HC + co + h * 8 + g] : __float2half(0.f);
+                f[h][half] = h2_as_u32(__halves2half2(lo, hi));
             }
+        s_tb[u * 32 + lane] = make_uint4(f[0][0], f[0][1], f[1][0], f[1][1]);
     }
-
     S3D_PHASE_DECL
 #ifdef S3D_PHASE_CLOCK
     const unsigned ablate = g_ablate_bwd;
 #endif
-    for (int64_t w = blockIdx.x; w < P.W; w += gridDim.x) {
-        const int n = __ldg(P.w_sizes + w);
-        if (n > QT) continue;                       // larger windows: two-sweep kernels
-        const int base = __ldg(P.w2n + w);
-        __syncthreads();
+    for (int it = 0;; ++it) {
+        const int s = it % BS_STAGES;
+        if (!mbar_wait(s_full + s, (it / BS_STAGES) & 1)) {
+            *s_fail = 1;
+            g_bwd_small_async_error = 2;
+        }
+        consumer_sync<NT>();          // the previous window's stores are over; the flag is settled
         S3D_PHASE_MARK(0)
-        // ---- stage the window: Q, K, V, dO rows, delta, lse, coordinates; clear the histograms ----------
+        const int n = s_n[s];
+        if (n == 0 || *s_fail) break;
+        const __half *s_q = s_rows + s * 2560, *s_k = s_q + 512, *s_v = s_q + 1024, *s_do = s_q + 1536, *s_o = s_q + 2048;
+        const float *s_c = s_cs + s * 384;
+        const int *s_row = s_rowi + s * 32;
+        const float *s_lse = s_lses + s * 64;
         float cx[D];
+        load_coords12<D>(s_c + lane * 12, cx);
+        if (tid < 64) {               // delta[voxel][slot] = sum_c dO . O
+            const int i = tid >> 1, h = tid & 1;
+            const uint4 a = *reinterpret_cast<const uint4 *>(s_do + i * 16 + h * 8);
+            const uint4 b = *reinterpret_cast<const uint4 *>(s_o + i * 16 + h * 8);
+            const __half2 *a2 = reinterpret_cast<const __half2 *>(&a), *b2 = reinterpret_cast<const __half2 *>(&b);
+            float acc = 0.f;
 #pragma unroll
-        for (int d = 0; d < D; ++d) {
-            cx[d] = lane < n ? __ldg(P.n_coords + (int64_t)(base + lane) * D + d) : 0.f;
-            if (wid == 0) s_c[lane * 12 + d] = cx[d];
-        }
-        // the global loads are issued first and consumed after the histograms have been cleared, so
-        // that their latency overlaps the clearing
-        const int st_i = tid >> 3, st_arr = (tid >> 1) & 3, st_hf = tid & 1;
-        const bool st_act = tid < 256 && st_i < n;
-        uint4 st_val = make_uint4(0, 0, 0, 0), st_o = make_uint4(0, 0, 0, 0);
-        float st_lse = 0.f;
-        int st_row = 0;
-        if (st_act) {
-            st_row = __ldg(P.n2n + base + st_i);
-            const __half *src = st_arr == 0 ? P.q : (st_arr == 1 ? P.k : (st_arr == 2 ? P.v : P.dout));
-            st_val = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)st_row * HC + co + st_hf * 8));
-            if (st_arr == 3) {
-                st_o = __ldg(reinterpret_cast<const uint4 *>(P.o + (int64_t)st_row * HC + co + st_hf * 8));
-                st_lse = __ldg(P.lse + (int64_t)st_row * H + (HD16 ? hp : 2 * hp + st_hf));
+            for (int c = 0; c < 4; ++c) {
+                const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
+                acc += fa.x * fb.x + fa.y * fb.y;
             }
+            s_del[tid] = acc;
         }
-        for (int i = tid; i < 2 * L.R16 * QT / 4; i += SM_THREADS)
-            reinterpret_cast<uint4 *>(s_hq)[i] = make_uint4(0, 0, 0, 0);     // histQ and histV are adjacent
-        if (tid < 256) {
-            if (st_act && st_arr == 0 && st_hf == 0) s_row[st_i] = st_row;
-            if (st_arr == 3) {
-                const __half2 *a2 = reinterpret_cast<const __half2 *>(&st_val);
-                const __half2 *b2 = reinterpret_cast<const __half2 *>(&st_o);
-                float acc = 0.f;
+        // ---- projections P_q, dB (lane-major), P_k (key-major); S0 = K.Q^T and dPV0 = V.dO^T -----------------
+        if (S3D_KEEP(0)) {
+            uint32_t bf[8][2];
+            int have = -1;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
-                    acc += fa.x * fb.x + fa.y * fb.y;
+            for (int i = 0; i < NPU; ++i) {
+                const int u = wid * NPU + i, tab = u / n_mt, mt = u - tab * n_mt;
+                if (tab < 3) {
+                    if (tab != have) {
+                        load_feat_bfrag(bf, tab == 0 ? s_q : (tab == 1 ? s_do : s_k), n, g, t);
+                        have = tab;
+                    }
+                    const uint4 f = s_ta[u * 32 + lane];
+                    const uint32_t taf[2][2] = {{f.x, f.y}, {f.z, f.w}};
+                    if (tab == 0) project_unit_b<true>(taf, bf, s_pq, mt, Rp, n, g, t);
+                    else if (tab == 1) project_unit_b<true>(taf, bf, s_db, mt, Rp, n, g, t);
+                    else project_unit_b<false>(taf, bf, s_pk, mt, Rp, n, g, t);
                 }
-                s_del[st_i * 2 + st_hf] = acc;         // zero beyond the window (both rows are zero there)
-                s_lse[st_i * 2 + st_hf] = st_lse;
             }
-            *reinterpret_cast<uint4 *>(s_q + st_arr * 512 + st_i * 16 + st_hf * 8) = st_val;
         }
-        __syncthreads();
+        for (int u = wid; u < 32 && S3D_KEEP(1); u += NW) {
+            const int a = u >> 4, mt = (u >> 3) & 1, j = u & 7;     // key rows 16mt.., query columns 4j..
+            if (16 * mt < n && 4 * j < n) {
+                const __half *ysrc = (a == 0 ? s_k : s_v) + mt * 256;
+                const __half *xsrc = a == 0 ? s_q : s_do;
+                const uint32_t wv = *reinterpret_cast<const uint32_t *>(xsrc + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
+                const uint32_t a0 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 2 * t);
+                const uint32_t a1 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 2 * t);
+                const uint32_t a2 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 8 + 2 * t);
+                const uint32_t a3 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 8 + 2 * t);
+                float c[4];
+                mma_k16_z(c, a0, a1, a2, a3, (g & 1) ? 0u : wv, (g & 1) ? wv : 0u);
+                float *e0 = reinterpret_cast<float *>(s_s0 + (16 * mt + g) * ES + 4 * j + t) + 2 * a;
+                float *e1 = reinterpret_cast<float *>(s_s0 + (16 * mt + g + 8) * ES + 4 * j + t) + 2 * a;
+                *reinterpret_cast<float2 *>(e0) = make_float2(c[0], c[1]);
+                *reinterpret_cast<float2 *>(e1) = make_float2(c[2], c[3]);
+            }
+        }
+        consumer_sync<NT>();
         S3D_PHASE_MARK(1)
-        const float xlse0 = s_lse[lane * 2], xlse1 = s_lse[lane * 2 + 1];
-        float xdel0 = s_del[lane * 2], xdel1 = s_del[lane * 2 + 1];
-        if (HD16) xdel0 = xdel1 = xdel0 + xdel1;   // delta of the whole head
-        // ---- projections P_q, dB (lane-major), P_k (tile-major); S0 = K.Q^T and dPV0 = V.dO^T ---------------
-#pragma unroll
-        for (int i = 0; i < NPU; ++i) {
-            const int u = wid + SM_NWARP * i;
-            const int tab = u / n_mt, mt = u - tab * n_mt;
-            if (!S3D_KEEP(0)) continue;
-            if (tab == 0) project_unit<true>(ta[i], s_q, s_pq, mt, Rp, n, g, t);
-            else if (tab == 1) project_unit<true>(ta[i], s_do, s_db, mt, Rp, n, g, t);
-            else if (tab == 2) project_unit<false>(ta[i], s_k, s_pk, mt, Rp, n, g, t);
-        }
+        // ---- scores: keys wid, wid + NW ; lane = query -------------------------------------------------------
         {
-            const int mt = wid >> 3, j = wid & 7;     // key rows 16mt.., query columns 4j..
-            if (16 * mt < n && 4 * j < n && S3D_KEEP(1)) {
+            const float xlse0 = s_lse[lane * 2] * LOG2E, xlse1 = s_lse[lane * 2 + 1] * LOG2E;
+            float xdel0 = s_del[lane * 2], xdel1 = s_del[lane * 2 + 1];
+            if (HD16) xdel0 = xdel1 = xdel0 + xdel1;   // delta of the whole head
+            const uint32_t *pq_lane = s_pq + mypos, *db_lane = s_db + mypos;
 #pragma unroll
-                for (int a = 0; a < 2; ++a) {
-                    const __half *ysrc = (a == 0 ? s_k : s_v) + mt * 256;
-                    const __half *xsrc = a == 0 ? s_q : s_do;
-                    const uint32_t wv = *reinterpret_cast<const uint32_t *>(xsrc + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
-                    const uint32_t a0 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 2 * t);
-                    const uint32_t a1 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 2 * t);
-                    const uint32_t a2 = *reinterpret_cast<const uint32_t *>(ysrc + g * 16 + 8 + 2 * t);
-                    const uint32_t a3 = *reinterpret_cast<const uint32_t *>(ysrc + (g + 8) * 16 + 8 + 2 * t);
-                    float c[4];
-                    mma_k16_z(c, a0, a1, a2, a3, (g & 1) ? 0u : wv, (g & 1) ? wv : 0u);
-                    float *e0 = reinterpret_cast<float *>(s_e + (16 * mt + g) * ES + 4 * j + t) + 2 * a;
-                    float *e1 = reinterpret_cast<float *>(s_e + (16 * mt + g + 8) * ES + 4 * j + t) + 2 * a;
-                    *reinterpret_cast<float2 *>(e0) = make_float2(c[0], c[1]);
-                    *reinterpret_cast<float2 *>(e1) = make_float2(c[2], c[3]);
+            for (int j = 0; j < KPW; ++j) {
+                const int kk = wid + NW * j;
+                if (kk < QT) {
+                    uint32_t pw = 0u, dsw = 0u, w0 = 0u, w1 = 0u;     // zero for keys beyond the window
+                    if (kk < n && S3D_KEEP(2)) {
+                        float ck[D];
+                        load_coords12<D>(s_c + kk * 12, ck);
+                        const uint32_t *pk_row = s_pk + kk * Rp;
+                        __half2 b0 = __float2half2_rn(0.f), b1 = b0, b2 = b0;
+#pragma unroll
+                        for (int d = 0; d < D; ++d) {
+                            const uint32_t idx = crse_index_pc(cx[d], ck[d], pc.half[d], pc.clamp[d]);
+                            const uint32_t row = meta.rowbase[d] + idx;
+                            b0 = __hadd2(b0, u32_as_h2(pq_lane[row * QT]));
+                            b1 = __hadd2(b1, u32_as_h2(pk_row[row]));
+                            b2 = __hadd2(b2, u32_as_h2(db_lane[row * QT]));
+                            if (d < 5) w0 |= idx << (IDX_BITS * d);
+                            else w1 |= idx << (IDX_BITS * (d - 5));
+                        }
+                        const float4 in = s_s0[kk * ES + lane];          // S0 (h0,h1), dPV0 (h0,h1)
+                        const float2 bs = __half22float2(__hadd2(b0, b1));
+                        const float2 bd = __half22float2(b2);
+                        float sc0 = in.x + bs.x, sc1 = in.y + bs.y, dq0 = in.z + bd.x, dq1 = in.w + bd.y;
+                        if (HD16) { sc0 = sc1 = sc0 + sc1; dq0 = dq1 = dq0 + dq1; }   // halves of one head add up
+                        float p0 = ex2_approx(fmaf(sc0, LOG2E, -xlse0));
+                        float p1 = ex2_approx(fmaf(sc1, LOG2E, -xlse1));
+                        float ds0 = p0 * (dq0 - xdel0);
+                        float ds1 = p1 * (dq1 - xdel1);
+                        if (lane >= n) { p0 = 0.f; p1 = 0.f; ds0 = 0.f; ds1 = 0.f; }
+                        pw = h2_as_u32(__floats2half2_rn(p0, p1));
+                        dsw = h2_as_u32(__floats2half2_rn(ds0, ds1));
+                    }
+                    s_P[kk * ES + lane] = pw;
+                    s_DS[kk * ES + lane] = dsw;
+                    s_W0[kk * ES + lane] = w0;
+                    s_W1[kk * ES + lane] = w1;
                 }
             }
         }
-        __syncthreads();
+        consumer_sync<NT>();
         S3D_PHASE_MARK(2)
-        // ---- phase 1: two keys per warp, lane = query -----------------------------------------------------
-#pragma unroll
-        for (int k2 = 0; k2 < 2; ++k2) {
-            const int kk = 2 * wid + k2;
-            uint4 ent = make_uint4(0u, 0u, 0u, 0u);
-            if (kk < n && S3D_KEEP(2)) {
-                __half2 b0 = __float2half2_rn(0.f), b1 = b0, b2 = b0;
-                uint32_t w0 = 0, w1 = 0;
-                float ckv[D];
-                load_coords12<D>(s_c + kk * 12, ckv);
-#pragma unroll
-                for (int d = 0; d < D; ++d) {
-                    const int idx = crse_index_fast(cx[d], ckv[d], meta.L[d], d == D - 1);
-                    const int row = meta.rowbase[d] + idx;
-                    b0 = __hadd2(b0, u32_as_h2(s_pq[row * QT + mypos]));
-                    b1 = __hadd2(b1, u32_as_h2(s_pk[kk * Rp + row]));
-                    b2 = __hadd2(b2, u32_as_h2(s_db[row * QT + mypos]));
-                    if (d < 5) w0 |= (uint32_t)idx << (IDX_BITS * d);
-                    else w1 |= (uint32_t)idx << (IDX_BITS * (d - 5));
-                }
-                const float4 in = *reinterpret_cast<const float4 *>(s_e + kk * ES + lane);   // S0 (h0,h1), dPV0 (h0,h1)
-                const float2 bs = __half22float2(__hadd2(b0, b1));
-                const float2 bd = __half22float2(b2);
-                float sc0 = in.x + bs.x, sc1 = in.y + bs.y, dq0 = in.z + bd.x, dq1 = in.w + bd.y;
-                if (HD16) { sc0 = sc1 = sc0 + sc1; dq0 = dq1 = dq0 + dq1; }   // halves of one head add up
-                float p0 = exp2f((sc0 - xlse0) * LOG2E);
-                float p1 = exp2f((sc1 - xlse1) * LOG2E);
-                float ds0 = p0 * (dq0 - xdel0);
-                float ds1 = p1 * (dq1 - xdel1);
-                if (lane >= n) { p0 = 0.f; p1 = 0.f; ds0 = 0.f; ds1 = 0.f; }
-                ent.x = h2_as_u32(__floats2half2_rn(p0, p1));
-                ent.y = h2_as_u32(__floats2half2_rn(ds0, ds1));
-                ent.z = w0;
-                ent.w = w1;
-            }
-            s_e[kk * ES + lane] = ent;
-        }
-        __syncthreads();
+        // ---- clear the three histograms (P_q, dB, P_k are dead) ------------------------------------------------
+        for (int i = tid; i < 3 * L.R16 * QT / 4; i += NT)
+            reinterpret_cast<uint4 *>(s_hq)[i] = make_uint4(0, 0, 0, 0);     // the three arrays are adjacent
+        consumer_sync<NT>();
         S3D_PHASE_MARK(3)
-        // ---- phase 2 (lanes = queries): histQ += ds, histV += p ; warps 13-15: dK, dV, dQ pair GEMMs ----------
-        if (wid < D && S3D_KEEP(3)) {
-            const int d = wid;
-            const int sh = IDX_BITS * (d % 5);
-            const int rb = meta.rowbase[d];
-            uint32_t *cell = s_hq + mypos;
-            for (int k4 = 0; k4 < n; k4 += 4) {
-                uint32_t vals[2][4];
-                int off[1][4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint4 e = s_e[(k4 + j) * ES + lane];        // zero entries beyond the window
-                    vals[0][j] = e.y;
-                    vals[1][j] = e.x;
-                    const int idx = ((d < 5 ? e.z : e.w) >> sh) & ((1 << IDX_BITS) - 1);
-                    off[0][j] = (rb + idx) * QT;
+        // ---- histograms and pair GEMMs ------------------------------------------------------------------------
+        if (wid < D) {
+            // histQ += ds, histV += p ; lanes = queries, two keys per step
+            if (S3D_KEEP(3)) {
+                const int d = wid;
+                const bool lo = d < 5;
+                const int sh = IDX_BITS * (lo ? d : d - 5);
+                const uint32_t *pcol = s_P + lane, *dcol = s_DS + lane, *wcol = (lo ? s_W0 : s_W1) + lane;
+                uint32_t *cell = s_hq + meta.rowbase[d] * QT + mypos;
+                const int hv = L.R16 * QT;                 // histV follows histQ
+                uint32_t p0 = pcol[0], d0 = dcol[0], x0 = wcol[0];
+                uint32_t p1 = pcol[ES], d1 = dcol[ES], x1 = wcol[ES];
+                int kk = 0;
+                for (; kk + 1 < n; kk += 2) {
+                    const uint32_t i0 = (x0 >> sh) & ((1u << IDX_BITS) - 1u), i1 = (x1 >> sh) & ((1u << IDX_BITS) - 1u);
+                    uint32_t *a0 = cell + i0 * QT, *a1 = cell + i1 * QT;
+                    const uint32_t q0 = a0[0], v0 = a0[hv], q1 = a1[0], v1 = a1[hv];
+                    const uint32_t cp0 = p0, cd0 = d0, cp1 = p1, cd1 = d1;
+                    const int k2 = min(kk + 2, QT - 1) * ES, k3 = min(kk + 3, QT - 1) * ES;
+                    p0 = pcol[k2]; d0 = dcol[k2]; x0 = wcol[k2];
+                    p1 = pcol[k3]; d1 = dcol[k3]; x1 = wcol[k3];
+                    const bool same = a1 == a0;
+                    const __half2 sq0 = __hadd2(u32_as_h2(q0), u32_as_h2(cd0));
+                    const __half2 sv0 = __hadd2(u32_as_h2(v0), u32_as_h2(cp0));
+                    const __half2 sq1 = __hadd2(same ? sq0 : u32_as_h2(q1), u32_as_h2(cd1));
+                    const __half2 sv1 = __hadd2(same ? sv0 : u32_as_h2(v1), u32_as_h2(cp1));
+                    a0[0] = h2_as_u32(sq0); a0[hv] = h2_as_u32(sv0);
+                    a1[0] = h2_as_u32(sq1); a1[hv] = h2_as_u32(sv1);
                 }
-                hist_add4<1, 2>(cell, L.R16 * QT, off, vals, n - k4);
+                if (kk < n) {
+                    const uint32_t i0 = (x0 >> sh) & ((1u << IDX_BITS) - 1u);
+                    uint32_t *a0 = cell + i0 * QT;
+                    a0[0] = h2_as_u32(__hadd2(u32_as_h2(a0[0]), u32_as_h2(d0)));
+                    a0[hv] = h2_as_u32(__hadd2(u32_as_h2(a0[hv]), u32_as_h2(p0)));
+                }
+            }
+        } else if (wid < D + NKW) {
+            // histK += ds ; lanes = keys, the planes are read column-wise, two queries per step
+            for (int d = 2 * (wid - D); d < 2 * (wid - D) + 2 && d < D && S3D_KEEP(7); ++d) {
+                const bool lo = d < 5;
+                const int sh = IDX_BITS * (lo ? d : d - 5);
+                const uint32_t *drow = s_DS + lane * ES, *wrow = (lo ? s_W0 : s_W1) + lane * ES;
+                uint32_t *cell = s_hk + meta.rowbase[d] * QT + mypos;
+                uint32_t d0 = drow[0], x0 = wrow[0], d1 = drow[1], x1 = wrow[1];
+                int qq = 0;
+                for (; qq + 1 < n; qq += 2) {
+                    const uint32_t i0 = (x0 >> sh) & ((1u << IDX_BITS) - 1u), i1 = (x1 >> sh) & ((1u << IDX_BITS) - 1u);
+                    uint32_t *a0 = cell + i0 * QT, *a1 = cell + i1 * QT;
+                    const uint32_t c0 = a0[0], c1 = a1[0];
+                    const uint32_t cd0 = d0, cd1 = d1;
+                    const int q2 = min(qq + 2, QT - 1), q3 = min(qq + 3, QT - 1);
+                    d0 = drow[q2]; x0 = wrow[q2];
+                    d1 = drow[q3]; x1 = wrow[q3];
+                    const __half2 s0 = __hadd2(u32_as_h2(c0), u32_as_h2(cd0));
+                    const __half2 s1 = __hadd2(a1 == a0 ? s0 : u32_as_h2(c1), u32_as_h2(cd1));
+                    a0[0] = h2_as_u32(s0);
+                    a1[0] = h2_as_u32(s1);
+                }
+                if (qq < n) {
+                    const uint32_t i0 = (x0 >> sh) & ((1u << IDX_BITS) - 1u);
+                    uint32_t *a0 = cell + i0 * QT;
+                    a0[0] = h2_as_u32(__hadd2(u32_as_h2(a0[0]), u32_as_h2(d0)));
+                }
             }
         }
-        float pg[2][2][4];
+        if (wid == GEMM_WARP || wid == DV_WARP) {
+            float pg[2][2][4];
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+            for (int a = 0; a < 2; ++a) {
+                if (a == 1 && wid != GEMM_WARP) break;
 #pragma unroll
-            for (int i = 0; i < 2; ++i) pg[h][i][0] = pg[h][i][1] = pg[h][i][2] = pg[h][i][3] = 0.f;
-        if (!S3D_KEEP(4)) {}
-        else if (wid == 15) pair_gemm<1, false>(pg, s_e, s_k, n, g, t);        // dQ[q] += sum_k ds K[k]
-        else if (wid == 14) pair_gemm<0, true>(pg, s_e, s_do, n, g, t);   // dV[k] += sum_q p  dO[q]
-        else if (wid == 13) pair_gemm<1, true>(pg, s_e, s_q, n, g, t);    // dK[k] += sum_q ds Q[q]
-        __syncthreads();
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) pg[h][i][0] = pg[h][i][1] = pg[h][i][2] = pg[h][i][3] = 0.f;
+                if (S3D_KEEP(4)) {
+                    if (wid == DV_WARP) pair_gemm1<true>(pg, s_P, s_do, n, g, t);          // dV[k]  = sum_q p  dO[q]
+                    else if (a == 0) pair_gemm1<false>(pg, s_DS, s_k, n, g, t);            // dQ[q] += sum_k ds K[k]
+                    else pair_gemm1<true>(pg, s_DS, s_q, n, g, t);                         // dK[k] += sum_q ds Q[q]
+                }
+                store_part(s_pg + (wid == DV_WARP ? 1 : 2 * a) * 512, pg, g, t);
+            }
+        }
+        consumer_sync<NT>();
         S3D_PHASE_MARK(4)
-        // ---- query side: dTq, dTv ; dQ partials ; clear histK (= P_q storage) ------------------------------------
+        // ---- dTq, dTv, dTk ; dQ += histQ.Tq, dK += histK.Tk -------------------------------------------------------
+        if (S3D_KEEP(5)) {
+            uint32_t xb[2][2][2];
+            int have = -1;
 #pragma unroll
-        for (int i = 0; i < NPU; ++i) {
-            const int u = wid + SM_NWARP * i;
-            const int tab = u / n_mt, mt = u - tab * n_mt;
-            if (!S3D_KEEP(5)) continue;
-            if (tab == 0) dt_unit(dt_acc[i], s_hq, s_q, mt, g, t);
-            else if (tab == 1) dt_unit(dt_acc[i], s_hv, s_do, mt, g, t);
-        }
-        float part[2][2][4];
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int i = 0; i < 2; ++i) part[h][i][0] = part[h][i][1] = part[h][i][2] = part[h][i][3] = 0.f;
-#pragma unroll
-        for (int i = 0; i < NHU; ++i) {
-            const int v = wid + SM_NWARP * i;
-            if (v < n_mt && S3D_KEEP(6)) ht_unit(part, s_hq, tb[i], v, g, t);
-        }
-        for (int i = tid; i < L.R16 * QT / 4; i += SM_THREADS)
-            reinterpret_cast<uint4 *>(s_hk)[i] = make_uint4(0, 0, 0, 0);
-        store_part(s_red + wid * 512, part, g, t);            // dB (aliased by s_red) is dead since phase 1
-        if (wid == 15) store_part(s_red_dq, pg, g, t);
-        else if (wid == 14) store_part(s_red_dv, pg, g, t);
-        else if (wid == 13) store_part(s_red_dk, pg, g, t);
-        __syncthreads();
-        S3D_PHASE_MARK(5)
-        {
-            const int xx = tid >> 4, ch = tid & 15;
-            if (xx < n) {
-                float a = s_red_dq[xx * 16 + ch];
-#pragma unroll
-                for (int ww = 0; ww < SM_NWARP; ++ww) a += s_red[ww * 512 + xx * 16 + ch];
-                const int64_t row = s_row[xx];
-                P.dq[row * HC + co + ch] = __float2half_rn(a);
-                P.dv[row * HC + co + ch] = __float2half_rn(s_red_dv[xx * 16 + ch]);
-            }
-        }
-        // ---- key side (lanes = keys): histK += ds, read column-wise from the pair array --------------------------
-        if (wid < D && S3D_KEEP(7)) {
-            const int d = wid;
-            const int sh = IDX_BITS * (d % 5);
-            const int rb = meta.rowbase[d];
-            uint32_t *cell = s_hk + mypos;
-            for (int q4 = 0; q4 < n; q4 += 4) {
-                uint32_t vals[1][4];
-                int off[1][4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const bool ok = q4 + j < n && lane < n;
-                    const uint4 e = s_e[lane * ES + min(q4 + j, QT - 1)];
-                    vals[0][j] = ok ? e.y : 0u;
-                    const int idx = ok ? ((d < 5 ? e.z : e.w) >> sh) & ((1 << IDX_BITS) - 1) : 0;
-                    off[0][j] = (rb + idx) * QT;
+            for (int i = 0; i < NPU; ++i) {
+                const int u = wid * NPU + i, tab = u / n_mt, mt = u - tab * n_mt;
+                if (tab < 3) {
+                    if (tab != have) {
+                        load_dt_bfrag(xb, tab == 0 ? s_q : (tab == 1 ? s_do : s_k), g, t);
+                        have = tab;
+                    }
+                    dt_unit_b(dt_acc[i], tab == 0 ? s_hq : (tab == 1 ? s_hv : s_hk), xb, mt, g, t);
                 }
-                hist_add4<1, 1>(cell, 0, off, vals, n - q4);
             }
         }
-        __syncthreads();
-        S3D_PHASE_MARK(6)
-        // ---- dTk ; dK partials ---------------------------------------------------------------------------------------
+        if (side < 2) {
+            float part[2][2][4];
 #pragma unroll
-        for (int i = 0; i < NPU; ++i) {
-            const int u = wid + SM_NWARP * i;
-            const int tab = u / n_mt, mt = u - tab * n_mt;
-            if (tab == 2 && S3D_KEEP(5)) dt_unit(dt_acc[i], s_hk, s_k, mt, g, t);
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) part[h][i][0] = part[h][i][1] = part[h][i][2] = part[h][i][3] = 0.f;
+#pragma unroll
+            for (int i = 0; i < NHU; ++i) {
+                const int ks = ws2 + SG * i;
+                if (ks < n_mt && S3D_KEEP(6)) {
+                    const uint4 f = s_tb[(side * n_mt + ks) * 32 + lane];
+                    const uint32_t tbf[2][2] = {{f.x, f.y}, {f.z, f.w}};
+                    ht_unit(part, side == 0 ? s_hq : s_hk, tbf, ks, g, t);
+                }
+            }
+            store_part(s_part + (side * SG + ws2) * 512, part, g, t);
         }
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int i = 0; i < 2; ++i) part[h][i][0] = part[h][i][1] = part[h][i][2] = part[h][i][3] = 0.f;
-#pragma unroll
-        for (int i = 0; i < NHU; ++i) {
-            const int v = wid + SM_NWARP * i;
-            if (v >= n_mt && v < 2 * n_mt && S3D_KEEP(6)) ht_unit(part, s_hk, tb[i], v - n_mt, g, t);
-        }
-        store_part(s_red + wid * 512, part, g, t);            // the previous contents were consumed before the last barrier
-        __syncthreads();
-        S3D_PHASE_MARK(7)
-        {
-            const int xx = tid >> 4, ch = tid & 15;
+        consumer_sync<NT>();
+        S3D_PHASE_MARK(5)
+        // ---- reduce and store dQ, dV (threads 0..255), dK (threads 256..511) ----------------------------------------
+        for (int e = tid; e < 512; e += NT) {
+            const int sd = e >> 8, xx = (e >> 3) & 31, ch = (e & 7) * 2;
             if (xx < n) {
-                float a = s_red_dk[xx * 16 + ch];
+                const float *pg = s_pg + (sd == 0 ? 0 : 2) * 512 + xx * 16 + ch;
+                float a = pg[0], b = pg[1];
+                const float *pp = s_part + sd * SG * 512 + xx * 16 + ch;
 #pragma unroll
-                for (int ww = 0; ww < SM_NWARP; ++ww) a += s_red[ww * 512 + xx * 16 + ch];
-                P.dk[(int64_t)s_row[xx] * HC + co + ch] = __float2half_rn(a);
+                for (int ww = 0; ww < SG; ++ww) {
+                    const float2 pr = *reinterpret_cast<const float2 *>(pp + ww * 512);
+                    a += pr.x;
+                    b += pr.y;
+                }
+                const int64_t o = (int64_t)s_row[xx] * HC + co + ch;
+                *reinterpret_cast<__half2 *>((sd == 0 ? P.dq : P.dk) + o) = __floats2half2_rn(a, b);
+                if (sd == 0) {
+                    const float2 dvv = *reinterpret_cast<const float2 *>(s_pg + 512 + xx * 16 + ch);
+                    *reinterpret_cast<__half2 *>(P.dv + o) = __floats2half2_rn(dvv.x, dvv.y);
+                }
             }
         }
+        // this warp is done with the stage
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_empty + s);
     }  // windows
     S3D_PHASE_FLUSH(0)
 
     // ---- flush the table gradients of this block ---------------------------------------------------------------------
+    {
 #pragma unroll
-    for (int i = 0; i < NPU; ++i) {
-        const int u = wid + SM_NWARP * i;
-        const int tab = u / n_mt, mt = u - tab * n_mt;
-        if (tab < 3) {
+        for (int i = 0; i < NPU; ++i) {
+            const int u = wid * NPU + i, tab = u / n_mt, mt = u - tab * n_mt;
             float *dst = tab == 0 ? P.dtq : (tab == 1 ? P.dtv : P.dtk);
+            if (tab < 3) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+                for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int rr = 0; rr < 2; ++rr) {
-                    const int row = table_row(meta, mt * 16 + g + 8 * rr);   // aliases flush into the row they stand for
-                    if (row >= 0) {
-                        float *p = dst + (int64_t)row * HC + co + h * 8 + 2 * t;
-                        atomicAdd(p, dt_acc[i][h][2 * rr]);
-                        atomicAdd(p + 1, dt_acc[i][h][2 * rr + 1]);
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const int row = table_row(meta, mt * 16 + g + 8 * rr);   // aliases flush into the row they stand for
+                        if (row >= 0) {
+                            float *p = dst + (int64_t)row * HC + co + h * 8 + 2 * t;
+                            atomicAdd(p, dt_acc[i][h][2 * rr]);
+                            atomicAdd(p + 1, dt_acc[i][h][2 * rr + 1]);
+                        }
                     }
-                }
+            }
         }
     }
 }
@@ -417,20 +571,29 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta)
 template <int D, int NPU, int NHU, bool HD16>
 static int launch_small(const SmallParams &p, const CrseMeta &meta, cudaStream_t st)
 {
-    const SmallSmem L = make_small_layout(meta.R);
+    constexpr int NW = bwd_small_warps(D);
+    const SmallSmem L = make_small_layout(meta.R, NW);
     auto kern = attn_bwd_small_kernel<D, NPU, NHU, HD16>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total) != cudaSuccess)
-        return S3D_ERR_LAUNCH;
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    static int sms_of[64] = {0};     // 0: this instantiation has not been set up on the device yet
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return S3D_ERR_LAUNCH;
+    if (sms_of[dev] == 0) {
+        int sms = 0;
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        note_cuda_error(e);
+        if (e != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+            return S3D_ERR_LAUNCH;
+        sms_of[dev] = sms;
+    }
     const int hp = HD16 ? p.H : p.H / 2;
-    int gx = sms / hp;
+    int gx = sms_of[dev] / hp;
     if (gx > p.W) gx = (int)p.W;
     if (gx < 1) gx = 1;
     dim3 grid((unsigned)gx, (unsigned)hp);
-    kern<<<grid, SM_THREADS, L.total, st>>>(p, meta);
-    return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
+    kern<<<grid, (NW + 1) * 32, L.total, st>>>(p, meta, make_pair_consts(meta));
+    const cudaError_t le = cudaGetLastError();
+    note_cuda_error(le);
+    return le == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
 }
 
 }  // namespace tc
@@ -458,10 +621,11 @@ bool attn_tc_bwd_small_supported(const AttnArgs &a)
     if (!(a.hd == 16 || (a.hd == 8 && !(a.H & 1)))) return false;
     const int Rint = a.meta.R + a.meta.D - 1;
     const int n_mt = (Rint + 15) / 16;
-    if (3 * n_mt > 5 * tc::SM_NWARP) return false;
+    const int nw = tc::bwd_small_warps(a.meta.D);
+    if (3 * n_mt > 5 * nw || n_mt > 4 * (nw / 2)) return false;
     for (int d = 0; d < a.meta.D; ++d)
         if (a.meta.L[d] >= (1 << tc::IDX_BITS)) return false;
-    return tc::make_small_layout(Rint).total <= 227 * 1024;
+    return tc::make_small_layout(Rint, nw).total <= 227 * 1024;
 }
 
 // Windows of at most 32 voxels; dtq, dtk, dtv must be zero on entry (accumulated into).
@@ -479,19 +643,13 @@ int attn_tc_backward_small(const AttnArgs &a0, cudaStream_t st)
     p.w_sizes = a.w_sizes; p.w2n = a.w2n; p.n2n = a.n2n; p.n_coords = a.n_coords;
     p.W = a.W; p.H = a.H;
     const int n_mt = (a.meta.R + 15) / 16;
-    const int npu = (3 * n_mt + tc::SM_NWARP - 1) / tc::SM_NWARP;   // <= 5
-    const int nhu = (2 * n_mt + tc::SM_NWARP - 1) / tc::SM_NWARP;   // <= 3
-#define S3D_SMALL(DD)                                                                   \
-    if (a.hd == 16) {                                                                   \
-        if (npu <= 2 && nhu <= 1) return tc::launch_small<DD, 2, 1, true>(p, a.meta, st);  \
-        if (npu <= 3 && nhu <= 2) return tc::launch_small<DD, 3, 2, true>(p, a.meta, st);  \
-        if (npu <= 4 && nhu <= 3) return tc::launch_small<DD, 4, 3, true>(p, a.meta, st);  \
-        return tc::launch_small<DD, 5, 3, true>(p, a.meta, st);                          \
-    }                                                                                   \
-    if (npu <= 2 && nhu <= 1) return tc::launch_small<DD, 2, 1, false>(p, a.meta, st);  \
-    if (npu <= 3 && nhu <= 2) return tc::launch_small<DD, 3, 2, false>(p, a.meta, st);  \
-    if (npu <= 4 && nhu <= 3) return tc::launch_small<DD, 4, 3, false>(p, a.meta, st);  \
-    return tc::launch_small<DD, 5, 3, false>(p, a.meta, st);
+    const int nw = tc::bwd_small_warps(a.meta.D);
+    const int npu = (3 * n_mt + nw - 1) / nw;         // <= 5
+    const int nhu = (n_mt + nw / 2 - 1) / (nw / 2);   // <= 4
+#define S3D_SMALL_H(DD, HH)                                                              \
+    if (npu <= 4 && nhu <= 3) return tc::launch_small<DD, 4, 3, HH>(p, a.meta, st);      \
+    return tc::launch_small<DD, 5, 4, HH>(p, a.meta, st);
+#define S3D_SMALL(DD) if (a.hd == 16) { S3D_SMALL_H(DD, true) } else { S3D_SMALL_H(DD, false) }
     switch (a.meta.D) {
         case 3: S3D_SMALL(3)
         case 6: S3D_SMALL(6)
@@ -499,6 +657,7 @@ int attn_tc_backward_small(const AttnArgs &a0, cudaStream_t st)
         default: return S3D_ERR_UNSUPPORTED;
     }
 #undef S3D_SMALL
+#undef S3D_SMALL_H
 }
 
 }  // namespace s3d

@@ -433,8 +433,9 @@ static int launch_fwd_small(const FwdSmallParams &p, const CrseMeta &meta, cudaS
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return S3D_ERR_LAUNCH;
     if (sms_of[dev] == 0) {
         int sms = 0;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        note_cuda_error(e);
+        if (e != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
             return S3D_ERR_LAUNCH;
         sms_of[dev] = sms;
     }

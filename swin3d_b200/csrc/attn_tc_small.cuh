@@ -175,6 +175,57 @@ __device__ __forceinline__ void pair_gemm2(float (&acc)[2][2][4], const uint2 *s
     }
 }
 
+// pair_gemm on a [32][ES] plane of 4-byte entries (one half2 per pair).
+template <bool TRANSPOSED>
+__device__ __forceinline__ void pair_gemm1(float (&acc)[2][2][4], const uint32_t *e32, const __half *rows, int nk, int g, int t)
+{
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+        if (16 * ks < nk) {
+            uint32_t fa[2][2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int kh = 0; kh < 2; ++kh)
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const int m = 16 * i + g + 8 * rr, ka = 16 * ks + 2 * t + 8 * kh;
+                        const uint32_t u = TRANSPOSED ? e32[m * ES + ka] : e32[ka * ES + m];
+                        const uint32_t w = TRANSPOSED ? e32[m * ES + ka + 1] : e32[(ka + 1) * ES + m];
+                        fa[0][i][2 * kh + rr] = pack_lo(u, w);
+                        fa[1][i][2 * kh + rr] = pack_hi(u, w);
+                    }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t yb[2];
+#pragma unroll
+                for (int kh = 0; kh < 2; ++kh) {
+                    const int ka = 16 * ks + 2 * t + 8 * kh;
+                    yb[kh] = h2_as_u32(__halves2half2(rows[ka * 16 + h * 8 + g], rows[(ka + 1) * 16 + h * 8 + g]));
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+                    mma_k16(acc[h][i], fa[h][i][0], fa[h][i][1], fa[h][i][2], fa[h][i][3], yb[0], yb[1]);
+            }
+        }
+    }
+}
+
+// B fragments (k = voxel, n = channel; [k-step][slot][b0, b1]) of a staged feature array for dt_unit_b.
+__device__ __forceinline__ void load_dt_bfrag(uint32_t (&b)[2][2][2], const __half *xrows, int g, int t)
+{
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int p0 = 16 * ks + 4 * t + 2 * half, p1 = p0 + 1;   // column -> voxel: (p >> 2) + 8 (p & 3)
+                const int xa = (p0 >> 2) + 8 * (p0 & 3), xb = (p1 >> 2) + 8 * (p1 & 3);
+                b[ks][h][half] = h2_as_u32(__halves2half2(xrows[xa * 16 + h * 8 + g], xrows[xb * 16 + h * 8 + g]));
+            }
+}
+
 // dT[rows of tile mt][c] += sum over the 32 voxels of hist[row][voxel] * X[voxel][c]  (both heads).
 __device__ __forceinline__ void dt_unit(float (&acc)[2][4], const uint32_t *hist, const __half *xrows, int mt, int g, int t)
 {

@@ -10,6 +10,11 @@
 
 using namespace s3d;
 
+namespace s3d {
+static int g_last_cuda_error = 0;
+void note_cuda_error(cudaError_t e) { if (e != cudaSuccess) g_last_cuda_error = (int)e; }
+}  // namespace s3d
+
 namespace {
 
 // S3D_FORCE_SCALAR=1 in the environment routes every attention call to the generic kernels
@@ -65,6 +70,11 @@ const char *s3d_status_string(int status)
 }
 
 int s3d_version(void) { return 1000; }
+
+const char *s3d_last_cuda_error_string(void)
+{
+    return cudaGetErrorString(static_cast<cudaError_t>(s3d::g_last_cuda_error));
+}
 
 int s3d_attn_fwd(const void *q, const void *k, const void *v, const void *tq, const void *tk,
                  const void *tv, const int32_t *table_sizes_host, int D, const int32_t *w_sizes,
