@@ -736,12 +736,9 @@ int attn_tc_backward(const AttnArgs &a0, cudaStream_t st)
     a.meta = tc::internal_meta(a0.meta);   // kernels work in the internal row numbering
     const int hdm = attn_tc_head_mode(a0);
     int skip_upto = 0;
-    // the single-sweep kernel serves head pairs of 8 channels and single heads of 16
-    if (hdm != tc::HDM_PAIR16 && attn_tc_bwd_small_supported(a0)) {
-        const int rc = attn_tc_backward_small(a0, st);
-        if (rc != S3D_OK) return rc;
-        skip_upto = tc::QT;
-    }
+    // the single-sweep kernel serves head pairs of 8 channels and single heads of 16, windows of any size
+    if (hdm != tc::HDM_PAIR16 && attn_tc_bwd_small_supported(a0))
+        return attn_tc_backward_small(a0, st);      // tile pairs: windows of any size
     const int n_mt = (a.meta.R + 15) / 16;
     const int mtw = (n_mt + tc::BW_NWARP - 1) / tc::BW_NWARP;
 #define S3D_TC_BWD(DD)                                            \

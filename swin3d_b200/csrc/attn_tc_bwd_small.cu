@@ -1,11 +1,20 @@
-// Backward of the cRSE window attention for windows of at most 32 voxels, tensor-core path
-// (fp16 storage): ONE sweep per window instead of a query sweep plus a key sweep.
+// Backward of the cRSE window attention, tensor-core path (fp16 storage), for windows of any size:
+// ONE sweep over the pairs instead of a query sweep plus a key sweep.
+//
+// A window of n voxels is cut into nt = ceil(n / 32) tiles of equal size (at most 32 voxels) and the
+// work item is a tile pair (query tile i, key tile j): since p = exp(s - lse) needs nothing from the
+// other key tiles, every tile pair is an independent 32 x 32 problem that adds its share to dQ of
+// tile i, to dK and dV of tile j and to the table gradients.  The nt^2 items of a window run one after
+// the other in the same block (j inner), and a share that is not the first one is added to the rows
+// already written (read-modify-write of the fp16 rows in global memory by the block that wrote them).
+// Windows of at most 32 voxels -- most of them -- are a single item.
 //
 // Block = 15 / 11 / 7 consumer warps (9 / 6 / 3 signal dimensions) + one producer warp, one block per SM, serving one head pair
 // (head_dim 8) or one head (head_dim 16) for the windows x, x + gridDim.x, ...  The producer walks
-// the block's windows ahead of the consumers: row numbers, coordinates and lse by plain loads, the
-// 32-byte Q, K, V, dO, O pieces of the voxels by the copy engine (cp.async.bulk) into the next
-// stage of shared memory; stages are handed over through "full" / "empty" mbarriers.
+// the block's items ahead of the consumers: row numbers, coordinates, lse and delta = dO.O by plain
+// loads, the 32-byte Q, dO pieces of the query tile and K, V pieces of the key tile by the copy
+// engine (cp.async.bulk) into the next stage of shared memory; stages are handed over through
+// "full" / "empty" mbarriers.
 // Per window (consumers, phases separated by a barrier among the consumer warps):
 //   GEMM    P_q = Tq.Q^T, dB = Tv.dO^T (lane-major), P_k = Tk.K^T (key-major); a warp owns consecutive
 //           (table, row tile) units, so it builds the B fragments of a feature array once per
@@ -20,7 +29,7 @@
 //   GEMM    dTq += histQ^T.Q, dTv += histV^T.dO, dTk += histK^T.K (accumulated in registers over
 //           all windows of the block), dQ += histQ.Tq, dK += histK.Tk                [tensor cores]
 //   store   reduce the partial dQ, dK over the warps, write dQ, dK, dV
-// grid = (x, H/2) or (x, H).  Larger windows go through attn_tc_bwd.cu.
+// grid = (x, H/2) or (x, H).
 #include "attn_kernels.cuh"
 #include "attn_tc.cuh"
 #include "attn_tc_small.cuh"
@@ -75,8 +84,8 @@ __host__ __device__ inline SmallSmem make_small_layout(int R, int nw)
     L.off_s0 = off; off += 32 * ES * 16;                           // S0 and dPV0 of every pair
     L.off_pl = off; off += 4 * 32 * ES * 4;                        // planes p, ds, idx 0-4, idx 5-8
     if (part > s0pl) off += part - s0pl;
-    L.off_rows = off; off += BS_STAGES * 5 * 32 * 16 * 2;          // Q, K, V, dO, O rows, per stage
-    L.off_c = off; off += BS_STAGES * 32 * 12 * 4;
+    L.off_rows = off; off += BS_STAGES * 4 * 32 * 16 * 2;          // Q, dO (query tile), K, V (key tile) rows, per stage
+    L.off_c = off; off += BS_STAGES * 2 * 32 * 12 * 4;             // coordinates of the query and of the key tile
     L.off_pg = off; off += 3 * 2048;                               // dQ, dV, dK of the pair GEMMs
     L.off_ta = off; off += 3 * (L.R16 / 16) * 512;                 // Tq, Tv, Tk as A fragments of the projections
     L.off_tb = off; off += 2 * (L.R16 / 16) * 512;                 // Tq and Tk as B fragments of the hist.T products
@@ -121,18 +130,18 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
     float4 *s_s0 = reinterpret_cast<float4 *>(smem + L.off_s0);         // [32][ES] (S0 h0, S0 h1, dPV0 h0, dPV0 h1)
     uint32_t *s_P = reinterpret_cast<uint32_t *>(smem + L.off_pl);      // [32][ES] half2 p
     uint32_t *s_DS = s_P + 32 * ES, *s_W0 = s_DS + 32 * ES, *s_W1 = s_W0 + 32 * ES;
-    __half *s_rows = reinterpret_cast<__half *>(smem + L.off_rows);     // [stage][Q,K,V,dO,O][32][16]
-    float *s_cs = reinterpret_cast<float *>(smem + L.off_c);            // [stage][32][12]
+    __half *s_rows = reinterpret_cast<__half *>(smem + L.off_rows);     // [stage][Q,dO,K,V][32][16]
+    float *s_cs = reinterpret_cast<float *>(smem + L.off_c);            // [stage][query tile, key tile][32][12]
     float *s_part = reinterpret_cast<float *>(smem + L.off_s0);         // [2][SG][32][16], over S0 and the planes
     uint4 *s_ta = reinterpret_cast<uint4 *>(smem + L.off_ta);           // [Tq, Tv, Tk][row tile][lane]
     float *s_pg = reinterpret_cast<float *>(smem + L.off_pg);           // [3][32][16]
     uint4 *s_tb = reinterpret_cast<uint4 *>(smem + L.off_tb);           // [Tq, Tk][k-step][lane]
     float *s_lses = reinterpret_cast<float *>(smem + L.off_misc);       // [stage][32][2]
-    float *s_del = s_lses + BS_STAGES * 64;                             // [32][2]
-    int *s_rowi = reinterpret_cast<int *>(s_del + 64);                  // [stage][32]
-    int *s_n = s_rowi + BS_STAGES * 32;                                 // [stage]
-    int *s_fail = s_n + BS_STAGES;
-    uint64_t *s_full = reinterpret_cast<uint64_t *>(smem + L.off_misc + 1536);   // [stage]
+    float *s_dels = s_lses + BS_STAGES * 64;                            // [stage][32][2]
+    int *s_rowi = reinterpret_cast<int *>(s_dels + BS_STAGES * 64);     // [stage][query tile, key tile][32]
+    int *s_n = s_rowi + BS_STAGES * 64;                                 // [stage][4]: nq, nk, j > 0, i > 0 ; nq = 0: no more items
+    int *s_fail = s_n + BS_STAGES * 4;
+    uint64_t *s_full = reinterpret_cast<uint64_t *>(smem + L.off_misc + 1792);   // [stage]
     uint64_t *s_empty = s_full + BS_STAGES;
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
@@ -148,78 +157,172 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
         *s_fail = 0;
         mbar_init_fence();
     }
+    // ---- this block's windows: a contiguous range of equal cost --------------------------------------------------
+    // cost of a window = its number of tile pairs; every block scans all window sizes (a few hundred KB
+    // from L2) and takes the range whose cumulative cost falls into its share, so the assignment is
+    // balanced to within one window, needs no global counter and is the same on every run.
+    {
+        constexpr int NTA = (NW + 1) * 32;
+        int64_t *s_seg = reinterpret_cast<int64_t *>(smem + L.off_pq);     // [NTA + 1] segment sums, then their exclusive scan
+        int64_t *s_range = s_seg + NTA + 2;                                // [2] first window, one past the last
+        const int64_t per = (P.W + NTA - 1) / NTA;
+        const int64_t w0 = (int64_t)tid * per, w1 = w0 + per < P.W ? w0 + per : P.W;
+        int64_t sum = 0;
+        for (int64_t w = w0; w < w1; ++w) {
+            const int nt = (__ldg(P.w_sizes + w) + QT - 1) / QT;
+            sum += (int64_t)nt * nt;
+        }
+        s_seg[tid] = sum;
+        __syncthreads();
+        if (wid == 0) {                       // exclusive scan of the NTA segment sums by one warp
+            int64_t carry = 0;
+            for (int b0 = 0; b0 < NTA; b0 += 32) {
+                const int64_t v = s_seg[b0 + lane];
+                int64_t x = v;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int64_t y = __shfl_up_sync(0xffffffffu, x, o);
+                    if (lane >= o) x += y;
+                }
+                s_seg[b0 + lane] = carry + x - v;
+                carry += __shfl_sync(0xffffffffu, x, 31);
+            }
+            if (lane == 0) s_seg[NTA] = carry;
+        }
+        __syncthreads();
+        const int64_t total = s_seg[NTA];
+        // window index at which the cumulative cost reaches the target: first w with prefix(w) >= target
+        const int64_t lo_t = total * blockIdx.x / gridDim.x, hi_t = total * (blockIdx.x + 1) / gridDim.x;
+        const int64_t mine = s_seg[tid], next = tid + 1 < NTA ? s_seg[tid + 1] : total + 1;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int64_t target = k == 0 ? lo_t : hi_t;
+            if (target >= total) {
+                if (tid == 0) s_range[k] = P.W;
+            } else if (mine <= target && target < next && w0 < w1) {
+                int64_t acc = mine, w = w0;
+                for (; w < w1; ++w) {
+                    if (acc >= target) break;
+                    const int nt = (__ldg(P.w_sizes + w) + QT - 1) / QT;
+                    acc += (int64_t)nt * nt;
+                }
+                s_range[k] = w;
+            }
+        }
+        __syncthreads();
+    }
+    const int64_t w_begin = reinterpret_cast<const int64_t *>(smem + L.off_pq)[(NW + 1) * 32 + 2];
+    const int64_t w_end = reinterpret_cast<const int64_t *>(smem + L.off_pq)[(NW + 1) * 32 + 3];
     __syncthreads();
 
     if (wid == NW) {
         // ================================ producer warp ================================================
-        int64_t w = (int64_t)blockIdx.x - gridDim.x;
+        int64_t w = w_begin - 1;
+        int n = 0, base = 0, nt = 0, ts = 0, ti = 0, tj = 0;
+        bool have = false;
         for (int it = 0;; ++it) {
-            int n = 0;
-            for (;;) {
-                const int64_t cand = w + (int64_t)(lane + 1) * gridDim.x;
-                const int nn = cand < P.W ? __ldg(P.w_sizes + cand) : 0;
-                const unsigned ok = __ballot_sync(0xffffffffu, nn >= 1 && nn <= QT);
-                if (ok) {
-                    const int j = __ffs(ok) - 1;
-                    w += (int64_t)(j + 1) * gridDim.x;
-                    n = __shfl_sync(0xffffffffu, nn, j);
-                    break;
+            // next item: key tiles inner, query tiles outer, then the block's next window
+            if (have && tj + 1 < nt) {
+                ++tj;
+            } else if (have && ti + 1 < nt) {
+                ++ti;
+                tj = 0;
+            } else {
+                ++w;
+                have = w < w_end;
+                if (have) {
+                    n = __ldg(P.w_sizes + w);
+                    base = __ldg(P.w2n + w);
+                    nt = (n + QT - 1) / QT;
+                    ts = (n + nt - 1) / nt;          // equal tiles of at most QT voxels
+                    ti = tj = 0;
+                    have = n > 0;
                 }
-                w += (int64_t)32 * gridDim.x;
-                if (w + gridDim.x >= P.W) break;         // n stays 0: no more windows
             }
-            int row = 0;
-            float c[D];
-            float ls0 = 0.f, ls1 = 0.f;
+            int nq = have ? min(ts, n - ti * ts) : 0, nk = have ? min(ts, n - tj * ts) : 0;
+            int rowq = 0, rowk = 0;
+            float cq[D], ck[D];
+            float ls0 = 0.f, ls1 = 0.f, de0 = 0.f, de1 = 0.f;
 #pragma unroll
-            for (int d = 0; d < D; ++d) c[d] = 0.f;
-            if (n > 0) {
-                const int base = __ldg(P.w2n + w);
-                if (lane < n) {
-                    row = __ldg(P.n2n + base + lane);
+            for (int d = 0; d < D; ++d) cq[d] = ck[d] = 0.f;
+            if (lane < nq) {
+                const int pos = base + ti * ts + lane;
+                rowq = __ldg(P.n2n + pos);
 #pragma unroll
-                    for (int d = 0; d < D; ++d) c[d] = __ldg(P.n_coords + (int64_t)(base + lane) * D + d);
-                    if (HD16) {
-                        ls0 = ls1 = __ldg(P.lse + (int64_t)row * H + hp);
-                    } else {
-                        ls0 = __ldg(P.lse + (int64_t)row * H + 2 * hp);
-                        ls1 = __ldg(P.lse + (int64_t)row * H + 2 * hp + 1);
-                    }
+                for (int d = 0; d < D; ++d) cq[d] = __ldg(P.n_coords + (int64_t)pos * D + d);
+                if (HD16) {
+                    ls0 = ls1 = __ldg(P.lse + (int64_t)rowq * H + hp);
+                } else {
+                    ls0 = __ldg(P.lse + (int64_t)rowq * H + 2 * hp);
+                    ls1 = __ldg(P.lse + (int64_t)rowq * H + 2 * hp + 1);
                 }
+                // delta[slot] = sum_c dO . O over the eight channels of the slot
+                const uint4 *gd = reinterpret_cast<const uint4 *>(P.dout + (int64_t)rowq * HC + co);
+                const uint4 *go = reinterpret_cast<const uint4 *>(P.o + (int64_t)rowq * HC + co);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint4 a = __ldg(gd + h), b = __ldg(go + h);
+                    const __half2 *a2 = reinterpret_cast<const __half2 *>(&a), *b2 = reinterpret_cast<const __half2 *>(&b);
+                    float acc = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
+                        acc += fa.x * fb.x + fa.y * fb.y;
+                    }
+                    if (h == 0) de0 = acc; else de1 = acc;
+                }
+            }
+            if (lane < nk) {
+                const int pos = base + tj * ts + lane;
+                rowk = __ldg(P.n2n + pos);
+#pragma unroll
+                for (int d = 0; d < D; ++d) ck[d] = __ldg(P.n_coords + (int64_t)pos * D + d);
             }
             const int s = it % BS_STAGES;
             if (it >= BS_STAGES && !mbar_wait(s_empty + s, ((it / BS_STAGES) - 1) & 1)) {
                 g_bwd_small_async_error = 1;
-                n = 0;                                    // tell the consumers to stop
+                nq = nk = 0;                              // tell the consumers to stop
             }
-            __half *rq = s_rows + s * 2560;
-            float *cs = s_cs + s * 384;
+            __half *rq = s_rows + s * 2048;
+            float *cs = s_cs + s * 768;
 #pragma unroll
-            for (int d = 0; d < D; ++d) cs[lane * 12 + d] = c[d];
-            s_rowi[s * 32 + lane] = row;
+            for (int d = 0; d < D; ++d) {
+                cs[lane * 12 + d] = cq[d];
+                cs[384 + lane * 12 + d] = ck[d];
+            }
+            s_rowi[s * 64 + lane] = rowq;
+            s_rowi[s * 64 + 32 + lane] = rowk;
             s_lses[s * 64 + lane * 2] = ls0;
             s_lses[s * 64 + lane * 2 + 1] = ls1;
-            if (lane >= n) {                              // rows beyond the window are zero
+            s_dels[s * 64 + lane * 2] = de0;
+            s_dels[s * 64 + lane * 2 + 1] = de1;
 #pragma unroll
-                for (int a = 0; a < 5; ++a) {
+            for (int a = 0; a < 4; ++a)                   // rows beyond the tiles are zero
+                if (lane >= (a < 2 ? nq : nk)) {
                     *reinterpret_cast<uint4 *>(rq + a * 512 + lane * 16) = make_uint4(0, 0, 0, 0);
                     *reinterpret_cast<uint4 *>(rq + a * 512 + lane * 16 + 8) = make_uint4(0, 0, 0, 0);
                 }
+            if (lane == 0) {
+                s_n[s * 4] = nq;
+                s_n[s * 4 + 1] = nk;
+                s_n[s * 4 + 2] = tj > 0;
+                s_n[s * 4 + 3] = ti > 0;
             }
-            if (lane == 0) s_n[s] = n;
             async_proxy_fence();
             __syncwarp();
-            if (lane == 0) mbar_arrive_expect_tx(s_full + s, (unsigned)(n * 160));
+            if (lane == 0) mbar_arrive_expect_tx(s_full + s, (unsigned)((nq + nk) * 64));
             __syncwarp();
-            if (lane < n) {
-                const int64_t off = (int64_t)row * HC + co;
+            if (lane < nq) {
+                const int64_t off = (int64_t)rowq * HC + co;
                 bulk_copy_g2s(rq + lane * 16, P.q + off, 32, s_full + s);
-                bulk_copy_g2s(rq + 512 + lane * 16, P.k + off, 32, s_full + s);
-                bulk_copy_g2s(rq + 1024 + lane * 16, P.v + off, 32, s_full + s);
-                bulk_copy_g2s(rq + 1536 + lane * 16, P.dout + off, 32, s_full + s);
-                bulk_copy_g2s(rq + 2048 + lane * 16, P.o + off, 32, s_full + s);
+                bulk_copy_g2s(rq + 512 + lane * 16, P.dout + off, 32, s_full + s);
             }
-            if (n == 0) break;
+            if (lane < nk) {
+                const int64_t off = (int64_t)rowk * HC + co;
+                bulk_copy_g2s(rq + 1024 + lane * 16, P.k + off, 32, s_full + s);
+                bulk_copy_g2s(rq + 1536 + lane * 16, P.v + off, 32, s_full + s);
+            }
+            if (nq == 0) break;
         }
         return;
     }
@@ -285,27 +388,15 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
         }
         consumer_sync<NT>();          // the previous window's stores are over; the flag is settled
         S3D_PHASE_MARK(0)
-        const int n = s_n[s];
-        if (n == 0 || *s_fail) break;
-        const __half *s_q = s_rows + s * 2560, *s_k = s_q + 512, *s_v = s_q + 1024, *s_do = s_q + 1536, *s_o = s_q + 2048;
-        const float *s_c = s_cs + s * 384;
-        const int *s_row = s_rowi + s * 32;
-        const float *s_lse = s_lses + s * 64;
+        const int nq = s_n[s * 4], nk = s_n[s * 4 + 1];
+        const bool add_q = s_n[s * 4 + 2] != 0, add_k = s_n[s * 4 + 3] != 0;   // not the first share of dQ / of dK, dV
+        if (nq == 0 || *s_fail) break;
+        const __half *s_q = s_rows + s * 2048, *s_do = s_q + 512, *s_k = s_q + 1024, *s_v = s_q + 1536;
+        const float *s_c = s_cs + s * 768, *s_ck = s_c + 384;
+        const int *s_rowq = s_rowi + s * 64, *s_rowk = s_rowq + 32;
+        const float *s_lse = s_lses + s * 64, *s_del = s_dels + s * 64;
         float cx[D];
         load_coords12<D>(s_c + lane * 12, cx);
-        if (tid < 64) {               // delta[voxel][slot] = sum_c dO . O
-            const int i = tid >> 1, h = tid & 1;
-            const uint4 a = *reinterpret_cast<const uint4 *>(s_do + i * 16 + h * 8);
-            const uint4 b = *reinterpret_cast<const uint4 *>(s_o + i * 16 + h * 8);
-            const __half2 *a2 = reinterpret_cast<const __half2 *>(&a), *b2 = reinterpret_cast<const __half2 *>(&b);
-            float acc = 0.f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
-                acc += fa.x * fb.x + fa.y * fb.y;
-            }
-            s_del[tid] = acc;
-        }
         // ---- projections P_q, dB (lane-major), P_k (key-major); S0 = K.Q^T and dPV0 = V.dO^T -----------------
         if (S3D_KEEP(0)) {
             uint32_t bf[8][2];
@@ -315,20 +406,20 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                 const int u = wid * NPU + i, tab = u / n_mt, mt = u - tab * n_mt;
                 if (tab < 3) {
                     if (tab != have) {
-                        load_feat_bfrag(bf, tab == 0 ? s_q : (tab == 1 ? s_do : s_k), n, g, t);
+                        load_feat_bfrag(bf, tab == 0 ? s_q : (tab == 1 ? s_do : s_k), tab == 2 ? nk : nq, g, t);
                         have = tab;
                     }
                     const uint4 f = s_ta[u * 32 + lane];
                     const uint32_t taf[2][2] = {{f.x, f.y}, {f.z, f.w}};
-                    if (tab == 0) project_unit_b<true>(taf, bf, s_pq, mt, Rp, n, g, t);
-                    else if (tab == 1) project_unit_b<true>(taf, bf, s_db, mt, Rp, n, g, t);
-                    else project_unit_b<false>(taf, bf, s_pk, mt, Rp, n, g, t);
+                    if (tab == 0) project_unit_b<true>(taf, bf, s_pq, mt, Rp, nq, g, t);
+                    else if (tab == 1) project_unit_b<true>(taf, bf, s_db, mt, Rp, nq, g, t);
+                    else project_unit_b<false>(taf, bf, s_pk, mt, Rp, nk, g, t);
                 }
             }
         }
         for (int u = wid; u < 32 && S3D_KEEP(1); u += NW) {
             const int a = u >> 4, mt = (u >> 3) & 1, j = u & 7;     // key rows 16mt.., query columns 4j..
-            if (16 * mt < n && 4 * j < n) {
+            if (16 * mt < nk && 4 * j < nq) {
                 const __half *ysrc = (a == 0 ? s_k : s_v) + mt * 256;
                 const __half *xsrc = a == 0 ? s_q : s_do;
                 const uint32_t wv = *reinterpret_cast<const uint32_t *>(xsrc + (4 * j + (g >> 1)) * 16 + (g & 1) * 8 + 2 * t);
@@ -357,9 +448,9 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                 const int kk = wid + NW * j;
                 if (kk < QT) {
                     uint32_t pw = 0u, dsw = 0u, w0 = 0u, w1 = 0u;     // zero for keys beyond the window
-                    if (kk < n && S3D_KEEP(2)) {
+                    if (kk < nk && S3D_KEEP(2)) {
                         float ck[D];
-                        load_coords12<D>(s_c + kk * 12, ck);
+                        load_coords12<D>(s_ck + kk * 12, ck);
                         const uint32_t *pk_row = s_pk + kk * Rp;
                         __half2 b0 = __float2half2_rn(0.f), b1 = b0, b2 = b0;
 #pragma unroll
@@ -381,7 +472,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                         float p1 = ex2_approx(fmaf(sc1, LOG2E, -xlse1));
                         float ds0 = p0 * (dq0 - xdel0);
                         float ds1 = p1 * (dq1 - xdel1);
-                        if (lane >= n) { p0 = 0.f; p1 = 0.f; ds0 = 0.f; ds1 = 0.f; }
+                        if (lane >= nq) { p0 = 0.f; p1 = 0.f; ds0 = 0.f; ds1 = 0.f; }
                         pw = h2_as_u32(__floats2half2_rn(p0, p1));
                         dsw = h2_as_u32(__floats2half2_rn(ds0, ds1));
                     }
@@ -412,7 +503,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                 uint32_t p0 = pcol[0], d0 = dcol[0], x0 = wcol[0];
                 uint32_t p1 = pcol[ES], d1 = dcol[ES], x1 = wcol[ES];
                 int kk = 0;
-                for (; kk + 1 < n; kk += 2) {
+                for (; kk + 1 < nk; kk += 2) {
                     const uint32_t i0 = (x0 >> sh) & ((1u << IDX_BITS) - 1u), i1 = (x1 >> sh) & ((1u << IDX_BITS) - 1u);
                     uint32_t *a0 = cell + i0 * QT, *a1 = cell + i1 * QT;
                     const uint32_t q0 = a0[0], v0 = a0[hv], q1 = a1[0], v1 = a1[hv];
@@ -428,7 +519,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                     a0[0] = h2_as_u32(sq0); a0[hv] = h2_as_u32(sv0);
                     a1[0] = h2_as_u32(sq1); a1[hv] = h2_as_u32(sv1);
                 }
-                if (kk < n) {
+                if (kk < nk) {
                     const uint32_t i0 = (x0 >> sh) & ((1u << IDX_BITS) - 1u);
                     uint32_t *a0 = cell + i0 * QT;
                     a0[0] = h2_as_u32(__hadd2(u32_as_h2(a0[0]), u32_as_h2(d0)));
@@ -444,7 +535,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                 uint32_t *cell = s_hk + meta.rowbase[d] * QT + mypos;
                 uint32_t d0 = drow[0], x0 = wrow[0], d1 = drow[1], x1 = wrow[1];
                 int qq = 0;
-                for (; qq + 1 < n; qq += 2) {
+                for (; qq + 1 < nq; qq += 2) {
                     const uint32_t i0 = (x0 >> sh) & ((1u << IDX_BITS) - 1u), i1 = (x1 >> sh) & ((1u << IDX_BITS) - 1u);
                     uint32_t *a0 = cell + i0 * QT, *a1 = cell + i1 * QT;
                     const uint32_t c0 = a0[0], c1 = a1[0];
@@ -457,7 +548,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                     a0[0] = h2_as_u32(s0);
                     a1[0] = h2_as_u32(s1);
                 }
-                if (qq < n) {
+                if (qq < nq) {
                     const uint32_t i0 = (x0 >> sh) & ((1u << IDX_BITS) - 1u);
                     uint32_t *a0 = cell + i0 * QT;
                     a0[0] = h2_as_u32(__hadd2(u32_as_h2(a0[0]), u32_as_h2(d0)));
@@ -474,9 +565,9 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
 #pragma unroll
                     for (int i = 0; i < 2; ++i) pg[h][i][0] = pg[h][i][1] = pg[h][i][2] = pg[h][i][3] = 0.f;
                 if (S3D_KEEP(4)) {
-                    if (wid == DV_WARP) pair_gemm1<true>(pg, s_P, s_do, n, g, t);          // dV[k]  = sum_q p  dO[q]
-                    else if (a == 0) pair_gemm1<false>(pg, s_DS, s_k, n, g, t);            // dQ[q] += sum_k ds K[k]
-                    else pair_gemm1<true>(pg, s_DS, s_q, n, g, t);                         // dK[k] += sum_q ds Q[q]
+                    if (wid == DV_WARP) pair_gemm1<true>(pg, s_P, s_do, nq, g, t);         // dV[k]  = sum_q p  dO[q]
+                    else if (a == 0) pair_gemm1<false>(pg, s_DS, s_k, nk, g, t);           // dQ[q] += sum_k ds K[k]
+                    else pair_gemm1<true>(pg, s_DS, s_q, nq, g, t);                        // dK[k] += sum_q ds Q[q]
                 }
                 store_part(s_pg + (wid == DV_WARP ? 1 : 2 * a) * 512, pg, g, t);
             }
@@ -521,7 +612,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
         // ---- reduce and store dQ, dV (threads 0..255), dK (threads 256..511) ----------------------------------------
         for (int e = tid; e < 512; e += NT) {
             const int sd = e >> 8, xx = (e >> 3) & 31, ch = (e & 7) * 2;
-            if (xx < n) {
+            if (xx < (sd == 0 ? nq : nk)) {
                 const float *pg = s_pg + (sd == 0 ? 0 : 2) * 512 + xx * 16 + ch;
                 float a = pg[0], b = pg[1];
                 const float *pp = s_part + sd * SG * 512 + xx * 16 + ch;
@@ -531,11 +622,25 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                     a += pr.x;
                     b += pr.y;
                 }
-                const int64_t o = (int64_t)s_row[xx] * HC + co + ch;
-                *reinterpret_cast<__half2 *>((sd == 0 ? P.dq : P.dk) + o) = __floats2half2_rn(a, b);
-                if (sd == 0) {
-                    const float2 dvv = *reinterpret_cast<const float2 *>(s_pg + 512 + xx * 16 + ch);
-                    *reinterpret_cast<__half2 *>(P.dv + o) = __floats2half2_rn(dvv.x, dvv.y);
+                // a later share of a large window is added to the rows this block wrote before
+                const bool add = sd == 0 ? add_q : add_k;
+                const int64_t o = (int64_t)(sd == 0 ? s_rowq : s_rowk)[xx] * HC + co + ch;
+                __half2 *dst = reinterpret_cast<__half2 *>((sd == 0 ? P.dq : P.dk) + o);
+                if (add) {
+                    const float2 old = __half22float2(*dst);
+                    a += old.x;
+                    b += old.y;
+                }
+                *dst = __floats2half2_rn(a, b);
+                if (sd == 1) {
+                    float2 dvv = *reinterpret_cast<const float2 *>(s_pg + 512 + xx * 16 + ch);
+                    __half2 *dvp = reinterpret_cast<__half2 *>(P.dv + o);
+                    if (add) {
+                        const float2 old = __half22float2(*dvp);
+                        dvv.x += old.x;
+                        dvv.y += old.y;
+                    }
+                    *dvp = __floats2half2_rn(dvv.x, dvv.y);
                 }
             }
         }
@@ -628,7 +733,7 @@ bool attn_tc_bwd_small_supported(const AttnArgs &a)
     return tc::make_small_layout(Rint, nw).total <= 227 * 1024;
 }
 
-// Windows of at most 32 voxels; dtq, dtk, dtv must be zero on entry (accumulated into).
+// All windows; dtq, dtk, dtv must be zero on entry (accumulated into).
 int attn_tc_backward_small(const AttnArgs &a0, cudaStream_t st)
 {
     if (a0.W == 0) return S3D_OK;
