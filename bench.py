@@ -9,9 +9,11 @@ shifted window set, as consecutive Swin blocks do).  Metric: voxels per second, 
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload attn|knn]
 
-N > 1: launched under torchrun, one rank per GPU; every rank owns its own batch of rooms (weak
-scaling, as in data-parallel training) and the only exchange is the NCCL all-reduce of the three
-table-gradient arrays.  `--impl reference` times the CPU restatement of the reference kernels
+N > 1: launched under torchrun, one rank per GPU.  Default: the SAME batch split over the ranks by
+window ranges of equal cost (strong scaling); out, dq, dk, dv rows are all-gathered and the table
+gradients all-reduced inside the timed region.  `--workload attn-replicas`: every rank owns its own
+batch of rooms (weak scaling, as in data-parallel training), the only exchange is the all-reduce of
+the three table-gradient arrays.  `--impl reference` times the CPU restatement of the reference kernels
 (the reference has no CPU code of its own) on the host cores, on a bounded sample.
 """
 import argparse
@@ -464,11 +466,11 @@ def run_attention(args):
     line = {
         "metric": "attn fwd+bwd voxels/sec @Swin3D-L stage1", "value": value, "unit": "voxels/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "strong" if args.workload == "attn" else "weak", "vs_baseline": None,
         "dtype": "f16 storage, f32 accumulate", "data": "synthetic", "config": workload_config(),
         "voxels_per_gpu": N, "pairs_per_gpu": M, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
         "window_build_ms": wb_ms, "window_build_device_ms": wb_dev_ms,
-        "roofline": {"bound": "hbm", "kernel": "attention backward (single-tile launch for windows <= 32 voxels + query-sweep and key-sweep launches for larger ones)", "achieved": bwd_gbs, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "attention backward (tile-pair single-sweep kernel, windows of any size)", "achieved": bwd_gbs, "peak": peak,
                      "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": traffic, "peak_source": peak_src,
                      "algorithmic_bytes_per_voxel": {"fwd": pv_fwd, "bwd": pv_bwd},
                      "fwd": {"achieved": fwd_gbs, "frac": fwd_gbs / peak},
@@ -477,7 +479,7 @@ def run_attention(args):
         "e2e": {"value": n_total / (e2e_ms * 1e-3), "unit": "voxels/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 4 * N * Cc * 2,
                 "d2h_bytes_per_step": 4 * N * Cc * 2 + 3 * sum(sizes) * 4},
-        "gpu_launches": 5 * args.steps,   # forward single-tile + tiled, backward single-tile + query sweep + key sweep
+        "gpu_launches": 3 * args.steps,   # forward single-tile + tiled, backward (tile pairs)
         "clocks": clocks,
     }
     print(json.dumps(line))
@@ -487,61 +489,187 @@ def run_attention(args):
 
 
 def run_attention_split(args):
-    """Secondary workload: ONE 8-room batch split over the ranks by window ranges (strong scaling):
-    every rank computes its windows, per-voxel outputs and gradients are all-gathered (NCCL), table
-    gradients all-reduced.  Device-resident timing, max over ranks."""
+    """The multi-GPU mode of the benchmark (default for --gpus N > 1): ONE 8-room batch split over the
+    ranks by contiguous window ranges of equal cost (strong scaling).  Every rank runs forward +
+    backward of its windows chunk by chunk; the rows of out, dq, dk, dv are exchanged packed (one
+    NCCL all-gather per chunk, overlapping the next chunk's kernels, one un-permute), the table
+    gradients are all-reduced.  All of it is inside the timed region; time = max over ranks."""
     import torch
     import torch.distributed as dist
     from swin3d_b200 import synthetic as S
-    from swin3d_b200.dist import sharded_attention
+    from swin3d_b200.dist import get_plan, sharded_attention_step
     from swin3d_b200.window import build_windows
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
+        bind_to_gpu_numa_node(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     c = CFG
     H, hd, ws, quant, crse = c["H"], c["hd"], c["ws"], c["quant"], c["crse"]
+    Cc = H * hd
     sc = make_batch(0, args.rooms or c["rooms"], c["voxels_per_room"])      # the same batch on every rank
     N = sc.coords.shape[0]
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     sizes = S.table_sizes(ws, quant, H, hd, crse)
-    wi = build_windows(dev(sc.coords), dev(S.signal_feats(sc, crse)), ws, 0)
-    ncr = wi.n_coords.clone()
-    ncr[:, :3] *= quant
-    ncr[:, 3:] *= 2 * quant
+    D = len(sizes)
+    coords_d, feats_d = dev(sc.coords), dev(S.signal_feats(sc, crse))
+    win = []
+    for shift in (0, ws // 2):
+        wi = build_windows(coords_d, feats_d, ws, shift)
+        ncr = wi.n_coords.clone()
+        ncr[:, :3] *= quant
+        ncr[:, 3:] *= 2 * quant
+        win.append((wi, ncr.contiguous()))
     gen = torch.Generator(device="cuda").manual_seed(1234)
     rnd = lambda: torch.randn((N, H, hd), device="cuda", generator=gen, dtype=torch.float32)
     q = (rnd() * hd ** -0.5).half()
     k, v, g = rnd().half(), rnd().half(), rnd().half()
     tabs = [dev(t).half() for t in S.make_tables(1, sizes)]
+    chunks = 1 if world == 1 else args.chunks
+    plans = [get_plan(wi.w_sizes, wi.w2n, wi.n2n, world, rank, chunks) for wi, _ in win]   # host read, once
 
-    def step():
-        return sharded_attention(q, k, v, *tabs, sizes, wi.w_sizes, wi.w2n, wi.n2n, ncr, dout=g)
+    def step(i, bufs=None):
+        wi, ncr = win[i % 2]
+        x = bufs if bufs is not None else (q, k, v, g)
+        return sharded_attention_step(x[0], x[1], x[2], *tabs, sizes, wi.w_sizes, wi.w2n, wi.n2n, ncr, x[3],
+                                      plan=plans[i % 2])
 
-    for _ in range(max(args.warmup, 3)):
-        step()
+    for i in range(max(args.warmup, 3)):
+        step(i)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
     t0.record()
-    for _ in range(args.steps):
-        step()
+    for i in range(args.steps):
+        res = step(i)
     t1.record()
     torch.cuda.synchronize()
-    ms = torch.tensor([t0.elapsed_time(t1) / args.steps], dtype=torch.float64, device="cuda")
     if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    if rank == 0:
-        print(json.dumps({"metric": "attn fwd+bwd voxels/sec @Swin3D-L stage1, one batch split over the GPUs",
-                          "value": N / (float(ms[0]) * 1e-3), "unit": "voxels/s", "n_gpus": world,
-                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": float(ms[0]),
-                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                          "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
-                          "config": workload_config(), "voxels_total": N,
-                          "exchange": "all-gather of out, dq, dk, dv rows (4 x N x 160 B) + all-reduce of 3 table gradients"}))
+        dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t0.elapsed_time(t1)
+
+    # kernels of this rank alone (no exchange), for the roofline figure of the dominant kernel
+    from swin3d_b200.sparse_dl.attn import attn_coff as C
+    pl = plans[0]
+    wi, ncr = win[0]
+    a0, b0 = pl.parts[rank]
+    ws_l, w2n_l = wi.w_sizes[a0:b0].contiguous(), wi.w2n[a0:b0].contiguous()
+    n_local = int(ws_l.sum().item())
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    for _ in range(2):
+        e0.record()
+        o_l, lse_l = C.attn_forward_raw(q, k, v, *tabs, sizes, ws_l, w2n_l, wi.n2n, ncr)
+        e1.record()
+        C.attn_backward_raw(q, k, v, *tabs, sizes, ws_l, w2n_l, wi.n2n, ncr, o_l, lse_l, g)
+        e2.record()
+    torch.cuda.synchronize()
+    fwd_ms, bwd_ms = e0.elapsed_time(e1), e1.elapsed_time(e2)
+    # the same chunked kernel sequence as in the step, without packing, collectives and un-permute:
+    # step time minus this is what the exchange costs after overlap
+    o_b, lse_b = torch.empty_like(q), torch.empty((N, H), dtype=torch.float32, device="cuda")
+    g_b = [torch.empty_like(q) for _ in range(3)]
+    e0.record()
+    for _ in range(3):
+        for cc in range(pl.chunks):
+            C.attn_forward_raw(q, k, v, *tabs, sizes, pl.w_sizes_chunk[cc], pl.w2n_chunk[cc], wi.n2n, ncr, out=o_b, lse=lse_b)
+            C.attn_backward_raw(q, k, v, *tabs, sizes, pl.w_sizes_chunk[cc], pl.w2n_chunk[cc], wi.n2n, ncr, o_b, lse_b, g,
+                                dq=g_b[0], dk=g_b[1], dv=g_b[2])
+    e1.record()
+    torch.cuda.synchronize()
+    compute_ms = e0.elapsed_time(e1) / 3
+
+    # ---- end to end: host buffers in and out.  A rank copies in the band of voxel rows its windows
+    # touch (rooms are contiguous in voxel order and window ranges follow the rooms), runs the sharded
+    # step, and copies the same band of out, dq, dk, dv back; the bands of all ranks cover the batch.
+    x_pin = [t.cpu().pin_memory() for t in (q, k, v, g)]
+    out_pin = [torch.empty((N, H, hd), dtype=torch.float16).pin_memory() for _ in range(4)]
+    bands = []
+    for (wi_s, _), pl_s in zip(win, plans):
+        rows = torch.cat([wi_s.n2n[lo:hi] for lo, hi in pl_s.chunk_rows]) if pl_s.chunk_rows else wi_s.n2n[:0]
+        bands.append((int(rows.min().item()), int(rows.max().item()) + 1) if rows.numel() else (0, 0))
+    dbuf = [torch.empty((N, H, hd), dtype=torch.float16, device="cuda") for _ in range(4)]
+
+    def e2e_step(i):
+        lo, hi = bands[i % 2]
+        for dst, src in zip(dbuf, x_pin):
+            dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
+        r = step(i, dbuf)
+        for dst, src in zip(out_pin, r[:4]):
+            dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
+        return r
+
+    e2e_steps = max(2, min(args.steps, 10))
+    for i in range(2):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    t1.record()
+    torch.cuda.synchronize()
+    e2e_ms = t0.elapsed_time(t1) / e2e_steps
+    lo, hi = bands[(e2e_steps - 1) % 2]
+    ref = step(e2e_steps - 1)
+    torch.cuda.synchronize()
+    for name, got, want in zip(("out", "dq", "dk", "dv"), out_pin, ref[:4]):
+        if not torch.equal(got[lo:hi], want[lo:hi].cpu()):
+            raise RuntimeError(f"end-to-end sharded step: {name} differs from the device-resident result")
+    band_rows = float(sum(b - a for a, b in bands)) / len(bands)
+
+    stats = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e_ms, band_rows, compute_ms], dtype=torch.float64, device="cuda")
+    compute_mean = compute_ms
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms, fwd_ms, bwd_ms, e2e_ms = (float(x) for x in mx[:4])
+        compute_ms = float(mx[5])
+        compute_mean = float(sm[5]) / world
+        band_total = float(sm[4])
+    else:
+        band_total = band_rows
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+    ms_per_step = total_ms / args.steps
+    peak, peak_src = load_peaks()
+    pv_fwd, pv_bwd = bytes_fwd(Cc, 2, D, H), bytes_bwd(Cc, 2, D, H)
+    bwd_gbs = n_local * pv_bwd / (bwd_ms * 1e-3) / 1e9
+    line = {
+        "metric": "attn fwd+bwd voxels/sec @Swin3D-L stage1", "value": N / (ms_per_step * 1e-3), "unit": "voxels/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+        "config": dict(workload_config(), partition=f"one batch, windows split over {world} GPU(s) by cost, "
+                       f"{chunks} chunk(s) per rank", rooms_total=args.rooms or c["rooms"]),
+        "voxels_total": N, "voxels_of_rank0": n_local, "fwd_ms_rank_max": fwd_ms, "bwd_ms_rank_max": bwd_ms,
+        "compute_ms_rank_max": compute_ms, "compute_ms_rank_mean": compute_mean,
+        "exchange_ms_after_overlap": ms_per_step - compute_ms,
+        "exchange": "per chunk: all_gather_into_tensor of the packed out|dq|dk|dv rows (4 x 160 B per voxel), "
+                    "one un-permute gather; all-reduce of the 3 table gradients",
+        "roofline": {"bound": "hbm", "kernel": "attention backward, this rank's windows (tile-pair single-sweep kernel)",
+                     "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": None,
+                     "peak_source": peak_src, "algorithmic_bytes_per_voxel": {"fwd": pv_fwd, "bwd": pv_bwd}},
+        "cpu_baseline": None,
+        "e2e": {"value": N / (e2e_ms * 1e-3), "unit": "voxels/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": int(4 * band_total * Cc * 2), "d2h_bytes_per_step": int(4 * band_total * Cc * 2),
+                "note": "bytes summed over the ranks: each copies the band of voxel rows its windows touch"},
+        "gpu_launches": 3 * chunks * args.steps,   # per chunk: forward single-tile + tiled, backward
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
     return 0
@@ -845,7 +973,9 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="attn", choices=["attn", "knn", "attn-split", "stages", "reference-gpu"])
+    ap.add_argument("--workload", default="attn",
+                    choices=["attn", "attn-replicas", "attn-split", "knn", "stages", "reference-gpu"])
+    ap.add_argument("--chunks", type=int, default=2, help="chunks per rank of the split mode (exchange/compute overlap)")
     ap.add_argument("--rooms", type=int, default=0, help="rooms per GPU (default 8)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -853,8 +983,9 @@ def main():
         return run_reference_arm(args)
     if args.workload == "knn":
         return run_knn(args)
-    if args.workload == "attn-split":
-        return run_attention_split(args)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.workload == "attn-split" or (args.workload == "attn" and world > 1):
+        return run_attention_split(args)      # one batch split over the GPUs (strong scaling)
     if args.workload == "stages":
         return run_stages(args)
     if args.workload == "reference-gpu":

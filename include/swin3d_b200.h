@@ -109,6 +109,15 @@ int s3d_debug_crse_indices_variant(const float *n_coords, const int32_t *table_s
 int s3d_debug_crse_index_values(const float *cq, const float *ck, int64_t n, int L, int last_dim,
                                 int variant, int32_t *idx_out, void *stream);
 
+/* Row gather for the multi-GPU window split: dst[a][i][:] = src_a[idx[i]][:] for A <= 4 per-voxel
+ * arrays that share one index list (rows of row_bytes, a multiple of 16; array a of the result
+ * starts dst_array_stride_bytes after array a-1).  srcs_host: HOST array of A device pointers.
+ * The reference has no multi-GPU code; within one GPU it scatters results through n2n_indices
+ * inside its kernels (Swin3D/src/attn/attn_utils.cuh:391-409), which is what this un-permutation
+ * undoes for rows that arrive from other ranks in window-sorted order.                        */
+int s3d_gather_rows(const void *const *srcs_host, int A, const int64_t *idx, int64_t n_rows,
+                    int64_t row_bytes, void *dst, int64_t dst_array_stride_bytes, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Window builder.  Replaces BasicLayer.get_map_pair / get_window_mapping / get_index01 and
  * sparse_self_attention (Swin3D/modules/swin3d_layers.py:713-822 and :76-150), i.e. the

@@ -1,0 +1,59 @@
+// Row gather: dst[a][i][:] = src_a[idx[i]][:] for up to four per-voxel arrays sharing one index list.
+// Used by the multi-GPU window split to pack a rank's rows into its send buffer and to put gathered
+// rows back into voxel order.  HBM-bound byte work: one thread moves one 16-byte piece of a row, so
+// a warp reads and writes whole 160- to 1280-byte rows in consecutive pieces.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/swin3d_b200.h"
+
+namespace s3d {
+
+struct GatherArgs {
+    const uint4 *src[4];
+    uint4 *dst;
+    const int64_t *idx;
+    int64_t n_rows;
+    int64_t dst_array_stride;   // in 16-byte pieces
+    int ppr;                    // 16-byte pieces per row
+};
+
+__global__ void __launch_bounds__(256) gather_rows_kernel(const GatherArgs a)
+{
+    const uint4 *src = a.src[blockIdx.y];
+    uint4 *dst = a.dst + blockIdx.y * a.dst_array_stride;
+    const int64_t total = a.n_rows * a.ppr;
+    for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = t / a.ppr;
+        const int p = (int)(t - i * a.ppr);
+        dst[t] = __ldg(src + __ldg(a.idx + i) * a.ppr + p);
+    }
+}
+
+}  // namespace s3d
+
+extern "C" int s3d_gather_rows(const void *const *srcs_host, int A, const int64_t *idx, int64_t n_rows,
+                               int64_t row_bytes, void *dst, int64_t dst_array_stride_bytes, void *stream)
+{
+    if (A < 1 || A > 4 || n_rows < 0 || row_bytes <= 0 || (row_bytes & 15) || (dst_array_stride_bytes & 15))
+        return S3D_ERR_BAD_ARG;
+    if (n_rows == 0) return S3D_OK;
+    if (!srcs_host || !idx || !dst || (reinterpret_cast<uintptr_t>(dst) & 15)) return S3D_ERR_BAD_ARG;
+    s3d::GatherArgs a{};
+    for (int i = 0; i < A; ++i) {
+        if (!srcs_host[i] || (reinterpret_cast<uintptr_t>(srcs_host[i]) & 15)) return S3D_ERR_BAD_ARG;
+        a.src[i] = static_cast<const uint4 *>(srcs_host[i]);
+    }
+    a.dst = static_cast<uint4 *>(dst);
+    a.idx = idx;
+    a.n_rows = n_rows;
+    a.dst_array_stride = dst_array_stride_bytes / 16;
+    a.ppr = (int)(row_bytes / 16);
+    const int64_t total = n_rows * a.ppr;
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = 148 * 16;
+    if (blocks > cap) blocks = cap;
+    dim3 grid((unsigned)blocks, (unsigned)A);
+    s3d::gather_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
+}

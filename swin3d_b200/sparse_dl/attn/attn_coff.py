@@ -90,8 +90,10 @@ def _aligned16(*tensors):
     return [t if t.data_ptr() % 16 == 0 else t.clone(memory_format=torch.contiguous_format) for t in tensors]
 
 
-def attn_forward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n_coords):
-    """One fused forward launch.  Tensors must already have the compute dtype.  -> (out, lse)."""
+def attn_forward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n_coords, out=None, lse=None):
+    """One fused forward launch.  Tensors must already have the compute dtype.  -> (out, lse).
+    `out` / `lse` may be given (full-size, contiguous): only the rows of the voxels of the windows
+    in `w_sizes` / `w2n` are written, so a window list can be processed in several calls."""
     import ctypes
     q, k, v, tq, tk, tv = _aligned16(q, k, v, tq, tk, tv)
     N, H, hd = q.shape
@@ -99,8 +101,12 @@ def attn_forward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n
     D = len(sizes)
     if n_coords.shape != (N, D):
         raise ValueError(f"n_coords must have shape [{N}, {D}]")
-    out = torch.empty_like(q)
-    lse = torch.empty((N, H), dtype=torch.float32, device=q.device)
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((N, H), dtype=torch.float32, device=q.device)
+    if out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous() or lse.shape != (N, H):
+        raise ValueError("out / lse buffers must be contiguous and match the query")
     arr = (ctypes.c_int32 * D)(*sizes)
     with torch.cuda.device(q.device):
         st = torch.cuda.current_stream().cuda_stream
@@ -114,14 +120,21 @@ def attn_forward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n
 
 
 def attn_backward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n_coords,
-                      out, lse, dout):
-    """One fused backward launch -> (dq, dk, dv, dtq, dtk, dtv); table grads are fp32."""
+                      out, lse, dout, dq=None, dk=None, dv=None):
+    """One fused backward launch -> (dq, dk, dv, dtq, dtk, dtv); table grads are fp32 (fresh arrays,
+    zeroed by the library).  `dq`, `dk`, `dv` may be given (full-size, contiguous): only the rows of
+    the voxels of the windows in `w_sizes` / `w2n` are written."""
     import ctypes
     q, k, v, tq, tk, tv, out, dout = _aligned16(q, k, v, tq, tk, tv, out, dout)
     N, H, hd = q.shape
     W = w_sizes.shape[0]
     D = len(sizes)
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dq = torch.empty_like(q) if dq is None else dq
+    dk = torch.empty_like(k) if dk is None else dk
+    dv = torch.empty_like(v) if dv is None else dv
+    for t in (dq, dk, dv):
+        if t.shape != q.shape or t.dtype != q.dtype or not t.is_contiguous():
+            raise ValueError("dq / dk / dv buffers must be contiguous and match the query")
     tn = sum(sizes)
     dt = torch.empty((3, tn), dtype=torch.float32, device=q.device)
     arr = (ctypes.c_int32 * D)(*sizes)

@@ -9,7 +9,8 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from oracle import oracle as O
-from swin3d_b200.dist import all_gather_window_rows, allreduce_table_grads, shard_voxel_range, shard_windows
+from swin3d_b200.dist import (ShardPlan, all_gather_window_rows, allreduce_table_grads, exchange_rows,
+                              shard_voxel_range, shard_windows, window_cost)
 from tests.helpers import make_problem
 
 
@@ -114,6 +115,67 @@ def test_all_gather_of_window_shards_reassembles_the_output(world):
     ref, _, _ = O.attn_forward(p.q, p.k, p.v, p.tq, p.tk, p.tv, p.sizes, p.w_sizes, p.w2n, p.n2n, p.n_crse)
     for r in range(world):                  # every rank ends with the full, identical array
         assert np.array_equal(got[r], ref)
+
+
+def _rank_plan_exchange(rank, world, port, chunks, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    p = make_problem(seed=73, n_voxels=800, grid=22, H=2, hd=8, crse="XYZ_RGB")
+    ws, w2n, n2n = torch.from_numpy(p.w_sizes), torch.from_numpy(p.w2n), torch.from_numpy(p.n2n)
+    plan = ShardPlan(ws, w2n, n2n, world, rank, chunks)
+    out = torch.full((p.q.shape[0], p.H, p.hd), float("nan"), dtype=torch.float64)
+    twice = out.clone()
+    for c in range(chunks):                     # this rank's windows only, chunk by chunk
+        a, b = plan.chunk_windows[c]
+        o, _, _ = O.attn_forward(p.q, p.k, p.v, p.tq, p.tk, p.tv, p.sizes, p.w_sizes[a:b], p.w2n[a:b],
+                                 p.n2n, p.n_crse)
+        lo, hi = plan.chunk_rows[c]
+        rows = n2n[lo:hi].long()
+        out[rows] = torch.from_numpy(o)[rows].double()
+        twice[rows] = 2 * out[rows]
+    full, full2 = exchange_rows(plan, [out, twice])
+    q.put((rank, full.numpy(), full2.numpy()))
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("world,chunks", [(2, 1), (2, 2), (3, 2)])
+def test_packed_exchange_of_a_shard_plan_reassembles_every_array(world, chunks):
+    """ShardPlan + exchange_rows: one packed all-gather per chunk, one un-permute; every rank ends
+    with the full arrays although it only ever computed (and holds NaN outside) its own windows."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_plan_exchange, args=(r, world, port, chunks, q)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    got = [q.get(timeout=240) for _ in range(world)]
+    for pr in procs:
+        pr.join(60)
+        assert pr.exitcode == 0
+    p = make_problem(seed=73, n_voxels=800, grid=22, H=2, hd=8, crse="XYZ_RGB")
+    ref, _, _ = O.attn_forward(p.q, p.k, p.v, p.tq, p.tk, p.tv, p.sizes, p.w_sizes, p.w2n, p.n2n, p.n_crse)
+    for _, full, full2 in got:
+        assert np.array_equal(full, ref.astype(np.float64))
+        assert np.array_equal(full2, 2 * ref.astype(np.float64))
+
+
+def test_shard_plan_ranges_follow_the_kernel_cost_model():
+    rng = np.random.default_rng(3)
+    w = rng.integers(1, 126, size=4000)
+    w2n = np.cumsum(w) - w
+    n2n = rng.permutation(int(w.sum()))
+    plans = [ShardPlan(torch.from_numpy(w), torch.from_numpy(w2n), torch.from_numpy(n2n), 4, r, 2) for r in range(4)]
+    cost = window_cost(w)
+    shares = [sum(int(cost[a:b].sum()) for a, b in pl.chunk_windows) for pl in plans]
+    assert sum(shares) == int(cost.sum())
+    assert max(shares) <= cost.sum() / 4 + 2 * cost.max()
+    # chunk c of every rank has the same padded size, and the chunks of a rank tile its range
+    assert all(pl.pad == plans[0].pad for pl in plans)
+    for r, pl in enumerate(plans):
+        assert pl.chunk_windows[0][0] == pl.parts[r][0] and pl.chunk_windows[-1][1] == pl.parts[r][1]
+        assert pl.chunk_windows[0][1] == pl.chunk_windows[1][0]
 
 
 def test_all_gather_window_rows_single_process_unpermutes():
