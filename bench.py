@@ -747,35 +747,83 @@ def run_stages(args):
     return 0
 
 
-def run_knn(args):
-    """Secondary workload: KNN stress (200k queries x 50k sources per scene, 8 scenes, K=16 and 3)."""
+def measure_fp32_fma_peak():
+    """TFLOP/s of eight independent FFMA chains per thread on every SM (CUDA events, best of 3)."""
     import torch
+    from swin3d_b200 import _lib
+    blocks, iters = 148 * 2 * 8, 4096
+    out = torch.empty(blocks * 1024, dtype=torch.float32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    best = 0.0
+    for _ in range(4):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _lib.check(_lib.lib.s3d_debug_ffma_probe(out.data_ptr(), blocks, iters, st), "s3d_debug_ffma_probe")
+        e1.record()
+        torch.cuda.synchronize()
+        best = max(best, blocks * 1024 * iters * 8 * 2 / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    return best
+
+
+def run_knn(args):
+    """Secondary workload: KNN stress (200k queries x 50k sources per scene, 8 scenes, K=16 and 3).
+    With N > 1 ranks the query list is split into equal contiguous ranges (every rank holds the source
+    points), the [Nq_r, K] results are all-gathered inside the timed region; rank 0 checks that the
+    gathered result equals its own unsplit run bit for bit."""
+    import torch
+    import torch.distributed as dist
     from swin3d_b200 import synthetic as S
+    from swin3d_b200.dist import sharded_knn
     from swin3d_b200.sparse_dl.knn.knn import knn_raw
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-    scenes = [S.make_knn_scene(100 * rank + s, 200_000, 50_000) for s in range(8)]
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    scenes = [S.make_knn_scene(s, 200_000, 50_000) for s in range(8)]         # the same scenes on every rank
     src = torch.from_numpy(np.concatenate([s for s, _ in scenes])).cuda()
     qry = torch.from_numpy(np.concatenate([q for _, q in scenes])).cuda()
     so = torch.arange(1, 9, dtype=torch.int32, device="cuda") * 50_000
     qo = torch.arange(1, 9, dtype=torch.int32, device="cuda") * 200_000
-    res = {}
+    fma_peak = measure_fp32_fma_peak()
+    res = {"fp32_fma_peak_measured_tflops": fma_peak}
     for K in (16, 3):
         for _ in range(max(args.warmup, 1)):
-            knn_raw(K, src, qry, so, qo)
+            got = sharded_knn(K, src, qry, so, qo)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         e0.record()
         for _ in range(args.steps):
-            knn_raw(K, src, qry, so, qo)
+            got = sharded_knn(K, src, qry, so, qo)
         e1.record()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / args.steps
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        if world > 1 and rank == 0:
+            ref = knn_raw(K, src, qry, so, qo)
+            if not (torch.equal(got[0], ref[0]) and torch.equal(got[1].view(torch.int32), ref[1].view(torch.int32))):
+                raise RuntimeError("sharded KNN differs from the single-GPU result")
         evals = 8 * 200_000 * 50_000 / (ms * 1e-3)
-        # 8 fp32 operations per candidate (3 sub, 1 mul, 2 fma); nominal CUDA-core peak of a B200:
-        # 148 SMs x 128 lanes x 2 x 1.965 GHz = 74.4 TFLOP/s (no measured figure is recorded)
+        # 8 fp32 operations per candidate (3 sub, 1 mul, 2 fma) against the measured FFMA throughput of
+        # all ranks (nominal CUDA-core peak of one B200: 148 SMs x 128 lanes x 2 x 1.965 GHz = 74.4 TFLOP/s)
         res[f"K{K}"] = {"ms": ms, "queries_per_s": qry.shape[0] / (ms * 1e-3), "pair_evals_per_s": evals,
-                        "fp32_tflops": evals * 8 / 1e12, "frac_of_nominal_fp32_peak": evals * 8 / 74.4e12}
+                        "fp32_tflops": evals * 8 / 1e12,
+                        "frac_of_measured_fp32_peak": evals * 8 / 1e12 / (fma_peak * world),
+                        "frac_of_nominal_fp32_peak": evals * 8 / (74.4e12 * world)}
+    if world > 1:
+        if rank == 0:
+            print(json.dumps({"metric": "knn queries/sec (8 scenes x 200k queries x 50k sources)",
+                              "unit": "queries/s", "value": res["K16"]["queries_per_s"], "detail": res,
+                              "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "data": "synthetic",
+                              "dtype": "f32", "higher_is_better": True, "scaling": "strong",
+                              "partition": "queries in equal contiguous ranges, results all-gathered, bit-exact check on rank 0"}))
+        dist.destroy_process_group()
+        return 0
     # consumers of the K=3 result: inverse-distance interpolation fwd+bwd, C = 160 (HBM-bound gathers);
     # algorithmic bytes per query: K gathered rows + the output row + K (index, distance) pairs,
     # backward: the dOut row + K read-modify-writes of source rows

@@ -87,6 +87,18 @@ int s3d_attn_bwd(const void *q, const void *k, const void *v,
                  void *dq, void *dk, void *dv, float *dtq, float *dtk, float *dtv,
                  void *stream);
 
+/* fp32 FMA throughput probe (the roofline denominator of the KNN kernel, which stays on the CUDA cores
+ * because its distance expression must match the reference bit for bit): launches `blocks` blocks
+ * of 1024 threads, each thread running 8 independent chains of `iters` fused multiply-adds; the caller
+ * times it.  out: float[blocks * 1024].  Replaces nothing in the reference.                      */
+int s3d_debug_ffma_probe(float *out, int blocks, int iters, void *stream);
+
+/* Debug switch: on != 0 routes every later attention call of this process to the generic kernels
+ * (any window size, head_dim 8/16/32, fp32 arithmetic) instead of the tensor-core kernels, so that
+ * the two implementations can be compared on the same GPU; returns the previous setting.
+ * Replaces nothing in the reference.                                                          */
+int s3d_debug_force_generic(int on);
+
 /* Dump of the cRSE row indices idx[q,k,n] of one window (for bit-exact index tests).
  * Replaces nothing callable in the reference; it exposes PositionEmbedding::set_qk_offset
  * (Swin3D/src/attn/attn_utils.cuh:437-453).  idx_out: int32[n*n*D], n = w_sizes[window].    */
@@ -144,7 +156,7 @@ int s3d_window_build(const int32_t *coords, const float *feats, int64_t N, int F
 
 /* Window builder for callers that cannot allocate device memory (no counterpart in the
  * reference, whose builder allocates freely through PyTorch).  Same inputs, outputs and results as
- * s3d_window_build, but the scratch memory is a fixed 4.25 MiB array that is part of the library
+ * s3d_window_build, but the scratch memory is a fixed 4.07 MiB array (the scratch layout of the largest accepted call) that is part of the library
  * image on every GPU that loads it, so neither the caller nor the library allocates anything: no
  * cudaMalloc, no cudaFree, no allocating library routine.  Meant for hosts whose memory is
  * frozen after start-up (an inference server that gave its arena every spare byte) or that

@@ -9,7 +9,8 @@ the repository, rewrites `.type()` to `.scalar_type()` at exactly those call sit
 compiles them (nvcc, no GPU needed) together with oracle/ref_binding/ref_aio_api.cpp into
 oracle/_ref/ref_swin3d_cuda.so.  No reference source is written into this repository.
 
-Usage:  python oracle/build_ref.py [--reference /path/to/Swin3D-checkout]
+Usage:  python oracle/build_ref.py [--reference /path/to/Swin3D-checkout]   (default: $SWIN3D_REFERENCE,
+        else a directory `reference` beside this repository)
 The product never loads the result; only tests/ and bench.py's reference-kernel timing do.
 
 Safe-use note for callers: the reference forward kernel keeps a `__shared__ scalar_t[32]`
@@ -32,6 +33,12 @@ NAME = "ref_swin3d_cuda"
 ATTN_FILES = ["self_attn_aio_fwd.cu", "self_attn_aio_fwd.h", "self_attn_aio_bwd.cu",
               "self_attn_aio_bwd.h", "attn_utils.cuh", "torch_utils.h"]
 KNN_FILES = ["knn_cuda_kernel.cu", "knn_cuda_kernel.h", "cuda_utils.cuh", "torch_utils.h"]
+
+
+def default_reference_root() -> str:
+    """$SWIN3D_REFERENCE, else a directory `reference` beside this repository."""
+    env = os.environ.get("SWIN3D_REFERENCE")
+    return env if env else os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
 
 
 def stage_sources(ref_root: str, scratch: str):
@@ -73,7 +80,8 @@ def build(ref_root: str, verbose: bool = True) -> str:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=default_reference_root(),
+                    help="checkout of microsoft/Swin3D (default: $SWIN3D_REFERENCE, else ../reference beside this repository)")
     a = ap.parse_args()
     if not os.path.isdir(os.path.join(a.reference, "Swin3D", "src", "attn")):
         print("reference checkout not found at", a.reference, "- nothing built")

@@ -22,6 +22,8 @@ SIGNATURES = {
     "s3d_status_string": (ctypes.c_char_p, [_i32]),
     "s3d_version": (_i32, []),
     "s3d_last_cuda_error_string": (ctypes.c_char_p, []),
+    "s3d_debug_force_generic": (_i32, [_i32]),
+    "s3d_debug_ffma_probe": (_i32, [_c_void_p, _i32, _i32, _c_void_p]),
     "s3d_attn_fwd": (_i32, [_c_void_p] * 6 + [_c_void_p, _i32] + [_c_void_p] * 4 +
                      [_i64, _i64, _i32, _i32, _i32, _c_void_p, _c_void_p, _c_void_p]),
     "s3d_attn_bwd": (_i32, [_c_void_p] * 6 + [_c_void_p, _i32] + [_c_void_p] * 4 +

@@ -170,6 +170,111 @@ __device__ __forceinline__ int table_row(const CrseMeta &im, int r)
     return r < im.R ? r - n : -1;
 }
 
+// Row numbering of the single-tile kernels.  Within a window the cRSE indices of a signal dimension
+// rarely leave a narrow band around L/2 (voxels of a planar patch share one cell coordinate, colours
+// lie in [0,1], normals vary slowly), so a window touches well under half of the table rows.  The
+// rows are therefore numbered so that the bands ("centres") of all dimensions come first, followed by
+// the remaining rows ("periphery") dimension by dimension; a window then touches few 16-row tiles,
+// and every per-tile piece of work (projection, clearing, table-gradient and hist.T products) is
+// skipped for tiles outside the index ranges of the window, which the producer warp derives from the
+// minima and maxima of the coordinates (the index is monotone in both coordinates).  Skipping is
+// exact: a skipped tile is neither written nor read.  As in internal_meta(), index L of a dimension
+// but the last is a row of its own (an alias of row 0 of the next dimension).
+struct PermMeta {
+    int D, R;                                  // R = internal rows
+    int n[S3D_MAX_SIGNAL_DIMS];                // index values of the dimension: L + 1 (L for the last)
+    int c0[S3D_MAX_SIGNAL_DIMS], c1[S3D_MAX_SIGNAL_DIMS];       // centre = indices [c0, c1)
+    int cbase[S3D_MAX_SIGNAL_DIMS], pbase[S3D_MAX_SIGNAL_DIMS]; // first internal row of the centre / periphery
+    int tbase[S3D_MAX_SIGNAL_DIMS];            // first table row of the dimension
+    int lut_stride;                            // entries per dimension of the index -> row table
+};
+
+__host__ inline PermMeta make_perm_meta(const CrseMeta &m)
+{
+    PermMeta p{};
+    p.D = m.D;
+    const int quant = m.D >= 6 ? m.L[3] / 8 : 0;             // colour / normal tables have 8 * quant rows
+    int rows = 0, mx = 0;
+    for (int d = 0; d < m.D; ++d) {
+        const int L = m.L[d];
+        p.n[d] = d == m.D - 1 ? L : L + 1;
+        p.tbase[d] = m.rowbase[d];
+        int half = d < 3 ? (quant > 0 ? quant : (L + 9) / 10) : (d >= 6 ? 2 : L / 4);
+        if (half < 1) half = 1;
+        p.c0[d] = L / 2 - half < 0 ? 0 : L / 2 - half;
+        p.c1[d] = d < 3 ? L / 2 + half : L / 2 + half + 1;
+        if (p.c1[d] > p.n[d]) p.c1[d] = p.n[d];
+        p.cbase[d] = rows;
+        rows += p.c1[d] - p.c0[d];
+        if (p.n[d] > mx) mx = p.n[d];
+    }
+    for (int d = 0; d < m.D; ++d) {
+        p.pbase[d] = rows;
+        rows += p.n[d] - (p.c1[d] - p.c0[d]);
+    }
+    p.R = rows;
+    p.lut_stride = (mx + 7) / 8 * 8;
+    return p;
+}
+
+// internal row of (dimension, index)
+__host__ __device__ __forceinline__ int perm_row(const PermMeta &p, int d, int idx)
+{
+    if (idx >= p.c0[d] && idx < p.c1[d]) return p.cbase[d] + idx - p.c0[d];
+    return p.pbase[d] + (idx < p.c0[d] ? idx : idx - (p.c1[d] - p.c0[d]));
+}
+
+// table row an internal row stands for (-1 past the end); an alias row stands for row 0 of the next dimension
+__device__ __forceinline__ int perm_table_row(const PermMeta &p, int r)
+{
+    if (r >= p.R || r < 0) return -1;
+    for (int d = 0; d < p.D; ++d) {
+        const int nc = p.c1[d] - p.c0[d];
+        int idx = -1;
+        if (r >= p.cbase[d] && r < p.cbase[d] + nc) idx = p.c0[d] + r - p.cbase[d];
+        else if (r >= p.pbase[d] && r < p.pbase[d] + p.n[d] - nc) {
+            const int rel = r - p.pbase[d];
+            idx = rel < p.c0[d] ? rel : rel + nc;
+        }
+        if (idx >= 0) return p.tbase[d] + idx;      // idx == L: tbase[d] + L = tbase[d+1], row 0 of the next dimension
+    }
+    return -1;
+}
+
+// index -> internal row table in shared memory: lut[d * lut_stride + idx]
+__device__ __forceinline__ void fill_perm_lut(uint16_t *lut, const PermMeta &p, int tid, int nthreads)
+{
+    for (int i = tid; i < p.D * p.lut_stride; i += nthreads) {
+        const int d = i / p.lut_stride, idx = i - d * p.lut_stride;
+        lut[i] = (uint16_t)(idx < p.n[d] ? perm_row(p, d, idx) : 0);
+    }
+}
+
+// Order-preserving integer key of a finite float (for the warp-wide integer min / max reductions).
+__device__ __forceinline__ int float_order_key(float x)
+{
+    const int i = __float_as_int(x);
+    return i < 0 ? i ^ 0x7fffffff : i;
+}
+__device__ __forceinline__ float float_from_order_key(int k)
+{
+    return __int_as_float(k < 0 ? k ^ 0x7fffffff : k);
+}
+
+// Bit t set: 16-row tile t holds a row that the index range [lo, hi] of dimension d can reach.
+// Warp-wide: lane l looks at the indices l and l + 32 through the index -> row table (at most 64
+// index values per dimension) and the bits are OR-reduced; every lane returns the mask.
+__device__ __forceinline__ uint32_t perm_tile_mask_warp(const uint16_t *lut_d, int n_d, int lo, int hi, int lane)
+{
+    uint32_t m = 0;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int idx = lane + 32 * k;
+        if (idx >= lo && idx <= hi && idx < n_d) m |= 1u << (lut_d[idx] >> 4);
+    }
+    return __reduce_or_sync(0xffffffffu, m);
+}
+
 // Head modes of the tiled kernels.  A thread block always works on two "slots" packed as half2:
 //   HDM_PAIR8   head_dim 8 : slots = heads 2hp, 2hp+1, 8 channels each, one plane
 //   HDM_SINGLE16 head_dim 16: slots = the two 8-channel halves of head hp (partial scores are summed)

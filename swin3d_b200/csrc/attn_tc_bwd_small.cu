@@ -64,10 +64,10 @@ __host__ __device__ constexpr int bwd_small_warps(int D) { return D == 9 ? 15 : 
 
 struct SmallSmem {
     int R16, Rp;
-    int off_pq, off_db, off_pk, off_s0, off_pl, off_rows, off_c, off_pg, off_ta, off_tb, off_misc, total;
+    int off_pq, off_db, off_pk, off_s0, off_pl, off_rows, off_c, off_pg, off_ta, off_tb, off_lut, off_misc, total;
 };
 
-__host__ __device__ inline SmallSmem make_small_layout(int R, int nw)
+__host__ __device__ inline SmallSmem make_small_layout(int R, int nw, int lut_entries)
 {
     SmallSmem L;
     L.R16 = (R + 15) / 16 * 16;
@@ -89,6 +89,7 @@ __host__ __device__ inline SmallSmem make_small_layout(int R, int nw)
     L.off_pg = off; off += 3 * 2048;                               // dQ, dV, dK of the pair GEMMs
     L.off_ta = off; off += 3 * (L.R16 / 16) * 512;                 // Tq, Tv, Tk as A fragments of the projections
     L.off_tb = off; off += 2 * (L.R16 / 16) * 512;                 // Tq and Tk as B fragments of the hist.T products
+    L.off_lut = off; off += (lut_entries * 2 + 15) / 16 * 16;      // index -> internal row, per dimension
     L.off_misc = off; off += 2048;
     L.total = off;
     return L;
@@ -111,10 +112,11 @@ __device__ int g_bwd_small_async_error;
 
 template <int D, int NPU /*projection + dT units per warp*/, int NHU /*hist.T units per warp*/, bool HD16>
 __global__ void __launch_bounds__((bwd_small_warps(D) + 1) * 32, 1)
-attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts pc)
+attn_bwd_small_kernel(const SmallParams P, const PermMeta pm, const PairConsts pc)
 {
     constexpr int NW = bwd_small_warps(D);       // consumer warps
     constexpr int NT = NW * 32;
+    constexpr int TG = NW / 3;                   // warps per table (projection and table-gradient units)
     constexpr int NKW = (D + 1) / 2;             // warps of the key-side histogram, two dimensions each
     constexpr int GEMM_WARP = D + NKW;           // dQ and dK pair GEMMs
     constexpr int DV_WARP = (D & 1) ? D + NKW - 1 : D + NKW + 1;   // dV: the key-side warp with one dimension, or a spare one
@@ -122,7 +124,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
     constexpr int SG = NW / 2;                   // warps per hist.T side
     constexpr int KPW = (QT + NW - 1) / NW;      // keys per warp in the score phase
     extern __shared__ __align__(16) unsigned char smem[];
-    const SmallSmem L = make_small_layout(meta.R, NW);
+    const SmallSmem L = make_small_layout(pm.R, NW, pm.D * pm.lut_stride);
     uint32_t *s_pq = reinterpret_cast<uint32_t *>(smem + L.off_pq);
     uint32_t *s_db = reinterpret_cast<uint32_t *>(smem + L.off_db);
     uint32_t *s_pk = reinterpret_cast<uint32_t *>(smem + L.off_pk);
@@ -136,11 +138,12 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
     uint4 *s_ta = reinterpret_cast<uint4 *>(smem + L.off_ta);           // [Tq, Tv, Tk][row tile][lane]
     float *s_pg = reinterpret_cast<float *>(smem + L.off_pg);           // [3][32][16]
     uint4 *s_tb = reinterpret_cast<uint4 *>(smem + L.off_tb);           // [Tq, Tk][k-step][lane]
+    uint16_t *s_lut = reinterpret_cast<uint16_t *>(smem + L.off_lut);   // [dimension][index] -> internal row
     float *s_lses = reinterpret_cast<float *>(smem + L.off_misc);       // [stage][32][2]
     float *s_dels = s_lses + BS_STAGES * 64;                            // [stage][32][2]
     int *s_rowi = reinterpret_cast<int *>(s_dels + BS_STAGES * 64);     // [stage][query tile, key tile][32]
-    int *s_n = s_rowi + BS_STAGES * 64;                                 // [stage][4]: nq, nk, j > 0, i > 0 ; nq = 0: no more items
-    int *s_fail = s_n + BS_STAGES * 4;
+    int *s_n = s_rowi + BS_STAGES * 64;                                 // [stage][8]: nq, nk, j > 0, i > 0, used tiles ; nq = 0: no more items
+    int *s_fail = s_n + BS_STAGES * 8;
     uint64_t *s_full = reinterpret_cast<uint64_t *>(smem + L.off_misc + 1792);   // [stage]
     uint64_t *s_empty = s_full + BS_STAGES;
 
@@ -157,6 +160,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
         *s_fail = 0;
         mbar_init_fence();
     }
+    fill_perm_lut(s_lut, pm, tid, blockDim.x);
     // ---- this block's windows: a contiguous range of equal cost --------------------------------------------------
     // cost of a window = its number of tile pairs; every block scans all window sizes (a few hundred KB
     // from L2) and takes the range whose cumulative cost falls into its share, so the assignment is
@@ -217,11 +221,22 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
 
     if (wid == NW) {
         // ================================ producer warp ================================================
+        // Software-pipelined so that no load is consumed right after it is issued: the sizes of the next
+        // window are fetched when a window is opened, the row numbers and coordinates of the next item
+        // (indexed by sorted position) at the end of the current iteration, and only lse / dO / O (indexed
+        // by the row number) inside the iteration, under the tile-mask arithmetic.
         int64_t w = w_begin - 1;
         int n = 0, base = 0, nt = 0, ts = 0, ti = 0, tj = 0;
+        int n_nx = 0, base_nx = 0;                         // sizes of window w + 1
+        if (w_begin < w_end) {
+            n_nx = __ldg(P.w_sizes + w_begin);
+            base_nx = __ldg(P.w2n + w_begin);
+        }
         bool have = false;
-        for (int it = 0;; ++it) {
-            // next item: key tiles inner, query tiles outer, then the block's next window
+        int nq = 0, nk = 0, rowq = 0, rowk = 0;
+        float cq[D], ck[D];
+        // descriptor of the next item and the loads that depend on the sorted position only
+        auto advance = [&]() {
             if (have && tj + 1 < nt) {
                 ++tj;
             } else if (have && ti + 1 < nt) {
@@ -231,18 +246,21 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                 ++w;
                 have = w < w_end;
                 if (have) {
-                    n = __ldg(P.w_sizes + w);
-                    base = __ldg(P.w2n + w);
+                    n = n_nx;
+                    base = base_nx;
+                    if (w + 1 < w_end) {
+                        n_nx = __ldg(P.w_sizes + w + 1);
+                        base_nx = __ldg(P.w2n + w + 1);
+                    }
                     nt = (n + QT - 1) / QT;
-                    ts = (n + nt - 1) / nt;          // equal tiles of at most QT voxels
+                    ts = nt > 0 ? (n + nt - 1) / nt : 0;      // equal tiles of at most QT voxels
                     ti = tj = 0;
                     have = n > 0;
                 }
             }
-            int nq = have ? min(ts, n - ti * ts) : 0, nk = have ? min(ts, n - tj * ts) : 0;
-            int rowq = 0, rowk = 0;
-            float cq[D], ck[D];
-            float ls0 = 0.f, ls1 = 0.f, de0 = 0.f, de1 = 0.f;
+            nq = have ? min(ts, n - ti * ts) : 0;
+            nk = have ? min(ts, n - tj * ts) : 0;
+            rowq = rowk = 0;
 #pragma unroll
             for (int d = 0; d < D; ++d) cq[d] = ck[d] = 0.f;
             if (lane < nq) {
@@ -250,33 +268,59 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                 rowq = __ldg(P.n2n + pos);
 #pragma unroll
                 for (int d = 0; d < D; ++d) cq[d] = __ldg(P.n_coords + (int64_t)pos * D + d);
-                if (HD16) {
-                    ls0 = ls1 = __ldg(P.lse + (int64_t)rowq * H + hp);
-                } else {
-                    ls0 = __ldg(P.lse + (int64_t)rowq * H + 2 * hp);
-                    ls1 = __ldg(P.lse + (int64_t)rowq * H + 2 * hp + 1);
-                }
-                // delta[slot] = sum_c dO . O over the eight channels of the slot
-                const uint4 *gd = reinterpret_cast<const uint4 *>(P.dout + (int64_t)rowq * HC + co);
-                const uint4 *go = reinterpret_cast<const uint4 *>(P.o + (int64_t)rowq * HC + co);
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint4 a = __ldg(gd + h), b = __ldg(go + h);
-                    const __half2 *a2 = reinterpret_cast<const __half2 *>(&a), *b2 = reinterpret_cast<const __half2 *>(&b);
-                    float acc = 0.f;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
-                        acc += fa.x * fb.x + fa.y * fb.y;
-                    }
-                    if (h == 0) de0 = acc; else de1 = acc;
-                }
             }
             if (lane < nk) {
                 const int pos = base + tj * ts + lane;
                 rowk = __ldg(P.n2n + pos);
 #pragma unroll
                 for (int d = 0; d < D; ++d) ck[d] = __ldg(P.n_coords + (int64_t)pos * D + d);
+            }
+        };
+        advance();
+        for (int it = 0;; ++it) {
+            float ls0 = 0.f, ls1 = 0.f, de0 = 0.f, de1 = 0.f;
+            uint4 gdo[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)}, go[2] = {gdo[0], gdo[0]};
+            if (lane < nq) {
+                if (HD16) {
+                    ls0 = ls1 = __ldg(P.lse + (int64_t)rowq * H + hp);
+                } else {
+                    ls0 = __ldg(P.lse + (int64_t)rowq * H + 2 * hp);
+                    ls1 = __ldg(P.lse + (int64_t)rowq * H + 2 * hp + 1);
+                }
+                const uint4 *gd = reinterpret_cast<const uint4 *>(P.dout + (int64_t)rowq * HC + co);
+                const uint4 *gg = reinterpret_cast<const uint4 *>(P.o + (int64_t)rowq * HC + co);
+                gdo[0] = __ldg(gd); gdo[1] = __ldg(gd + 1);
+                go[0] = __ldg(gg); go[1] = __ldg(gg + 1);
+            }
+            // tiles this item can touch: index range of every dimension from the coordinate extrema
+            uint32_t used = 0;
+            {
+                bool odd = false;           // a NaN or infinite coordinate: no range argument, use every tile
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    odd = odd || (lane < nq && !(fabsf(cq[d]) < INFINITY)) || (lane < nk && !(fabsf(ck[d]) < INFINITY));
+                    const int kq = float_order_key(cq[d]), kk = float_order_key(ck[d]);
+                    const float qmn = float_from_order_key(__reduce_min_sync(0xffffffffu, lane < nq ? kq : 0x7fffffff));
+                    const float qmx = float_from_order_key(__reduce_max_sync(0xffffffffu, lane < nq ? kq : (int)0x80000000));
+                    const float kmn = float_from_order_key(__reduce_min_sync(0xffffffffu, lane < nk ? kk : 0x7fffffff));
+                    const float kmx = float_from_order_key(__reduce_max_sync(0xffffffffu, lane < nk ? kk : (int)0x80000000));
+                    const int lo = (int)crse_index_pc(qmn, kmx, pc.half[d], pc.clamp[d]);
+                    const int hi = (int)crse_index_pc(qmx, kmn, pc.half[d], pc.clamp[d]);
+                    used |= perm_tile_mask_warp(s_lut + d * pm.lut_stride, pm.n[d], lo, hi, lane);
+                }
+                if (__any_sync(0xffffffffu, odd)) used = 0xffffffffu;
+            }
+            // delta[slot] = sum_c dO . O over the eight channels of the slot
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const __half2 *a2 = reinterpret_cast<const __half2 *>(&gdo[h]), *b2 = reinterpret_cast<const __half2 *>(&go[h]);
+                float acc = 0.f;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float2 fa = __half22float2(a2[c]), fb = __half22float2(b2[c]);
+                    acc += fa.x * fb.x + fa.y * fb.y;
+                }
+                if (h == 0) de0 = acc; else de1 = acc;
             }
             const int s = it % BS_STAGES;
             if (it >= BS_STAGES && !mbar_wait(s_empty + s, ((it / BS_STAGES) - 1) & 1)) {
@@ -303,10 +347,11 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                     *reinterpret_cast<uint4 *>(rq + a * 512 + lane * 16 + 8) = make_uint4(0, 0, 0, 0);
                 }
             if (lane == 0) {
-                s_n[s * 4] = nq;
-                s_n[s * 4 + 1] = nk;
-                s_n[s * 4 + 2] = tj > 0;
-                s_n[s * 4 + 3] = ti > 0;
+                s_n[s * 8] = nq;
+                s_n[s * 8 + 1] = nk;
+                s_n[s * 8 + 2] = tj > 0;
+                s_n[s * 8 + 3] = ti > 0;
+                s_n[s * 8 + 4] = (int)used;
             }
             async_proxy_fence();
             __syncwarp();
@@ -323,6 +368,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                 bulk_copy_g2s(rq + 1536 + lane * 16, P.v + off, 32, s_full + s);
             }
             if (nq == 0) break;
+            advance();                                    // the next item's position-indexed loads fly during the wait above
         }
         return;
     }
@@ -333,10 +379,12 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
     const int mypos = qpos(lane);
     constexpr float LOG2E = 1.4426950408889634f;
 
-    // (table, row tile) units of this warp, for the projections and the table gradients: u = wid NPU + i,
-    // table = u / n_mt: 0 = Tq with Q (-> P_q, dTq), 1 = Tv with dO (-> dB, dTv), 2 = Tk with K (-> P_k, dTk).
-    // Consecutive units mostly share their table, so the B fragments of a feature array are rebuilt
-    // only where the table changes.
+    // (table, row tile) units of this warp, for the projections and the table gradients: the warps are
+    // split into three groups, one per table -- 0 = Tq with Q (-> P_q, dTq), 1 = Tv with dO (-> dB, dTv),
+    // 2 = Tk with K (-> P_k, dTk) -- so a warp builds the B fragments of one feature array only, and
+    // the tiles are dealt round-robin inside a group (tile = wsub + TG i), so that the tiles a window
+    // leaves out (see PermMeta) thin out every warp's share alike.
+    const int tg = wid / TG, wsub = wid - tg * TG;
     // The A fragments of the table slices are built once per block and kept in shared memory (one
     // 16-byte load per unit and window); the table-gradient accumulators stay in registers.
     float dt_acc[NPU][2][4];
@@ -347,7 +395,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
     for (int u = wid; u < 3 * n_mt; u += NW) {
         const int tab = u / n_mt, mt = u - tab * n_mt;
         const __half *T = tab == 0 ? P.tq : (tab == 1 ? P.tv : P.tk);
-        const int r0 = table_row(meta, mt * 16 + g), r1 = table_row(meta, mt * 16 + g + 8);
+        const int r0 = perm_table_row(pm, mt * 16 + g), r1 = perm_table_row(pm, mt * 16 + g + 8);
         uint32_t f[2][2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -368,8 +416,8 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
         for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const int ra = table_row(meta, ks * 16 + ht_krow(t, half, 0));
-                const int rb = table_row(meta, ks * 16 + ht_krow(t, half, 1));
+                const int ra = perm_table_row(pm, ks * 16 + ht_krow(t, half, 0));
+                const int rb = perm_table_row(pm, ks * 16 + ht_krow(t, half, 1));
                 const __half lo = ra >= 0 ? T[(int64_t)ra * HC + co + h * 8 + g] : __float2half(0.f);
                 const __half hi = rb >= 0 ? T[(int64_t)rb * HC + co + h * 8 + g] : __float2half(0.f);
                 f[h][half] = h2_as_u32(__halves2half2(lo, hi));
@@ -388,8 +436,9 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
         }
         consumer_sync<NT>();          // the previous window's stores are over; the flag is settled
         S3D_PHASE_MARK(0)
-        const int nq = s_n[s * 4], nk = s_n[s * 4 + 1];
-        const bool add_q = s_n[s * 4 + 2] != 0, add_k = s_n[s * 4 + 3] != 0;   // not the first share of dQ / of dK, dV
+        const int nq = s_n[s * 8], nk = s_n[s * 8 + 1];
+        const bool add_q = s_n[s * 8 + 2] != 0, add_k = s_n[s * 8 + 3] != 0;   // not the first share of dQ / of dK, dV
+        const uint32_t used = (uint32_t)s_n[s * 8 + 4];                        // tiles this item can touch
         if (nq == 0 || *s_fail) break;
         const __half *s_q = s_rows + s * 2048, *s_do = s_q + 512, *s_k = s_q + 1024, *s_v = s_q + 1536;
         const float *s_c = s_cs + s * 768, *s_ck = s_c + 384;
@@ -398,21 +447,17 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
         float cx[D];
         load_coords12<D>(s_c + lane * 12, cx);
         // ---- projections P_q, dB (lane-major), P_k (key-major); S0 = K.Q^T and dPV0 = V.dO^T -----------------
-        if (S3D_KEEP(0)) {
+        if (tg < 3 && S3D_KEEP(0)) {
             uint32_t bf[8][2];
-            int have = -1;
+            load_feat_bfrag(bf, tg == 0 ? s_q : (tg == 1 ? s_do : s_k), tg == 2 ? nk : nq, g, t);
 #pragma unroll
             for (int i = 0; i < NPU; ++i) {
-                const int u = wid * NPU + i, tab = u / n_mt, mt = u - tab * n_mt;
-                if (tab < 3) {
-                    if (tab != have) {
-                        load_feat_bfrag(bf, tab == 0 ? s_q : (tab == 1 ? s_do : s_k), tab == 2 ? nk : nq, g, t);
-                        have = tab;
-                    }
-                    const uint4 f = s_ta[u * 32 + lane];
+                const int mt = wsub + TG * i;
+                if (mt < n_mt && ((used >> mt) & 1u)) {
+                    const uint4 f = s_ta[(tg * n_mt + mt) * 32 + lane];
                     const uint32_t taf[2][2] = {{f.x, f.y}, {f.z, f.w}};
-                    if (tab == 0) project_unit_b<true>(taf, bf, s_pq, mt, Rp, nq, g, t);
-                    else if (tab == 1) project_unit_b<true>(taf, bf, s_db, mt, Rp, nq, g, t);
+                    if (tg == 0) project_unit_b<true>(taf, bf, s_pq, mt, Rp, nq, g, t);
+                    else if (tg == 1) project_unit_b<true>(taf, bf, s_db, mt, Rp, nq, g, t);
                     else project_unit_b<false>(taf, bf, s_pk, mt, Rp, nk, g, t);
                 }
             }
@@ -456,7 +501,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
 #pragma unroll
                         for (int d = 0; d < D; ++d) {
                             const uint32_t idx = crse_index_pc(cx[d], ck[d], pc.half[d], pc.clamp[d]);
-                            const uint32_t row = meta.rowbase[d] + idx;
+                            const uint32_t row = s_lut[d * pm.lut_stride + idx];
                             b0 = __hadd2(b0, u32_as_h2(pq_lane[row * QT]));
                             b1 = __hadd2(b1, u32_as_h2(pk_row[row]));
                             b2 = __hadd2(b2, u32_as_h2(db_lane[row * QT]));
@@ -486,8 +531,13 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
         consumer_sync<NT>();
         S3D_PHASE_MARK(2)
         // ---- clear the three histograms (P_q, dB, P_k are dead) ------------------------------------------------
-        for (int i = tid; i < 3 * L.R16 * QT / 4; i += NT)
-            reinterpret_cast<uint4 *>(s_hq)[i] = make_uint4(0, 0, 0, 0);     // the three arrays are adjacent
+        for (int i = tid; i < L.R16 * QT / 4; i += NT)                       // 128 16-byte pieces per 16-row tile
+            if ((used >> (i >> 7)) & 1u) {
+                uint4 *h = reinterpret_cast<uint4 *>(s_hq) + i;              // the three arrays are adjacent
+                h[0] = make_uint4(0, 0, 0, 0);
+                h[L.R16 * QT / 4] = make_uint4(0, 0, 0, 0);
+                h[2 * (L.R16 * QT / 4)] = make_uint4(0, 0, 0, 0);
+            }
         consumer_sync<NT>();
         S3D_PHASE_MARK(3)
         // ---- histograms and pair GEMMs ------------------------------------------------------------------------
@@ -498,13 +548,14 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                 const bool lo = d < 5;
                 const int sh = IDX_BITS * (lo ? d : d - 5);
                 const uint32_t *pcol = s_P + lane, *dcol = s_DS + lane, *wcol = (lo ? s_W0 : s_W1) + lane;
-                uint32_t *cell = s_hq + meta.rowbase[d] * QT + mypos;
+                const uint16_t *lut = s_lut + d * pm.lut_stride;
+                uint32_t *cell = s_hq + mypos;
                 const int hv = L.R16 * QT;                 // histV follows histQ
                 uint32_t p0 = pcol[0], d0 = dcol[0], x0 = wcol[0];
                 uint32_t p1 = pcol[ES], d1 = dcol[ES], x1 = wcol[ES];
                 int kk = 0;
                 for (; kk + 1 < nk; kk += 2) {
-                    const uint32_t i0 = (x0 >> sh) & ((1u << IDX_BITS) - 1u), i1 = (x1 >> sh) & ((1u << IDX_BITS) - 1u);
+                    const uint32_t i0 = lut[(x0 >> sh) & ((1u << IDX_BITS) - 1u)], i1 = lut[(x1 >> sh) & ((1u << IDX_BITS) - 1u)];
                     uint32_t *a0 = cell + i0 * QT, *a1 = cell + i1 * QT;
                     const uint32_t q0 = a0[0], v0 = a0[hv], q1 = a1[0], v1 = a1[hv];
                     const uint32_t cp0 = p0, cd0 = d0, cp1 = p1, cd1 = d1;
@@ -520,7 +571,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                     a1[0] = h2_as_u32(sq1); a1[hv] = h2_as_u32(sv1);
                 }
                 if (kk < nk) {
-                    const uint32_t i0 = (x0 >> sh) & ((1u << IDX_BITS) - 1u);
+                    const uint32_t i0 = lut[(x0 >> sh) & ((1u << IDX_BITS) - 1u)];
                     uint32_t *a0 = cell + i0 * QT;
                     a0[0] = h2_as_u32(__hadd2(u32_as_h2(a0[0]), u32_as_h2(d0)));
                     a0[hv] = h2_as_u32(__hadd2(u32_as_h2(a0[hv]), u32_as_h2(p0)));
@@ -532,11 +583,12 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                 const bool lo = d < 5;
                 const int sh = IDX_BITS * (lo ? d : d - 5);
                 const uint32_t *drow = s_DS + lane * ES, *wrow = (lo ? s_W0 : s_W1) + lane * ES;
-                uint32_t *cell = s_hk + meta.rowbase[d] * QT + mypos;
+                const uint16_t *lut = s_lut + d * pm.lut_stride;
+                uint32_t *cell = s_hk + mypos;
                 uint32_t d0 = drow[0], x0 = wrow[0], d1 = drow[1], x1 = wrow[1];
                 int qq = 0;
                 for (; qq + 1 < nq; qq += 2) {
-                    const uint32_t i0 = (x0 >> sh) & ((1u << IDX_BITS) - 1u), i1 = (x1 >> sh) & ((1u << IDX_BITS) - 1u);
+                    const uint32_t i0 = lut[(x0 >> sh) & ((1u << IDX_BITS) - 1u)], i1 = lut[(x1 >> sh) & ((1u << IDX_BITS) - 1u)];
                     uint32_t *a0 = cell + i0 * QT, *a1 = cell + i1 * QT;
                     const uint32_t c0 = a0[0], c1 = a1[0];
                     const uint32_t cd0 = d0, cd1 = d1;
@@ -549,7 +601,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
                     a1[0] = h2_as_u32(s1);
                 }
                 if (qq < nq) {
-                    const uint32_t i0 = (x0 >> sh) & ((1u << IDX_BITS) - 1u);
+                    const uint32_t i0 = lut[(x0 >> sh) & ((1u << IDX_BITS) - 1u)];
                     uint32_t *a0 = cell + i0 * QT;
                     a0[0] = h2_as_u32(__hadd2(u32_as_h2(a0[0]), u32_as_h2(d0)));
                 }
@@ -575,19 +627,14 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
         consumer_sync<NT>();
         S3D_PHASE_MARK(4)
         // ---- dTq, dTv, dTk ; dQ += histQ.Tq, dK += histK.Tk -------------------------------------------------------
-        if (S3D_KEEP(5)) {
+        if (tg < 3 && S3D_KEEP(5)) {
             uint32_t xb[2][2][2];
-            int have = -1;
+            load_dt_bfrag(xb, tg == 0 ? s_q : (tg == 1 ? s_do : s_k), g, t);
+            const uint32_t *hist = tg == 0 ? s_hq : (tg == 1 ? s_hv : s_hk);
 #pragma unroll
             for (int i = 0; i < NPU; ++i) {
-                const int u = wid * NPU + i, tab = u / n_mt, mt = u - tab * n_mt;
-                if (tab < 3) {
-                    if (tab != have) {
-                        load_dt_bfrag(xb, tab == 0 ? s_q : (tab == 1 ? s_do : s_k), g, t);
-                        have = tab;
-                    }
-                    dt_unit_b(dt_acc[i], tab == 0 ? s_hq : (tab == 1 ? s_hv : s_hk), xb, mt, g, t);
-                }
+                const int mt = wsub + TG * i;
+                if (mt < n_mt && ((used >> mt) & 1u)) dt_unit_b(dt_acc[i], hist, xb, mt, g, t);
             }
         }
         if (side < 2) {
@@ -599,7 +646,7 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
 #pragma unroll
             for (int i = 0; i < NHU; ++i) {
                 const int ks = ws2 + SG * i;
-                if (ks < n_mt && S3D_KEEP(6)) {
+                if (ks < n_mt && ((used >> ks) & 1u) && S3D_KEEP(6)) {
                     const uint4 f = s_tb[(side * n_mt + ks) * 32 + lane];
                     const uint32_t tbf[2][2] = {{f.x, f.y}, {f.z, f.w}};
                     ht_unit(part, side == 0 ? s_hq : s_hk, tbf, ks, g, t);
@@ -651,17 +698,17 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
     S3D_PHASE_FLUSH(0)
 
     // ---- flush the table gradients of this block ---------------------------------------------------------------------
-    {
+    if (tg < 3) {
+        float *dst = tg == 0 ? P.dtq : (tg == 1 ? P.dtv : P.dtk);
 #pragma unroll
         for (int i = 0; i < NPU; ++i) {
-            const int u = wid * NPU + i, tab = u / n_mt, mt = u - tab * n_mt;
-            float *dst = tab == 0 ? P.dtq : (tab == 1 ? P.dtv : P.dtk);
-            if (tab < 3) {
+            const int mt = wsub + TG * i;
+            if (mt < n_mt) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
 #pragma unroll
                     for (int rr = 0; rr < 2; ++rr) {
-                        const int row = table_row(meta, mt * 16 + g + 8 * rr);   // aliases flush into the row they stand for
+                        const int row = perm_table_row(pm, mt * 16 + g + 8 * rr);   // aliases flush into the row they stand for
                         if (row >= 0) {
                             float *p = dst + (int64_t)row * HC + co + h * 8 + 2 * t;
                             atomicAdd(p, dt_acc[i][h][2 * rr]);
@@ -674,10 +721,10 @@ attn_bwd_small_kernel(const SmallParams P, const CrseMeta meta, const PairConsts
 }
 
 template <int D, int NPU, int NHU, bool HD16>
-static int launch_small(const SmallParams &p, const CrseMeta &meta, cudaStream_t st)
+static int launch_small(const SmallParams &p, const CrseMeta &meta, const PermMeta &pm, cudaStream_t st)
 {
     constexpr int NW = bwd_small_warps(D);
-    const SmallSmem L = make_small_layout(meta.R, NW);
+    const SmallSmem L = make_small_layout(pm.R, NW, pm.D * pm.lut_stride);
     auto kern = attn_bwd_small_kernel<D, NPU, NHU, HD16>;
     static int sms_of[64] = {0};     // 0: this instantiation has not been set up on the device yet
     int dev = 0;
@@ -695,7 +742,7 @@ static int launch_small(const SmallParams &p, const CrseMeta &meta, cudaStream_t
     if (gx > p.W) gx = (int)p.W;
     if (gx < 1) gx = 1;
     dim3 grid((unsigned)gx, (unsigned)hp);
-    kern<<<grid, (NW + 1) * 32, L.total, st>>>(p, meta, make_pair_consts(meta));
+    kern<<<grid, (NW + 1) * 32, L.total, st>>>(p, pm, make_pair_consts(meta));
     const cudaError_t le = cudaGetLastError();
     note_cuda_error(le);
     return le == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
@@ -724,13 +771,13 @@ bool attn_tc_bwd_small_supported(const AttnArgs &a)
 {
     if (a.dtype != S3D_F16) return false;
     if (!(a.hd == 16 || (a.hd == 8 && !(a.H & 1)))) return false;
-    const int Rint = a.meta.R + a.meta.D - 1;
-    const int n_mt = (Rint + 15) / 16;
+    const tc::PermMeta pm = tc::make_perm_meta(a.meta);
+    const int n_mt = (pm.R + 15) / 16;
     const int nw = tc::bwd_small_warps(a.meta.D);
-    if (3 * n_mt > 5 * nw || n_mt > 4 * (nw / 2)) return false;
+    if (n_mt > 32 || n_mt > 5 * (nw / 3) || n_mt > 4 * (nw / 2)) return false;     // the tile mask is one word
     for (int d = 0; d < a.meta.D; ++d)
         if (a.meta.L[d] >= (1 << tc::IDX_BITS)) return false;
-    return tc::make_small_layout(Rint, nw).total <= 227 * 1024;
+    return tc::make_small_layout(pm.R, nw, pm.D * pm.lut_stride).total <= 227 * 1024;
 }
 
 // All windows; dtq, dtk, dtv must be zero on entry (accumulated into).
@@ -738,7 +785,7 @@ int attn_tc_backward_small(const AttnArgs &a0, cudaStream_t st)
 {
     if (a0.W == 0) return S3D_OK;
     AttnArgs a = a0;
-    a.meta = tc::internal_meta(a0.meta);   // kernels work in the internal row numbering
+    const tc::PermMeta pm = tc::make_perm_meta(a0.meta);   // the kernel works in its own row numbering
     tc::SmallParams p{};
     p.q = (const __half *)a.q; p.k = (const __half *)a.k; p.v = (const __half *)a.v;
     p.dout = (const __half *)a.dout; p.o = (const __half *)a.out; p.lse = a.lse;
@@ -747,13 +794,13 @@ int attn_tc_backward_small(const AttnArgs &a0, cudaStream_t st)
     p.dtq = a.dtq; p.dtk = a.dtk; p.dtv = a.dtv;
     p.w_sizes = a.w_sizes; p.w2n = a.w2n; p.n2n = a.n2n; p.n_coords = a.n_coords;
     p.W = a.W; p.H = a.H;
-    const int n_mt = (a.meta.R + 15) / 16;
+    const int n_mt = (pm.R + 15) / 16;
     const int nw = tc::bwd_small_warps(a.meta.D);
-    const int npu = (3 * n_mt + nw - 1) / nw;         // <= 5
+    const int npu = (n_mt + nw / 3 - 1) / (nw / 3);   // <= 5
     const int nhu = (n_mt + nw / 2 - 1) / (nw / 2);   // <= 4
-#define S3D_SMALL_H(DD, HH)                                                              \
-    if (npu <= 4 && nhu <= 3) return tc::launch_small<DD, 4, 3, HH>(p, a.meta, st);      \
-    return tc::launch_small<DD, 5, 4, HH>(p, a.meta, st);
+#define S3D_SMALL_H(DD, HH)                                                                  \
+    if (npu <= 4 && nhu <= 3) return tc::launch_small<DD, 4, 3, HH>(p, a.meta, pm, st);      \
+    return tc::launch_small<DD, 5, 4, HH>(p, a.meta, pm, st);
 #define S3D_SMALL(DD) if (a.hd == 16) { S3D_SMALL_H(DD, true) } else { S3D_SMALL_H(DD, false) }
     switch (a.meta.D) {
         case 3: S3D_SMALL(3)

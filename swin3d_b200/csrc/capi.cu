@@ -17,13 +17,11 @@ void note_cuda_error(cudaError_t e) { if (e != cudaSuccess) g_last_cuda_error = 
 
 namespace {
 
-// S3D_FORCE_SCALAR=1 in the environment routes every attention call to the generic kernels
-// (used by the tests to cross-check the two paths on the GPU).
-bool force_scalar()
-{
-    const char *e = std::getenv("S3D_FORCE_SCALAR");
-    return e && e[0] == '1';
-}
+// Set through s3d_debug_force_generic(): routes every attention call of the process to the generic
+// kernels (the tests cross-check the two implementations on the GPU with it).  Off by default; the
+// product path reads one plain int.
+int g_force_generic = 0;
+bool force_scalar() { return g_force_generic != 0; }
 
 int make_meta(const int32_t *table_sizes_host, int D, int H, int hd, CrseMeta &m)
 {
@@ -70,6 +68,13 @@ const char *s3d_status_string(int status)
 }
 
 int s3d_version(void) { return 1000; }
+
+int s3d_debug_force_generic(int on)
+{
+    const int was = g_force_generic;
+    g_force_generic = on ? 1 : 0;
+    return was;
+}
 
 const char *s3d_last_cuda_error_string(void)
 {

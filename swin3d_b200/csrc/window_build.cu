@@ -388,16 +388,16 @@ __global__ void wb_init_kernel(int64_t *counts, int *cur, int *range)
 }
 
 // ---- host ------------------------------------------------------------------------------------------------
-static inline int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+static constexpr int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 
 struct WbLayout {
     int64_t keys0, keys1, vals0, vals1, hist, excl, sums, flags, cur, skip, total;
     int nblk;
 };
 
-static WbLayout wb_layout(int64_t N)
+static constexpr WbLayout wb_layout(int64_t N)
 {
-    WbLayout L;
+    WbLayout L{};
     const int64_t n = N < 1 ? 1 : N;
     L.nblk = (int)((n + WB_TILE - 1) / WB_TILE);
     const int64_t hist_n = (int64_t)256 * L.nblk;
@@ -474,7 +474,11 @@ int window_build_launch(const int32_t *coords, const float *feats, int64_t N, in
 // cudaGetSymbolAddress, once per device, with that device current, and cached.
 namespace {
 
-constexpr long long WB_STATIC_BYTES = 4456448;   // 4.25 MiB: the layout of S3D_WINDOW_BUILD_STATIC_MAX_VOXELS voxels
+// The array is exactly as large as the scratch layout of the largest call the entry point accepts, so
+// a change of the tile sizes or of the number of radix passes changes both together.
+constexpr long long WB_STATIC_BYTES = s3d::wb_layout(S3D_WINDOW_BUILD_STATIC_MAX_VOXELS).total;
+static_assert(WB_STATIC_BYTES > 0 && WB_STATIC_BYTES <= (5ll << 20), "static scratch of s3d_window_build_static: 5 MiB at most");
+static_assert(s3d::wb_layout(S3D_WINDOW_BUILD_STATIC_MAX_VOXELS / 2).total <= WB_STATIC_BYTES, "the layout grows with the voxel count");
 static __device__ __align__(256) unsigned char g_wb_static_scratch[WB_STATIC_BYTES];
 
 constexpr int WB_MAX_DEVICES = 64;

@@ -339,3 +339,53 @@ def sharded_attention(q, k, v, tq, tk, tv, sizes, w_sizes, w2n, n2n, n_coords, d
     plan = get_plan(w_sizes, w2n, n2n, world, rank, 1)
     out, _ = attn_forward_raw(q, k, v, tq, tk, tv, sizes, plan.w_sizes_chunk[0], plan.w2n_chunk[0], n2n, n_coords)
     return exchange_rows(plan, [out], group)[0]
+
+
+# ---- KNN over several GPUs ---------------------------------------------------------------------------
+
+def shard_queries(n_query: int, world_size: int) -> List[Tuple[int, int]]:
+    """Contiguous, equal query ranges [(begin, end)] per rank (queries are independent; a range may
+    span several scenes)."""
+    if world_size < 1:
+        raise ValueError("world_size must be >= 1")
+    per = -(-n_query // world_size) if n_query else 0
+    return [(min(r * per, n_query), min((r + 1) * per, n_query)) for r in range(world_size)]
+
+
+def local_query_offsets(query_offset, begin: int, end: int):
+    """The cumulative per-scene END offsets of the queries [begin, end) taken alone: scenes that lie
+    before the range end at 0, scenes after it at end - begin, so that the kernel's scene search
+    (first scene whose end is above the query number, Swin3D/src/knn/knn_cuda_kernel.cu:170-173) finds
+    the same scene for a query as in the full problem.  Works on numpy arrays and torch tensors."""
+    return (query_offset - begin).clip(0, end - begin)
+
+
+def sharded_knn(K: int, src_xyz, query_xyz, src_offset, query_offset, group=None, knn_fn=None):
+    """KNN of all queries with the query list split over the ranks of `group` in equal contiguous
+    ranges; every rank holds the source points (50 k x 12 B per scene in the stress test) and its
+    slice of the queries is enough.  The [Nq_r, K] index and squared-distance blocks are all-gathered
+    (padded to equal size).  -> (idx int32 [Nq,K], d2 float32 [Nq,K]) on every rank, bit for bit the
+    single-GPU result.  `knn_fn(K, src, query, src_offset, query_offset) -> (idx, d2)` defaults to
+    the library's kernel; the CPU tests pass the oracle."""
+    import torch
+    import torch.distributed as dist
+    if knn_fn is None:
+        from .sparse_dl.knn.knn import knn_raw as knn_fn
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if world > 1 else 0
+    Nq = query_xyz.shape[0]
+    ranges = shard_queries(Nq, world)
+    a, b = ranges[rank]
+    qo_l = local_query_offsets(query_offset, a, b)
+    idx_l, d2_l = knn_fn(K, src_xyz, query_xyz[a:b].contiguous(), src_offset, qo_l)
+    if world == 1:
+        return idx_l, d2_l
+    pad = max(hi - lo for lo, hi in ranges)
+    # one packed exchange: indices and distance bits side by side as int32 [pad, 2K]
+    piece = torch.zeros((pad, 2 * K), dtype=torch.int32, device=idx_l.device)
+    piece[:b - a, :K] = idx_l
+    piece[:b - a, K:] = d2_l.view(torch.int32)
+    full = torch.empty((world, pad, 2 * K), dtype=torch.int32, device=idx_l.device)
+    dist.all_gather_into_tensor(full.view(-1), piece.view(-1), group=group)
+    rows = torch.cat([full[r, :hi - lo] for r, (lo, hi) in enumerate(ranges)])
+    return rows[:, :K].contiguous(), rows[:, K:].contiguous().view(torch.float32)

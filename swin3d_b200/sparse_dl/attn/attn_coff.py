@@ -61,11 +61,38 @@ def _as_int32(t: Tensor) -> Tensor:
     return conv
 
 
-def _table_sizes_host(table_offsets) -> List[int]:
-    """Elements per signal dimension as Python ints (a device tensor costs one D2H copy)."""
-    if isinstance(table_offsets, Tensor):
-        return [int(x) for x in table_offsets.detach().cpu().tolist()]
-    return [int(x) for x in table_offsets]
+# The reference's WindowAttention builds a fresh CUDA IntTensor of table offsets on every forward
+# (swin3d_layers.py:511); reading it back costs a blocking device-to-host copy per attention block.
+# The offsets of a module never change (they are its table shapes), so the host copy is kept per
+# (number of offsets, total table elements, heads, head_dim) and a device tensor is read only the
+# first time such a module is seen.  Set ``CACHE_TABLE_OFFSETS = False`` to read every time.
+CACHE_TABLE_OFFSETS = True
+
+# PrecisionMode.HALF_FORWARD (fp16_mode=1): the reference runs the backward on fp32 casts of q, k, v,
+# the tables and the gradient (attn_coff.py:207-217).  That is the default here too (generic fp32
+# kernels, 1e-4 agreement with the reference's fp32 backward).  With this switch on, the backward of
+# that mode instead runs the tensor-core kernels on the fp16 values the forward used (fp16 storage,
+# fp32 accumulation, the 2e-2 tolerance of the fp16 modes) and returns fp32 gradients: about four
+# times faster, for callers who accept fp16-mode accuracy in the backward of fp16_mode=1.
+HALF_FORWARD_FAST_BACKWARD = False
+_table_sizes_cache = {}
+
+
+def _table_sizes_host(table_offsets, table_numel: int = -1, H: int = 0, hd: int = 0) -> List[int]:
+    """Elements per signal dimension as Python ints."""
+    if not isinstance(table_offsets, Tensor):
+        return [int(x) for x in table_offsets]
+    if not table_offsets.is_cuda:
+        return [int(x) for x in table_offsets.detach().tolist()]
+    key = (int(table_offsets.numel()), int(table_numel), int(H), int(hd))
+    if CACHE_TABLE_OFFSETS and table_numel >= 0:
+        hit = _table_sizes_cache.get(key)
+        if hit is not None:
+            return list(hit)
+    sizes = [int(x) for x in table_offsets.detach().cpu().tolist()]      # one blocking copy
+    if table_numel >= 0 and sum(sizes) == table_numel:
+        _table_sizes_cache[key] = tuple(sizes)
+    return sizes
 
 
 def _check_inputs(q: Tensor, k: Tensor, v: Tensor, tables, indices):
@@ -177,7 +204,8 @@ class SelfAttnAIOFunction(Function):
 
         qkv = [t.to(c_dtype) for t in (raw_query_feats, raw_key_feats, raw_value_feats)]
         tabs = [t.to(c_dtype).contiguous() for t in (query_table, key_table, value_table)]
-        sizes = _table_sizes_host(table_offsets)
+        sizes = _table_sizes_host(table_offsets, query_table.numel(), raw_query_feats.shape[1],
+                                  raw_query_feats.shape[2])
         _, w_sizes, _, w2n, n2n, n_coords = indices
         w_sizes, w2n, n2n = _as_int32(w_sizes), _as_int32(w2n), _as_int32(n2n)
         n_coords = n_coords.to(torch.float32).contiguous()
@@ -197,6 +225,8 @@ class SelfAttnAIOFunction(Function):
         # dtype policy of the reference (attn_coff.py:207-217)
         if precision == PrecisionMode.HALF_ALL:
             c_dtype = grad.dtype
+        elif precision == PrecisionMode.HALF_FORWARD and HALF_FORWARD_FAST_BACKWARD and out.dtype == torch.float16:
+            c_dtype = torch.float16       # opt-in: tensor-core backward on the forward's fp16 values
         else:
             c_dtype = torch.float32
         if c_dtype not in _DTYPE_CODE:

@@ -41,7 +41,9 @@ def scene(rng, ns, nq):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SWIN3D_REFERENCE")
+    if not root:
+        raise SystemExit("usage: python " + sys.argv[0] + " <reference_root>   (or set SWIN3D_REFERENCE)")
     layers, _ = import_reference(root)
     layers.KNN = OracleKNN
     rng = np.random.default_rng(7)

@@ -6,7 +6,7 @@ Swin3D.modules.swin3d_layers and to run, on CPU tensors,
   * sparse_self_attention(protocol="v2")      (swin3d_layers.py:76-150)
   * WindowAttention.__init__ table shapes     (swin3d_layers.py:404-478)
   * the enum values of attn_coff.py:20-40.
-Usage: python tests/golden/make_golden_offsets.py [reference_root]
+Usage: python tests/golden/make_golden_offsets.py <reference_root>   (or set SWIN3D_REFERENCE)
 """
 import os
 import sys
@@ -44,7 +44,9 @@ def import_reference(root):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SWIN3D_REFERENCE")
+    if not root:
+        raise SystemExit("usage: python " + sys.argv[0] + " <reference_root>   (or set SWIN3D_REFERENCE)")
     layers, coff = import_reference(root)
     out = {}
     rng = np.random.default_rng(0)

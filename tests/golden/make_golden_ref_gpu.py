@@ -1,13 +1,14 @@
 """Runs the reference's own compiled CUDA kernels (oracle/_ref/ref_swin3d_cuda.so, built by
 oracle/build_ref.py from the sources of microsoft/Swin3D) on seeded inputs on a GPU and writes
-their outputs to ref_gpu_golden.npz in the run's output folder.  A copy of that file is committed as
-tests/golden/ref_gpu_golden.npz and pins the CPU oracle (tests/test_golden_ref_gpu.py).
+their outputs to the .npz file given as the first argument (default: ref_gpu_golden.npz beside this
+script).  That file is committed as tests/golden/ref_gpu_golden.npz and pins the CPU oracle
+(tests/test_golden_ref_gpu.py).
 
 Only shapes for which the reference forward kernel stays inside its 32-entry shared staging
 array are used: head_dim/pack >= 16, i.e. fp32/fp64 with head_dim 16 or 32 and fp16 with
 head_dim 32 (see oracle/build_ref.py).
 
-Usage (on a machine with a GPU):  python tests/golden/make_golden_ref_gpu.py
+Usage (on a machine with a GPU):  python tests/golden/make_golden_ref_gpu.py [output.npz]
 """
 import importlib.machinery
 import importlib.util
@@ -107,8 +108,8 @@ def main():
         src, qry, so, qo = knn_inputs(c["seed"])
         idx, d2 = run_ref_knn(ref, c["K"], src, qry, so, qo)
         out[f"{name}.idx"], out[f"{name}.d2"] = idx, d2
-    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    dst = os.path.join(ROOT, "gpurun_out", "ref_gpu_golden.npz")
+    dst = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_gpu_golden.npz")
+    os.makedirs(os.path.dirname(os.path.abspath(dst)), exist_ok=True)
     np.savez_compressed(dst, **out)
     print("wrote", dst, os.path.getsize(dst), "bytes")
     return 0

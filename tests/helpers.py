@@ -51,3 +51,18 @@ def rel_err(a, b):
     b = np.asarray(b, dtype=np.float64)
     den = np.abs(b).max()
     return float(np.abs(a - b).max() / (den if den > 0 else 1.0))
+
+
+def table_row_errors(a, b, row_len, tol, floor_frac):
+    """Per table ROW check of a table gradient (flat [rows * row_len]): for every row the largest
+    deviation must stay below tol * max(largest reference entry of that row, floor_frac * largest
+    entry of the whole table).  A gradient that landed in the wrong row (an alias row of the flat
+    cRSE addressing, a rarely hit row) fails here even when it is invisible in a whole-tensor norm.
+    -> list of offending rows (empty = pass)."""
+    a = np.asarray(a, dtype=np.float64).reshape(-1, row_len)
+    b = np.asarray(b, dtype=np.float64).reshape(-1, row_len)
+    err = np.abs(a - b).max(1)
+    ref = np.abs(b).max(1)
+    floor = floor_frac * (ref.max() if ref.size and ref.max() > 0 else 1.0)
+    bad = np.nonzero(err > tol * np.maximum(ref, floor))[0]
+    return [(int(r), float(err[r]), float(ref[r])) for r in bad[:8]]

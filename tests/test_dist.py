@@ -9,7 +9,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from oracle import oracle as O
-from swin3d_b200.dist import (ShardPlan, all_gather_window_rows, allreduce_table_grads, exchange_rows,
+from swin3d_b200.dist import (ShardPlan, local_query_offsets, shard_queries, sharded_knn, all_gather_window_rows, allreduce_table_grads, exchange_rows,
                               shard_voxel_range, shard_windows, window_cost)
 from tests.helpers import make_problem
 
@@ -176,6 +176,61 @@ def test_shard_plan_ranges_follow_the_kernel_cost_model():
     for r, pl in enumerate(plans):
         assert pl.chunk_windows[0][0] == pl.parts[r][0] and pl.chunk_windows[-1][1] == pl.parts[r][1]
         assert pl.chunk_windows[0][1] == pl.chunk_windows[1][0]
+
+
+def _oracle_knn(K, src, qry, so, qo):
+    idx, d2 = O.knn(K, src.numpy(), qry.numpy(), so.numpy(), qo.numpy())
+    return torch.from_numpy(idx), torch.from_numpy(d2)
+
+
+def _rank_knn(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from swin3d_b200 import synthetic as S
+    scenes = [S.make_knn_scene(40 + s, 300 + 37 * s, 150 + 11 * s) for s in range(3)]
+    src = torch.from_numpy(np.concatenate([a for a, _ in scenes]))
+    qry = torch.from_numpy(np.concatenate([b for _, b in scenes]))
+    so = torch.tensor(np.cumsum([a.shape[0] for a, _ in scenes]), dtype=torch.int32)
+    qo = torch.tensor(np.cumsum([b.shape[0] for _, b in scenes]), dtype=torch.int32)
+    idx, d2 = sharded_knn(5, src, qry, so, qo, knn_fn=_oracle_knn)
+    q.put((rank, idx.numpy(), d2.numpy()))
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("world", [2, 3])
+def test_query_sharded_knn_equals_the_single_rank_result_bit_for_bit(world):
+    """Query ranges that cut through scenes: the clipped per-scene offsets make every rank search the
+    right scene; indices and distance bits after the all-gather equal the unsplit run."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_knn, args=(r, world, port, q)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    got = [q.get(timeout=240) for _ in range(world)]
+    for pr in procs:
+        pr.join(60)
+        assert pr.exitcode == 0
+    from swin3d_b200 import synthetic as S
+    scenes = [S.make_knn_scene(40 + s, 300 + 37 * s, 150 + 11 * s) for s in range(3)]
+    src = np.concatenate([a for a, _ in scenes])
+    qry = np.concatenate([b for _, b in scenes])
+    so = np.cumsum([a.shape[0] for a, _ in scenes]).astype(np.int32)
+    qo = np.cumsum([b.shape[0] for _, b in scenes]).astype(np.int32)
+    ref_idx, ref_d2 = O.knn(5, src, qry, so, qo)
+    for _, idx, d2 in got:
+        assert np.array_equal(idx, ref_idx)
+        assert np.array_equal(d2.view(np.int32), ref_d2.view(np.int32))
+
+
+def test_query_ranges_and_local_offsets():
+    assert shard_queries(10, 3) == [(0, 4), (4, 8), (8, 10)]
+    assert shard_queries(0, 2) == [(0, 0), (0, 0)]
+    qo = np.array([5, 9, 20])
+    assert local_query_offsets(qo, 4, 8).tolist() == [1, 4, 4]       # scene 0: one query, scene 1: three
+    assert local_query_offsets(qo, 9, 20).tolist() == [0, 0, 11]
 
 
 def test_all_gather_window_rows_single_process_unpermutes():

@@ -9,7 +9,7 @@ import torch
 
 from oracle import oracle as O
 from swin3d_b200 import synthetic as S
-from tests.helpers import make_problem, oracle_fwd_bwd, rel_err
+from tests.helpers import make_problem, oracle_fwd_bwd, rel_err, table_row_errors
 
 pytestmark = pytest.mark.gpu
 
@@ -37,6 +37,8 @@ def test_fp32_forward_backward_match_oracle(crse, H, hd, ws, shift):
     assert np.abs(lse - lse_ref).max() < 1e-4
     for name, a, b in zip("dq dk dv dtq dtk dtv".split(), grads, g_ref):
         assert rel_err(a, b) < FP32_TOL, name
+    for name, a, b in zip("dtq dtk dtv".split(), grads[3:], g_ref[3:]):     # row by row: no row may hide
+        assert table_row_errors(a, b, H * hd, FP32_TOL, 1e-3) == [], name
 
 
 @pytest.mark.parametrize("crse,H,hd,ws,shift", CASES[1:5])
@@ -49,6 +51,8 @@ def test_fp16_forward_backward_match_oracle(crse, H, hd, ws, shift):
     assert rel_err(out, o_ref) < FP16_TOL
     for name, a, b in zip("dq dk dv dtq dtk dtv".split(), grads, g_ref):
         assert rel_err(a, b) < FP16_TOL, name
+    for name, a, b in zip("dtq dtk dtv".split(), grads[3:], g_ref[3:]):     # row by row: no row may hide
+        assert table_row_errors(a, b, H * hd, FP16_TOL, 2e-2) == [], name
 
 
 def test_config1_full_size_fp32():
@@ -106,18 +110,36 @@ def test_crse_indices_bit_exact_including_clamp_quirk():
     assert np.array_equal(out.cpu().numpy(), ref)
 
 
-def test_index_equal_to_L_uses_next_dimension_row_zero():
+@pytest.mark.parametrize("dtype", ["fp32", "fp16"])
+def test_index_equal_to_L_uses_next_dimension_row_zero(dtype):
     """With idx == L in a non-last dimension the flat table addressing of the reference selects
-    row 0 of the next dimension; the kernels and the oracle must agree on that."""
+    row 0 of the next dimension; the kernels (generic fp32 path and tensor-core fp16 path, whose
+    internal row numbering gives that case a private alias row) and the oracle must agree on it,
+    row by row of the table gradients."""
     from tests.gpu_helpers import cuda_fwd_bwd
-    p = make_problem(seed=22, n_voxels=500, grid=20, H=2, hd=8, crse="XYZ_RGB")
-    p.n_crse[::7, 3] = 8.0
+    half = dtype == "fp16"
+    p = make_problem(seed=22, n_voxels=500, grid=20, H=2, hd=8, crse="XYZ_RGB", round_fp16=half)
+    p.n_crse[::7, 3] = 8.0          # colour differences of exactly +-16: idx == L = 32 in dimension 3
     p.n_crse[3::7, 3] = -8.0
+    idx = O.crse_indices(p.n_crse, p.sizes, p.H, p.hd, int(p.w2n[np.argmax(p.w_sizes)]), int(p.w_sizes.max()))
+    assert (idx[:, :, 3] == 32).any()
     o_ref, _, g_ref = oracle_fwd_bwd(p, np.float64)
-    out, _, grads = cuda_fwd_bwd(p, torch.float32)
-    assert rel_err(out, o_ref) < FP32_TOL
+    out, _, grads = cuda_fwd_bwd(p, torch.float16 if half else torch.float32)
+    tol = FP16_TOL if half else FP32_TOL
+    assert rel_err(out, o_ref) < tol
     for a, b in zip(grads, g_ref):
-        assert rel_err(a, b) < FP32_TOL
+        assert rel_err(a, b) < tol
+    HC = p.H * p.hd
+    for name, a, b in zip("dtq dtk dtv".split(), grads[3:], g_ref[3:]):
+        assert table_row_errors(a, b, HC, tol, 2e-2 if half else 1e-3) == [], name
+    # row 0 of dimension 4 (the row the alias stands for) carries gradient from the idx == L pairs:
+    # with the dimension-3 signal flattened (no pair reaches L) it gets visibly less
+    row0_dim4 = sum(p.sizes[:4]) // HC
+    p2 = make_problem(seed=22, n_voxels=500, grid=20, H=2, hd=8, crse="XYZ_RGB", round_fp16=half)
+    _, _, g_flat = oracle_fwd_bwd(p2, np.float64)
+    r = slice(row0_dim4 * HC, (row0_dim4 + 1) * HC)
+    assert np.abs(g_ref[5][r] - g_flat[5][r]).max() > 1e-3 * np.abs(g_ref[5]).max()
+    assert np.abs(grads[5][r] - g_ref[5][r]).max() <= tol * np.abs(g_ref[5]).max()
 
 
 def test_autograd_function_all_precision_modes():
@@ -147,6 +169,38 @@ def test_autograd_function_all_precision_modes():
         for t, b in zip((q, k, v, tq, tk, tv), g_ref):
             assert t.grad is not None and t.grad.dtype == torch.float32
             assert rel_err(t.grad.double().cpu().numpy(), b) < tol
+
+
+def test_half_forward_fast_backward_switch():
+    """fp16_mode=1 with HALF_FORWARD_FAST_BACKWARD: the backward runs the tensor-core kernels on the
+    forward's fp16 values and still returns fp32 gradients within the fp16 tolerance; off (the
+    default) the backward is the fp32 one."""
+    import swin3d_b200.sparse_dl.attn.attn_coff as C
+    from tests.gpu_helpers import dev
+    p = make_problem(seed=33, n_voxels=900, grid=24, H=6, hd=8, crse="XYZ_RGB_NORM", round_fp16=True)
+    _, _, g_ref = oracle_fwd_bwd(p, np.float64)
+    x_off, y_off, m2w, ws64, w2n64, w2m = O.window_offsets(p.w_sizes)
+    indices = [dev(m2w), dev(ws64), dev(w2m), dev(w2n64), dev(p.n2n.astype(np.int64)), dev(p.n_crse)]
+    offsets = torch.IntTensor(p.sizes).cuda()
+    results = {}
+    assert C.HALF_FORWARD_FAST_BACKWARD is False
+    for fast in (False, True):
+        C.HALF_FORWARD_FAST_BACKWARD = fast
+        try:
+            q, k, v = (dev(a).requires_grad_() for a in (p.q, p.k, p.v))
+            tq, tk, tv = (dev(a).requires_grad_() for a in (p.tq, p.tk, p.tv))
+            with torch.autocast("cuda", dtype=torch.float16):
+                out = C.SelfAttnAIOFunction.apply(q, k, v, tq, tk, tv, offsets, indices, C.PosEmb.SEPARATE,
+                                                  C.TableDims.D0, C.IndexMode.INDIRECT, C.PrecisionMode.HALF_FORWARD)
+            out.backward(dev(p.g).half())
+        finally:
+            C.HALF_FORWARD_FAST_BACKWARD = False
+        grads = [t.grad for t in (q, k, v, tq, tk, tv)]
+        assert all(g.dtype == torch.float32 for g in grads)
+        for g, b in zip(grads, g_ref):
+            assert rel_err(g.double().cpu().numpy(), b) < FP16_TOL
+        results[fast] = [g.clone() for g in grads]
+    assert any(not torch.equal(a, b) for a, b in zip(results[False], results[True]))   # two different code paths
 
 
 def test_empty_and_degenerate_inputs():
@@ -211,17 +265,17 @@ def test_fp16_tensor_core_path_large_scores_stay_finite():
 
 def test_room_scale_tensor_core_path_equals_generic_path():
     """A 60k-voxel room, Swin3D-L stage-1 head layout: the tensor-core kernels against the
-    generic kernels of the same library (forced with S3D_FORCE_SCALAR=1), same inputs."""
+    generic kernels of the same library (forced with s3d_debug_force_generic), same inputs."""
     import os
     from tests.gpu_helpers import cuda_fwd_bwd
     sc = S.make_room(7, target_voxels=60_000)
     p = make_problem(seed=61, ws=5, shift=2, H=10, hd=8, crse="XYZ_RGB_NORM", scene=sc, round_fp16=True)
     fast = cuda_fwd_bwd(p, torch.float16)
-    os.environ["S3D_FORCE_SCALAR"] = "1"
+    _lib_force = __import__("swin3d_b200._lib", fromlist=["lib"]).lib.s3d_debug_force_generic(1)
     try:
         slow = cuda_fwd_bwd(p, torch.float16)
     finally:
-        os.environ.pop("S3D_FORCE_SCALAR")
+        __import__("swin3d_b200._lib", fromlist=["lib"]).lib.s3d_debug_force_generic(0)
     assert rel_err(fast[0], slow[0]) < 5e-3
     assert np.abs(fast[1] - slow[1]).max() < 1e-2
     for a, b in zip(fast[2], slow[2]):
@@ -362,6 +416,19 @@ def test_full_benchmark_size_properties():
                                  w2n[pick], n2n, ncr.cpu().numpy(), dtype=np.float64)
     rows = np.concatenate([n2n[w2n[w]:w2n[w] + w_sizes[w]] for w in pick])
     assert rel_err(f64(of)[rows], o_ref[rows]) < FP16_TOL
+    # the BACKWARD of the same sample of windows: the library is run on exactly these windows (full-size
+    # arrays, window list cut to the sample), so all six gradients are comparable with the oracle's
+    o_s, s_s, m_s = O.attn_forward(f64(q), f64(k), f64(v1), f64(tq), f64(tk), f64(tv), sizes, w_sizes[pick],
+                                   w2n[pick], n2n, ncr.cpu().numpy(), dtype=np.float64)
+    g_ref = O.attn_backward(f64(q), f64(k), f64(v1), f64(tq), f64(tk), f64(tv), sizes, w_sizes[pick], w2n[pick],
+                            n2n, ncr.cpu().numpy(), o_s, s_s, m_s, f64(g), dtype=np.float64)
+    ws_s, w2n_s = dev(w_sizes[pick].astype(np.int32)), dev(w2n[pick].astype(np.int32))
+    g_s = C.attn_backward_raw(q, k, v1, tq, tk, tv, sizes, ws_s, w2n_s, wi.n2n, ncr, of, lse_f, g)
+    for name, a, b in zip("dq dk dv".split(), g_s[:3], g_ref[:3]):
+        assert rel_err(f64(a)[rows], b[rows]) < FP16_TOL, name
+    for name, a, b in zip("dtq dtk dtv".split(), g_s[3:], g_ref[3:]):
+        assert rel_err(f64(a), b) < FP16_TOL, name
+        assert table_row_errors(f64(a), b, H * hd, FP16_TOL, 2e-2) == [], name
 
 
 def test_c_abi_calls_can_be_captured_in_a_cuda_graph():
@@ -420,11 +487,11 @@ def test_tiled_kernels_work_list_overflow_falls_back_to_a_direct_walk():
     p = make_problem(seed=3, ws=7, H=150, hd=8, crse="XYZ", scene=sc, round_fp16=True)
     assert p.w_sizes.max() == 343 and len(p.w_sizes) == 9
     fast = cuda_fwd_bwd(p, torch.float16)
-    os.environ["S3D_FORCE_SCALAR"] = "1"
+    _lib_force = __import__("swin3d_b200._lib", fromlist=["lib"]).lib.s3d_debug_force_generic(1)
     try:
         slow = cuda_fwd_bwd(p, torch.float16)
     finally:
-        os.environ.pop("S3D_FORCE_SCALAR")
+        __import__("swin3d_b200._lib", fromlist=["lib"]).lib.s3d_debug_force_generic(0)
     assert rel_err(fast[0], slow[0]) < 5e-3
     for a, b in zip(fast[2], slow[2]):
         assert rel_err(a, b) < 1.5e-2

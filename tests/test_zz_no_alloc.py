@@ -112,3 +112,20 @@ def test_static_window_build_rejects_inputs_beyond_its_capacity():
     assert rc == 5
     assert b"capacity" in lib.s3d_status_string(rc)
     assert int(o["counts"][0]) == -7        # nothing was launched
+
+
+def test_static_window_build_at_exactly_its_capacity():
+    """N == S3D_WINDOW_BUILD_STATIC_MAX_VOXELS: the largest input the entry point accepts uses the
+    whole static array and must agree with the ordinary entry point."""
+    from swin3d_b200 import _lib
+    lib = _lib.lib
+    sc = S.concat_scenes([S.make_room(21, target_voxels=90_000), S.make_room(22, target_voxels=90_000)])
+    assert sc.coords.shape[0] >= MAX_VOXELS
+    coords = torch.from_numpy(np.ascontiguousarray(sc.coords[:MAX_VOXELS])).cuda()
+    feats = torch.from_numpy(np.ascontiguousarray(S.signal_feats(sc, "XYZ_RGB_NORM")[:MAX_VOXELS])).cuda()
+    N, F = feats.shape
+    assert N == MAX_VOXELS
+    o_dyn, o_sta = _outputs(N, F), _outputs(N, F)
+    assert _call_dynamic(lib, coords, feats, 5, 2, o_dyn) == 0
+    assert _call_static(lib, coords, feats, 5, 2, o_sta) == 0
+    _same(o_sta, o_dyn)
