@@ -492,7 +492,7 @@ def run_attention_split(args):
     """The multi-GPU mode of the benchmark (default for --gpus N > 1): ONE 8-room batch split over the
     ranks by contiguous window ranges of equal cost (strong scaling).  Every rank runs forward +
     backward of its windows chunk by chunk; the rows of out, dq, dk, dv are exchanged packed (one
-    NCCL all-gather per chunk, overlapping the next chunk's kernels, one un-permute), the table
+    NCCL all-gather and one row scatter per chunk and array group, overlapping the next kernels), the table
     gradients are all-reduced.  All of it is inside the timed region; time = max over ranks."""
     import torch
     import torch.distributed as dist
@@ -572,7 +572,7 @@ def run_attention_split(args):
         e2.record()
     torch.cuda.synchronize()
     fwd_ms, bwd_ms = e0.elapsed_time(e1), e1.elapsed_time(e2)
-    # the same chunked kernel sequence as in the step, without packing, collectives and un-permute:
+    # the same chunked kernel sequence as in the step, without packing, collectives and scatter:
     # step time minus this is what the exchange costs after overlap
     o_b, lse_b = torch.empty_like(q), torch.empty((N, H), dtype=torch.float32, device="cuda")
     g_b = [torch.empty_like(q) for _ in range(3)]
@@ -595,26 +595,48 @@ def run_attention_split(args):
     for (wi_s, _), pl_s in zip(win, plans):
         rows = torch.cat([wi_s.n2n[lo:hi] for lo, hi in pl_s.chunk_rows]) if pl_s.chunk_rows else wi_s.n2n[:0]
         bands.append((int(rows.min().item()), int(rows.max().item()) + 1) if rows.numel() else (0, 0))
-    dbuf = [torch.empty((N, H, hd), dtype=torch.float16, device="cuda") for _ in range(4)]
+    # copies on their own streams, two sets of device input buffers: the band of step i+1 arrives and the
+    # results of step i-1 leave while step i computes
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    comp = torch.cuda.current_stream()
+    dbuf = [[torch.empty((N, H, hd), dtype=torch.float16, device="cuda") for _ in range(4)] for _ in range(2)]
+    set_free = [None, None]     # event: the step that last read this buffer set has finished
 
     def e2e_step(i):
         lo, hi = bands[i % 2]
-        for dst, src in zip(dbuf, x_pin):
-            dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
-        r = step(i, dbuf)
-        for dst, src in zip(out_pin, r[:4]):
-            dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
+        bufs = dbuf[i % 2]
+        with torch.cuda.stream(s_in):
+            if set_free[i % 2] is not None:
+                s_in.wait_event(set_free[i % 2])
+            for dst, src in zip(bufs, x_pin):
+                dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
+            ev_in = torch.cuda.Event()
+            ev_in.record(s_in)
+        comp.wait_event(ev_in)
+        r = step(i, bufs)
+        ev_c = torch.cuda.Event()
+        ev_c.record(comp)
+        set_free[i % 2] = ev_c
+        for t in r[:4]:
+            t.record_stream(s_out)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_c)
+            for dst, src in zip(out_pin, r[:4]):
+                dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
         return r
 
+    def e2e_run(nsteps):
+        for i in range(nsteps):
+            e2e_step(i)
+        comp.wait_stream(s_out)     # the run ends when the last result has reached the host buffer
+
     e2e_steps = max(2, min(args.steps, 10))
-    for i in range(2):
-        e2e_step(i)
+    e2e_run(3)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     t0.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
+    e2e_run(e2e_steps)
     t1.record()
     torch.cuda.synchronize()
     e2e_ms = t0.elapsed_time(t1) / e2e_steps
@@ -657,8 +679,9 @@ def run_attention_split(args):
         "voxels_total": N, "voxels_of_rank0": n_local, "fwd_ms_rank_max": fwd_ms, "bwd_ms_rank_max": bwd_ms,
         "compute_ms_rank_max": compute_ms, "compute_ms_rank_mean": compute_mean,
         "exchange_ms_after_overlap": ms_per_step - compute_ms,
-        "exchange": "per chunk: all_gather_into_tensor of the packed out|dq|dk|dv rows (4 x 160 B per voxel), "
-                    "one un-permute gather; all-reduce of the 3 table gradients",
+        "exchange": "in place, per chunk: rows of out (after the forward) and of dq|dk|dv (after the backward) packed by "
+                    "one gather launch, one async all_gather_into_tensor, one scatter launch on a side stream; "
+                    "all-reduce of the 3 table gradients",
         "roofline": {"bound": "hbm", "kernel": "attention backward, this rank's windows (tile-pair single-sweep kernel)",
                      "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": None,
                      "peak_source": peak_src, "algorithmic_bytes_per_voxel": {"fwd": pv_fwd, "bwd": pv_bwd}},
@@ -666,7 +689,8 @@ def run_attention_split(args):
         "e2e": {"value": N / (e2e_ms * 1e-3), "unit": "voxels/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(4 * band_total * Cc * 2), "d2h_bytes_per_step": int(4 * band_total * Cc * 2),
                 "note": "bytes summed over the ranks: each copies the band of voxel rows its windows touch"},
-        "gpu_launches": 3 * chunks * args.steps,   # per chunk: forward single-tile + tiled, backward
+        # per chunk: forward single-tile + tiled, backward; with an exchange two gathers and two scatters more
+        "gpu_launches": (3 + (4 if world > 1 else 0)) * chunks * args.steps,
         "clocks": clocks,
     }
     print(json.dumps(line))
@@ -781,11 +805,12 @@ def run_knn(args):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    scenes = [S.make_knn_scene(s, 200_000, 50_000) for s in range(8)]         # the same scenes on every rank
+    n_sc = args.rooms or 8                     # --rooms: fewer scenes for a profiler capture
+    scenes = [S.make_knn_scene(s, 200_000, 50_000) for s in range(n_sc)]      # the same scenes on every rank
     src = torch.from_numpy(np.concatenate([s for s, _ in scenes])).cuda()
     qry = torch.from_numpy(np.concatenate([q for _, q in scenes])).cuda()
-    so = torch.arange(1, 9, dtype=torch.int32, device="cuda") * 50_000
-    qo = torch.arange(1, 9, dtype=torch.int32, device="cuda") * 200_000
+    so = torch.arange(1, n_sc + 1, dtype=torch.int32, device="cuda") * 50_000
+    qo = torch.arange(1, n_sc + 1, dtype=torch.int32, device="cuda") * 200_000
     fma_peak = measure_fp32_fma_peak()
     res = {"fp32_fma_peak_measured_tflops": fma_peak}
     for K in (16, 3):
@@ -808,7 +833,7 @@ def run_knn(args):
             ref = knn_raw(K, src, qry, so, qo)
             if not (torch.equal(got[0], ref[0]) and torch.equal(got[1].view(torch.int32), ref[1].view(torch.int32))):
                 raise RuntimeError("sharded KNN differs from the single-GPU result")
-        evals = 8 * 200_000 * 50_000 / (ms * 1e-3)
+        evals = n_sc * 200_000 * 50_000 / (ms * 1e-3)
         # 8 fp32 operations per candidate (3 sub, 1 mul, 2 fma) against the measured FFMA throughput of
         # all ranks (nominal CUDA-core peak of one B200: 148 SMs x 128 lanes x 2 x 1.965 GHz = 74.4 TFLOP/s)
         res[f"K{K}"] = {"ms": ms, "queries_per_s": qry.shape[0] / (ms * 1e-3), "pair_evals_per_s": evals,
@@ -817,7 +842,7 @@ def run_knn(args):
                         "frac_of_nominal_fp32_peak": evals * 8 / (74.4e12 * world)}
     if world > 1:
         if rank == 0:
-            print(json.dumps({"metric": "knn queries/sec (8 scenes x 200k queries x 50k sources)",
+            print(json.dumps({"metric": f"knn queries/sec ({n_sc} scenes x 200k queries x 50k sources)",
                               "unit": "queries/s", "value": res["K16"]["queries_per_s"], "detail": res,
                               "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "data": "synthetic",
                               "dtype": "f32", "higher_is_better": True, "scaling": "strong",
@@ -862,7 +887,7 @@ def run_knn(args):
                                     "algorithmic_bytes_per_query": byt, "achieved_gbs": gbs,
                                     "frac_of_hbm_peak": gbs / peak, "peak_source": peak_src}
     if rank == 0:
-        print(json.dumps({"metric": "knn queries/sec (8 scenes x 200k queries x 50k sources)",
+        print(json.dumps({"metric": f"knn queries/sec ({n_sc} scenes x 200k queries x 50k sources)",
                           "unit": "queries/s", "value": res["K16"]["queries_per_s"], "detail": res,
                           "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "data": "synthetic",
                           "dtype": "f32", "higher_is_better": True}))

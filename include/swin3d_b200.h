@@ -130,6 +130,15 @@ int s3d_debug_crse_index_values(const float *cq, const float *ck, int64_t n, int
 int s3d_gather_rows(const void *const *srcs_host, int A, const int64_t *idx, int64_t n_rows,
                     int64_t row_bytes, void *dst, int64_t dst_array_stride_bytes, void *stream);
 
+/* Row scatter, the other half of the exchange: rows that arrived packed as
+ * [block][array][block_rows] (one block per sending rank) go to their voxel rows,
+ * dst_a[idx[i]][:] = src[i / block_rows][a][i % block_rows][:] for i < n_rows; rows with idx[i] < 0
+ * (padding, and the receiving rank's own rows, which its kernels already wrote in place) are
+ * skipped.  dsts_host: HOST array of A <= 4 device pointers; strides in bytes, multiples of 16.  */
+int s3d_scatter_rows(const void *src, int A, const int64_t *idx, int64_t n_rows, int64_t row_bytes,
+                     int64_t block_rows, int64_t src_block_stride_bytes, int64_t src_array_stride_bytes,
+                     void *const *dsts_host, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Window builder.  Replaces BasicLayer.get_map_pair / get_window_mapping / get_index01 and
  * sparse_self_attention (Swin3D/modules/swin3d_layers.py:713-822 and :76-150), i.e. the

@@ -34,6 +34,7 @@ SIGNATURES = {
                                               _c_void_p, _c_void_p]),
     "s3d_debug_crse_index_values": (_i32, [_c_void_p, _c_void_p, _i64, _i32, _i32, _i32, _c_void_p, _c_void_p]),
     "s3d_gather_rows": (_i32, [_c_void_p, _i32, _c_void_p, _i64, _i64, _c_void_p, _i64, _c_void_p]),
+    "s3d_scatter_rows": (_i32, [_c_void_p, _i32, _c_void_p, _i64, _i64, _i64, _i64, _i64, _c_void_p, _c_void_p]),
     "s3d_window_build_workspace_bytes": (_i64, [_i64]),
     "s3d_window_build": (_i32, [_c_void_p, _c_void_p, _i64, _i32, _i32, _i32, _i32] +
                          [_c_void_p] * 5 + [_c_void_p, _i64, _c_void_p]),

@@ -9,8 +9,11 @@
 //
 // What differs is the data path: a block of queries streams its scene's source points through
 // shared memory in tiles (one coalesced global read per point per block instead of one per
-// thread), candidates are read back as one broadcast 16-byte shared load, and the heap root is
-// held in a register so the common "not closer" case costs one compare.  Candidates that beat the
+// thread) stored as three coordinate planes, so that one broadcast 16-byte shared load returns a
+// coordinate of four candidates; the six fp32 operations of a distance are issued as packed
+// two-candidate instructions (sub/mul/fma .f32x2: IEEE round-to-nearest per element, the same bits
+// as the scalar operations at half the issue slots), and the heap root is held in a register so
+// the common "not closer" case costs one compare per eight candidates.  Candidates that beat the
 // (possibly stale) root are parked in a small per-thread queue in shared memory and offered to the
 // heap later, in index order and against the then current root, by all lanes of the warp at the
 // same time: the heap sees exactly the reference's sequence of replacements (a parked candidate
@@ -49,13 +52,43 @@ __device__ __forceinline__ float knn_dist2(float dx, float dy, float dz)
     return __fmaf_rn(dz, dz, __fmaf_rn(dx, dx, __fmul_rn(dy, dy)));
 }
 
+// Two candidates per instruction: element 0 in the low half of the 64-bit register.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+// knn_dist2 of two candidates: fma(dz,dz, fma(dx,dx, dy*dy)) per element
+__device__ __forceinline__ uint64_t knn_dist2x2(uint64_t dx, uint64_t dy, uint64_t dz)
+{
+    uint64_t t;
+    asm("{\n\t.reg .b64 m;\n\t"
+        "mul.rn.f32x2 m, %2, %2;\n\t"
+        "fma.rn.f32x2 m, %1, %1, m;\n\t"
+        "fma.rn.f32x2 %0, %3, %3, m;\n\t}"
+        : "=l"(t) : "l"(dx), "l"(dy), "l"(dz));
+    return t;
+}
+
 template <int KMAX>
 __global__ void __launch_bounds__(KNN_THREADS)
 knn_kernel(int K, const float *__restrict__ src, const float *__restrict__ query,
            const int32_t *__restrict__ src_offset, const int32_t *__restrict__ query_offset,
            int B, int64_t Nq, int32_t *__restrict__ ret_idx, float *__restrict__ ret_dist)
 {
-    __shared__ float4 s_pts[KNN_TILE + 8];         // a step of eight may read past the last point
+    // coordinate planes x, y, z of a tile; a step of eight may read past the last point
+    __shared__ __align__(16) float s_xyz[3][KNN_TILE + 8];
     __shared__ int s_qi[KNN_QCAP * KNN_THREADS];   // parked candidates (source rows), [slot][thread]
     __shared__ int s_lo, s_hi;
 
@@ -92,6 +125,7 @@ knn_kernel(int K, const float *__restrict__ src, const float *__restrict__ query
     __syncthreads();
     const int lo = s_lo, hi = s_hi;
     float top = heap[0];
+    const uint64_t qx2 = pack2(qx, qx), qy2 = pack2(qy, qy), qz2 = pack2(qz, qz);
     int qn = 0;                                   // parked candidates of this thread
     int *qi = s_qi + threadIdx.x;                 // this thread's column of the queue
 
@@ -118,9 +152,10 @@ knn_kernel(int K, const float *__restrict__ src, const float *__restrict__ query
     for (int t0 = lo; t0 < hi; t0 += KNN_TILE) {
         const int cnt = min(KNN_TILE, hi - t0);
         __syncthreads();
-        for (int i = threadIdx.x; i < cnt; i += KNN_THREADS) {
-            const float *p = src + (int64_t)(t0 + i) * 3;
-            s_pts[i] = make_float4(__ldg(p), __ldg(p + 1), __ldg(p + 2), 0.f);
+        {
+            const float *p = src + (int64_t)t0 * 3;                  // 3 * cnt consecutive floats
+            for (int i = threadIdx.x; i < 3 * cnt; i += KNN_THREADS)
+                s_xyz[i % 3][i / 3] = __ldg(p + i);
         }
         __syncthreads();
         // clip the tile to this thread's own scene
@@ -130,12 +165,16 @@ knn_kernel(int K, const float *__restrict__ src, const float *__restrict__ query
         const int jb_w = __reduce_min_sync(0xffffffffu, jb), je_w = __reduce_max_sync(0xffffffffu, je);
         // eight candidates per step: one test for "none is closer than the heap root" (the common
         // case); the others are parked
-        for (int j = jb_w; j < je_w; j += 8) {
+        // (steps start on a multiple of four points: 16-byte loads from the planes)
+        for (int j = jb_w & ~3; j < je_w; j += 8) {
             float dd[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const float4 p = s_pts[j + u];
-                dd[u] = knn_dist2(p.x - qx, p.y - qy, p.z - qz);
+            for (int u = 0; u < 8; u += 4) {
+                const ulonglong2 x = *reinterpret_cast<const ulonglong2 *>(&s_xyz[0][j + u]);
+                const ulonglong2 y = *reinterpret_cast<const ulonglong2 *>(&s_xyz[1][j + u]);
+                const ulonglong2 z = *reinterpret_cast<const ulonglong2 *>(&s_xyz[2][j + u]);
+                unpack2(knn_dist2x2(sub2(x.x, qx2), sub2(y.x, qy2), sub2(z.x, qz2)), dd[u], dd[u + 1]);
+                unpack2(knn_dist2x2(sub2(x.y, qx2), sub2(y.y, qy2), sub2(z.y, qz2)), dd[u + 2], dd[u + 3]);
             }
             if (j >= jb && j + 8 <= je) {           // the whole step lies in this thread's scene (the common case)
                 const float m = fminf(fminf(fminf(dd[0], dd[1]), fminf(dd[2], dd[3])),

@@ -8,12 +8,15 @@ ranks, is what this module does:
 * ``shard_windows`` cuts the window list into contiguous ranges of equal cost;
 * ``ShardPlan`` holds everything about one (window set, world size, rank) that does not change
   between calls -- ranges, the rank's slice of the window arrays, the gather index of its rows and
-  the inverse index that puts gathered rows back into voxel order.  Building it reads the window
-  sizes on the host once; it is cached per window set, so a step does no host synchronisation;
-* ``exchange_rows`` packs any number of per-voxel arrays of a rank into ONE buffer, runs ONE
-  ``all_gather_into_tensor`` (equal, padded shards) and un-permutes everything with ONE gather;
-* ``sharded_attention_step`` runs forward + backward of the rank's windows in chunks so that the
-  all-gather of a chunk overlaps the kernels of the next one, and sums the table gradients.
+  the scatter index of the rows it receives.  Building it reads the window sizes on the host once;
+  it is cached per window set, so a step does no host synchronisation;
+* ``RowExchange`` / ``exchange_rows`` work IN PLACE: the kernels write a rank's rows in voxel order;
+  per chunk the rows are packed by one row-gather launch, exchanged by one asynchronous
+  ``all_gather_into_tensor`` (equal, padded shards) and the other ranks' rows are put in place by one
+  row-scatter launch on a side stream;
+* ``sharded_attention_step`` runs forward + backward of the rank's windows in chunks; `out` leaves
+  right after the forward of a chunk (it travels while the backward runs), `dq`, `dk`, `dv` after
+  the backward, so only the gradients of the last chunk are exposed; the table gradients are summed.
 
 Only NCCL (gloo on CPU) collectives on the caller's buffers are used: no peer-memory loads, no
 symmetric memory.
@@ -122,9 +125,8 @@ class ShardPlan:
     further cut into `chunks` sub-ranges of equal cost (chunk c of every rank is exchanged together).
     For chunk c: ``chunk_windows[c]`` = this rank's (first, end) windows, ``pad[c]`` = rows of the
     largest shard of that chunk over the ranks, ``gather_idx[c]`` = int64 [pad[c]] voxel rows of this
-    rank's shard in sorted order (padded with row 0).  ``slot`` = int64 [N]: for voxel row v the row of
-    the gathered buffer (laid out [chunk][rank][array][pad]) that holds v, for array 0 of `A` arrays:
-    ``slot_base + a * pad_of_voxel``, see ``exchange_rows``.
+    rank's shard in sorted order (padded with row 0), ``scatter_index(c)`` = where the rows of the
+    gathered block of chunk c (laid out [rank][array][pad]) belong.
     """
 
     def __init__(self, w_sizes, w2n, n2n, world: int, rank: int, chunks: int = 1):
@@ -157,45 +159,23 @@ class ShardPlan:
             idx = torch.zeros(self.pad[c], dtype=torch.int64, device=dev)
             idx[:hi - lo] = n2n64[lo:hi]
             self.gather_idx.append(idx)
-        # inverse map: sorted position -> (chunk, rank, offset); stored per voxel row as
-        # slot_chunk_base (row offset of the chunk's block for ONE array) and slot_in_chunk
-        pos_chunk = np.zeros(self.N, dtype=np.int64)
-        pos_rank = np.zeros(self.N, dtype=np.int64)
-        pos_off = np.zeros(self.N, dtype=np.int64)
-        for r in range(world):
-            for c in range(chunks):
-                _, _, lo, hi = sub[r][c]
-                pos_chunk[lo:hi] = c
-                pos_rank[lo:hi] = r
-                pos_off[lo:hi] = np.arange(hi - lo)
-        n2n_host = n2n64.cpu().numpy()
-        self._v_chunk = np.empty(self.N, dtype=np.int64)
-        self._v_rank = np.empty(self.N, dtype=np.int64)
-        self._v_off = np.empty(self.N, dtype=np.int64)
-        self._v_chunk[n2n_host] = pos_chunk
-        self._v_rank[n2n_host] = pos_rank
-        self._v_off[n2n_host] = pos_off
+        self._sub = sub
+        self._n2n_host = n2n64.cpu().numpy()
         self._dev = dev
-        self._unperm = {}      # number of arrays -> int64 [A * N] gather index into the flat gathered buffer
+        self._scatter = {}     # chunk -> int64 [world * pad] scatter index of the gathered block
 
-    def gathered_rows(self, A: int) -> int:
-        """Rows of the flat gathered buffer for `A` arrays: sum over chunks of world * A * pad."""
-        return sum(self.world * A * p for p in self.pad)
-
-    def chunk_offset(self, A: int, c: int) -> int:
-        return sum(self.world * A * p for p in self.pad[:c])
-
-    def unpermute_index(self, A: int):
-        """int64 [A * N]: entry a * N + v is the row of the flat gathered buffer holding array a of voxel v."""
+    def scatter_index(self, c: int):
+        """int64 [world * pad[c]]: the voxel row of entry (rank, offset) of chunk c's gathered block,
+        -1 for padding and for this rank's own rows (its kernels wrote them in place)."""
         import torch
-        if A not in self._unperm:
-            pad = np.asarray(self.pad, dtype=np.int64)
-            base = np.asarray([self.chunk_offset(A, c) for c in range(self.chunks)], dtype=np.int64)
-            p = pad[self._v_chunk]
-            first = base[self._v_chunk] + self._v_rank * A * p + self._v_off
-            idx = np.concatenate([first + a * p for a in range(A)])
-            self._unperm[A] = torch.from_numpy(idx).to(self._dev)
-        return self._unperm[A]
+        if c not in self._scatter:
+            idx = np.full((self.world, self.pad[c]), -1, dtype=np.int64)
+            for r in range(self.world):
+                if r != self.rank:
+                    _, _, lo, hi = self._sub[r][c]
+                    idx[r, :hi - lo] = self._n2n_host[lo:hi]
+            self._scatter[c] = torch.from_numpy(idx.reshape(-1)).to(self._dev)
+        return self._scatter[c]
 
 
 _PLAN_CACHE = {}
@@ -241,53 +221,104 @@ def gather_rows(srcs: Sequence, idx, out):
     return out
 
 
+def scatter_rows(src, idx, block_rows: int, dsts: Sequence):
+    """dsts[a][idx[i]] = src[i // block_rows][a][i % block_rows] for every i with idx[i] >= 0
+    (`src`: [blocks, A, block_rows, C] contiguous, `dsts`: A contiguous [rows, C] arrays).  One launch
+    of the library's row-scatter kernel on CUDA tensors, torch on CPU tensors (the gloo tests)."""
+    import torch
+    nb, A, br, C = src.shape
+    if br != block_rows or len(dsts) != A:
+        raise ValueError("scatter_rows: shape mismatch")
+    if not src.is_cuda:
+        keep = idx >= 0
+        rows = idx[keep]
+        for a, d in enumerate(dsts):
+            d[rows] = src[:, a].reshape(nb * br, C)[keep]
+        return
+    import ctypes
+    from . import _lib
+    row_bytes = C * src.element_size()
+    for d in dsts:
+        if not d.is_contiguous() or d.dtype != src.dtype or d.shape[1] != C:
+            raise ValueError("scatter_rows: destinations must be contiguous [rows, C] arrays of the source's dtype")
+    ptrs = (ctypes.c_void_p * A)(*[d.data_ptr() for d in dsts])
+    with torch.cuda.device(src.device):
+        rc = _lib.lib.s3d_scatter_rows(src.data_ptr(), A, idx.data_ptr(), nb * br, row_bytes, br,
+                                       A * br * row_bytes, br * row_bytes, ctypes.cast(ptrs, ctypes.c_void_p),
+                                       torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "s3d_scatter_rows")
+
+
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device):
+    import torch
+    key = (device.type, device.index)
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return _SIDE_STREAMS[key]
+
+
 class RowExchange:
-    """The in-flight exchange of one step: packs chunk after chunk, one collective per chunk
-    (asynchronous, so it overlaps whatever the caller launches next), one un-permute at the end."""
+    """The in-flight exchange of `A` per-voxel arrays of one step, IN PLACE: a rank's kernels wrote the
+    rows of its own windows into ``arrays``; ``send_chunk(c)`` packs those of chunk c (one row-gather
+    launch), starts one asynchronous all-gather and queues, on a side stream behind it, the one
+    row-scatter launch that puts the other ranks' rows of that chunk into ``arrays``.  Pack and
+    collective are ordered behind the kernels already launched; everything the caller launches
+    afterwards overlaps them.  ``finish()`` makes the current stream wait for the scatters."""
 
-    def __init__(self, plan: ShardPlan, A: int, C: int, dtype, group=None):
+    def __init__(self, plan: ShardPlan, arrays: Sequence, group=None):
         import torch
-        self.plan, self.A, self.C, self.group = plan, A, C, group
-        self.flat = torch.empty((plan.gathered_rows(A), C), dtype=dtype, device=plan._dev)
-        self.piece = [torch.empty((A, plan.pad[c], C), dtype=dtype, device=plan._dev) for c in range(plan.chunks)]
-        self.works = []
+        self.plan, self.group = plan, group
+        self.A = len(arrays)
+        self.C = int(np.prod(arrays[0].shape[1:]))
+        self.arrays = list(arrays)
+        self.rows = [x.reshape(plan.N, self.C) for x in arrays]
+        for x, r in zip(arrays, self.rows):
+            if r.data_ptr() != x.data_ptr():
+                raise ValueError("RowExchange: arrays must be contiguous")
+        self.cuda = arrays[0].is_cuda
+        self.side = _side_stream(arrays[0].device) if (self.cuda and plan.world > 1) else None
+        self.keep = []         # buffers in flight
 
-    def send_chunk(self, c: int, arrays: Sequence):
-        """arrays: `A` tensors [N, C] whose rows of this rank's chunk c are valid."""
+    def send_chunk(self, c: int):
         import torch
         import torch.distributed as dist
         plan = self.plan
-        if len(arrays) != self.A:
-            raise ValueError("wrong number of arrays")
-        gather_rows([x.reshape(plan.N, self.C) for x in arrays], plan.gather_idx[c], self.piece[c])
-        rows = plan.world * self.A * plan.pad[c]
-        off = plan.chunk_offset(self.A, c)
-        dst = self.flat[off:off + rows]
         if plan.world == 1:
-            dst.copy_(self.piece[c].reshape(rows, self.C))
             return
-        self.works.append(dist.all_gather_into_tensor(dst.reshape(-1), self.piece[c].reshape(-1),
-                                                      group=self.group, async_op=True))
+        dtype, dev = self.rows[0].dtype, self.rows[0].device
+        piece = torch.empty((self.A, plan.pad[c], self.C), dtype=dtype, device=dev)
+        block = torch.empty((plan.world, self.A, plan.pad[c], self.C), dtype=dtype, device=dev)
+        gather_rows(self.rows, plan.gather_idx[c], piece)
+        work = dist.all_gather_into_tensor(block.reshape(-1), piece.reshape(-1), group=self.group, async_op=True)
+        self.keep.append((piece, block))
+        if self.cuda:
+            with torch.cuda.stream(self.side):
+                work.wait()                                   # the side stream waits, the host does not
+                scatter_rows(block, plan.scatter_index(c), plan.pad[c], self.rows)
+        else:
+            work.wait()
+            scatter_rows(block, plan.scatter_index(c), plan.pad[c], self.rows)
 
     def finish(self):
-        """-> `A` tensors [N, C] in voxel order, identical on every rank."""
+        """-> the `A` arrays, complete and identical on every rank."""
         import torch
-        for w in self.works:
-            w.wait()
-        self.works = []
-        full = torch.empty((1, self.A * self.plan.N, self.C), dtype=self.flat.dtype, device=self.flat.device)
-        gather_rows([self.flat], self.plan.unpermute_index(self.A), full)
-        return [full[0, a * self.plan.N:(a + 1) * self.plan.N] for a in range(self.A)]
+        if self.side is not None:
+            torch.cuda.current_stream().wait_stream(self.side)
+        self.keep = []          # freed in current-stream order, i.e. behind the scatters
+        return self.arrays
 
 
 def exchange_rows(plan: ShardPlan, arrays: Sequence, group=None):
-    """All ranks end with the full per-voxel arrays: rank r contributes the rows of its windows.
-    One packed buffer, one all-gather per chunk of the plan, one un-permute."""
-    C = int(np.prod(arrays[0].shape[1:]))
-    ex = RowExchange(plan, len(arrays), C, arrays[0].dtype, group)
+    """All ranks end with the full per-voxel arrays: rank r contributes the rows of its windows, the
+    other rows of ``arrays`` are overwritten in place.  One packed all-gather and one scatter per chunk
+    of the plan."""
+    ex = RowExchange(plan, arrays, group)
     for c in range(plan.chunks):
-        ex.send_chunk(c, arrays)
-    return [x.reshape(arrays[0].shape) for x in ex.finish()]
+        ex.send_chunk(c)
+    return ex.finish()
 
 
 def sharded_attention_step(q, k, v, tq, tk, tv, sizes, w_sizes, w2n, n2n, n_coords, dout, group=None,
@@ -307,21 +338,24 @@ def sharded_attention_step(q, k, v, tq, tk, tv, sizes, w_sizes, w2n, n2n, n_coor
         plan = get_plan(w_sizes, w2n, n2n, world, rank, chunks)
     N, H, hd = q.shape
     C = H * hd
-    ex = RowExchange(plan, 4, C, q.dtype, group)
     out = torch.empty_like(q)
     lse = torch.empty((N, H), dtype=torch.float32, device=q.device)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    ex_out = RowExchange(plan, (out,), group)          # leaves right after the forward of a chunk
+    ex_grad = RowExchange(plan, (dq, dk, dv), group)
     tg = None
     for c in range(plan.chunks):
         ws_c, w2n_c = plan.w_sizes_chunk[c], plan.w2n_chunk[c]
         attn_forward_raw(q, k, v, tq, tk, tv, sizes, ws_c, w2n_c, n2n, n_coords, out=out, lse=lse)
+        ex_out.send_chunk(c)
         g = attn_backward_raw(q, k, v, tq, tk, tv, sizes, ws_c, w2n_c, n2n, n_coords, out, lse, dout,
                               dq=dq, dk=dk, dv=dv)
         tg = list(g[3:6]) if tg is None else [a + b for a, b in zip(tg, g[3:6])]
-        ex.send_chunk(c, (out, dq, dk, dv))
+        ex_grad.send_chunk(c)
     tg = allreduce_table_grads(tuple(tg), group)
-    o_f, dq_f, dk_f, dv_f = (x.view(N, H, hd) for x in ex.finish())
-    return o_f, dq_f, dk_f, dv_f, tg
+    ex_out.finish()
+    ex_grad.finish()
+    return out, dq, dk, dv, tg
 
 
 def sharded_attention(q, k, v, tq, tk, tv, sizes, w_sizes, w2n, n2n, n_coords, dout=None, group=None):

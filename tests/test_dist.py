@@ -142,7 +142,7 @@ def _rank_plan_exchange(rank, world, port, chunks, q):
 @pytest.mark.timeout(300)
 @pytest.mark.parametrize("world,chunks", [(2, 1), (2, 2), (3, 2)])
 def test_packed_exchange_of_a_shard_plan_reassembles_every_array(world, chunks):
-    """ShardPlan + exchange_rows: one packed all-gather per chunk, one un-permute; every rank ends
+    """ShardPlan + exchange_rows: one packed all-gather and one scatter per chunk, in place; every rank ends
     with the full arrays although it only ever computed (and holds NaN outside) its own windows."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()

@@ -43,3 +43,55 @@ def test_sharded_step_on_one_rank_equals_the_plain_calls(chunks):
     assert torch.equal(o2, out) and torch.equal(dq, ref[0]) and torch.equal(dk, ref[1]) and torch.equal(dv, ref[2])
     for a, b in zip(tg, ref[3:6]):      # summed over chunks in a different order
         assert torch.allclose(a, b, rtol=1e-4, atol=1e-5 * float(b.abs().max()))
+
+
+def test_scatter_rows_kernel_matches_indexed_assignment():
+    from swin3d_b200.dist import scatter_rows
+    g = torch.Generator(device="cuda").manual_seed(6)
+    for C, dtype, A in ((80, torch.float16, 3), (160, torch.float16, 1), (8, torch.float32, 4)):
+        blocks, br, rows = 3, 1000, 5000
+        src = torch.randn((blocks, A, br, C), device="cuda", generator=g).to(dtype)
+        idx = torch.randperm(rows, device="cuda", generator=g)[:blocks * br].clone()
+        idx[::7] = -1                                   # padding and own rows are skipped
+        dsts = [torch.full((rows, C), -3.0, dtype=dtype, device="cuda") for _ in range(A)]
+        want = [d.clone() for d in dsts]
+        keep = idx >= 0
+        for a in range(A):
+            want[a][idx[keep]] = src[:, a].reshape(blocks * br, C)[keep]
+        scatter_rows(src, idx, br, dsts)
+        for a in range(A):
+            assert torch.equal(dsts[a], want[a])
+
+
+@pytest.mark.parametrize("world,chunks", [(2, 2), (4, 3)])
+def test_pack_and_scatter_of_every_rank_reassemble_the_arrays(world, chunks):
+    """The exchange of `world` ranks replayed in one process: every rank packs its rows of a chunk with
+    its plan's gather index, the blocks are concatenated as the all-gather would, and each rank's
+    scatter index puts the other ranks' rows in place."""
+    from swin3d_b200.dist import ShardPlan, gather_rows, scatter_rows
+    from tests.gpu_helpers import dev
+    from tests.helpers import make_problem
+    p = make_problem(seed=33, n_voxels=2500, grid=28, H=2, hd=8, crse="XYZ_RGB")
+    ws, w2n, n2n = dev(p.w_sizes), dev(p.w2n), dev(p.n2n)
+    N, C = p.q.shape[0], 16
+    g = torch.Generator(device="cuda").manual_seed(7)
+    truth = [torch.randn((N, C), device="cuda", generator=g).half() for _ in range(3)]
+    plans = [ShardPlan(ws, w2n, n2n, world, r, chunks) for r in range(world)]
+    mine = []
+    for pl in plans:                                   # a rank only holds the rows of its own windows
+        arrs = [torch.full((N, C), float("nan"), dtype=torch.float16, device="cuda") for _ in range(3)]
+        for lo, hi in pl.chunk_rows:
+            rows = n2n[lo:hi].long()
+            for a in range(3):
+                arrs[a][rows] = truth[a][rows]
+        mine.append(arrs)
+    for c in range(chunks):
+        pad = plans[0].pad[c]
+        block = torch.empty((world, 3, pad, C), dtype=torch.float16, device="cuda")
+        for r, pl in enumerate(plans):
+            gather_rows(mine[r], pl.gather_idx[c], block[r])
+        for r, pl in enumerate(plans):
+            scatter_rows(block, pl.scatter_index(c), pad, mine[r])
+    for r in range(world):
+        for a in range(3):
+            assert torch.equal(mine[r][a], truth[a])
