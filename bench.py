@@ -834,12 +834,15 @@ def run_knn(args):
             if not (torch.equal(got[0], ref[0]) and torch.equal(got[1].view(torch.int32), ref[1].view(torch.int32))):
                 raise RuntimeError("sharded KNN differs from the single-GPU result")
         evals = n_sc * 200_000 * 50_000 / (ms * 1e-3)
-        # 8 fp32 operations per candidate (3 sub, 1 mul, 2 fma) against the measured FFMA throughput of
-        # all ranks (nominal CUDA-core peak of one B200: 148 SMs x 128 lanes x 2 x 1.965 GHz = 74.4 TFLOP/s)
+        # The reference's distance is 8 fp32 operations per candidate (3 sub, 1 mul, 2 fma); the scan
+        # evaluates a 3-fma lower bound (6 operations) for every candidate and the full expression only for
+        # the few that pass.  Both accountings against the measured FFMA throughput of all ranks (nominal
+        # CUDA-core peak of one B200: 148 SMs x 128 lanes x 2 x 1.965 GHz = 74.4 TFLOP/s).
         res[f"K{K}"] = {"ms": ms, "queries_per_s": qry.shape[0] / (ms * 1e-3), "pair_evals_per_s": evals,
-                        "fp32_tflops": evals * 8 / 1e12,
-                        "frac_of_measured_fp32_peak": evals * 8 / 1e12 / (fma_peak * world),
-                        "frac_of_nominal_fp32_peak": evals * 8 / (74.4e12 * world)}
+                        "fp32_tflops_executed": evals * 6 / 1e12,
+                        "frac_of_measured_fp32_peak": evals * 6 / 1e12 / (fma_peak * world),
+                        "reference_equivalent_fp32_tflops": evals * 8 / 1e12,
+                        "reference_equivalent_frac_of_measured_fp32_peak": evals * 8 / 1e12 / (fma_peak * world)}
     if world > 1:
         if rank == 0:
             print(json.dumps({"metric": f"knn queries/sec ({n_sc} scenes x 200k queries x 50k sources)",

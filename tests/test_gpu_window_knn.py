@@ -92,6 +92,47 @@ def test_knn_ties_follow_the_reference_heap():
         assert np.array_equal(idx, ridx) and np.array_equal(d2, rd2)
 
 
+def _two_scenes(seed):
+    srcs, qrys = zip(*[S.make_knn_scene(seed + s, 1300, 1100 + 90 * s) for s in range(2)])
+    return (np.concatenate(srcs), np.concatenate(qrys), np.cumsum([len(x) for x in srcs]),
+            np.cumsum([len(x) for x in qrys]))
+
+
+@pytest.mark.parametrize("case", ["offset_1e3", "offset_1e5", "scale_1e-18", "scale_1e-22", "scale_1e18",
+                                  "scale_3e19", "nonfinite", "duplicates"])
+def test_knn_lower_bound_filter_never_changes_the_result(case):
+    """The scan rejects candidates with a rounded lower bound |p|^2 - 2 p.q + margin before the exact
+    distance is evaluated; the margin scales with the coordinate magnitudes.  Magnitudes that stress
+    it -- far from the origin, products in the subnormal range, squares that overflow, NaN and
+    infinite coordinates, sources equal to queries -- must give the literal heap's bits."""
+    src, qry, so, qo = _two_scenes(40)
+    rng = np.random.default_rng(5)
+    if case.startswith("offset"):
+        off = np.float32(case.split("_")[1])
+        src, qry = src + off, qry + off
+    elif case.startswith("scale"):
+        sc = np.float32(case.split("_")[1])
+        src, qry = src * sc, qry * sc
+    elif case == "nonfinite":
+        src, qry = src.copy(), qry.copy()
+        bad = rng.choice(len(src), 60, replace=False)
+        src[bad[:20], rng.integers(0, 3, 20)] = np.nan
+        src[bad[20:40], rng.integers(0, 3, 20)] = np.inf
+        src[bad[40:], rng.integers(0, 3, 20)] = -np.inf
+        qry[5, 1], qry[6, 0], qry[7, 2] = np.nan, np.inf, -np.inf
+        src[bad[0] + 1] = 3e19                                   # |p|^2 overflows, the point itself is finite
+    elif case == "duplicates":
+        src = src.copy()
+        src[:400] = qry[:400]
+        src[400:600] = qry[:200]                                 # the same point twice: distance 0 ties
+    for K in (3, 16):
+        idx, d2 = _knn_gpu(K, src, qry, so, qo)
+        with np.errstate(all="ignore"):
+            ridx, rd2 = O.knn(K, src, qry, so, qo, fma_mode=2)
+        assert np.array_equal(d2.view(np.uint32), rd2.view(np.uint32)), case
+        assert np.array_equal(idx, ridx), case
+
+
 def test_knn_fewer_candidates_than_k_and_empty_scene():
     src = np.array([[0, 0, 0], [1, 0, 0]], dtype=np.float32)
     qry = np.array([[0.1, 0, 0], [5, 5, 5]], dtype=np.float32)
