@@ -505,7 +505,13 @@ def run_attention_split(args):
     torch.cuda.set_device(local)
     if world > 1:
         bind_to_gpu_numa_node(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # collectives on a high-priority stream: their blocks take the SMs that the attention kernels'
+        # blocks free, instead of queueing behind the whole launch, so that the exchange of a chunk
+        # really runs under the next kernels
+        opts = None
+        if not args.nccl_default_priority:
+            opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), pg_options=opts)
     c = CFG
     H, hd, ws, quant, crse = c["H"], c["hd"], c["ws"], c["quant"], c["crse"]
     Cc = H * hd
@@ -527,12 +533,26 @@ def run_attention_split(args):
     q = (rnd() * hd ** -0.5).half()
     k, v, g = rnd().half(), rnd().half(), rnd().half()
     tabs = [dev(t).half() for t in S.make_tables(1, sizes)]
-    chunks = 1 if world == 1 else args.chunks
-    plans = [get_plan(wi.w_sizes, wi.w2n, wi.n2n, world, rank, chunks) for wi, _ in win]   # host read, once
+    chunk_spec = int(args.chunks) if args.chunks.isdigit() else tuple(float(x) for x in args.chunks.split(","))
+    p2p = world > 1 and args.exchange == "p2p"
+    if world == 1 or p2p:
+        chunk_spec = 1
+    chunks = chunk_spec if isinstance(chunk_spec, int) else len(chunk_spec)
+    plans = [get_plan(wi.w_sizes, wi.w2n, wi.n2n, world, rank, chunk_spec) for wi, _ in win]   # host read, once
 
-    def step(i, bufs=None):
+    peers = None
+    if p2p:
+        from swin3d_b200.dist import PeerResults, sharded_attention_step_p2p
+        peers = PeerResults((N, H, hd), torch.float16, torch.device("cuda", local))
+    calls = [0]                     # steps so far: the peers' result sets alternate, on every rank alike
+
+    def step(i, bufs=None, consumed=None):
         wi, ncr = win[i % 2]
         x = bufs if bufs is not None else (q, k, v, g)
+        if p2p:
+            calls[0] += 1
+            return sharded_attention_step_p2p(x[0], x[1], x[2], *tabs, sizes, wi.w_sizes, wi.w2n, wi.n2n, ncr, x[3],
+                                              peers, calls[0], plan=plans[i % 2], consumed=consumed)
         return sharded_attention_step(x[0], x[1], x[2], *tabs, sizes, wi.w_sizes, wi.w2n, wi.n2n, ncr, x[3],
                                       plan=plans[i % 2])
 
@@ -601,6 +621,7 @@ def run_attention_split(args):
     comp = torch.cuda.current_stream()
     dbuf = [[torch.empty((N, H, hd), dtype=torch.float16, device="cuda") for _ in range(4)] for _ in range(2)]
     set_free = [None, None]     # event: the step that last read this buffer set has finished
+    copied = [None]             # event: the previous step's results have left for the host
 
     def e2e_step(i):
         lo, hi = bands[i % 2]
@@ -613,7 +634,7 @@ def run_attention_split(args):
             ev_in = torch.cuda.Event()
             ev_in.record(s_in)
         comp.wait_event(ev_in)
-        r = step(i, bufs)
+        r = step(i, bufs, consumed=copied[0])
         ev_c = torch.cuda.Event()
         ev_c.record(comp)
         set_free[i % 2] = ev_c
@@ -623,6 +644,8 @@ def run_attention_split(args):
             s_out.wait_event(ev_c)
             for dst, src in zip(out_pin, r[:4]):
                 dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
+            copied[0] = torch.cuda.Event()
+            copied[0].record(s_out)
         return r
 
     def e2e_run(nsteps):
@@ -647,6 +670,16 @@ def run_attention_split(args):
         if not torch.equal(got[lo:hi], want[lo:hi].cpu()):
             raise RuntimeError(f"end-to-end sharded step: {name} differs from the device-resident result")
     band_rows = float(sum(b - a for a, b in bands)) / len(bands)
+    if world > 1:
+        # every rank must hold ALL rows: compare with the unsplit computation on this GPU
+        wi_c, ncr_c = win[(e2e_steps - 1) % 2]
+        o_c, lse_c = C.attn_forward_raw(q, k, v, *tabs, sizes, wi_c.w_sizes, wi_c.w2n, wi_c.n2n, ncr_c)
+        g_c = C.attn_backward_raw(q, k, v, *tabs, sizes, wi_c.w_sizes, wi_c.w2n, wi_c.n2n, ncr_c, o_c, lse_c, g)
+        ref = step(e2e_steps - 1)
+        torch.cuda.synchronize()
+        for name, got, want in zip(("out", "dq", "dk", "dv"), ref[:4], (o_c,) + tuple(g_c[:3])):
+            if not torch.equal(got, want):
+                raise RuntimeError(f"split step: {name} on rank {rank} differs from the unsplit computation")
 
     stats = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e_ms, band_rows, compute_ms], dtype=torch.float64, device="cuda")
     compute_mean = compute_ms
@@ -661,6 +694,8 @@ def run_attention_split(args):
         band_total = float(sm[4])
     else:
         band_total = band_rows
+    if peers is not None:
+        peers.close()               # collective: every rank has finished its steps
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -675,13 +710,16 @@ def run_attention_split(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
         "config": dict(workload_config(), partition=f"one batch, windows split over {world} GPU(s) by cost, "
-                       f"{chunks} chunk(s) per rank", rooms_total=args.rooms or c["rooms"]),
+                       f"{chunks} chunk(s) per rank" + ("" if isinstance(chunk_spec, int) else f" of relative cost {args.chunks}"), rooms_total=args.rooms or c["rooms"]),
         "voxels_total": N, "voxels_of_rank0": n_local, "fwd_ms_rank_max": fwd_ms, "bwd_ms_rank_max": bwd_ms,
         "compute_ms_rank_max": compute_ms, "compute_ms_rank_mean": compute_mean,
         "exchange_ms_after_overlap": ms_per_step - compute_ms,
-        "exchange": "in place, per chunk: rows of out (after the forward) and of dq|dk|dv (after the backward) packed by "
-                    "one gather launch, one async all_gather_into_tensor, one scatter launch on a side stream; "
-                    "all-reduce of the 3 table gradients",
+        "exchange": ("peer stores: the attention kernels write every result row into the arrays of all ranks (CUDA IPC "
+                     "mappings, plain stores over NVLink); the all-reduce of the 3 table gradients orders the ranks"
+                     if p2p else
+                     "in place, per chunk: rows of out (after the forward) and of dq|dk|dv (after the backward) packed by "
+                     "one gather launch, one async all_gather_into_tensor, one scatter launch on a side stream; "
+                     "all-reduce of the 3 table gradients"),
         "roofline": {"bound": "hbm", "kernel": "attention backward, this rank's windows (tile-pair single-sweep kernel)",
                      "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": None,
                      "peak_source": peak_src, "algorithmic_bytes_per_voxel": {"fwd": pv_fwd, "bwd": pv_bwd}},
@@ -690,7 +728,7 @@ def run_attention_split(args):
                 "h2d_bytes_per_step": int(4 * band_total * Cc * 2), "d2h_bytes_per_step": int(4 * band_total * Cc * 2),
                 "note": "bytes summed over the ranks: each copies the band of voxel rows its windows touch"},
         # per chunk: forward single-tile + tiled, backward; with an exchange two gathers and two scatters more
-        "gpu_launches": (3 + (4 if world > 1 else 0)) * chunks * args.steps,
+        "gpu_launches": (3 if p2p else (3 + (4 if world > 1 else 0)) * chunks) * args.steps,
         "clocks": clocks,
     }
     print(json.dumps(line))
@@ -1051,7 +1089,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="attn",
                     choices=["attn", "attn-replicas", "attn-split", "knn", "stages", "reference-gpu"])
-    ap.add_argument("--chunks", type=int, default=2, help="chunks per rank of the split mode (exchange/compute overlap)")
+    ap.add_argument("--chunks", default="2", help="split mode: chunks per rank (exchange/compute overlap), a count or "
+                    "relative costs such as 3,2,1 (a small last chunk leaves little exchange exposed)")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="split mode: how the rows reach the other ranks -- p2p: the kernels store them into every "
+                         "rank's arrays (peer stores, CUDA IPC); nccl: packed all-gathers per chunk")
+    ap.add_argument("--nccl-default-priority", action="store_true",
+                    help="split mode: do not ask for a high-priority NCCL stream (for comparison)")
     ap.add_argument("--rooms", type=int, default=0, help="rooms per GPU (default 8)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

@@ -87,6 +87,46 @@ int s3d_attn_bwd(const void *q, const void *k, const void *v,
                  void *dq, void *dk, void *dv, float *dtq, float *dtk, float *dtv,
                  void *stream);
 
+/* The same two calls for one window set split over several GPUs: every row of out (forward) or of
+ * dq, dk, dv (backward) that the call writes is ALSO stored to the same row of n_mirrors further
+ * buffers of the same shape -- the result arrays of the other GPUs, mapped into this process
+ * (s3d_ipc_open) -- by plain peer stores from inside the kernels, so that the exchange overlaps the
+ * computation and no pack / collective / un-permute pass follows.  *_mirrors_host: HOST arrays of
+ * n_mirrors <= S3D_MAX_MIRRORS device pointers, 16-byte aligned.  The caller orders the ranks
+ * afterwards (any collective issued on the same stream, e.g. the all-reduce of the table
+ * gradients: when it has completed on a rank, every rank's kernels have finished and their rows
+ * are in place).  S3D_ERR_UNSUPPORTED for shapes served by kernels without mirrored stores (the
+ * generic path and head_dim 16 with an even head count and large tables).  The reference has no
+ * multi-GPU attention; this replaces nothing in it.                                             */
+#define S3D_MAX_MIRRORS 7
+int s3d_attn_fwd_mirrored(const void *q, const void *k, const void *v,
+                          const void *tq, const void *tk, const void *tv,
+                          const int32_t *table_sizes_host, int D,
+                          const int32_t *w_sizes, const int32_t *w2n, const int32_t *n2n,
+                          const float *n_coords, int64_t N, int64_t W, int H, int hd, int dtype,
+                          void *out, float *lse, int n_mirrors, void *const *out_mirrors_host,
+                          void *stream);
+int s3d_attn_bwd_mirrored(const void *q, const void *k, const void *v,
+                          const void *tq, const void *tk, const void *tv,
+                          const int32_t *table_sizes_host, int D,
+                          const int32_t *w_sizes, const int32_t *w2n, const int32_t *n2n,
+                          const float *n_coords, int64_t N, int64_t W, int H, int hd, int dtype,
+                          const void *out, const float *lse, const void *dout,
+                          void *dq, void *dk, void *dv, float *dtq, float *dtk, float *dtv,
+                          int n_mirrors, void *const *dq_mirrors_host, void *const *dk_mirrors_host,
+                          void *const *dv_mirrors_host, void *stream);
+
+/* Result arrays that other processes of this node can map: s3d_peer_alloc allocates `bytes` on the
+ * current device (its own allocation, so that it can be exported) and writes the 64-byte CUDA IPC
+ * memory handle of it to handle64_out; the owner releases it with s3d_peer_free once no peer maps
+ * it any more.  s3d_ipc_open maps such an allocation of ANOTHER process into this process for the
+ * current device, with peer access enabled on first use (*ptr_out = its base address);
+ * s3d_ipc_close unmaps it.  These are the only calls of the library that allocate.             */
+int s3d_peer_alloc(int64_t bytes, void **ptr_out, void *handle64_out);
+int s3d_peer_free(void *ptr);
+int s3d_ipc_open(const void *handle64, void **ptr_out);
+int s3d_ipc_close(void *ptr);
+
 /* fp32 FMA throughput probe (the roofline denominator of the KNN kernel, which stays on the CUDA cores
  * because its distance expression must match the reference bit for bit): launches `blocks` blocks
  * of 1024 threads, each thread running 8 independent chains of `iters` fused multiply-adds; the caller

@@ -28,6 +28,15 @@ SIGNATURES = {
                      [_i64, _i64, _i32, _i32, _i32, _c_void_p, _c_void_p, _c_void_p]),
     "s3d_attn_bwd": (_i32, [_c_void_p] * 6 + [_c_void_p, _i32] + [_c_void_p] * 4 +
                      [_i64, _i64, _i32, _i32, _i32] + [_c_void_p] * 3 + [_c_void_p] * 6 + [_c_void_p]),
+    "s3d_attn_fwd_mirrored": (_i32, [_c_void_p] * 6 + [_c_void_p, _i32] + [_c_void_p] * 4 +
+                              [_i64, _i64, _i32, _i32, _i32, _c_void_p, _c_void_p, _i32, _c_void_p, _c_void_p]),
+    "s3d_attn_bwd_mirrored": (_i32, [_c_void_p] * 6 + [_c_void_p, _i32] + [_c_void_p] * 4 +
+                              [_i64, _i64, _i32, _i32, _i32] + [_c_void_p] * 3 + [_c_void_p] * 6 +
+                              [_i32, _c_void_p, _c_void_p, _c_void_p, _c_void_p]),
+    "s3d_peer_alloc": (_i32, [_i64, _c_void_p, _c_void_p]),
+    "s3d_peer_free": (_i32, [_c_void_p]),
+    "s3d_ipc_open": (_i32, [_c_void_p, _c_void_p]),
+    "s3d_ipc_close": (_i32, [_c_void_p]),
     "s3d_debug_crse_indices": (_i32, [_c_void_p, _c_void_p, _i32, _i32, _i32, _i32, _i32,
                                       _c_void_p, _c_void_p]),
     "s3d_debug_crse_indices_variant": (_i32, [_c_void_p, _c_void_p, _i32, _i32, _i32, _i32, _i32, _i32,

@@ -7,6 +7,13 @@
 
 namespace s3d {
 
+// Further copies of a result array: every row the kernels write is also stored to the same row of
+// these buffers (other GPUs' result arrays mapped into this process: plain peer stores).
+struct Mirrors {
+    int n;
+    void *p[S3D_MAX_MIRRORS];
+};
+
 struct AttnArgs {
     const void *q, *k, *v, *tq, *tk, *tv;
     CrseMeta meta;
@@ -19,6 +26,7 @@ struct AttnArgs {
     const void *dout; // backward only
     void *dq, *dk, *dv;
     float *dtq, *dtk, *dtv;
+    Mirrors m_out, m_dq, m_dk, m_dv;   // forward: m_out; backward: m_dq, m_dk, m_dv
 };
 
 // The last CUDA runtime error a launcher of this library ran into (cudaSuccess if none), for

@@ -25,6 +25,13 @@
 namespace s3d {
 namespace tc {
 
+// A half2 of a result row, to this GPU's array and to the same place of every mirror (peer stores).
+__device__ __forceinline__ void store_h2_mirrored(__half *base, const Mirrors &m, int64_t off, __half2 v)
+{
+    *reinterpret_cast<__half2 *>(base + off) = v;
+    for (int i = 0; i < m.n; ++i) *reinterpret_cast<__half2 *>(static_cast<__half *>(m.p[i]) + off) = v;
+}
+
 constexpr int QT = 32;        // queries per tile (= lanes)
 constexpr int KT = 16;        // keys per tile
 constexpr int NWARP = 8;

@@ -739,6 +739,7 @@ int attn_tc_backward(const AttnArgs &a0, cudaStream_t st)
     // the single-sweep kernel serves head pairs of 8 channels and single heads of 16, windows of any size
     if (hdm != tc::HDM_PAIR16 && attn_tc_bwd_small_supported(a0))
         return attn_tc_backward_small(a0, st);      // tile pairs: windows of any size
+    if (a0.m_dq.n) return S3D_ERR_UNSUPPORTED;      // the two-sweep kernels have no mirrored stores
     const int n_mt = (a.meta.R + 15) / 16;
     const int mtw = (n_mt + tc::BW_NWARP - 1) / tc::BW_NWARP;
 #define S3D_TC_BWD(DD)                                            \

@@ -105,6 +105,7 @@ struct SmallParams {
     const float *n_coords;
     int64_t W;
     int H;
+    Mirrors m_dq, m_dk, m_dv;
 };
 
 // Set when a bounded wait of a kernel in this file ran out (it never should).
@@ -112,7 +113,7 @@ __device__ int g_bwd_small_async_error;
 
 template <int D, int NPU /*projection + dT units per warp*/, int NHU /*hist.T units per warp*/, bool HD16>
 __global__ void __launch_bounds__((bwd_small_warps(D) + 1) * 32, 1)
-attn_bwd_small_kernel(const SmallParams P, const PermMeta pm, const PairConsts pc)
+attn_bwd_small_kernel(const __grid_constant__ SmallParams P, const PermMeta pm, const PairConsts pc)
 {
     constexpr int NW = bwd_small_warps(D);       // consumer warps
     constexpr int NT = NW * 32;
@@ -672,22 +673,23 @@ attn_bwd_small_kernel(const SmallParams P, const PermMeta pm, const PairConsts p
                 // a later share of a large window is added to the rows this block wrote before
                 const bool add = sd == 0 ? add_q : add_k;
                 const int64_t o = (int64_t)(sd == 0 ? s_rowq : s_rowk)[xx] * HC + co + ch;
-                __half2 *dst = reinterpret_cast<__half2 *>((sd == 0 ? P.dq : P.dk) + o);
+                // (the same thread writes every share of a row, to this GPU and to the mirrors: the last one stays)
+                __half *dst = sd == 0 ? P.dq : P.dk;
                 if (add) {
-                    const float2 old = __half22float2(*dst);
+                    const float2 old = __half22float2(*reinterpret_cast<const __half2 *>(dst + o));
                     a += old.x;
                     b += old.y;
                 }
-                *dst = __floats2half2_rn(a, b);
+                const Mirrors &mm = sd == 0 ? P.m_dq : P.m_dk;
+                store_h2_mirrored(dst, mm, o, __floats2half2_rn(a, b));
                 if (sd == 1) {
                     float2 dvv = *reinterpret_cast<const float2 *>(s_pg + 512 + xx * 16 + ch);
-                    __half2 *dvp = reinterpret_cast<__half2 *>(P.dv + o);
                     if (add) {
-                        const float2 old = __half22float2(*dvp);
+                        const float2 old = __half22float2(*reinterpret_cast<const __half2 *>(P.dv + o));
                         dvv.x += old.x;
                         dvv.y += old.y;
                     }
-                    *dvp = __floats2half2_rn(dvv.x, dvv.y);
+                    store_h2_mirrored(P.dv, P.m_dv, o, __floats2half2_rn(dvv.x, dvv.y));
                 }
             }
         }
@@ -791,6 +793,7 @@ int attn_tc_backward_small(const AttnArgs &a0, cudaStream_t st)
     p.dout = (const __half *)a.dout; p.o = (const __half *)a.out; p.lse = a.lse;
     p.tq = (const __half *)a.tq; p.tk = (const __half *)a.tk; p.tv = (const __half *)a.tv;
     p.dq = (__half *)a.dq; p.dk = (__half *)a.dk; p.dv = (__half *)a.dv;
+    p.m_dq = a.m_dq; p.m_dk = a.m_dk; p.m_dv = a.m_dv;
     p.dtq = a.dtq; p.dtk = a.dtk; p.dtv = a.dtv;
     p.w_sizes = a.w_sizes; p.w2n = a.w2n; p.n2n = a.n2n; p.n_coords = a.n_coords;
     p.W = a.W; p.H = a.H;

@@ -29,7 +29,7 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                    const CrseMeta meta, const int32_t *__restrict__ w_sizes,
                    const int32_t *__restrict__ w2n, const int32_t *__restrict__ n2n,
                    const float *__restrict__ n_coords, int64_t W, int H, int skip_upto,
-                   __half *__restrict__ out, float *__restrict__ lse)
+                   __half *__restrict__ out, float *__restrict__ lse, const __grid_constant__ Mirrors m_out)
 {
     constexpr bool HD16 = HDM == HDM_SINGLE16;       // the two slots are halves of one head
     constexpr bool PAIR16 = HDM == HDM_PAIR16;       // two heads of 16 channels, two planes
@@ -479,8 +479,8 @@ attn_fwd_tc_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                         }
                         const float inv = 1.f / ls;
                         const int64_t row = s_qrow[qq];
-                        *reinterpret_cast<__half2 *>(out + row * HC + slot_offset<HDM>(hp, h, pl) + (ch & 7)) =
-                            __floats2half2_rn(a * inv, b * inv);
+                        store_h2_mirrored(out, m_out, row * HC + slot_offset<HDM>(hp, h, pl) + (ch & 7),
+                                          __floats2half2_rn(a * inv, b * inv));
                         if (pl == 0) {
                             if (HD16) {
                                 if (ch == 0) lse[row * H + hp] = s_mtile[qq * 2] + __logf(ls);
@@ -517,7 +517,7 @@ static int launch(const AttnArgs &a, int skip_upto, cudaStream_t st)
     kern<<<grid, NTHREADS, L.total, st>>>(
         (const __half *)a.q, (const __half *)a.k, (const __half *)a.v, (const __half *)a.tq,
         (const __half *)a.tk, (const __half *)a.tv, a.meta, a.w_sizes, a.w2n, a.n2n, a.n_coords, a.W,
-        a.H, skip_upto, (__half *)a.out, a.lse);
+        a.H, skip_upto, (__half *)a.out, a.lse, a.m_out);
     return cudaGetLastError() == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
 }
 

@@ -76,6 +76,7 @@ struct FwdSmallParams {
     const float *n_coords;
     int64_t W;
     int H;
+    Mirrors m_out;
 };
 
 // Set when a bounded wait of a kernel in this file ran out (it never should); read and cleared by
@@ -89,7 +90,7 @@ __device__ int g_fwd_small_async_error;
 // "full" mbarrier); the consumers hand a stage back through its "empty" mbarrier.
 template <int D, int NW, int NPU /*projection units per warp*/, int NHU /*hist.T units per warp*/, bool HD16>
 __global__ void __launch_bounds__((NW + 1) * 32, 2)
-attn_fwd_small_kernel(const FwdSmallParams P, const CrseMeta meta, const PairConsts pc)
+attn_fwd_small_kernel(const __grid_constant__ FwdSmallParams P, const CrseMeta meta, const PairConsts pc)
 {
     constexpr int NT = NW * 32;                  // consumer threads
     constexpr int HALF = NW / 2;                 // warps per projection table
@@ -407,7 +408,7 @@ attn_fwd_small_kernel(const FwdSmallParams P, const CrseMeta meta, const PairCon
                 }
                 const float inv = 1.f / ls;
                 const int64_t row = s_row[qq];
-                *reinterpret_cast<__half2 *>(P.out + row * HC + co + ch) = __floats2half2_rn(a * inv, b * inv);
+                store_h2_mirrored(P.out, P.m_out, row * HC + co + ch, __floats2half2_rn(a * inv, b * inv));
                 if (HD16) {
                     if (ch == 0) P.lse[row * H + hp] = s_max[qq * 2] + __logf(ls);
                 } else if ((ch & 7) == 0) {
@@ -494,7 +495,7 @@ int attn_tc_forward_small(const AttnArgs &a0, cudaStream_t st)
     tc::FwdSmallParams p{};
     p.q = (const __half *)a.q; p.k = (const __half *)a.k; p.v = (const __half *)a.v;
     p.tq = (const __half *)a.tq; p.tk = (const __half *)a.tk; p.tv = (const __half *)a.tv;
-    p.out = (__half *)a.out; p.lse = a.lse;
+    p.out = (__half *)a.out; p.lse = a.lse; p.m_out = a.m_out;
     p.w_sizes = a.w_sizes; p.w2n = a.w2n; p.n2n = a.n2n; p.n_coords = a.n_coords;
     p.W = a.W; p.H = a.H;
     const int n_mt = (a.meta.R + 15) / 16;

@@ -1,5 +1,6 @@
 // extern "C" entry points of libswin3d_b200.so: argument validation and dispatch only.
 // The declarations, with the reference interfaces they replace, are in include/swin3d_b200.h.
+#include <string.h>
 #include "attn_kernels.cuh"
 #include <cstdint>
 #include <initializer_list>
@@ -81,10 +82,24 @@ const char *s3d_last_cuda_error_string(void)
     return cudaGetErrorString(static_cast<cudaError_t>(s3d::g_last_cuda_error));
 }
 
-int s3d_attn_fwd(const void *q, const void *k, const void *v, const void *tq, const void *tk,
-                 const void *tv, const int32_t *table_sizes_host, int D, const int32_t *w_sizes,
-                 const int32_t *w2n, const int32_t *n2n, const float *n_coords, int64_t N, int64_t W,
-                 int H, int hd, int dtype, void *out, float *lse, void *stream)
+static int fill_mirrors(s3d::Mirrors &m, int n, void *const *host)
+{
+    m.n = 0;
+    if (n == 0) return S3D_OK;
+    if (n < 0 || n > S3D_MAX_MIRRORS || !host) return S3D_ERR_BAD_ARG;
+    for (int i = 0; i < n; ++i) {
+        if (!host[i] || (reinterpret_cast<uintptr_t>(host[i]) & 15)) return S3D_ERR_BAD_ARG;
+        m.p[i] = host[i];
+    }
+    m.n = n;
+    return S3D_OK;
+}
+
+static int attn_fwd_impl(const void *q, const void *k, const void *v, const void *tq, const void *tk,
+                         const void *tv, const int32_t *table_sizes_host, int D, const int32_t *w_sizes,
+                         const int32_t *w2n, const int32_t *n2n, const float *n_coords, int64_t N, int64_t W,
+                         int H, int hd, int dtype, void *out, float *lse, int n_mirrors,
+                         void *const *out_mirrors_host, void *stream)
 {
     if (N < 0 || W < 0 || (dtype != S3D_F32 && dtype != S3D_F16)) return S3D_ERR_BAD_ARG;
     AttnArgs a{};
@@ -98,15 +113,95 @@ int s3d_attn_fwd(const void *q, const void *k, const void *v, const void *tq, co
     a.w_sizes = w_sizes; a.w2n = w2n; a.n2n = n2n; a.n_coords = n_coords;
     a.N = N; a.W = W; a.H = H; a.hd = hd; a.dtype = dtype;
     a.out = out; a.lse = lse;
+    const int mrc = fill_mirrors(a.m_out, n_mirrors, out_mirrors_host);
+    if (mrc != S3D_OK) return mrc;
     if (!force_scalar() && attn_tc_supported(a)) return attn_tc_forward(a, static_cast<cudaStream_t>(stream));
+    if (a.m_out.n) return S3D_ERR_UNSUPPORTED;
     return attn_scalar_forward(a, static_cast<cudaStream_t>(stream));
 }
 
-int s3d_attn_bwd(const void *q, const void *k, const void *v, const void *tq, const void *tk,
+int s3d_attn_fwd(const void *q, const void *k, const void *v, const void *tq, const void *tk,
                  const void *tv, const int32_t *table_sizes_host, int D, const int32_t *w_sizes,
                  const int32_t *w2n, const int32_t *n2n, const float *n_coords, int64_t N, int64_t W,
-                 int H, int hd, int dtype, const void *out, const float *lse, const void *dout,
-                 void *dq, void *dk, void *dv, float *dtq, float *dtk, float *dtv, void *stream)
+                 int H, int hd, int dtype, void *out, float *lse, void *stream)
+{
+    return attn_fwd_impl(q, k, v, tq, tk, tv, table_sizes_host, D, w_sizes, w2n, n2n, n_coords, N, W, H, hd,
+                         dtype, out, lse, 0, nullptr, stream);
+}
+
+int s3d_attn_fwd_mirrored(const void *q, const void *k, const void *v, const void *tq, const void *tk,
+                          const void *tv, const int32_t *table_sizes_host, int D, const int32_t *w_sizes,
+                          const int32_t *w2n, const int32_t *n2n, const float *n_coords, int64_t N, int64_t W,
+                          int H, int hd, int dtype, void *out, float *lse, int n_mirrors,
+                          void *const *out_mirrors_host, void *stream)
+{
+    return attn_fwd_impl(q, k, v, tq, tk, tv, table_sizes_host, D, w_sizes, w2n, n2n, n_coords, N, W, H, hd,
+                         dtype, out, lse, n_mirrors, out_mirrors_host, stream);
+}
+
+int s3d_peer_alloc(int64_t bytes, void **ptr_out, void *handle64_out)
+{
+    if (bytes <= 0 || !ptr_out || !handle64_out) return S3D_ERR_BAD_ARG;
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+    if (e == cudaSuccess) {
+        cudaIpcMemHandle_t h;
+        e = cudaIpcGetMemHandle(&h, p);
+        if (e == cudaSuccess) {
+            memcpy(handle64_out, &h, sizeof(h));
+            *ptr_out = p;
+            return S3D_OK;
+        }
+        cudaFree(p);
+    }
+    s3d::note_cuda_error(e);
+    return S3D_ERR_LAUNCH;
+}
+
+int s3d_peer_free(void *ptr)
+{
+    if (!ptr) return S3D_ERR_BAD_ARG;
+    const cudaError_t e = cudaFree(ptr);
+    if (e != cudaSuccess) {
+        s3d::note_cuda_error(e);
+        return S3D_ERR_LAUNCH;
+    }
+    return S3D_OK;
+}
+
+int s3d_ipc_open(const void *handle64, void **ptr_out)
+{
+    if (!handle64 || !ptr_out) return S3D_ERR_BAD_ARG;
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) == 64, "CUDA IPC memory handles are 64 bytes");
+    memcpy(&h, handle64, sizeof(h));
+    void *p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        s3d::note_cuda_error(e);
+        return S3D_ERR_LAUNCH;
+    }
+    *ptr_out = p;
+    return S3D_OK;
+}
+
+int s3d_ipc_close(void *ptr)
+{
+    if (!ptr) return S3D_ERR_BAD_ARG;
+    const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+    if (e != cudaSuccess) {
+        s3d::note_cuda_error(e);
+        return S3D_ERR_LAUNCH;
+    }
+    return S3D_OK;
+}
+
+static int attn_bwd_impl(const void *q, const void *k, const void *v, const void *tq, const void *tk,
+                         const void *tv, const int32_t *table_sizes_host, int D, const int32_t *w_sizes,
+                         const int32_t *w2n, const int32_t *n2n, const float *n_coords, int64_t N, int64_t W,
+                         int H, int hd, int dtype, const void *out, const float *lse, const void *dout,
+                         void *dq, void *dk, void *dv, float *dtq, float *dtk, float *dtv, int n_mirrors,
+                         void *const *dq_m, void *const *dk_m, void *const *dv_m, void *stream)
 {
     if (N < 0 || W < 0 || (dtype != S3D_F32 && dtype != S3D_F16)) return S3D_ERR_BAD_ARG;
     AttnArgs a{};
@@ -128,8 +223,35 @@ int s3d_attn_bwd(const void *q, const void *k, const void *v, const void *tq, co
     a.N = N; a.W = W; a.H = H; a.hd = hd; a.dtype = dtype;
     a.out = const_cast<void *>(out); a.lse = const_cast<float *>(lse); a.dout = dout;
     a.dq = dq; a.dk = dk; a.dv = dv; a.dtq = dtq; a.dtk = dtk; a.dtv = dtv;
+    if (fill_mirrors(a.m_dq, n_mirrors, dq_m) != S3D_OK || fill_mirrors(a.m_dk, n_mirrors, dk_m) != S3D_OK ||
+        fill_mirrors(a.m_dv, n_mirrors, dv_m) != S3D_OK)
+        return S3D_ERR_BAD_ARG;
     if (!force_scalar() && attn_tc_bwd_supported(a)) return attn_tc_backward(a, st);
+    if (n_mirrors) return S3D_ERR_UNSUPPORTED;
     return attn_scalar_backward(a, st);
+}
+
+int s3d_attn_bwd(const void *q, const void *k, const void *v, const void *tq, const void *tk,
+                 const void *tv, const int32_t *table_sizes_host, int D, const int32_t *w_sizes,
+                 const int32_t *w2n, const int32_t *n2n, const float *n_coords, int64_t N, int64_t W,
+                 int H, int hd, int dtype, const void *out, const float *lse, const void *dout,
+                 void *dq, void *dk, void *dv, float *dtq, float *dtk, float *dtv, void *stream)
+{
+    return attn_bwd_impl(q, k, v, tq, tk, tv, table_sizes_host, D, w_sizes, w2n, n2n, n_coords, N, W, H, hd,
+                         dtype, out, lse, dout, dq, dk, dv, dtq, dtk, dtv, 0, nullptr, nullptr, nullptr, stream);
+}
+
+int s3d_attn_bwd_mirrored(const void *q, const void *k, const void *v, const void *tq, const void *tk,
+                          const void *tv, const int32_t *table_sizes_host, int D, const int32_t *w_sizes,
+                          const int32_t *w2n, const int32_t *n2n, const float *n_coords, int64_t N, int64_t W,
+                          int H, int hd, int dtype, const void *out, const float *lse, const void *dout,
+                          void *dq, void *dk, void *dv, float *dtq, float *dtk, float *dtv, int n_mirrors,
+                          void *const *dq_mirrors_host, void *const *dk_mirrors_host,
+                          void *const *dv_mirrors_host, void *stream)
+{
+    return attn_bwd_impl(q, k, v, tq, tk, tv, table_sizes_host, D, w_sizes, w2n, n2n, n_coords, N, W, H, hd,
+                         dtype, out, lse, dout, dq, dk, dv, dtq, dtk, dtv, n_mirrors, dq_mirrors_host,
+                         dk_mirrors_host, dv_mirrors_host, stream);
 }
 
 int s3d_debug_crse_indices(const float *n_coords, const int32_t *table_sizes_host, int D, int H,

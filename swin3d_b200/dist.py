@@ -18,8 +18,13 @@ ranks, is what this module does:
   right after the forward of a chunk (it travels while the backward runs), `dq`, `dk`, `dv` after
   the backward, so only the gradients of the last chunk are exposed; the table gradients are summed.
 
-Only NCCL (gloo on CPU) collectives on the caller's buffers are used: no peer-memory loads, no
-symmetric memory.
+* ``PeerResults`` / ``sharded_attention_step_p2p`` are the second way to exchange the rows: the
+  result arrays of all ranks are mapped into every process (CUDA IPC) and the attention kernels store
+  each row they produce to all of them (plain peer stores); nothing is packed, gathered or
+  scattered, and the only collective is the all-reduce of the table gradients.
+
+The collectives are NCCL's (gloo on CPU); peer memory is only ever written by this library's own
+kernels with plain stores -- no peer loads, no bulk-copy engine and no library kernel touch it.
 """
 import weakref
 from typing import List, Optional, Sequence, Tuple
@@ -38,11 +43,12 @@ def window_cost(w_sizes) -> np.ndarray:
     return nt * nt * 600 + w * w
 
 
-def shard_windows(w_sizes, world_size: int, cost=None) -> List[Tuple[int, int]]:
+def shard_windows(w_sizes, world_size: int, cost=None, weights=None) -> List[Tuple[int, int]]:
     """Cuts the window list into `world_size` contiguous ranges of near-equal cost (default: the
     number of attention pairs, sum of w^2; pass ``window_cost(w_sizes)`` for the kernels' cost
-    model).  -> [(first_window, end_window)] per rank; ranges are disjoint, ordered and cover every
-    window; a rank may get an empty range when there are fewer windows than ranks."""
+    model), or of cost shares proportional to `weights`.  -> [(first_window, end_window)] per rank;
+    ranges are disjoint, ordered and cover every window; a rank may get an empty range when there
+    are fewer windows than ranks."""
     w = np.asarray(w_sizes, dtype=np.int64)
     W = len(w)
     if world_size < 1:
@@ -52,9 +58,16 @@ def shard_windows(w_sizes, world_size: int, cost=None) -> List[Tuple[int, int]]:
         raise ValueError("one cost per window is required")
     csum = np.cumsum(c)
     total = int(csum[-1]) if W else 0
+    if weights is None:
+        share = np.arange(world_size + 1) / world_size
+    else:
+        wt = np.asarray(weights, dtype=np.float64)
+        if len(wt) != world_size or (wt <= 0).any():
+            raise ValueError("one positive weight per range is required")
+        share = np.concatenate([[0.0], np.cumsum(wt) / wt.sum()])
     cuts = [0]
     for r in range(1, world_size):
-        target = total * r / world_size
+        target = total * share[r]
         x = int(np.searchsorted(csum, target, side="left")) + 1 if W else 0
         cuts.append(min(max(x, cuts[-1]), W))
     cuts.append(W)
@@ -122,15 +135,21 @@ class ShardPlan:
     """One window set split over `world` ranks, from the point of view of `rank`.
 
     parts[r] = (first_window, end_window) of rank r, cut by ``window_cost``; every rank's range is
-    further cut into `chunks` sub-ranges of equal cost (chunk c of every rank is exchanged together).
+    further cut into `chunks` sub-ranges of equal cost -- or, when `chunks` is a sequence of weights,
+    of costs in those proportions: a small last chunk leaves little exchange exposed after the last
+    kernel (chunk c of every rank is exchanged together).
     For chunk c: ``chunk_windows[c]`` = this rank's (first, end) windows, ``pad[c]`` = rows of the
     largest shard of that chunk over the ranks, ``gather_idx[c]`` = int64 [pad[c]] voxel rows of this
     rank's shard in sorted order (padded with row 0), ``scatter_index(c)`` = where the rows of the
     gathered block of chunk c (laid out [rank][array][pad]) belong.
     """
 
-    def __init__(self, w_sizes, w2n, n2n, world: int, rank: int, chunks: int = 1):
+    def __init__(self, w_sizes, w2n, n2n, world: int, rank: int, chunks=1):
         import torch
+        chunk_weights = None
+        if not isinstance(chunks, int):          # a sequence of relative chunk costs, e.g. (3, 2, 1)
+            chunk_weights = tuple(float(x) for x in chunks)
+            chunks = len(chunk_weights)
         ws = w_sizes.detach().cpu().numpy().astype(np.int64)       # the one host read, at plan time
         w2 = w2n.detach().cpu().numpy().astype(np.int64)
         if not (0 <= rank < world):
@@ -145,7 +164,7 @@ class ShardPlan:
         # sub-ranges of every rank
         sub = []                                   # [rank][chunk] -> (a, b, lo, hi)
         for a, b in self.parts:
-            cuts = shard_windows(ws[a:b], chunks, cost[a:b])
+            cuts = shard_windows(ws[a:b], chunks, cost[a:b], chunk_weights)
             sub.append([(a + x, a + y) + shard_voxel_range(ws, w2, a + x, a + y) for x, y in cuts])
         self.pad = [max(8, -(-max(sub[r][c][3] - sub[r][c][2] for r in range(world)) // 8) * 8)
                     for c in range(chunks)]
@@ -181,10 +200,12 @@ class ShardPlan:
 _PLAN_CACHE = {}
 
 
-def get_plan(w_sizes, w2n, n2n, world: int, rank: int, chunks: int = 1) -> ShardPlan:
+def get_plan(w_sizes, w2n, n2n, world: int, rank: int, chunks=1) -> ShardPlan:
     """The ShardPlan of this window set, built on first use and kept while the window tensors live
     (keyed by the identity and version of ``w_sizes`` / ``n2n``, like the int32 index cache of the
     attention Function)."""
+    if not isinstance(chunks, int):
+        chunks = tuple(float(x) for x in chunks)
     key = (id(w_sizes), w_sizes._version, id(n2n), n2n._version, world, rank, chunks)
     hit = _PLAN_CACHE.get(key)
     if hit is not None and hit[0]() is w_sizes and hit[1]() is n2n:
@@ -256,7 +277,7 @@ def _side_stream(device):
     import torch
     key = (device.type, device.index)
     if key not in _SIDE_STREAMS:
-        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device, priority=-1)    # ahead of the attention kernels
     return _SIDE_STREAMS[key]
 
 
@@ -358,6 +379,134 @@ def sharded_attention_step(q, k, v, tq, tk, tv, sizes, w_sizes, w2n, n2n, n_coor
     return out, dq, dk, dv, tg
 
 
+class _RawCudaArray:
+    """A device allocation presented through the CUDA array interface, for torch.as_tensor."""
+
+    def __init__(self, ptr: int, shape, dtype):
+        import torch
+        typestr = {torch.float16: "<f2", torch.float32: "<f4"}[dtype]
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False),
+                                         "version": 2, "strides": None}
+
+
+class PeerResults:
+    """Result arrays (out, dq, dk, dv) of the split step that every rank of the group can store into:
+    each rank allocates `sets` x 4 arrays of `shape`, exports the allocation as a CUDA IPC handle, and
+    maps the allocations of the other ranks (same node) into its own address space.  The attention
+    kernels then write every row they produce to the same row on all ranks (plain peer stores over
+    NVLink, from inside the kernels), so the exchange needs no packing, collective or scatter pass and
+    overlaps the computation row by row.  Two sets alternate between steps: a rank may still be
+    reading the results of step i while its peers already write those of step i + 1.
+    At most 8 ranks (7 mirrors per kernel launch)."""
+
+    def __init__(self, shape, dtype, device, group=None, sets: int = 2):
+        import ctypes
+        import torch
+        import torch.distributed as dist
+        from . import _lib
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        if self.world - 1 > 7:
+            raise ValueError("PeerResults: at most 8 ranks")
+        self.sets = sets
+        full = (sets, 4) + tuple(int(x) for x in shape)
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        nbytes = int(np.prod(full)) * itemsize
+        ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        with torch.cuda.device(device):
+            # an allocation of its own (not a piece of the caching allocator's segments): exportable
+            _lib.check(_lib.lib.s3d_peer_alloc(nbytes, ctypes.byref(ptr), ctypes.cast(handle, ctypes.c_void_p)),
+                       "s3d_peer_alloc")
+            self._ptr = ptr.value
+            self.own = torch.as_tensor(_RawCudaArray(self._ptr, full, dtype), device=device)
+        if self.own.data_ptr() != self._ptr:
+            raise RuntimeError("PeerResults: the tensor does not alias the exported allocation")
+        self.array_bytes = self.own[0, 0].numel() * itemsize
+        self.base = [None] * self.world            # address of rank r's block in this process
+        self.base[self.rank] = self._ptr
+        self._opened = []
+        if self.world > 1:
+            infos = [None] * self.world
+            dist.all_gather_object(infos, handle.raw, group=group)
+            with torch.cuda.device(device):
+                for r, h in enumerate(infos):
+                    if r == self.rank:
+                        continue
+                    buf = ctypes.create_string_buffer(h, 64)
+                    peer = ctypes.c_void_p()
+                    _lib.check(_lib.lib.s3d_ipc_open(ctypes.cast(buf, ctypes.c_void_p), ctypes.byref(peer)),
+                               "s3d_ipc_open")
+                    self._opened.append(peer.value)
+                    self.base[r] = peer.value
+            dist.barrier(group=group)
+
+    def arrays(self, s: int):
+        """This rank's (out, dq, dk, dv) of set s."""
+        return tuple(self.own[s % self.sets, a] for a in range(4))
+
+    def mirrors(self, s: int, a: int):
+        """Addresses of array a of set s on the other ranks."""
+        off = ((s % self.sets) * 4 + a) * self.array_bytes
+        return [self.base[r] + off for r in range(self.world) if r != self.rank]
+
+    def close(self):
+        """Unmaps the other ranks' arrays and frees this rank's (collective: no rank may still be
+        writing; the tensors handed out by ``arrays`` must not be used afterwards)."""
+        import torch
+        import torch.distributed as dist
+        from . import _lib
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        for p in self._opened:
+            _lib.lib.s3d_ipc_close(p)
+        self._opened = []
+        if self.world > 1:
+            dist.barrier(group=self.group)      # nobody maps this rank's allocation any more
+        if self._ptr is not None:
+            self.own = None
+            _lib.lib.s3d_peer_free(self._ptr)
+            self._ptr = None
+
+
+def sharded_attention_step_p2p(q, k, v, tq, tk, tv, sizes, w_sizes, w2n, n2n, n_coords, dout, peers: PeerResults,
+                               step: int, group=None, plan: Optional[ShardPlan] = None, consumed=None):
+    """Forward + backward of ONE window set split over the ranks, the rows exchanged by the kernels
+    themselves: every rank runs its window range once (no chunks) and its kernels store each result
+    row to all ranks (``PeerResults``).  The all-reduce of the table gradients that follows on the
+    same stream also orders the ranks: when it has completed, every rank's kernels have finished and
+    all rows of set ``step % sets`` are in place.  `consumed`: a CUDA event after which this rank no
+    longer reads the results of the previous step; the stream waits for it before the all-reduce
+    (a rank that passes the all-reduce of step i lets its peers overwrite, in step i + 1, the set that
+    held step i - 1).  Readers on the calling stream need no event.
+    -> out, dq, dk, dv [N,H,hd] (views of this rank's arrays of that set) and (dtq, dtk, dtv)."""
+    import torch
+    import torch.distributed as dist
+    from .sparse_dl.attn.attn_coff import attn_backward_raw, attn_forward_raw
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if world > 1 else 0
+    if plan is None:
+        plan = get_plan(w_sizes, w2n, n2n, world, rank, 1)
+    if plan.chunks != 1:
+        raise ValueError("the peer-store step runs a rank's windows in one piece")
+    N, H, hd = q.shape
+    out, dq, dk, dv = peers.arrays(step)
+    if out.shape != q.shape or out.dtype != q.dtype:
+        raise ValueError("PeerResults were allocated for another shape or dtype")
+    lse = torch.empty((N, H), dtype=torch.float32, device=q.device)
+    ws_c, w2n_c = plan.w_sizes_chunk[0], plan.w2n_chunk[0]
+    attn_forward_raw(q, k, v, tq, tk, tv, sizes, ws_c, w2n_c, n2n, n_coords, out=out, lse=lse,
+                     mirrors=peers.mirrors(step, 0))
+    g = attn_backward_raw(q, k, v, tq, tk, tv, sizes, ws_c, w2n_c, n2n, n_coords, out, lse, dout,
+                          dq=dq, dk=dk, dv=dv,
+                          mirrors=(peers.mirrors(step, 1), peers.mirrors(step, 2), peers.mirrors(step, 3)))
+    if consumed is not None:
+        torch.cuda.current_stream().wait_event(consumed)
+    tg = allreduce_table_grads(tuple(g[3:6]), group)
+    return out, dq, dk, dv, tg
+
+
 def sharded_attention(q, k, v, tq, tk, tv, sizes, w_sizes, w2n, n2n, n_coords, dout=None, group=None):
     """cRSE window attention on ONE window set split over the ranks of `group` (see
     ``sharded_attention_step``).  Forward only when `dout` is None -> out [N,H,hd]; otherwise
@@ -414,8 +563,16 @@ def sharded_knn(K: int, src_xyz, query_xyz, src_offset, query_offset, group=None
     idx_l, d2_l = knn_fn(K, src_xyz, query_xyz[a:b].contiguous(), src_offset, qo_l)
     if world == 1:
         return idx_l, d2_l
+    if all(hi - lo == b - a for lo, hi in ranges):
+        # equal ranges: the blocks are gathered straight into the results, no packing and no copy
+        idx = torch.empty((Nq, K), dtype=idx_l.dtype, device=idx_l.device)
+        d2 = torch.empty((Nq, K), dtype=d2_l.dtype, device=d2_l.device)
+        w1 = dist.all_gather_into_tensor(idx.view(-1), idx_l.contiguous().view(-1), group=group, async_op=True)
+        dist.all_gather_into_tensor(d2.view(-1), d2_l.contiguous().view(-1), group=group)
+        w1.wait()
+        return idx, d2
     pad = max(hi - lo for lo, hi in ranges)
-    # one packed exchange: indices and distance bits side by side as int32 [pad, 2K]
+    # unequal ranges, one packed exchange: indices and distance bits side by side as int32 [pad, 2K]
     piece = torch.zeros((pad, 2 * K), dtype=torch.int32, device=idx_l.device)
     piece[:b - a, :K] = idx_l
     piece[:b - a, K:] = d2_l.view(torch.int32)

@@ -117,10 +117,19 @@ def _aligned16(*tensors):
     return [t if t.data_ptr() % 16 == 0 else t.clone(memory_format=torch.contiguous_format) for t in tensors]
 
 
-def attn_forward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n_coords, out=None, lse=None):
+def _pointer_array(ptrs):
+    import ctypes
+    arr = (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+    return arr, ctypes.cast(arr, ctypes.c_void_p)
+
+
+def attn_forward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n_coords, out=None, lse=None,
+                     mirrors=None):
     """One fused forward launch.  Tensors must already have the compute dtype.  -> (out, lse).
     `out` / `lse` may be given (full-size, contiguous): only the rows of the voxels of the windows
-    in `w_sizes` / `w2n` are written, so a window list can be processed in several calls."""
+    in `w_sizes` / `w2n` are written, so a window list can be processed in several calls.
+    `mirrors`: device addresses (ints) of up to 7 further arrays of out's shape -- other GPUs' result
+    arrays mapped into this process -- that receive the same rows by peer stores from the kernels."""
     import ctypes
     q, k, v, tq, tk, tv = _aligned16(q, k, v, tq, tk, tv)
     N, H, hd = q.shape
@@ -137,20 +146,25 @@ def attn_forward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n
     arr = (ctypes.c_int32 * D)(*sizes)
     with torch.cuda.device(q.device):
         st = torch.cuda.current_stream().cuda_stream
-        rc = _lib.lib.s3d_attn_fwd(
-            q.data_ptr(), k.data_ptr(), v.data_ptr(), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(),
-            ctypes.cast(arr, ctypes.c_void_p), D, w_sizes.data_ptr(), w2n.data_ptr(),
-            n2n.data_ptr(), n_coords.data_ptr(), N, W, H, hd, _DTYPE_CODE[q.dtype],
-            out.data_ptr(), lse.data_ptr(), st)
+        args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(),
+                ctypes.cast(arr, ctypes.c_void_p), D, w_sizes.data_ptr(), w2n.data_ptr(),
+                n2n.data_ptr(), n_coords.data_ptr(), N, W, H, hd, _DTYPE_CODE[q.dtype],
+                out.data_ptr(), lse.data_ptr())
+        if mirrors:
+            keep, mp = _pointer_array(mirrors)
+            rc = _lib.lib.s3d_attn_fwd_mirrored(*args, len(mirrors), mp, st)
+        else:
+            rc = _lib.lib.s3d_attn_fwd(*args, st)
     _lib.check(rc, "s3d_attn_fwd")
     return out, lse
 
 
 def attn_backward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n_coords,
-                      out, lse, dout, dq=None, dk=None, dv=None):
+                      out, lse, dout, dq=None, dk=None, dv=None, mirrors=None):
     """One fused backward launch -> (dq, dk, dv, dtq, dtk, dtv); table grads are fp32 (fresh arrays,
     zeroed by the library).  `dq`, `dk`, `dv` may be given (full-size, contiguous): only the rows of
-    the voxels of the windows in `w_sizes` / `w2n` are written."""
+    the voxels of the windows in `w_sizes` / `w2n` are written.  `mirrors`: three equally long lists of
+    device addresses, further dq, dk and dv arrays that receive the same rows (see the forward)."""
     import ctypes
     q, k, v, tq, tk, tv, out, dout = _aligned16(q, k, v, tq, tk, tv, out, dout)
     N, H, hd = q.shape
@@ -167,12 +181,18 @@ def attn_backward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, 
     arr = (ctypes.c_int32 * D)(*sizes)
     with torch.cuda.device(q.device):
         st = torch.cuda.current_stream().cuda_stream
-        rc = _lib.lib.s3d_attn_bwd(
-            q.data_ptr(), k.data_ptr(), v.data_ptr(), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(),
-            ctypes.cast(arr, ctypes.c_void_p), D, w_sizes.data_ptr(), w2n.data_ptr(),
-            n2n.data_ptr(), n_coords.data_ptr(), N, W, H, hd, _DTYPE_CODE[q.dtype],
-            out.data_ptr(), lse.data_ptr(), dout.data_ptr(), dq.data_ptr(), dk.data_ptr(),
-            dv.data_ptr(), dt[0].data_ptr(), dt[1].data_ptr(), dt[2].data_ptr(), st)
+        args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(),
+                ctypes.cast(arr, ctypes.c_void_p), D, w_sizes.data_ptr(), w2n.data_ptr(),
+                n2n.data_ptr(), n_coords.data_ptr(), N, W, H, hd, _DTYPE_CODE[q.dtype],
+                out.data_ptr(), lse.data_ptr(), dout.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                dv.data_ptr(), dt[0].data_ptr(), dt[1].data_ptr(), dt[2].data_ptr())
+        if mirrors and len(mirrors[0]):
+            if not (len(mirrors) == 3 and len(mirrors[0]) == len(mirrors[1]) == len(mirrors[2])):
+                raise ValueError("mirrors: three equally long address lists (dq, dk, dv)")
+            keep = [_pointer_array(m) for m in mirrors]
+            rc = _lib.lib.s3d_attn_bwd_mirrored(*args, len(mirrors[0]), keep[0][1], keep[1][1], keep[2][1], st)
+        else:
+            rc = _lib.lib.s3d_attn_bwd(*args, st)
     _lib.check(rc, "s3d_attn_bwd")
     return dq, dk, dv, dt[0], dt[1], dt[2]
 

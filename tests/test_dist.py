@@ -261,3 +261,18 @@ def test_compat_aliases_resolve_reference_import_paths():
         for k in [k for k in sys.modules if k == "Swin3D" or k.startswith("Swin3D.")]:
             del sys.modules[k]
         sys.modules.update(saved)
+
+
+def test_weighted_chunks_follow_the_given_proportions():
+    rng = np.random.default_rng(4)
+    w = rng.integers(1, 100, size=6000)
+    w2n = np.cumsum(w) - w
+    n2n = rng.permutation(int(w.sum()))
+    pl = ShardPlan(torch.from_numpy(w), torch.from_numpy(w2n), torch.from_numpy(n2n), 2, 1, (3, 2, 1))
+    assert pl.chunks == 3
+    cost = window_cost(w)
+    shares = np.array([cost[a:b].sum() for a, b in pl.chunk_windows], dtype=np.float64)
+    assert np.allclose(shares / shares.sum(), [0.5, 1 / 3, 1 / 6], atol=0.01)
+    assert pl.chunk_windows[0][0] == pl.parts[1][0] and pl.chunk_windows[-1][1] == pl.parts[1][1]
+    with pytest.raises(ValueError):
+        shard_windows(w, 3, cost, weights=(1, 0, 1))

@@ -95,3 +95,130 @@ def test_pack_and_scatter_of_every_rank_reassemble_the_arrays(world, chunks):
     for r in range(world):
         for a in range(3):
             assert torch.equal(mine[r][a], truth[a])
+
+
+def _dense_block_scene():
+    """A full 12^3 block (windows of up to 125 voxels: several 32-voxel tiles) and a few lonely voxels."""
+    from swin3d_b200 import synthetic as S
+    g = np.stack(np.meshgrid(*[np.arange(12)] * 3, indexing="ij"), -1).reshape(-1, 3)
+    pts = np.concatenate([g, np.array([[40, 40, 40], [60, 3, 9], [90, 90, 90]])])
+    n = len(pts)
+    rng = np.random.default_rng(6)
+    return S.Scene(np.concatenate([np.zeros((n, 1)), pts], 1).astype(np.int32),
+                   rng.random((n, 3), dtype=np.float32) * 0.999, rng.random((n, 3), dtype=np.float32),
+                   np.tile(np.array([[0, 0, 1]], dtype=np.float32), (n, 1)))
+
+
+@pytest.mark.parametrize("H,hd,crse,n_vox,grid", [(4, 8, "XYZ_RGB_NORM", 3000, 30), (2, 8, "XYZ_RGB", 0, 0),
+                                                  (3, 16, "XYZ", 1500, 26)])
+def test_mirrored_stores_write_the_same_rows_to_every_buffer(H, hd, crse, n_vox, grid):
+    """The kernels of the split step store every result row to further buffers (other GPUs' arrays in
+    production; here three more buffers of this GPU): each mirror must hold exactly the rows of the
+    plain call for the voxels of the processed windows and stay untouched elsewhere.  The second shape
+    has windows of several 32-voxel tiles (rows written more than once by the backward)."""
+    from swin3d_b200.sparse_dl.attn.attn_coff import attn_backward_raw, attn_forward_raw
+    from tests.gpu_helpers import dev
+    from tests.helpers import make_problem
+    if n_vox:
+        p = make_problem(seed=35, n_voxels=n_vox, grid=grid, H=H, hd=hd, crse=crse)
+    else:
+        p = make_problem(seed=35, H=H, hd=hd, crse=crse, scene=_dense_block_scene())
+        assert p.w_sizes.max() > 64
+    h = lambda a: dev(a).half()
+    q, k, v, g = h(p.q), h(p.k), h(p.v), h(p.g)
+    tabs = [h(p.tq), h(p.tk), h(p.tv)]
+    ws, w2n, n2n, nc = dev(p.w_sizes), dev(p.w2n), dev(p.n2n), dev(p.n_crse)
+    W = ws.shape[0]
+    a, b = W // 3, W                                       # a window range, as a rank of a split step has
+    ws_r, w2n_r = ws[a:b].contiguous(), w2n[a:b].contiguous()
+    lo = int(w2n[a])
+    rows = n2n[lo:].long()
+    out, lse = attn_forward_raw(q, k, v, *tabs, p.sizes, ws_r, w2n_r, n2n, nc)
+    ref = attn_backward_raw(q, k, v, *tabs, p.sizes, ws_r, w2n_r, n2n, nc, out, lse, g)
+    fill = -7.0
+    mk = lambda: [torch.full_like(q, fill) for _ in range(3)]
+    m_out, m_dq, m_dk, m_dv = mk(), mk(), mk(), mk()
+    out2, lse2 = attn_forward_raw(q, k, v, *tabs, p.sizes, ws_r, w2n_r, n2n, nc,
+                                  mirrors=[t.data_ptr() for t in m_out])
+    got = attn_backward_raw(q, k, v, *tabs, p.sizes, ws_r, w2n_r, n2n, nc, out2, lse2, g,
+                            mirrors=([t.data_ptr() for t in m_dq], [t.data_ptr() for t in m_dk],
+                                     [t.data_ptr() for t in m_dv]))
+    torch.cuda.synchronize()
+    assert torch.equal(out2[rows], out[rows])
+    for x, y in zip(got[:3], ref[:3]):
+        assert torch.equal(x[rows], y[rows])
+    other = torch.ones(q.shape[0], dtype=torch.bool, device="cuda")
+    other[rows] = False
+    for mirrors, want in ((m_out, out), (m_dq, ref[0]), (m_dk, ref[1]), (m_dv, ref[2])):
+        for m in mirrors:
+            assert torch.equal(m[rows], want[rows])
+            assert bool((m[other] == fill).all())
+
+
+def _rank_p2p_step(rank, world, port, q_out):
+    import os
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from swin3d_b200.dist import PeerResults, sharded_attention_step_p2p
+    from swin3d_b200.sparse_dl.attn.attn_coff import attn_backward_raw, attn_forward_raw
+    from tests.gpu_helpers import dev
+    from tests.helpers import make_problem
+    p = make_problem(seed=36, n_voxels=4000, grid=40, H=4, hd=8, crse="XYZ_RGB_NORM")
+    h = lambda a: dev(a).half()
+    q, k, v, g = h(p.q), h(p.k), h(p.v), h(p.g)
+    tabs = [h(p.tq), h(p.tk), h(p.tv)]
+    ws, w2n, n2n, nc = dev(p.w_sizes), dev(p.w2n), dev(p.n2n), dev(p.n_crse)
+    out, lse = attn_forward_raw(q, k, v, *tabs, p.sizes, ws, w2n, n2n, nc)
+    ref = attn_backward_raw(q, k, v, *tabs, p.sizes, ws, w2n, n2n, nc, out, lse, g)
+    peers = PeerResults(q.shape, q.dtype, q.device)
+    ok = True
+    for step in range(4):                                   # both sets, each used twice
+        gs = g * (1.0 + step)
+        res = sharded_attention_step_p2p(q, k, v, *tabs, p.sizes, ws, w2n, n2n, nc, gs, peers, step)
+        torch.cuda.synchronize()
+        want = attn_backward_raw(q, k, v, *tabs, p.sizes, ws, w2n, n2n, nc, out, lse, gs)
+        ok = ok and torch.equal(res[0], out)
+        ok = ok and all(torch.equal(x, y) for x, y in zip(res[1:4], want[:3]))
+        ok = ok and all(torch.allclose(x, y, rtol=1e-4, atol=1e-5 * float(y.abs().max())) for x, y in zip(res[4], want[3:6]))
+    peers.close()
+    q_out.put((rank, bool(ok)))
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_peer_store_step_on_two_gpus_equals_the_plain_calls():
+    """Two ranks, two GPUs: the kernels of each rank store its rows into both ranks' arrays; after the
+    all-reduce of the table gradients every rank holds the complete out, dq, dk, dv, bit for bit the
+    single-GPU result (windows are independent, the kernels deterministic per window)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import socket
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    procs = [ctx.Process(target=_rank_p2p_step, args=(r, 2, port, q_out)) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    import queue
+    import time
+    got, deadline = {}, time.time() + 240
+    while len(got) < 2 and time.time() < deadline:
+        try:
+            r, ok = q_out.get(timeout=2)
+            got[r] = ok
+        except queue.Empty:
+            if any(pr.exitcode not in (None, 0) for pr in procs):      # a rank died: do not wait for the others
+                break
+    for pr in procs:
+        pr.join(20)
+        if pr.is_alive():
+            pr.kill()
+    assert [pr.exitcode for pr in procs] == [0, 0]
+    assert got == {0: True, 1: True}
