@@ -4,7 +4,8 @@
  *
  * Conventions
  *  - Every pointer is a DEVICE pointer unless its name ends in _host.  The caller owns every
- *    buffer; the library allocates nothing, frees nothing and keeps no state between calls.
+ *    buffer; the library allocates nothing, frees nothing and keeps no state between calls
+ *    (the one exception, for the multi-GPU split, is the explicit pair s3d_peer_alloc / s3d_peer_free).
  *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).  Calls only
  *    enqueue work; they never synchronise.
  *  - Return value: S3D_OK or an S3D_ERR_* code; s3d_status_string() names it.  Nothing here
