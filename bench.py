@@ -431,6 +431,44 @@ def run_attention(args):
         if not torch.equal(got, want.cpu()):
             raise RuntimeError(f"end-to-end pipeline: {name} differs from the device-resident result")
 
+    # ---- fp16_mode=1 (PrecisionMode.HALF_FORWARD), the mode the reference's README recommends: fp32 arrays in,
+    # fp16 forward, backward in fp32 as the reference does (generic kernels) -- and with the library's switch
+    # that runs that backward on the tensor-core kernels at the accuracy of the fp16 modes
+    half_forward = None
+    if world == 1:
+        wi_h, ncr_h = win[0]
+        idx_h = wi_h.reference_indices(ncr_h)
+        x32 = [t.float().requires_grad_() for t in (q, k, v)]
+        g32 = g.float()
+
+        def hf_step():
+            for t in x32 + tab_params:
+                t.grad = None
+            with torch.autocast("cuda", dtype=torch.float16):     # as the reference's examples run this mode
+                o = C.SelfAttnAIOFunction.apply(*x32, *tab_params, offsets_cpu, idx_h, C.PosEmb.SEPARATE,
+                                                C.TableDims.D0, C.IndexMode.INDIRECT, C.PrecisionMode.HALF_FORWARD)
+            o.backward(g32.to(o.dtype))
+
+        half_forward = {}
+        for name, fast in (("ms_per_step", False), ("ms_per_step_fast_backward_switch", True)):
+            saved = C.HALF_FORWARD_FAST_BACKWARD
+            C.HALF_FORWARD_FAST_BACKWARD = fast
+            try:
+                hf_step()
+                torch.cuda.synchronize()
+                t0.record()
+                for _ in range(3):
+                    hf_step()
+                t1.record()
+                torch.cuda.synchronize()
+                half_forward[name] = t0.elapsed_time(t1) / 3
+            finally:
+                C.HALF_FORWARD_FAST_BACKWARD = saved
+        half_forward["note"] = ("through SelfAttnAIOFunction under autocast with fp32 arrays (casts included), one window set; default: "
+                                "fp32 backward on the generic kernels as in the reference; switch "
+                                "attn_coff.HALF_FORWARD_FAST_BACKWARD: fp16 tensor-core backward")
+        del x32, g32
+
     stats = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e_ms, float(N)], dtype=torch.float64, device="cuda")
     if world > 1:
         mx = stats.clone()
@@ -479,6 +517,7 @@ def run_attention(args):
         "e2e": {"value": n_total / (e2e_ms * 1e-3), "unit": "voxels/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 4 * N * Cc * 2,
                 "d2h_bytes_per_step": 4 * N * Cc * 2 + 3 * sum(sizes) * 4},
+        "half_forward_mode": half_forward,
         "gpu_launches": 3 * args.steps,   # forward single-tile + tiled, backward (tile pairs)
         "clocks": clocks,
     }

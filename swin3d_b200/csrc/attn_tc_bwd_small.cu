@@ -105,15 +105,20 @@ struct SmallParams {
     const float *n_coords;
     int64_t W;
     int H;
-    Mirrors m_dq, m_dk, m_dv;
+};
+
+// The other GPUs' dq, dk, dv arrays of a split step (a kernel parameter of its own, after the others).
+struct BwdMirrors {
+    Mirrors dq, dk, dv;
 };
 
 // Set when a bounded wait of a kernel in this file ran out (it never should).
 __device__ int g_bwd_small_async_error;
 
-template <int D, int NPU /*projection + dT units per warp*/, int NHU /*hist.T units per warp*/, bool HD16>
+template <int D, int NPU /*projection + dT units per warp*/, int NHU /*hist.T units per warp*/, bool HD16,
+          bool MIRROR /*also store the rows to other GPUs' arrays*/>
 __global__ void __launch_bounds__((bwd_small_warps(D) + 1) * 32, 1)
-attn_bwd_small_kernel(const __grid_constant__ SmallParams P, const PermMeta pm, const PairConsts pc)
+attn_bwd_small_kernel(const SmallParams P, const PermMeta pm, const PairConsts pc, const __grid_constant__ BwdMirrors MM)
 {
     constexpr int NW = bwd_small_warps(D);       // consumer warps
     constexpr int NT = NW * 32;
@@ -680,8 +685,9 @@ attn_bwd_small_kernel(const __grid_constant__ SmallParams P, const PermMeta pm, 
                     a += old.x;
                     b += old.y;
                 }
-                const Mirrors &mm = sd == 0 ? P.m_dq : P.m_dk;
-                store_h2_mirrored(dst, mm, o, __floats2half2_rn(a, b));
+                const __half2 r2 = __floats2half2_rn(a, b);
+                *reinterpret_cast<__half2 *>(dst + o) = r2;
+                __half2 dv2 = r2;
                 if (sd == 1) {
                     float2 dvv = *reinterpret_cast<const float2 *>(s_pg + 512 + xx * 16 + ch);
                     if (add) {
@@ -689,7 +695,15 @@ attn_bwd_small_kernel(const __grid_constant__ SmallParams P, const PermMeta pm, 
                         dvv.x += old.x;
                         dvv.y += old.y;
                     }
-                    store_h2_mirrored(P.dv, P.m_dv, o, __floats2half2_rn(dvv.x, dvv.y));
+                    dv2 = __floats2half2_rn(dvv.x, dvv.y);
+                    *reinterpret_cast<__half2 *>(P.dv + o) = dv2;
+                }
+                if (MIRROR) {                        // the other GPUs' arrays (plain peer stores)
+                    for (int m = 0; m < MM.dq.n; ++m) {
+                        __half *mp = static_cast<__half *>(sd == 0 ? MM.dq.p[m] : MM.dk.p[m]);
+                        *reinterpret_cast<__half2 *>(mp + o) = r2;
+                        if (sd == 1) *reinterpret_cast<__half2 *>(static_cast<__half *>(MM.dv.p[m]) + o) = dv2;
+                    }
                 }
             }
         }
@@ -722,12 +736,12 @@ attn_bwd_small_kernel(const __grid_constant__ SmallParams P, const PermMeta pm, 
     }
 }
 
-template <int D, int NPU, int NHU, bool HD16>
-static int launch_small(const SmallParams &p, const CrseMeta &meta, const PermMeta &pm, cudaStream_t st)
+template <int D, int NPU, int NHU, bool HD16, bool MIRROR>
+static int launch_small_m(const SmallParams &p, const BwdMirrors &mm, const CrseMeta &meta, const PermMeta &pm, cudaStream_t st)
 {
     constexpr int NW = bwd_small_warps(D);
     const SmallSmem L = make_small_layout(pm.R, NW, pm.D * pm.lut_stride);
-    auto kern = attn_bwd_small_kernel<D, NPU, NHU, HD16>;
+    auto kern = attn_bwd_small_kernel<D, NPU, NHU, HD16, MIRROR>;
     static int sms_of[64] = {0};     // 0: this instantiation has not been set up on the device yet
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return S3D_ERR_LAUNCH;
@@ -744,10 +758,17 @@ static int launch_small(const SmallParams &p, const CrseMeta &meta, const PermMe
     if (gx > p.W) gx = (int)p.W;
     if (gx < 1) gx = 1;
     dim3 grid((unsigned)gx, (unsigned)hp);
-    kern<<<grid, (NW + 1) * 32, L.total, st>>>(p, pm, make_pair_consts(meta));
+    kern<<<grid, (NW + 1) * 32, L.total, st>>>(p, pm, make_pair_consts(meta), mm);
     const cudaError_t le = cudaGetLastError();
     note_cuda_error(le);
     return le == cudaSuccess ? S3D_OK : S3D_ERR_LAUNCH;
+}
+
+template <int D, int NPU, int NHU, bool HD16>
+static int launch_small(const SmallParams &p, const BwdMirrors &mm, const CrseMeta &meta, const PermMeta &pm, cudaStream_t st)
+{
+    return mm.dq.n ? launch_small_m<D, NPU, NHU, HD16, true>(p, mm, meta, pm, st)
+                   : launch_small_m<D, NPU, NHU, HD16, false>(p, mm, meta, pm, st);
 }
 
 }  // namespace tc
@@ -793,7 +814,7 @@ int attn_tc_backward_small(const AttnArgs &a0, cudaStream_t st)
     p.dout = (const __half *)a.dout; p.o = (const __half *)a.out; p.lse = a.lse;
     p.tq = (const __half *)a.tq; p.tk = (const __half *)a.tk; p.tv = (const __half *)a.tv;
     p.dq = (__half *)a.dq; p.dk = (__half *)a.dk; p.dv = (__half *)a.dv;
-    p.m_dq = a.m_dq; p.m_dk = a.m_dk; p.m_dv = a.m_dv;
+    tc::BwdMirrors mm{a.m_dq, a.m_dk, a.m_dv};
     p.dtq = a.dtq; p.dtk = a.dtk; p.dtv = a.dtv;
     p.w_sizes = a.w_sizes; p.w2n = a.w2n; p.n2n = a.n2n; p.n_coords = a.n_coords;
     p.W = a.W; p.H = a.H;
@@ -802,8 +823,8 @@ int attn_tc_backward_small(const AttnArgs &a0, cudaStream_t st)
     const int npu = (n_mt + nw / 3 - 1) / (nw / 3);   // <= 5
     const int nhu = (n_mt + nw / 2 - 1) / (nw / 2);   // <= 4
 #define S3D_SMALL_H(DD, HH)                                                                  \
-    if (npu <= 4 && nhu <= 3) return tc::launch_small<DD, 4, 3, HH>(p, a.meta, pm, st);      \
-    return tc::launch_small<DD, 5, 4, HH>(p, a.meta, pm, st);
+    if (npu <= 4 && nhu <= 3) return tc::launch_small<DD, 4, 3, HH>(p, mm, a.meta, pm, st);      \
+    return tc::launch_small<DD, 5, 4, HH>(p, mm, a.meta, pm, st);
 #define S3D_SMALL(DD) if (a.hd == 16) { S3D_SMALL_H(DD, true) } else { S3D_SMALL_H(DD, false) }
     switch (a.meta.D) {
         case 3: S3D_SMALL(3)
