@@ -312,9 +312,19 @@ def run_attention(args):
     # cross rooms): the first timed step works in room chunks of growing size (1, 1, 2, 4) so that
     # compute starts after one room has arrived, the last one in shrinking chunks (4, 2, 1, 1) so
     # that little is left to copy out when compute ends, the steps between take the whole batch.
+    # the pinned host buffers are allocated (and so placed) while this process runs on the cores next to
+    # its GPU; afterwards it may use all its cores again (the CPU baseline does)
+    cores_before = os.sched_getaffinity(0)
+    bind_to_gpu_numa_node(local)
     x_pin = [t.cpu().pin_memory() for t in (q, k, v, g)]
     out_pin = [torch.empty((N, H, hd), dtype=torch.float16).pin_memory() for _ in range(4)]
     tg_pin = torch.empty((3, sum(sizes)), dtype=torch.float32).pin_memory()
+    for buf in out_pin + [tg_pin]:
+        buf.zero_()                 # touch the pages here
+    try:
+        os.sched_setaffinity(0, cores_before)
+    except OSError:
+        pass
     offsets_cpu = torch.IntTensor(sizes)
     tab_params = [t.float().requires_grad_() for t in tabs]
     room_of = sc.coords[:, 0]
