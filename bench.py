@@ -592,7 +592,15 @@ def run_attention_split(args):
     peers = None
     if p2p:
         from swin3d_b200.dist import PeerResults, sharded_attention_step_p2p
-        peers = PeerResults((N, H, hd), torch.float16, torch.device("cuda", local))
+        try:                        # raises on every rank alike when any rank cannot map the others' arrays
+            peers = PeerResults((N, H, hd), torch.float16, torch.device("cuda", local))
+        except RuntimeError as e:
+            if rank == 0:
+                print(f"bench: peer stores unavailable, using the NCCL exchange ({e})", file=sys.stderr)
+            p2p = False
+            chunk_spec = int(args.chunks) if args.chunks.isdigit() else tuple(float(x) for x in args.chunks.split(","))
+            chunks = chunk_spec if isinstance(chunk_spec, int) else len(chunk_spec)
+            plans = [get_plan(wi.w_sizes, wi.w2n, wi.n2n, world, rank, chunk_spec) for wi, _ in win]
     calls = [0]                     # steps so far: the peers' result sets alternate, on every rank alike
 
     def step(i, bufs=None, consumed=None):
@@ -1131,6 +1139,8 @@ def run_reference_gpu(args):
 
 
 def main():
+    # stdout carries the one JSON line: NCCL's banner and warnings (NCCL_DEBUG=VERSION/WARN print there) go to stderr
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)

@@ -413,33 +413,60 @@ class PeerResults:
         full = (sets, 4) + tuple(int(x) for x in shape)
         itemsize = torch.empty((), dtype=dtype).element_size()
         nbytes = int(np.prod(full)) * itemsize
-        ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
-        with torch.cuda.device(device):
-            # an allocation of its own (not a piece of the caching allocator's segments): exportable
-            _lib.check(_lib.lib.s3d_peer_alloc(nbytes, ctypes.byref(ptr), ctypes.cast(handle, ctypes.c_void_p)),
-                       "s3d_peer_alloc")
-            self._ptr = ptr.value
-            self.own = torch.as_tensor(_RawCudaArray(self._ptr, full, dtype), device=device)
-        if self.own.data_ptr() != self._ptr:
-            raise RuntimeError("PeerResults: the tensor does not alias the exported allocation")
-        self.array_bytes = self.own[0, 0].numel() * itemsize
+        self._ptr, self.own, self._opened = None, None, []
         self.base = [None] * self.world            # address of rank r's block in this process
-        self.base[self.rank] = self._ptr
-        self._opened = []
+        ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        error = None
+        # Every rank goes through the same collectives whatever fails locally, so that a rank without
+        # CUDA IPC (or out of memory) makes ALL ranks raise instead of leaving the others waiting.
+        try:
+            with torch.cuda.device(device):
+                # an allocation of its own (not a piece of the caching allocator's segments): exportable
+                _lib.check(_lib.lib.s3d_peer_alloc(nbytes, ctypes.byref(ptr), ctypes.cast(handle, ctypes.c_void_p)),
+                           "s3d_peer_alloc")
+                self._ptr = ptr.value
+                self.own = torch.as_tensor(_RawCudaArray(self._ptr, full, dtype), device=device)
+            if self.own.data_ptr() != self._ptr:
+                raise RuntimeError("PeerResults: the tensor does not alias the exported allocation")
+            self.array_bytes = self.own[0, 0].numel() * itemsize
+            self.base[self.rank] = self._ptr
+        except Exception as e:          # noqa: BLE001 - reported to every rank below
+            error = f"rank {self.rank}: {e}"
         if self.world > 1:
             infos = [None] * self.world
-            dist.all_gather_object(infos, handle.raw, group=group)
-            with torch.cuda.device(device):
-                for r, h in enumerate(infos):
-                    if r == self.rank:
-                        continue
-                    buf = ctypes.create_string_buffer(h, 64)
-                    peer = ctypes.c_void_p()
-                    _lib.check(_lib.lib.s3d_ipc_open(ctypes.cast(buf, ctypes.c_void_p), ctypes.byref(peer)),
-                               "s3d_ipc_open")
-                    self._opened.append(peer.value)
-                    self.base[r] = peer.value
-            dist.barrier(group=group)
+            dist.all_gather_object(infos, None if error else handle.raw, group=group)
+            if error is None and all(h is not None for h in infos):
+                try:
+                    with torch.cuda.device(device):
+                        for r, h in enumerate(infos):
+                            if r == self.rank:
+                                continue
+                            buf = ctypes.create_string_buffer(h, 64)
+                            peer = ctypes.c_void_p()
+                            _lib.check(_lib.lib.s3d_ipc_open(ctypes.cast(buf, ctypes.c_void_p), ctypes.byref(peer)),
+                                       "s3d_ipc_open")
+                            self._opened.append(peer.value)
+                            self.base[r] = peer.value
+                except Exception as e:      # noqa: BLE001
+                    error = f"rank {self.rank}: {e}"
+            elif error is None:
+                error = "another rank could not allocate or export its arrays"
+            errors = [None] * self.world
+            dist.all_gather_object(errors, error, group=group)
+            error = next((e for e in errors if e), None)
+        if error:
+            self._release()
+            raise RuntimeError(f"PeerResults unavailable ({error})")
+
+    def _release(self):
+        from . import _lib
+        for p in self._opened:
+            _lib.lib.s3d_ipc_close(p)
+        self._opened = []
+        if self._ptr is not None:
+            self.own = None
+            _lib.lib.s3d_peer_free(self._ptr)
+            self._ptr = None
 
     def arrays(self, s: int):
         """This rank's (out, dq, dk, dv) of set s."""
@@ -464,10 +491,7 @@ class PeerResults:
         self._opened = []
         if self.world > 1:
             dist.barrier(group=self.group)      # nobody maps this rank's allocation any more
-        if self._ptr is not None:
-            self.own = None
-            _lib.lib.s3d_peer_free(self._ptr)
-            self._ptr = None
+        self._release()
 
 
 def sharded_attention_step_p2p(q, k, v, tq, tk, tv, sizes, w_sizes, w2n, n2n, n_coords, dout, peers: PeerResults,
