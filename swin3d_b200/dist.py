@@ -32,15 +32,18 @@ from typing import List, Optional, Sequence, Tuple
 import numpy as np
 
 TILE = 32   # voxels per tile of the attention kernels
+ITEM_COST = 10000   # cost of a 32 x 32 tile pair in units of one attention pair (see ``window_cost``)
 
 
 def window_cost(w_sizes) -> np.ndarray:
-    """Cost model of a window for the attention kernels: a fixed part per 32 x 32 tile pair (the
-    table projections and histogram products do not depend on how full a tile is) plus a part per
-    attention pair."""
+    """Cost model of a window for the attention kernels: a part per 32 x 32 tile pair (the table
+    projections, histogram products and barriers of a tile pair do not depend on how full it is) plus
+    a part per attention pair.  Measured on the benchmark batch, ranges cut by the tile-pair count
+    alone are the best balanced (the kernels' own split over their blocks uses it too); the pair
+    count only breaks ties."""
     w = np.asarray(w_sizes, dtype=np.int64)
     nt = (w + TILE - 1) // TILE
-    return nt * nt * 600 + w * w
+    return nt * nt * ITEM_COST + w * w
 
 
 def shard_windows(w_sizes, world_size: int, cost=None, weights=None) -> List[Tuple[int, int]]:
