@@ -75,6 +75,25 @@ def bind_to_gpu_numa_node(local_rank: int) -> None:
         pass
 
 
+def init_nccl(local_rank: int, pg_options=None) -> None:
+    """Process group over NCCL with the communicator created right away, and with stdout pointed at
+    stderr while that happens: NCCL prints its version banner (NCCL_DEBUG=VERSION or WARN) with a
+    plain printf, and stdout must carry nothing but the one JSON line."""
+    import torch
+    import torch.distributed as dist
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), pg_options=pg_options)
+        dist.barrier()
+        torch.cuda.synchronize()
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+
+
 def make_batch(rank: int, rooms: int, voxels_per_room: int):
     from swin3d_b200 import synthetic as S
     scenes = [S.make_room(1000 * rank + s, target_voxels=voxels_per_room, batch_index=s)
@@ -203,7 +222,7 @@ def run_attention(args):
     torch.cuda.set_device(local)
     if world > 1:
         bind_to_gpu_numa_node(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        init_nccl(local)
     c = CFG
     H, hd, ws, quant, crse = c["H"], c["hd"], c["ws"], c["quant"], c["crse"]
     Cc = H * hd
@@ -560,7 +579,7 @@ def run_attention_split(args):
         opts = None
         if not args.nccl_default_priority:
             opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local), pg_options=opts)
+        init_nccl(local, opts)
     c = CFG
     H, hd, ws, quant, crse = c["H"], c["hd"], c["ws"], c["quant"], c["crse"]
     Cc = H * hd
@@ -899,7 +918,7 @@ def run_knn(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        init_nccl(local)
     n_sc = args.rooms or 8                     # --rooms: fewer scenes for a profiler capture
     scenes = [S.make_knn_scene(s, 200_000, 50_000) for s in range(n_sc)]      # the same scenes on every rank
     src = torch.from_numpy(np.concatenate([s for s, _ in scenes])).cuda()
@@ -1139,8 +1158,6 @@ def run_reference_gpu(args):
 
 
 def main():
-    # stdout carries the one JSON line: NCCL's banner and warnings (NCCL_DEBUG=VERSION/WARN print there) go to stderr
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
