@@ -197,7 +197,7 @@ def run_reference_arm(args):
     line = {
         "impl": "reference", "metric": "attn fwd+bwd voxels/sec @Swin3D-L stage1",
         "value": base["value"], "unit": "voxels/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "voxels/s", "h2d_bytes_per_step": 0,
