@@ -1,4 +1,6 @@
-"""Makes the reference's import paths resolve to this package.
+"""Makes the reference's import paths resolve to this package (``install_as_swin3d``: the Python
+level, this package's Functions replace the reference's) or to this package's re-creation of its two
+compiled modules (``install_pybind_modules``: the pybind level, the reference's Python stays).
 
 ``Swin3D/modules/swin3d_layers.py:16-24`` imports ``Swin3D.sparse_dl.attn.attn_coff`` and
 ``Swin3D.sparse_dl.knn``.  ``install_as_swin3d()`` registers this package's modules under those
@@ -8,6 +10,19 @@ kernels of libswin3d_b200.so without a change to their source.
 import importlib
 import sys
 import types
+
+
+def install_pybind_modules(force: bool = False) -> None:
+    """The other level of the boundary: keeps the reference's own ``Swin3D/sparse_dl/attn/attn_coff.py``
+    and ``Swin3D/sparse_dl/knn/knn.py`` byte for byte and only supplies the two compiled modules they
+    import, ``Swin3D.sparse_dl.attn_cuda`` (Swin3D/src/attn/attn_api.cpp:20-24) and
+    ``Swin3D.sparse_dl.knn_cuda`` (Swin3D/src/knn/knn_api.cpp:4-6), implemented over libswin3d_b200.so.
+    Call before ``import Swin3D.sparse_dl`` (the reference package must be importable)."""
+    for alias, target in (("Swin3D.sparse_dl.attn_cuda", "swin3d_b200.sparse_dl.attn_cuda"),
+                          ("Swin3D.sparse_dl.knn_cuda", "swin3d_b200.sparse_dl.knn_cuda")):
+        if alias in sys.modules and not force:
+            continue
+        sys.modules[alias] = importlib.import_module(target)
 
 
 def install_as_swin3d(force: bool = False) -> None:

@@ -222,3 +222,34 @@ def test_peer_store_step_on_two_gpus_equals_the_plain_calls():
             pr.kill()
     assert [pr.exitcode for pr in procs] == [0, 0]
     assert got == {0: True, 1: True}
+
+
+def test_peer_store_step_on_one_rank_equals_the_plain_calls():
+    """World size 1 (no process group): the peer-store step allocates its arrays through the library,
+    has no mirrors, and must give the plain calls' results; two steps use both array sets."""
+    from swin3d_b200.dist import PeerResults, sharded_attention_step_p2p
+    from swin3d_b200.sparse_dl.attn.attn_coff import attn_backward_raw, attn_forward_raw
+    from tests.gpu_helpers import dev
+    from tests.helpers import make_problem
+    p = make_problem(seed=37, n_voxels=2000, grid=30, H=4, hd=8, crse="XYZ_RGB_NORM")
+    h = lambda a: dev(a).half()
+    q, k, v, g = h(p.q), h(p.k), h(p.v), h(p.g)
+    tabs = [h(p.tq), h(p.tk), h(p.tv)]
+    ws, w2n, n2n, nc = dev(p.w_sizes), dev(p.w2n), dev(p.n2n), dev(p.n_crse)
+    out, lse = attn_forward_raw(q, k, v, *tabs, p.sizes, ws, w2n, n2n, nc)
+    ref = attn_backward_raw(q, k, v, *tabs, p.sizes, ws, w2n, n2n, nc, out, lse, g)
+    peers = PeerResults(q.shape, q.dtype, q.device)
+    try:
+        assert peers.mirrors(0, 0) == [] and peers.own.shape == (2, 4) + tuple(q.shape)
+        for step in range(2):
+            res = sharded_attention_step_p2p(q, k, v, *tabs, p.sizes, ws, w2n, n2n, nc, g, peers, step)
+            torch.cuda.synchronize()
+            assert res[0].data_ptr() == peers.arrays(step)[0].data_ptr()
+            assert torch.equal(res[0], out)
+            for x, y in zip(res[1:4], ref[:3]):
+                assert torch.equal(x, y)
+            for x, y in zip(res[4], ref[3:6]):
+                assert torch.allclose(x, y, rtol=1e-5, atol=1e-6 * float(y.abs().max()))
+    finally:
+        peers.close()
+    assert peers.own is None
