@@ -565,7 +565,7 @@ def run_attention_split(args):
     import torch
     import torch.distributed as dist
     from swin3d_b200 import synthetic as S
-    from swin3d_b200.dist import get_plan, sharded_attention_step
+    from swin3d_b200.dist import forward_of_chunk, get_plan, sharded_attention_step
     from swin3d_b200.window import build_windows
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -675,7 +675,7 @@ def run_attention_split(args):
     e0.record()
     for _ in range(3):
         for cc in range(pl.chunks):
-            C.attn_forward_raw(q, k, v, *tabs, sizes, pl.w_sizes_chunk[cc], pl.w2n_chunk[cc], wi.n2n, ncr, out=o_b, lse=lse_b)
+            forward_of_chunk(pl, cc, q, k, v, *tabs, sizes, wi.n2n, ncr, o_b, lse_b)
             C.attn_backward_raw(q, k, v, *tabs, sizes, pl.w_sizes_chunk[cc], pl.w2n_chunk[cc], wi.n2n, ncr, o_b, lse_b, g,
                                 dq=g_b[0], dk=g_b[1], dv=g_b[2])
     e1.record()

@@ -97,8 +97,13 @@ int s3d_attn_bwd(const void *q, const void *k, const void *v,
  * afterwards (any collective issued on the same stream, e.g. the all-reduce of the table
  * gradients: when it has completed on a rank, every rank's kernels have finished and their rows
  * are in place).  S3D_ERR_UNSUPPORTED for shapes served by kernels without mirrored stores (the
- * generic path and head_dim 16 with an even head count and large tables).  The reference has no
- * multi-GPU attention; this replaces nothing in it.                                             */
+ * generic path and head_dim 16 with an even head count and large tables).
+ * window_class (forward): 0 = windows of any size; 1 = the caller guarantees that every window of
+ * this call has at most 32 voxels, 2 = that every window has more.  The forward runs one kernel for
+ * each class and each walks the whole window list for its own windows; a caller that has the sizes
+ * on the host (the multi-GPU split plans its ranges from them) passes the two classes in two calls
+ * and saves both walks.  A window that breaks the guarantee is NOT processed.
+ * The reference has no multi-GPU attention; this replaces nothing in it.                        */
 #define S3D_MAX_MIRRORS 7
 int s3d_attn_fwd_mirrored(const void *q, const void *k, const void *v,
                           const void *tq, const void *tk, const void *tv,
@@ -106,7 +111,7 @@ int s3d_attn_fwd_mirrored(const void *q, const void *k, const void *v,
                           const int32_t *w_sizes, const int32_t *w2n, const int32_t *n2n,
                           const float *n_coords, int64_t N, int64_t W, int H, int hd, int dtype,
                           void *out, float *lse, int n_mirrors, void *const *out_mirrors_host,
-                          void *stream);
+                          int window_class, void *stream);
 int s3d_attn_bwd_mirrored(const void *q, const void *k, const void *v,
                           const void *tq, const void *tk, const void *tv,
                           const int32_t *table_sizes_host, int D,

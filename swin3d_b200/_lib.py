@@ -29,7 +29,7 @@ SIGNATURES = {
     "s3d_attn_bwd": (_i32, [_c_void_p] * 6 + [_c_void_p, _i32] + [_c_void_p] * 4 +
                      [_i64, _i64, _i32, _i32, _i32] + [_c_void_p] * 3 + [_c_void_p] * 6 + [_c_void_p]),
     "s3d_attn_fwd_mirrored": (_i32, [_c_void_p] * 6 + [_c_void_p, _i32] + [_c_void_p] * 4 +
-                              [_i64, _i64, _i32, _i32, _i32, _c_void_p, _c_void_p, _i32, _c_void_p, _c_void_p]),
+                              [_i64, _i64, _i32, _i32, _i32, _c_void_p, _c_void_p, _i32, _c_void_p, _i32, _c_void_p]),
     "s3d_attn_bwd_mirrored": (_i32, [_c_void_p] * 6 + [_c_void_p, _i32] + [_c_void_p] * 4 +
                               [_i64, _i64, _i32, _i32, _i32] + [_c_void_p] * 3 + [_c_void_p] * 6 +
                               [_i32, _c_void_p, _c_void_p, _c_void_p, _c_void_p]),

@@ -27,6 +27,7 @@ struct AttnArgs {
     void *dq, *dk, *dv;
     float *dtq, *dtk, *dtv;
     Mirrors m_out, m_dq, m_dk, m_dv;   // forward: m_out; backward: m_dq, m_dk, m_dv
+    int window_class;                  // forward: 0 mixed window sizes, 1 all <= 32 voxels, 2 all larger
 };
 
 // The last CUDA runtime error a launcher of this library ran into (cudaSuccess if none), for

@@ -569,8 +569,13 @@ int attn_tc_forward(const AttnArgs &a0, cudaStream_t st)
     int skip_upto = 0;
     // the single-tile kernel serves head pairs of 8 channels and single heads of 16
     if (hdm != tc::HDM_PAIR16 && attn_tc_fwd_small_supported(a0)) {
-        const int rc = attn_tc_forward_small(a0, st);
-        if (rc != S3D_OK) return rc;
+        // window_class: the caller's word that every window has at most QT voxels (1) or more (2); each
+        // kernel otherwise walks the whole list to find its own windows
+        if (a0.window_class != 2) {
+            const int rc = attn_tc_forward_small(a0, st);
+            if (rc != S3D_OK) return rc;
+        }
+        if (a0.window_class == 1) return S3D_OK;
         skip_upto = tc::QT;
     }
     const int n_mt = (a.meta.R + 15) / 16;

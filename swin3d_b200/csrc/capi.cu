@@ -99,7 +99,7 @@ static int attn_fwd_impl(const void *q, const void *k, const void *v, const void
                          const void *tv, const int32_t *table_sizes_host, int D, const int32_t *w_sizes,
                          const int32_t *w2n, const int32_t *n2n, const float *n_coords, int64_t N, int64_t W,
                          int H, int hd, int dtype, void *out, float *lse, int n_mirrors,
-                         void *const *out_mirrors_host, void *stream)
+                         void *const *out_mirrors_host, int window_class, void *stream)
 {
     if (N < 0 || W < 0 || (dtype != S3D_F32 && dtype != S3D_F16)) return S3D_ERR_BAD_ARG;
     AttnArgs a{};
@@ -115,6 +115,8 @@ static int attn_fwd_impl(const void *q, const void *k, const void *v, const void
     a.out = out; a.lse = lse;
     const int mrc = fill_mirrors(a.m_out, n_mirrors, out_mirrors_host);
     if (mrc != S3D_OK) return mrc;
+    if (window_class < 0 || window_class > 2) return S3D_ERR_BAD_ARG;
+    a.window_class = window_class;
     if (!force_scalar() && attn_tc_supported(a)) return attn_tc_forward(a, static_cast<cudaStream_t>(stream));
     if (a.m_out.n) return S3D_ERR_UNSUPPORTED;
     return attn_scalar_forward(a, static_cast<cudaStream_t>(stream));
@@ -126,17 +128,17 @@ int s3d_attn_fwd(const void *q, const void *k, const void *v, const void *tq, co
                  int H, int hd, int dtype, void *out, float *lse, void *stream)
 {
     return attn_fwd_impl(q, k, v, tq, tk, tv, table_sizes_host, D, w_sizes, w2n, n2n, n_coords, N, W, H, hd,
-                         dtype, out, lse, 0, nullptr, stream);
+                         dtype, out, lse, 0, nullptr, 0, stream);
 }
 
 int s3d_attn_fwd_mirrored(const void *q, const void *k, const void *v, const void *tq, const void *tk,
                           const void *tv, const int32_t *table_sizes_host, int D, const int32_t *w_sizes,
                           const int32_t *w2n, const int32_t *n2n, const float *n_coords, int64_t N, int64_t W,
                           int H, int hd, int dtype, void *out, float *lse, int n_mirrors,
-                          void *const *out_mirrors_host, void *stream)
+                          void *const *out_mirrors_host, int window_class, void *stream)
 {
     return attn_fwd_impl(q, k, v, tq, tk, tv, table_sizes_host, D, w_sizes, w2n, n2n, n_coords, N, W, H, hd,
-                         dtype, out, lse, n_mirrors, out_mirrors_host, stream);
+                         dtype, out, lse, n_mirrors, out_mirrors_host, window_class, stream);
 }
 
 int s3d_peer_alloc(int64_t bytes, void **ptr_out, void *handle64_out)

@@ -175,6 +175,18 @@ class ShardPlan:
         self.chunk_rows = [(sub[rank][c][2], sub[rank][c][3]) for c in range(chunks)]
         self.w_sizes_chunk = [w_sizes[a:b].contiguous() for a, b in self.chunk_windows]
         self.w2n_chunk = [w2n[a:b].contiguous() for a, b in self.chunk_windows]
+        # the forward runs one kernel for windows of at most TILE voxels and one for larger ones, and each
+        # walks the whole list it is given: with the sizes on the host anyway, hand each kernel its own list
+        self.fwd_classes = []
+        for a, b in self.chunk_windows:
+            small = np.nonzero(ws[a:b] <= TILE)[0] + a
+            large = np.nonzero(ws[a:b] > TILE)[0] + a
+            lists = []
+            for cls, sel in ((1, small), (2, large)):
+                if len(sel):
+                    ix = torch.from_numpy(sel).to(dev)
+                    lists.append((cls, w_sizes[ix].contiguous(), w2n[ix].contiguous()))
+            self.fwd_classes.append(lists)
         self.gather_idx = []
         for c in range(chunks):
             lo, hi = self.chunk_rows[c]
@@ -284,6 +296,15 @@ def _side_stream(device):
     return _SIDE_STREAMS[key]
 
 
+def forward_of_chunk(plan: "ShardPlan", c: int, q, k, v, tq, tk, tv, sizes, n2n, n_coords, out, lse, mirrors=None):
+    """The forward of this rank's windows of chunk c, one call per size class of the plan (every call
+    writes only the rows of its own windows into `out` / `lse`)."""
+    from .sparse_dl.attn.attn_coff import attn_forward_raw
+    for cls, ws_c, w2n_c in plan.fwd_classes[c]:
+        attn_forward_raw(q, k, v, tq, tk, tv, sizes, ws_c, w2n_c, n2n, n_coords, out=out, lse=lse,
+                         mirrors=mirrors, window_class=cls)
+
+
 class RowExchange:
     """The in-flight exchange of `A` per-voxel arrays of one step, IN PLACE: a rank's kernels wrote the
     rows of its own windows into ``arrays``; ``send_chunk(c)`` packs those of chunk c (one row-gather
@@ -370,7 +391,7 @@ def sharded_attention_step(q, k, v, tq, tk, tv, sizes, w_sizes, w2n, n2n, n_coor
     tg = None
     for c in range(plan.chunks):
         ws_c, w2n_c = plan.w_sizes_chunk[c], plan.w2n_chunk[c]
-        attn_forward_raw(q, k, v, tq, tk, tv, sizes, ws_c, w2n_c, n2n, n_coords, out=out, lse=lse)
+        forward_of_chunk(plan, c, q, k, v, tq, tk, tv, sizes, n2n, n_coords, out, lse)
         ex_out.send_chunk(c)
         g = attn_backward_raw(q, k, v, tq, tk, tv, sizes, ws_c, w2n_c, n2n, n_coords, out, lse, dout,
                               dq=dq, dk=dk, dv=dv)
@@ -523,8 +544,7 @@ def sharded_attention_step_p2p(q, k, v, tq, tk, tv, sizes, w_sizes, w2n, n2n, n_
         raise ValueError("PeerResults were allocated for another shape or dtype")
     lse = torch.empty((N, H), dtype=torch.float32, device=q.device)
     ws_c, w2n_c = plan.w_sizes_chunk[0], plan.w2n_chunk[0]
-    attn_forward_raw(q, k, v, tq, tk, tv, sizes, ws_c, w2n_c, n2n, n_coords, out=out, lse=lse,
-                     mirrors=peers.mirrors(step, 0))
+    forward_of_chunk(plan, 0, q, k, v, tq, tk, tv, sizes, n2n, n_coords, out, lse, mirrors=peers.mirrors(step, 0))
     g = attn_backward_raw(q, k, v, tq, tk, tv, sizes, ws_c, w2n_c, n2n, n_coords, out, lse, dout,
                           dq=dq, dk=dk, dv=dv,
                           mirrors=(peers.mirrors(step, 1), peers.mirrors(step, 2), peers.mirrors(step, 3)))

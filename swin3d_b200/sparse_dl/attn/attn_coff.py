@@ -124,12 +124,14 @@ def _pointer_array(ptrs):
 
 
 def attn_forward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n_coords, out=None, lse=None,
-                     mirrors=None):
+                     mirrors=None, window_class: int = 0):
     """One fused forward launch.  Tensors must already have the compute dtype.  -> (out, lse).
     `out` / `lse` may be given (full-size, contiguous): only the rows of the voxels of the windows
     in `w_sizes` / `w2n` are written, so a window list can be processed in several calls.
     `mirrors`: device addresses (ints) of up to 7 further arrays of out's shape -- other GPUs' result
-    arrays mapped into this process -- that receive the same rows by peer stores from the kernels."""
+    arrays mapped into this process -- that receive the same rows by peer stores from the kernels.
+    `window_class`: 1 / 2 = the caller guarantees that every window of this call has at most 32 voxels /
+    more than 32 (a window that breaks the guarantee is not processed); 0 = any sizes."""
     import ctypes
     q, k, v, tq, tk, tv = _aligned16(q, k, v, tq, tk, tv)
     N, H, hd = q.shape
@@ -150,9 +152,9 @@ def attn_forward_raw(q, k, v, tq, tk, tv, sizes: List[int], w_sizes, w2n, n2n, n
                 ctypes.cast(arr, ctypes.c_void_p), D, w_sizes.data_ptr(), w2n.data_ptr(),
                 n2n.data_ptr(), n_coords.data_ptr(), N, W, H, hd, _DTYPE_CODE[q.dtype],
                 out.data_ptr(), lse.data_ptr())
-        if mirrors:
-            keep, mp = _pointer_array(mirrors)
-            rc = _lib.lib.s3d_attn_fwd_mirrored(*args, len(mirrors), mp, st)
+        if mirrors or window_class:
+            keep, mp = _pointer_array(mirrors) if mirrors else (None, None)
+            rc = _lib.lib.s3d_attn_fwd_mirrored(*args, len(mirrors) if mirrors else 0, mp, int(window_class), st)
         else:
             rc = _lib.lib.s3d_attn_fwd(*args, st)
     _lib.check(rc, "s3d_attn_fwd")

@@ -253,3 +253,32 @@ def test_peer_store_step_on_one_rank_equals_the_plain_calls():
     finally:
         peers.close()
     assert peers.own is None
+
+
+def test_forward_by_window_class_equals_the_mixed_call():
+    """The plan hands the forward its windows in two lists (at most 32 voxels / more) with the
+    matching class hint, so that neither kernel walks the other's windows: same bits as one call."""
+    from swin3d_b200.dist import ShardPlan, forward_of_chunk
+    from swin3d_b200.sparse_dl.attn.attn_coff import attn_forward_raw
+    from tests.gpu_helpers import dev
+    from tests.helpers import make_problem
+    p = make_problem(seed=38, H=4, hd=8, crse="XYZ_RGB_NORM", scene=_dense_block_scene())
+    assert (p.w_sizes > 32).any() and (p.w_sizes <= 32).any()
+    h = lambda a: dev(a).half()
+    q, k, v = h(p.q), h(p.k), h(p.v)
+    tabs = [h(p.tq), h(p.tk), h(p.tv)]
+    ws, w2n, n2n, nc = dev(p.w_sizes), dev(p.w2n), dev(p.n2n), dev(p.n_crse)
+    out, lse = attn_forward_raw(q, k, v, *tabs, p.sizes, ws, w2n, n2n, nc)
+    plan = ShardPlan(ws, w2n, n2n, 1, 0, 1)
+    assert [c for c, _, _ in plan.fwd_classes[0]] == [1, 2]
+    out2 = torch.full_like(q, float("nan"))
+    lse2 = torch.full((q.shape[0], p.H), float("nan"), dtype=torch.float32, device="cuda")
+    forward_of_chunk(plan, 0, q, k, v, *tabs, p.sizes, n2n, nc, out2, lse2)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out) and torch.equal(lse2, lse)
+    # a hint that is not true leaves the other class's windows untouched (documented, not an error)
+    out3 = torch.full_like(q, float("nan"))
+    attn_forward_raw(q, k, v, *tabs, p.sizes, ws, w2n, n2n, nc, out=out3, window_class=1)
+    torch.cuda.synchronize()
+    small_rows = torch.cat([n2n[int(a):int(a) + int(n)] for a, n in zip(p.w2n, p.w_sizes) if n <= 32]).long()
+    assert torch.equal(out3[small_rows], out[small_rows]) and bool(torch.isnan(out3.float()).any())
