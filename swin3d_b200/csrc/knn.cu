@@ -320,8 +320,17 @@ int knn_launch(int K, const float *src, const float *query, const int32_t *src_o
     if (Nq == 0) return S3D_OK;
     // few neighbours: the scan dominates, two queries per thread halve its shared-memory loads;
     // more neighbours: heap updates dominate, one query per thread keeps more warps resident
-    if (K <= 4) return knn_launch_as<4, 2, 128, KNN_STEP + 4>(K, src, query, src_offset, query_offset, B, Nq, ret_idx, ret_dist, st);
-    if (K <= 16) return knn_launch_as<16, 1, 256, KNN_STEP + 4>(K, src, query, src_offset, query_offset, B, Nq, ret_idx, ret_dist, st);
+    // a short query list (a rank's share of a split call) does not fill the SMs with blocks of 256
+    // queries: smaller blocks of one query per thread keep more warps resident (measured on 200 k to
+    // 1.6 M queries: the smaller blocks win below about 300 k queries for K <= 4, 600 k for K <= 16)
+    if (K <= 4) {
+        if (Nq < 300000) return knn_launch_as<4, 1, 128, KNN_STEP + 4>(K, src, query, src_offset, query_offset, B, Nq, ret_idx, ret_dist, st);
+        return knn_launch_as<4, 2, 128, KNN_STEP + 4>(K, src, query, src_offset, query_offset, B, Nq, ret_idx, ret_dist, st);
+    }
+    if (K <= 16) {
+        if (Nq < 600000) return knn_launch_as<16, 1, 128, KNN_STEP + 4>(K, src, query, src_offset, query_offset, B, Nq, ret_idx, ret_dist, st);
+        return knn_launch_as<16, 1, 256, KNN_STEP + 4>(K, src, query, src_offset, query_offset, B, Nq, ret_idx, ret_dist, st);
+    }
     return knn_launch_as<64, 1, 256, KNN_STEP + 4>(K, src, query, src_offset, query_offset, B, Nq, ret_idx, ret_dist, st);
 }
 

@@ -165,6 +165,19 @@ def test_knn_config5_scale_properties():
     assert np.array_equal(idx[sel], ridx) and np.array_equal(d2[sel], rd2)
 
 
+@pytest.mark.parametrize("K", [3, 16])
+def test_knn_block_configurations_agree(K):
+    """Long query lists run blocks of 256 queries (two per thread for K <= 4), short ones blocks of 128
+    with one query per thread; the same queries through both must give the same bits (the short
+    configuration is the one the oracle tests above pin)."""
+    src, qry = S.make_knn_scene(11, 700_000, 20_000)
+    long_idx, long_d2 = _knn_gpu(K, src, qry, [20_000], [700_000])
+    for a, b in ((0, 250_000), (250_000, 500_000), (500_000, 700_000)):
+        idx, d2 = _knn_gpu(K, src, qry[a:b], [20_000], [b - a])
+        assert np.array_equal(idx, long_idx[a:b])
+        assert np.array_equal(d2.view(np.uint32), long_d2[a:b].view(np.uint32))
+
+
 class _FakeMapKey:
     def __init__(self, stride):
         self._s = [stride] * 3
